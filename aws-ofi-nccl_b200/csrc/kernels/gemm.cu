@@ -1,0 +1,188 @@
+// bf16 GEMM entry points built on the tcgen05 mainloop.
+//
+//   C[M,N] (+)= op(A) * op(B)     fp32 accumulation in TMEM, bf16 or fp32 output
+//
+// Operand storage is described by two flags instead of BLAS transposes:
+//   a_mn = 0 : A stored [M][K] (K contiguous)      a_mn = 1 : A stored [K][M] (M contiguous)
+//   b_mn = 0 : B stored [N][K] (K contiguous)      b_mn = 1 : B stored [K][N] (N contiguous)
+// so a linear layer's forward (x W^T), input gradient (dy W) and weight gradient (dy^T x) all run
+// on the same kernel without materialising a transpose.
+#include "gemm_tcgen05.cuh"
+#include "host_util.h"
+
+namespace b200 {
+
+int* device_status_word() {
+  static int* words[16] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) dev = 0;
+  if (!words[dev]) {
+    if (cudaMalloc(&words[dev], 256) != cudaSuccess) return nullptr;
+    cudaMemset(words[dev], 0, 256);
+  }
+  return words[dev];
+}
+
+template <typename OutT>
+struct StoreEpilogue {
+  OutT* C;
+  int64_t ldc;
+  int accumulate;
+  __device__ __forceinline__ void tile_begin(int, int) {}
+  __device__ __forceinline__ void tile_end(int, int) {}
+  __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&acc)[32], const GemmShape& s) {
+    if (row >= s.M || col0 >= s.N) return;
+    OutT* dst = C + static_cast<int64_t>(row) * ldc + col0;
+    const int ncols = min(32, s.N - col0);
+    if constexpr (sizeof(OutT) == 2) {
+      if (ncols == 32) {
+        uint32_t packed[16];
+        if (accumulate) {
+          const uint4* old = reinterpret_cast<const uint4*>(dst);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o = old[v];
+            const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const __nv_bfloat162 ob = *reinterpret_cast<const __nv_bfloat162*>(&ow[j]);
+              packed[v * 4 + j] = pack_bf16x2(__uint_as_float(acc[v * 8 + 2 * j]) + __low2float(ob),
+                                              __uint_as_float(acc[v * 8 + 2 * j + 1]) + __high2float(ob));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            packed[j] = pack_bf16x2(__uint_as_float(acc[2 * j]), __uint_as_float(acc[2 * j + 1]));
+        }
+        uint4* out = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+          out[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+      } else {
+        for (int j = 0; j < ncols; ++j) {
+          float v = __uint_as_float(acc[j]);
+          if (accumulate) v += __bfloat162float(reinterpret_cast<__nv_bfloat16*>(dst)[j]);
+          reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16(v);
+        }
+      }
+    } else {
+      if (ncols == 32) {
+        float4* out = reinterpret_cast<float4*>(dst);
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          float4 o = accumulate ? out[v] : make_float4(0.f, 0.f, 0.f, 0.f);
+          out[v] = make_float4(o.x + __uint_as_float(acc[4 * v]), o.y + __uint_as_float(acc[4 * v + 1]),
+                               o.z + __uint_as_float(acc[4 * v + 2]), o.w + __uint_as_float(acc[4 * v + 3]));
+        }
+      } else {
+        for (int j = 0; j < ncols; ++j) {
+          float v = __uint_as_float(acc[j]);
+          if (accumulate) v += reinterpret_cast<float*>(dst)[j];
+          reinterpret_cast<float*>(dst)[j] = v;
+        }
+      }
+    }
+  }
+};
+
+template <int BN, bool A_MN, bool B_MN, typename OutT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, OutT* C,
+                     int64_t ldc, GemmShape shape, int accumulate, int* err_word) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  StoreEpilogue<OutT> epi{C, ldc, accumulate};
+  NoGate gate;
+  gemm_mainloop<BN, A_MN, B_MN>(&tmA, &tmB, shape, epi, gate, err_word, smem_raw);
+}
+
+template <int BN, bool A_MN, bool B_MN, typename OutT>
+static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                       int64_t ldc, int accumulate, int max_ctas, cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!A_MN)
+    rc = make_tmap_2d(&tmA, A, M, K, lda, GEMM_BM, GEMM_BK, 2, true);
+  else
+    rc = make_tmap_2d(&tmA, A, K, M, lda, GEMM_BK, 64, 2, true);
+  if (rc) return rc;
+  if (!B_MN)
+    rc = make_tmap_2d(&tmB, B, N, K, ldb, BN, GEMM_BK, 2, true);
+  else
+    rc = make_tmap_2d(&tmB, B, K, N, ldb, GEMM_BK, 64, 2, true);
+  if (rc) return rc;
+  GemmShape shape{M, N, K, (M + GEMM_BM - 1) / GEMM_BM, (N + BN - 1) / BN};
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL));
+    attr_set = true;
+  }
+  int grid = shape.tiles_m * shape.tiles_n;
+  int cap = sm_count();
+  if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
+  if (grid > cap) grid = cap;
+  int* err = device_status_word();
+  kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(tmA, tmB, static_cast<OutT*>(C), ldc, shape, accumulate,
+                                                           err);
+  B200_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+template <int BN, typename OutT>
+static int dispatch_major(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                          int64_t ldc, int a_mn, int b_mn, int accumulate, int max_ctas, cudaStream_t stream) {
+  if (!a_mn && !b_mn) return launch_gemm<BN, false, false, OutT>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, max_ctas, stream);
+  if (!a_mn && b_mn) return launch_gemm<BN, false, true, OutT>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, max_ctas, stream);
+  if (a_mn && !b_mn) return launch_gemm<BN, true, false, OutT>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, max_ctas, stream);
+  return launch_gemm<BN, true, true, OutT>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, max_ctas, stream);
+}
+
+}  // namespace b200
+
+extern "C" {
+
+// Returns 0 on success. Alignment: base pointers and row pitches must be multiples of 16 bytes.
+// out_fp32 selects an fp32 C; accumulate adds to the existing C. bn is 128 or 256 (0 = choose).
+int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                   long long ldc, int a_mn, int b_mn, int out_fp32, int accumulate, int bn, int max_ctas,
+                   void* stream) {
+  b200::ensure_context();
+  using namespace b200;
+  if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return B200_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
+    return B200_ERR_BAD_ARG;
+  if ((lda % 8) || (ldb % 8) || (ldc % (out_fp32 ? 4 : 8))) return B200_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bn == 0) {
+    // 256-wide tiles halve the A re-reads; fall back to 128 when that fills the SMs better.
+    const int sms = sm_count();
+    const long t256 = static_cast<long>((M + 127) / 128) * ((N + 255) / 256);
+    const long t128 = static_cast<long>((M + 127) / 128) * ((N + 127) / 128);
+    const double eff256 = static_cast<double>(t256) / (((t256 + sms - 1) / sms) * sms);
+    const double eff128 = static_cast<double>(t128) / (((t128 + sms - 1) / sms) * sms);
+    bn = (N >= 256 && eff256 + 0.08 >= eff128) ? 256 : 128;
+  }
+  if (bn == 256) {
+    return out_fp32 ? dispatch_major<256, float>(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, accumulate, max_ctas, s)
+                    : dispatch_major<256, __nv_bfloat16>(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, accumulate,
+                                                         max_ctas, s);
+  }
+  return out_fp32 ? dispatch_major<128, float>(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, accumulate, max_ctas, s)
+                  : dispatch_major<128, __nv_bfloat16>(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, accumulate,
+                                                       max_ctas, s);
+}
+
+// Reads and clears the device status word (0 = no kernel gave up on a wait). Synchronises the device.
+int b200_read_status(int clear) {
+  b200::ensure_context();
+  int* w = b200::device_status_word();
+  if (!w) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
+  if (clear && v) cudaMemset(w, 0, sizeof(int));
+  return v;
+}
+
+}  // extern "C"

@@ -1,0 +1,223 @@
+// Persistent warp-specialised bf16 GEMM mainloop for sm_100a: TMA -> shared memory -> tcgen05.mma
+// with the accumulator in TMEM, double-buffered so the epilogue of tile i overlaps the MMAs of
+// tile i+1. The epilogue is a functor, so the same mainloop serves the plain GEMM, the fused
+// SwiGLU GEMM and the GEMMs that push their tiles to peer GPUs.
+//
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner),
+// warps 2..5 = epilogue (each reads the TMEM lane quarter `warp_id % 4`).
+#pragma once
+#include "sm100_common.cuh"
+
+namespace b200 {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int GEMM_THREADS = 192;
+constexpr uint64_t GEMM_WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait, then the kernel gives up
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int TOTAL = 1024 + STAGES * STAGE_BYTES + BAR_BYTES;
+};
+
+struct GemmShape {
+  int M, N, K;
+  int tiles_m, tiles_n;
+};
+
+// The tile id -> (tile_m, tile_n) map: M fastest inside a band of 8 N-tiles... kept simple and
+// L2-friendly: consecutive CTAs share the same B (weight) tile.
+__device__ __forceinline__ void tile_coords(const GemmShape& s, int tile, int& tm, int& tn) {
+  tm = tile % s.tiles_m;
+  tn = tile / s.tiles_m;
+}
+
+// Epilogue functor contract:
+//   __device__ void operator()(int row, int col0, const uint32_t (&acc)[32], const GemmShape&)
+// called by one thread per accumulator row for 32 consecutive columns starting at col0 (fp32 bits).
+// Optional hooks: tile_begin(tm, tn) / tile_end(tm, tn) called by every epilogue thread.
+
+template <int BN, bool A_MN, bool B_MN, class Epilogue, class LoadGate>
+__device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUtensorMap* tmB, GemmShape shape,
+                                              Epilogue& epi, LoadGate& gate, int* err_word, uint8_t* smem_raw) {
+  using S = GemmSmem<BN>;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // 1024-byte aligned tile area (required by the 128-byte swizzle).
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + S::STAGES * S::STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (S::STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * S::STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * S::STAGES + 2 + b); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * S::STAGES + 4);
+  volatile int* abort_flag =
+      reinterpret_cast<volatile int*>(smem_raw + (bar_base - smem_u32(smem_raw)) + 8u * (2 * S::STAGES + 4) + 8);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(tmA);
+    tma_prefetch_desc(tmB);
+  }
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // 256 or 512: a power of two >= 32
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+  const int num_tiles = shape.tiles_m * shape.tiles_n;
+  const int num_kb = (shape.K + GEMM_BK - 1) / GEMM_BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one_sync()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(shape, tile, tm, tn);
+        if (!gate.wait_rows(tm, abort_flag, err_word)) break;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1, abort_flag, err_word, DEV_ERR_EMPTY_BAR_TIMEOUT,
+                                 GEMM_WAIT_LIMIT_NS)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * S::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + S::A_BYTES;
+          mbar_expect_tx(full_bar(stage), S::STAGE_BYTES);
+          if constexpr (!A_MN) {
+            tma_load_2d(a_dst, tmA, kb * GEMM_BK, tm * GEMM_BM, full_bar(stage));
+          } else {
+#pragma unroll
+            for (int j = 0; j < GEMM_BM / 64; ++j)
+              tma_load_2d(a_dst + j * 8192, tmA, tm * GEMM_BM + j * 64, kb * GEMM_BK, full_bar(stage));
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(b_dst, tmB, kb * GEMM_BK, tn * BN, full_bar(stage));
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_dst + j * 8192, tmB, tn * BN + j * 64, kb * GEMM_BK, full_bar(stage));
+          }
+          if (++stage == S::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one_sync()) {
+      constexpr uint32_t idesc = make_instr_desc(1, 1, GEMM_BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc_buf = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait_bounded(tempty_bar(acc_buf), acc_phase ^ 1, abort_flag, err_word, DEV_ERR_TMEM_EMPTY_TIMEOUT,
+                               GEMM_WAIT_LIMIT_NS))
+          break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc_buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, err_word, DEV_ERR_FULL_BAR_TIMEOUT,
+                                 GEMM_WAIT_LIMIT_NS)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_src = smem_base + stage * S::STAGE_BYTES;
+          const uint32_t b_src = a_src + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? make_smem_desc_sw128(a_src + k * 2048, 8192, 1024)
+                                        : make_smem_desc_sw128(a_src + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc_sw128(b_src + k * 2048, 8192, 1024)
+                                        : make_smem_desc_sw128(b_src + k * 32, 16, 1024);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          if (++stage == S::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(tfull_bar(acc_buf));  // accumulator complete -> epilogue
+        acc_buf ^= 1;
+        if (acc_buf == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;
+    int acc_buf = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(shape, tile, tm, tn);
+      if (!mbar_wait_bounded(tfull_bar(acc_buf), acc_phase, abort_flag, err_word, DEV_ERR_TMEM_FULL_TIMEOUT,
+                             GEMM_WAIT_LIMIT_NS))
+        break;
+      tc_fence_after();
+      epi.tile_begin(tm, tn);
+      const int row = tm * GEMM_BM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc_buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t acc[32];
+        tmem_ld_32x32(taddr + c * 32, acc);
+        tmem_ld_wait();
+        epi(row, tn * BN + c * 32, acc, shape);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc_buf));
+      epi.tile_end(tm, tn);
+      acc_buf ^= 1;
+      if (acc_buf == 0) acc_phase ^= 1;
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // Give copies that may still be in flight time to land before shared memory is released.
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// Gate that never waits (all operand rows are local and ready).
+struct NoGate {
+  __device__ __forceinline__ bool wait_rows(int, volatile int*, int*) { return true; }
+};
+
+}  // namespace b200
