@@ -1,0 +1,161 @@
+// Typed runtime parameters. Each parameter has a default, may be overridden by the environment
+// (name OFI_NCCL_<NAME>, or B200NET_<NAME> which wins when both are set) and may be set through
+// the API — but only until its first get(): after a value has been observed it is frozen, so the
+// plugin never sees two different values of one knob (reference: include/nccl_ofi_param_impl.h
+// :197-314, the list in include/nccl_ofi_param.h).
+#pragma once
+#include <cstdint>
+#include <cstdlib>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+namespace b200net {
+
+enum class ParamSource { DEFAULT, ENVIRONMENT, API };
+
+class ParamBase {
+ public:
+  ParamBase(const char* name, const char* doc);
+  virtual ~ParamBase() = default;
+  const std::string& name() const { return name_; }
+  const std::string& doc() const { return doc_; }
+  virtual std::string value_string() = 0;
+  virtual int load_from_env() = 0;  // 0 ok, -EINVAL on an unparsable value
+  ParamSource source() const { return source_; }
+
+ protected:
+  static const char* find_env(const std::string& name);
+  std::string name_, doc_;
+  ParamSource source_ = ParamSource::DEFAULT;
+};
+
+// Registry of every parameter object (for init-time env parsing and for dumps).
+std::vector<ParamBase*>& param_registry();
+// Parse the environment for every registered parameter; returns -EINVAL if any value is malformed.
+int parameters_init();
+
+namespace detail {
+bool parse_value(const char* s, bool& out);
+bool parse_value(const char* s, int64_t& out);
+bool parse_value(const char* s, uint64_t& out);
+bool parse_value(const char* s, int& out);
+bool parse_value(const char* s, unsigned& out);
+bool parse_value(const char* s, float& out);
+bool parse_value(const char* s, std::string& out);
+std::string to_string_value(bool v);
+std::string to_string_value(const std::string& v);
+template <typename T>
+std::string to_string_value(const T& v) { return std::to_string(v); }
+}  // namespace detail
+
+template <typename T>
+class Param : public ParamBase {
+ public:
+  Param(const char* name, T def, const char* doc = "") : ParamBase(name, doc), value_(std::move(def)) {}
+
+  // First get() freezes the value.
+  const T& get() {
+    std::lock_guard<std::mutex> g(mu_);
+    if (!loaded_) load_locked();
+    frozen_ = true;
+    return value_;
+  }
+  const T& operator()() { return get(); }
+
+  // 0 on success; -EINVAL once the value has been read.
+  int set(const T& v) {
+    std::lock_guard<std::mutex> g(mu_);
+    if (frozen_) return -22;
+    value_ = v;
+    source_ = ParamSource::API;
+    loaded_ = true;
+    return 0;
+  }
+  int load_from_env() override {
+    std::lock_guard<std::mutex> g(mu_);
+    return load_locked();
+  }
+  std::string value_string() override { return detail::to_string_value(get()); }
+  // test hook: forget the frozen state and the cached value
+  void reset_for_testing(const T& def) {
+    std::lock_guard<std::mutex> g(mu_);
+    value_ = def; loaded_ = false; frozen_ = false; source_ = ParamSource::DEFAULT;
+  }
+
+ protected:
+  virtual bool accept(const T&) const { return true; }
+  int load_locked() {
+    loaded_ = true;
+    if (source_ == ParamSource::API) return 0;
+    const char* e = find_env(name_);
+    if (!e) return 0;
+    T parsed{};
+    if (!detail::parse_value(e, parsed) || !accept(parsed)) return -22;
+    value_ = parsed;
+    source_ = ParamSource::ENVIRONMENT;
+    return 0;
+  }
+  std::mutex mu_;
+  T value_;
+  bool loaded_ = false, frozen_ = false;
+};
+
+// String parameter restricted to a fixed set of spellings (case-insensitive), e.g. PROTOCOL.
+class EnumParam : public Param<std::string> {
+ public:
+  EnumParam(const char* name, std::string def, std::vector<std::string> allowed, const char* doc = "")
+      : Param<std::string>(name, std::move(def), doc), allowed_(std::move(allowed)) {}
+  const std::vector<std::string>& allowed() const { return allowed_; }
+
+ protected:
+  bool accept(const std::string& v) const override;
+  std::vector<std::string> allowed_;
+};
+
+// ---- the knobs ---------------------------------------------------------------------------------
+struct Params {
+  EnumParam protocol{"PROTOCOL", "", {"", "RDMA", "SENDRECV"}, "transport protocol; empty = choose by rail count"};
+  Param<uint64_t> eager_max_size{"EAGER_MAX_SIZE", 8192, "largest message sent eagerly (bytes); 0 disables eager"};
+  Param<uint64_t> min_stripe_size{"MIN_STRIPE_SIZE", 128 * 1024, "smallest stripe when a message is split over rails"};
+  Param<uint64_t> sched_max_small_rr_size{"SCHED_MAX_SMALL_RR_SIZE", 64, "messages below this go to one rail round-robin"};
+  Param<int> cq_read_count{"CQ_READ_COUNT", 4, "completions drained per poll of one rail"};
+  Param<int> cq_size{"CQ_SIZE", 12288, "entries of a completion ring"};
+  Param<bool> mr_cache_disable{"MR_CACHE_DISABLE", false, "do not cache registrations"};
+  Param<int> min_posted_eager_buffers{"RDMA_MIN_POSTED_EAGER_BUFFERS", 64, ""};
+  Param<int> max_posted_eager_buffers{"RDMA_MAX_POSTED_EAGER_BUFFERS", 128, ""};
+  Param<int> min_posted_control_buffers{"RDMA_MIN_POSTED_CONTROL_BUFFERS", 16, ""};
+  Param<int> max_posted_control_buffers{"RDMA_MAX_POSTED_CONTROL_BUFFERS", 32, ""};
+  Param<bool> early_completion{"EARLY_COMPLETION", true, "complete LL/LL128 receives without waiting for write completions"};
+  Param<bool> disable_close_message{"DISABLE_CLOSE_MESSAGE", false, "skip the close handshake"};
+  Param<bool> abort_on_error{"ABORT_ON_ERROR", false, "abort() instead of returning an error code"};
+  Param<int> force_num_rails{"FORCE_NUM_RAILS", 0, "override the number of copy channels per peer (0 = from topology)"};
+  EnumParam tuner_type{"TUNER_TYPE", "Measured", {"Internal", "Region", "Model", "Measured"}, "tuner back-end"};
+  Param<int> tuner_num_channels{"TUNER_NUM_CHANNELS", 8, ""};
+  Param<float> tuner_net_latency{"TUNER_NET_LATENCY", 20.f, "network latency assumed by the model tuner (us)"};
+  Param<std::string> tuner_table{"TUNER_TABLE", "", "path of a measured-bandwidth JSON table"};
+  Param<std::string> platform{"PLATFORM", "", "force a platform implementation by name"};
+  EnumParam nvtx_trace_dimension{"NVTX_TRACE_DIMENSION", "PER_COMM", {"PER_COMM", "PER_DEV"}, ""};
+  Param<int> cm_num_rx_buffers{"CM_NUM_RX_BUFFERS", 32, "connection-manager receive slots"};
+  Param<bool> errorcheck_mutex{"ERRORCHECK_MUTEX",
+#ifdef NDEBUG
+                               false,
+#else
+                               true,
+#endif
+                               "use error-checking mutexes"};
+  Param<bool> disable_dmabuf{"DISABLE_DMABUF", false, ""};
+  Param<bool> cuda_flush_enable{"CUDA_FLUSH_ENABLE", false, "flush with the driver instead of a fence"};
+  Param<bool> disable_cma{"DISABLE_CMA", false, "never use cross-memory attach for host rendezvous writes"};
+  Param<bool> nvls_enable{"NVLS_ENABLE", true, "use NVSwitch multicast where available"};
+  Param<uint64_t> device_wait_limit_ms{"DEVICE_WAIT_LIMIT_MS", 20000, "bound of every device-side wait"};
+  Param<int> gin_ack_interval{"GIN_ACK_INTERVAL", 64, "operations between GIN acknowledgements"};
+  Param<bool> rr_ctrl_msg{"RR_CTRL_MSG", true, "rotate control messages over the control rails"};
+  EnumParam progress_model{"PROGRESS_MODEL", "unspec", {"unspec", "auto", "manual"}, ""};
+  Param<std::string> topo_file_write{"TOPO_FILE_WRITE_PATH", "", "also write the generated NCCL topology here"};
+};
+Params& params();
+
+}  // namespace b200net

@@ -1,0 +1,50 @@
+"""Multi-GPU tests: each launches a torchrun job over the visible GPUs (2..8) and checks its exit code."""
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(worker: str, nproc: int, env_extra: dict | None = None, timeout: int = 600):
+    env = dict(os.environ)
+    env.update(env_extra or {})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(ROOT / "tests" / "workers" / worker)]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
+    assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-4000:]
+    return res.stdout
+
+
+def _ngpus() -> int:
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.skipif(_ngpus() < 2, reason="needs at least 2 GPUs")
+def test_device_collectives_all_gpus():
+    out = _run("collectives_worker.py", min(_ngpus(), 8))
+    assert "collectives worker OK" in out
+
+
+@pytest.mark.skipif(_ngpus() < 2, reason="needs at least 2 GPUs")
+def test_device_collectives_p2p_only():
+    out = _run("collectives_worker.py", 2, {"B200NET_NVLS_ENABLE": "0"})
+    assert "collectives worker OK" in out
+
+
+@pytest.mark.skipif(_ngpus() < 2, reason="needs at least 2 GPUs")
+def test_data_parallel_gradients_and_replicas():
+    out = _run("dp_worker.py", min(_ngpus(), 4))
+    assert "dp worker OK" in out
