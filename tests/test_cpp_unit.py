@@ -1,0 +1,16 @@
+"""Runs every C++ unit-test program (csrc/tests/*.cpp|.c); each reports through its exit status."""
+import subprocess
+from pathlib import Path
+
+import pytest
+
+CSRC_TESTS = Path(__file__).resolve().parent.parent / "aws-ofi-nccl_b200" / "csrc" / "tests"
+NAMES = sorted(p.stem for p in list(CSRC_TESTS.glob("*.cpp")) + list(CSRC_TESTS.glob("*.c")))
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_cpp_unit(built, name):
+    exe = built / "tests" / name
+    assert exe.exists(), f"{exe} was not built"
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, cwd=built)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
