@@ -1,0 +1,59 @@
+// CUDA driver access for the host plugin. The plugin links against no CUDA library: libcuda.so.1
+// is dlopen()ed at init and every entry point is resolved by name, so the same shared object loads
+// on a machine without a GPU (host-memory transport only)
+// (reference: src/nccl_ofi_cuda.cpp — driver API only, resolved at run time; :481-568 VMM
+// allocation; :453 dma-buf export; :252 GPUDirect flush).
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+namespace b200net::cuda {
+
+using Stream = void*;
+using Event = void*;
+using Context = void*;
+
+// Loads the driver and calls cuInit. 0 on success, -ENOSYS when there is no driver or no device.
+int init();
+bool available();
+int device_count();
+
+// Pointer classification. Returns 0 and fills the outputs if `ptr` is device memory.
+int pointer_info(const void* ptr, int* device, void** alloc_base, size_t* alloc_size, bool* is_vmm);
+bool is_host_pointer(const void* ptr);
+
+// Legacy IPC (cudaMalloc-style allocations): 64-byte handles.
+int ipc_get_handle(void* alloc_base, uint8_t out[64]);
+int ipc_open(const uint8_t handle[64], void** mapped);
+int ipc_close(void* mapped);
+
+// Context handling: the proxy thread that calls into the plugin may have no current context.
+int ctx_get_current(Context* ctx);
+int ctx_set_current(Context ctx);
+int ensure_primary_ctx(int device);
+
+int stream_create(Stream* s);
+int stream_destroy(Stream s);
+int event_create(Event* e);
+int event_destroy(Event e);
+int event_record(Event e, Stream s);
+int event_query(Event e);  // 0 done, 1 not yet, <0 error
+int memcpy_async(void* dst, const void* src, size_t n, Stream s);  // unified addressing: any direction
+int stream_synchronize(Stream s);
+
+// VMM allocation that can be exported to peers as a POSIX fd (granularity rounded).
+int vmm_alloc(int device, size_t bytes, void** ptr, size_t* rounded, uint64_t* handle_out);
+int vmm_free(void* ptr, size_t rounded, uint64_t handle);
+int vmm_export_fd(uint64_t handle, int* fd);
+// dma-buf descriptor of an address range (for regMrDmaBuf users); -ENOTSUP when unsupported.
+int get_dmabuf_fd(void* ptr, size_t size, int* fd, uint64_t* offset);
+bool dmabuf_supported(int device);
+// Orders earlier remote writes before later reads of the GPU; -ENOTSUP when not offered.
+int flush_gpudirect_rdma_writes();
+// NVLink topology of the box.
+int p2p_attribute(int attr, int src_dev, int dst_dev, int* value);
+int device_attribute(int attr, int dev, int* value);
+int device_pci_bus_id(int dev, char* out, int len);
+int device_uuid(int dev, uint8_t out[16]);
+
+}  // namespace b200net::cuda

@@ -154,6 +154,7 @@ struct Params {
   Param<int> gin_ack_interval{"GIN_ACK_INTERVAL", 64, "operations between GIN acknowledgements"};
   Param<bool> rr_ctrl_msg{"RR_CTRL_MSG", true, "rotate control messages over the control rails"};
   EnumParam progress_model{"PROGRESS_MODEL", "unspec", {"unspec", "auto", "manual"}, ""};
+  Param<bool> nccl_topo_inject{"NCCL_TOPO_INJECT", false, "publish the generated topology through NCCL_TOPO_FILE"};
   Param<std::string> topo_file_write{"TOPO_FILE_WRITE_PATH", "", "also write the generated NCCL topology here"};
 };
 Params& params();

@@ -103,6 +103,29 @@ __device__ __forceinline__ void broadcast_vec(const GinDevHandle& h, size_t off,
   }
 }
 
+// Walk vectors [v0, v1) of the window range starting at byte `off` with the whole grid, U vectors
+// per thread per trip: the U reductions (multimem loads, or nranks peer loads each) are issued
+// before any result is consumed, which keeps enough bytes in flight to cover the NVLink latency.
+template <bool BF16, bool NVLS, int U, class Sink>
+__device__ __forceinline__ void reduce_range(const GinDevHandle& h, size_t off, size_t v0, size_t v1, float scale,
+                                             Sink&& sink) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t v = v0 + blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < v1; v += stride * U) {
+    float acc[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t idx = v + u * stride;
+      int n;
+      if (idx < v1) reduce_vec<BF16, NVLS>(h, off + (idx << 4), scale, acc[u], n);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t idx = v + u * stride;
+      if (idx < v1) sink(idx, acc[u]);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- all-reduce (in place in the window)
 // Two-shot: rank r reduces slice r of the range and broadcasts the result to every rank.
 template <bool BF16, bool NVLS>
@@ -112,30 +135,21 @@ __global__ void __launch_bounds__(512) all_reduce_kernel(GinDevHandle h, size_t 
   const size_t per = (nvec + h.nranks - 1) / h.nranks;
   const size_t v0 = min(nvec, per * h.rank);
   const size_t v1 = min(nvec, v0 + per);
-  for (size_t v = v0 + blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < v1;
-       v += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    float acc[8];
-    int n;
-    const size_t o = off + (v << 4);
-    reduce_vec<BF16, NVLS>(h, o, scale, acc, n);
-    broadcast_vec<NVLS>(h, o, pack_vec<BF16>(acc));
-  }
+  reduce_range<BF16, NVLS, NVLS ? 4 : 2>(h, off, v0, v1, scale, [&](size_t idx, const float(&acc)[8]) {
+    broadcast_vec<NVLS>(h, off + (idx << 4), pack_vec<BF16>(acc));
+  });
   gin_barrier(h, ch, blockIdx.x);
 }
 
-// One-shot all-reduce reads inputs that peers overwrite with results when done in place, so the
-// one-shot form writes to a separate local output buffer instead.
+// One-shot (latency form): every rank reduces the whole range into a local output buffer. It
+// cannot run in place, because a fast rank would overwrite inputs a slow rank still has to read.
 template <bool BF16, bool NVLS>
 __global__ void __launch_bounds__(512) all_reduce_oneshot_kernel(GinDevHandle h, size_t off, size_t nvec, float scale,
                                                                 void* out, int ch) {
   if (!gin_barrier(h, ch, blockIdx.x)) return;
-  for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec;
-       v += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    float acc[8];
-    int n;
-    reduce_vec<BF16, NVLS>(h, off + (v << 4), scale, acc, n);
-    reinterpret_cast<uint4*>(out)[v] = pack_vec<BF16>(acc);
-  }
+  reduce_range<BF16, NVLS, NVLS ? 4 : 2>(h, off, 0, nvec, scale, [&](size_t idx, const float(&acc)[8]) {
+    reinterpret_cast<uint4*>(out)[idx] = pack_vec<BF16>(acc);
+  });
   gin_barrier(h, ch, blockIdx.x);
 }
 
@@ -146,19 +160,15 @@ __global__ void __launch_bounds__(512) reduce_scatter_kernel(GinDevHandle h, siz
                                                             float scale, void* out, int ch) {
   if (!gin_barrier(h, ch, blockIdx.x)) return;
   const size_t base = off + ((nvec_per_rank * h.rank) << 4);
-  for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec_per_rank;
-       v += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    float acc[8];
-    int n;
-    reduce_vec<BF16, NVLS>(h, base + (v << 4), scale, acc, n);
+  reduce_range<BF16, NVLS, NVLS ? 4 : 2>(h, base, 0, nvec_per_rank, scale, [&](size_t idx, const float(&acc)[8]) {
     if constexpr (OUT_MODE == 1 && BF16) {
-      float4* o = reinterpret_cast<float4*>(out) + 2 * v;
+      float4* o = reinterpret_cast<float4*>(out) + 2 * idx;
       o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
       o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     } else {
-      reinterpret_cast<uint4*>(out)[v] = pack_vec<BF16>(acc);
+      reinterpret_cast<uint4*>(out)[idx] = pack_vec<BF16>(acc);
     }
-  }
+  });
   gin_barrier(h, ch, blockIdx.x);
 }
 
@@ -167,16 +177,25 @@ template <bool NVLS>
 __global__ void __launch_bounds__(512) all_gather_kernel(GinDevHandle h, size_t off, size_t nvec_per_rank, int ch) {
   if (!gin_barrier(h, ch, blockIdx.x)) return;
   const size_t base = off + ((nvec_per_rank * h.rank) << 4);
-  for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec_per_rank;
-       v += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const size_t o = base + (v << 4);
-    const uint4 val = *reinterpret_cast<const uint4*>(h.window[h.rank] + o);
-    if constexpr (NVLS) {
-      mc_st_16(h.mc_window + o, val);
-    } else {
-      for (int p = 1; p < h.nranks; ++p) {
-        const int peer = (h.rank + p) % h.nranks;
-        *reinterpret_cast<uint4*>(h.window[peer] + o) = val;
+  constexpr int U = 4;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec_per_rank; v += stride * U) {
+    uint4 val[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (v + u * stride < nvec_per_rank)
+        val[u] = *reinterpret_cast<const uint4*>(h.window[h.rank] + base + ((v + u * stride) << 4));
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (v + u * stride >= nvec_per_rank) continue;
+      const size_t o = base + ((v + u * stride) << 4);
+      if constexpr (NVLS) {
+        mc_st_16(h.mc_window + o, val[u]);
+      } else {
+        for (int p = 1; p < h.nranks; ++p) {
+          const int peer = (h.rank + p) % h.nranks;
+          *reinterpret_cast<uint4*>(h.window[peer] + o) = val[u];
+        }
       }
     }
   }
@@ -194,9 +213,17 @@ __global__ void __launch_bounds__(512) all_to_all_kernel(GinDevHandle h, size_t 
   const int sub = static_cast<int>(blockIdx.x) / h.nranks;
   const uint4* src = reinterpret_cast<const uint4*>(h.window[h.rank] + send_off) + nvec_per_peer * peer;
   uint4* dst = reinterpret_cast<uint4*>(h.window[peer] + recv_off) + nvec_per_peer * h.rank;
-  for (size_t v = sub * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec_per_peer;
-       v += static_cast<size_t>(per_peer) * blockDim.x)
-    dst[v] = src[v];
+  constexpr int U = 4;
+  const size_t stride = static_cast<size_t>(per_peer) * blockDim.x;
+  for (size_t v = sub * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec_per_peer; v += stride * U) {
+    uint4 val[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (v + u * stride < nvec_per_peer) val[u] = src[v + u * stride];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (v + u * stride < nvec_per_peer) dst[v + u * stride] = val[u];
+  }
   gin_barrier(h, ch, blockIdx.x);
 }
 

@@ -194,7 +194,8 @@ __device__ __forceinline__ uint64_t* gin_signal_ptr(const GinDevHandle& h, int r
 // Release-ordered: everything this THREAD wrote (and, after a __syncthreads(), everything its CTA
 // wrote) to the peer is visible there before the signal value changes.
 __device__ __forceinline__ void gin_signal(const GinDevHandle& h, int peer, int sig, uint64_t value, uint32_t op) {
-  fence_acq_rel_sys();
+  // the release on the atomic orders it after this thread's earlier writes and, through a preceding
+  // __syncthreads(), after its CTA's writes: no separate fence is needed
   red_release_sys_add_u64(gin_signal_ptr(h, peer, sig), op == GIN_SIGNAL_INC ? 1ull : value);
 }
 __device__ __forceinline__ uint64_t gin_read_signal(const GinDevHandle& h, int sig) {

@@ -1,0 +1,632 @@
+// Functional test of the net plugin through its public ABI only (dlopen + ncclNetPlugin_v11), two
+// processes on one host, host buffers. Scenarios: connection set-up on every device (1 and 4
+// threads), message transfer over a table of (send, recv) sizes incl. truncation with 32 requests
+// in flight, the 8 B - 4 MiB ping-pong with tags 0-7 and 8 concurrent requests, grouped receives,
+// eager early/late receives, many connections on one listen communicator, close with requests in
+// flight. Every poll loop has a 20 s deadline; ranks report through exit codes.
+// usage: func_net [plugin.so] [scenario]      env: B200NET_* / OFI_NCCL_* parameters apply
+#include <dlfcn.h>
+#include <sys/socket.h>
+#include <sys/wait.h>
+#include <unistd.h>
+
+#include <cstdarg>
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <random>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "nccl_abi.h"
+
+static int g_rank = 0;
+static int g_sock = -1;
+static ncclNet_v11_t* net = nullptr;
+static void* g_ctx = nullptr;
+
+#define FAIL(...)                                                     \
+  do {                                                                \
+    fprintf(stderr, "[rank %d] %s:%d: ", g_rank, __FILE__, __LINE__); \
+    fprintf(stderr, __VA_ARGS__);                                     \
+    fprintf(stderr, "\n");                                            \
+    return 1;                                                         \
+  } while (0)
+#define OK(call)                                                          \
+  do {                                                                    \
+    ncclResult_t _r = (call);                                             \
+    if (_r != ncclSuccess) FAIL("%s returned %d", #call, (int)_r);        \
+  } while (0)
+
+using Clock = std::chrono::steady_clock;
+static bool expired(Clock::time_point t0, int seconds = 20) { return Clock::now() - t0 > std::chrono::seconds(seconds); }
+
+static void logger(ncclDebugLogLevel level, unsigned long, const char* file, int line, const char* fmt, ...) {
+  if (level > NCCL_LOG_WARN && !getenv("FUNC_NET_VERBOSE")) return;
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  fprintf(stderr, "[rank %d] %s (%s:%d)\n", g_rank, buf, file, line);
+}
+
+static int xchg(int sock, const void* mine, void* theirs, size_t n) {
+  if (write(sock, mine, n) != (ssize_t)n) return 1;
+  size_t got = 0;
+  while (got < n) {
+    ssize_t r = read(sock, (char*)theirs + got, n - got);
+    if (r <= 0) return 1;
+    got += (size_t)r;
+  }
+  return 0;
+}
+static int barrier(int sock) {
+  char a = 'b', b = 0;
+  return xchg(sock, &a, &b, 1);
+}
+
+struct Pair {
+  void* l = nullptr;
+  void* s = nullptr;
+  void* r = nullptr;
+};
+
+// Both ranks listen, swap handles and drive connect/accept until both directions are up.
+static int connect_pair(int dev, int sock, Pair* p, bool keep_listen = false) {
+  char mine[NCCL_NET_HANDLE_MAXSIZE] = {0}, theirs[NCCL_NET_HANDLE_MAXSIZE] = {0};
+  OK(net->listen(g_ctx, dev, mine, &p->l));
+  if (xchg(sock, mine, theirs, sizeof(mine))) FAIL("handle exchange failed");
+  p->s = p->r = nullptr;
+  auto t0 = Clock::now();
+  while (!p->s || !p->r) {
+    if (!p->s) OK(net->connect(g_ctx, dev, theirs, &p->s, nullptr));
+    if (!p->r) OK(net->accept(p->l, &p->r, nullptr));
+    if (expired(t0)) FAIL("connect/accept did not finish (s=%p r=%p)", p->s, p->r);
+  }
+  if (!keep_listen) {
+    OK(net->closeListen(p->l));
+    p->l = nullptr;
+  }
+  return 0;
+}
+static int close_pair(Pair* p) {
+  if (p->s) OK(net->closeSend(p->s));
+  if (p->r) OK(net->closeRecv(p->r));
+  if (p->l) OK(net->closeListen(p->l));
+  *p = Pair();
+  return 0;
+}
+
+static int wait_all(std::vector<void*>& reqs, std::vector<int>* sizes_out = nullptr, int nsub = 1) {
+  auto t0 = Clock::now();
+  std::vector<bool> done(reqs.size(), false);
+  size_t ndone = 0;
+  if (sizes_out) sizes_out->assign(reqs.size() * nsub, -1);
+  while (ndone < reqs.size()) {
+    for (size_t i = 0; i < reqs.size(); ++i) {
+      if (done[i]) continue;
+      int d = 0, sz[8] = {0};
+      OK(net->test(reqs[i], &d, sz));
+      if (d) {
+        done[i] = true;
+        ++ndone;
+        if (sizes_out)
+          for (int k = 0; k < nsub; ++k) (*sizes_out)[i * nsub + k] = sz[k];
+      }
+    }
+    if (expired(t0)) FAIL("requests did not complete: %zu of %zu done", ndone, reqs.size());
+  }
+  return 0;
+}
+
+static void fill(std::vector<uint8_t>& b, uint32_t seed) {
+  std::mt19937 g(seed);
+  for (auto& x : b) x = (uint8_t)g();
+}
+
+// isend / irecv may return a null request: retry with a deadline.
+static int post_send(void* s, void* data, size_t n, int tag, void* mh, void** req) {
+  auto t0 = Clock::now();
+  *req = nullptr;
+  while (!*req) {
+    OK(net->isend(s, data, n, tag, mh, nullptr, req));
+    if (expired(t0)) FAIL("isend kept returning no request (size %zu tag %d)", n, tag);
+  }
+  return 0;
+}
+static int post_recv(void* r, int n, void** data, size_t* sizes, int* tags, void** mh, void** req) {
+  auto t0 = Clock::now();
+  *req = nullptr;
+  while (!*req) {
+    OK(net->irecv(r, n, data, sizes, tags, mh, nullptr, req));
+    if (expired(t0)) FAIL("irecv kept returning no request");
+  }
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------ scenarios
+static int scenario_connection(int sock) {
+  int ndev = 0;
+  OK(net->devices(&ndev));
+  if (ndev < 1) FAIL("no devices");
+  for (int dev = 0; dev < ndev; ++dev) {
+    ncclNetProperties_v11_t props;
+    memset(&props, 0, sizeof(props));
+    OK(net->getProperties(dev, &props));
+    if (!props.name || !(props.ptrSupport & NCCL_PTR_HOST) || props.maxRecvs < 1 || props.maxComms < 1)
+      FAIL("implausible properties for device %d", dev);
+    Pair p;
+    if (connect_pair(dev, sock, &p)) return 1;
+    if (close_pair(&p)) return 1;
+  }
+  return barrier(sock);
+}
+
+static int scenario_message_transfer(int sock) {
+  Pair p;
+  if (connect_pair(0, sock, &p)) return 1;
+  const size_t pairs[][2] = {{512, 512},       {4096, 4096},         {8192, 8192},       {8200, 16384},
+                             {65536, 65536},   {1 << 20, 1 << 20},   {2 << 20, 2 << 20}, {1 << 20, 4096} /* truncated */,
+                             {100, 1 << 20},   {0, 64}};
+  for (auto& sr : pairs) {
+    const size_t ssz = sr[0], rsz = sr[1], expect = ssz < rsz ? ssz : rsz;
+    const int NREQ = 32;
+    std::vector<std::vector<uint8_t>> sbuf(NREQ, std::vector<uint8_t>(ssz ? ssz : 1)), rbuf(NREQ, std::vector<uint8_t>(rsz, 0xEE));
+    void *smh[NREQ], *rmh[NREQ];
+    std::vector<void*> reqs;
+    for (int i = 0; i < NREQ; ++i) {
+      fill(sbuf[i], 1000 * (1 - g_rank) + i);  // what the peer sends to me is seeded with MY rank
+      OK(net->regMr(p.s, sbuf[i].data(), sbuf[i].size(), NCCL_PTR_HOST, &smh[i]));
+      OK(net->regMr(p.r, rbuf[i].data(), rbuf[i].size(), NCCL_PTR_HOST, &rmh[i]));
+    }
+    for (int i = 0; i < NREQ; ++i) {
+      void* req;
+      void* d = rbuf[i].data();
+      size_t sz = rsz;
+      int tag = 7;
+      if (post_recv(p.r, 1, &d, &sz, &tag, &rmh[i], &req)) return 1;
+      reqs.push_back(req);
+    }
+    std::vector<void*> sreqs;
+    for (int i = 0; i < NREQ; ++i) {
+      void* req;
+      if (post_send(p.s, sbuf[i].data(), ssz, 7, smh[i], &req)) return 1;
+      sreqs.push_back(req);
+    }
+    std::vector<int> sizes;
+    if (wait_all(reqs, &sizes)) FAIL("receives of pair (%zu,%zu)", ssz, rsz);
+    if (wait_all(sreqs)) FAIL("sends of pair (%zu,%zu)", ssz, rsz);
+    for (int i = 0; i < NREQ; ++i) {
+      if ((size_t)sizes[i] != expect) FAIL("pair (%zu,%zu) req %d: size %d, expected %zu", ssz, rsz, i, sizes[i], expect);
+      std::vector<uint8_t> want(ssz ? ssz : 1);
+      fill(want, 1000 * g_rank + i);
+      if (expect && memcmp(want.data(), rbuf[i].data(), expect)) FAIL("pair (%zu,%zu) req %d: payload differs", ssz, rsz, i);
+      if (rsz > expect && rbuf[i][expect] != 0xEE) FAIL("pair (%zu,%zu): bytes past the message were touched", ssz, rsz);
+    }
+    void* freq;
+    void* d0 = rbuf[0].data();
+    int fs = (int)expect;
+    OK(net->iflush(p.r, 1, &d0, &fs, &rmh[0], &freq));
+    if (freq) {
+      std::vector<void*> fr{freq};
+      if (wait_all(fr)) return 1;
+    }
+    for (int i = 0; i < NREQ; ++i) {
+      OK(net->deregMr(p.s, smh[i]));
+      OK(net->deregMr(p.r, rmh[i]));
+    }
+    if (barrier(sock)) FAIL("barrier");
+  }
+  return close_pair(&p);
+}
+
+// 8 B - 4 MiB, powers of two, uniform random bytes from seed 0, tags 0-7, 8 concurrent requests.
+static int scenario_pingpong(int sock) {
+  Pair p;
+  if (connect_pair(0, sock, &p)) return 1;
+  std::mt19937 gen(0);
+  for (size_t sz = 8; sz <= (4u << 20); sz <<= 1) {
+    const int NREQ = 8;
+    std::vector<std::vector<uint8_t>> payload(NREQ, std::vector<uint8_t>(sz)), rbuf(NREQ, std::vector<uint8_t>(sz));
+    for (auto& b : payload)
+      for (auto& x : b) x = (uint8_t)gen();  // both ranks draw the same stream: same expected data
+    void *smh[NREQ], *rmh[NREQ];
+    for (int i = 0; i < NREQ; ++i) {
+      OK(net->regMr(p.s, payload[i].data(), sz, NCCL_PTR_HOST, &smh[i]));
+      OK(net->regMr(p.r, rbuf[i].data(), sz, NCCL_PTR_HOST, &rmh[i]));
+    }
+    for (int leg = 0; leg < 2; ++leg) {
+      const bool sender = (leg == g_rank);
+      std::vector<void*> reqs;
+      for (int i = 0; i < NREQ; ++i) {
+        void* req;
+        if (sender) {
+          if (post_send(p.s, payload[i].data(), sz, i, smh[i], &req)) return 1;
+        } else {
+          void* d = rbuf[i].data();
+          size_t s = sz;
+          int tag = i;
+          memset(d, 0, sz);
+          if (post_recv(p.r, 1, &d, &s, &tag, &rmh[i], &req)) return 1;
+        }
+        reqs.push_back(req);
+      }
+      std::vector<int> sizes;
+      if (wait_all(reqs, &sizes)) return 1;
+      if (!sender)
+        for (int i = 0; i < NREQ; ++i) {
+          if ((size_t)sizes[i] != sz) FAIL("size %zu req %d: got %d bytes", sz, i, sizes[i]);
+          if (memcmp(rbuf[i].data(), payload[i].data(), sz)) FAIL("size %zu req %d: payload differs", sz, i);
+        }
+    }
+    for (int i = 0; i < NREQ; ++i) {
+      OK(net->deregMr(p.s, smh[i]));
+      OK(net->deregMr(p.r, rmh[i]));
+    }
+  }
+  if (barrier(sock)) FAIL("barrier");
+  return close_pair(&p);
+}
+
+static int scenario_grouped_recv(int sock) {
+  ncclNetProperties_v11_t props;
+  memset(&props, 0, sizeof(props));
+  OK(net->getProperties(0, &props));
+  Pair p;
+  if (connect_pair(0, sock, &p)) return 1;
+  for (int n : {1, 2, 4, 8}) {
+    if (n > props.maxRecvs) continue;
+    for (size_t base : {(size_t)64, (size_t)4096, (size_t)(256 << 10)}) {
+      // mixed sizes: sub-receive k gets base*(k+1) bytes, tag 100+k; sends go out in reverse tag order
+      std::vector<std::vector<uint8_t>> sbuf(n), rbuf(n);
+      void* data[8];
+      size_t sizes[8];
+      int tags[8];
+      void *rmh[8], *smh[8];
+      for (int k = 0; k < n; ++k) {
+        sbuf[k].resize(base * (k + 1));
+        rbuf[k].assign(base * (k + 1) + 32, 0);
+        fill(sbuf[k], 50 * (1 - g_rank) + k + (uint32_t)base);
+        data[k] = rbuf[k].data();
+        sizes[k] = rbuf[k].size();
+        tags[k] = 100 + k;
+        OK(net->regMr(p.r, rbuf[k].data(), rbuf[k].size(), NCCL_PTR_HOST, &rmh[k]));
+        OK(net->regMr(p.s, sbuf[k].data(), sbuf[k].size(), NCCL_PTR_HOST, &smh[k]));
+      }
+      void* rreq;
+      if (post_recv(p.r, n, data, sizes, tags, rmh, &rreq)) return 1;
+      std::vector<void*> sreqs;
+      for (int k = n - 1; k >= 0; --k) {
+        void* req;
+        if (post_send(p.s, sbuf[k].data(), sbuf[k].size(), 100 + k, smh[k], &req)) return 1;
+        sreqs.push_back(req);
+      }
+      std::vector<void*> rr{rreq};
+      std::vector<int> got;
+      if (wait_all(rr, &got, n)) return 1;
+      if (wait_all(sreqs)) return 1;
+      for (int k = 0; k < n; ++k) {
+        if ((size_t)got[k] != base * (k + 1)) FAIL("n=%d base=%zu sub %d: size %d", n, base, k, got[k]);
+        std::vector<uint8_t> want(base * (k + 1));
+        fill(want, 50 * g_rank + k + (uint32_t)base);
+        if (memcmp(want.data(), rbuf[k].data(), want.size())) FAIL("n=%d base=%zu sub %d: payload differs", n, base, k);
+        OK(net->deregMr(p.r, rmh[k]));
+        OK(net->deregMr(p.s, smh[k]));
+      }
+      if (barrier(sock)) FAIL("barrier");
+    }
+  }
+  return close_pair(&p);
+}
+
+// Eager paths: sends posted before any receive exists (early), after it (late), more eager sends
+// than the queue holds, the size boundary around the eager limit, and grouped receives fed eagerly.
+static int scenario_eager(int sock) {
+  Pair p;
+  if (connect_pair(0, sock, &p)) return 1;
+  ncclNetProperties_v11_t props;
+  memset(&props, 0, sizeof(props));
+  OK(net->getProperties(0, &props));
+  const char* em = getenv("B200NET_EAGER_MAX_SIZE");
+  const bool eager_off = em && atoi(em) == 0;  // with eager disabled nothing can be sent before a receive exists
+  for (size_t sz : {(size_t)8, (size_t)1024, (size_t)8191, (size_t)8192, (size_t)8193}) {
+    for (int early = 0; early < (eager_off ? 1 : 2); ++early) {
+      const int N = 40;  // more than the 32-deep eager queue
+      std::vector<std::vector<uint8_t>> sbuf(N, std::vector<uint8_t>(sz)), rbuf(N, std::vector<uint8_t>(sz));
+      for (int i = 0; i < N; ++i) fill(sbuf[i], 7 * (1 - g_rank) + i + (uint32_t)sz);
+      void* smh;
+      void* rmh;
+      std::vector<void*> sreqs, rreqs;
+      // rank 0 sends first when `early`, rank 1 receives; then roles swap through the barrier order
+      auto do_sends = [&](int first, int last) -> int {
+        for (int i = first; i < last; ++i) {
+          OK(net->regMr(p.s, sbuf[i].data(), sz, NCCL_PTR_HOST, &smh));
+          void* req = nullptr;
+          auto t0 = Clock::now();
+          while (!req) {
+            OK(net->isend(p.s, sbuf[i].data(), sz, 3, smh, nullptr, &req));
+            // keep earlier sends moving while the queue is full
+            for (size_t k = 0; k < sreqs.size(); ++k) {
+              if (!sreqs[k]) continue;
+              int d = 0;
+              OK(net->test(sreqs[k], &d, nullptr));
+              if (d) sreqs[k] = nullptr;
+            }
+            if (expired(t0)) FAIL("eager isend stuck at message %d (size %zu)", i, sz);
+          }
+          sreqs.push_back(req);
+          OK(net->deregMr(p.s, smh));
+        }
+        return 0;
+      };
+      auto do_recvs = [&]() -> int {
+        for (int i = 0; i < N; ++i) {
+          OK(net->regMr(p.r, rbuf[i].data(), sz, NCCL_PTR_HOST, &rmh));
+          void* d = rbuf[i].data();
+          size_t s = sz;
+          int tag = 3;
+          void* req;
+          if (post_recv(p.r, 1, &d, &s, &tag, &rmh, &req)) return 1;
+          rreqs.push_back(req);
+          OK(net->deregMr(p.r, rmh));
+        }
+        return 0;
+      };
+      if (early) {
+        // only 32 eager sends may be outstanding with no receive posted: the 33rd must be refused
+        // (null request) until the receiver shows up
+        // (the tagged protocol has no such window: it buffers at the receiver, so it sends all at once)
+        const bool windowed = props.maxRecvs > 1;
+        const int first_batch = !windowed ? N : (sz <= 8192 ? 32 : 0);
+        if (g_rank == 0 && do_sends(0, first_batch)) return 1;
+        if (g_rank == 0 && first_batch && windowed) {
+          void* extra = nullptr;
+          OK(net->regMr(p.s, sbuf[first_batch].data(), sz, NCCL_PTR_HOST, &smh));
+          OK(net->isend(p.s, sbuf[first_batch].data(), sz, 3, smh, nullptr, &extra));
+          OK(net->deregMr(p.s, smh));
+          if (extra) FAIL("a 33rd eager send was accepted with no receive posted");
+        }
+        if (barrier(sock)) FAIL("barrier");
+        if (g_rank == 1 && do_recvs()) return 1;
+        if (g_rank == 0 && do_sends(first_batch, N)) return 1;
+      } else {
+        if (g_rank == 1 && do_recvs()) return 1;
+        if (barrier(sock)) FAIL("barrier");
+        if (g_rank == 0 && do_sends(0, N)) return 1;
+      }
+      std::vector<void*> live;
+      for (void* r : sreqs)
+        if (r) live.push_back(r);
+      // both ranks must keep polling: the sender's eager requests finish when control messages arrive
+      std::vector<int> sizes;
+      if (g_rank == 1) {
+        if (wait_all(rreqs, &sizes)) return 1;
+        for (int i = 0; i < N; ++i) {
+          std::vector<uint8_t> want(sz);
+          fill(want, 7 * g_rank + i + (uint32_t)sz);
+          if ((size_t)sizes[i] != sz || memcmp(want.data(), rbuf[i].data(), sz))
+            FAIL("eager size %zu early=%d msg %d: wrong size (%d) or payload", sz, early, i, sizes[i]);
+        }
+      } else {
+        if (wait_all(live)) return 1;
+      }
+      if (barrier(sock)) FAIL("barrier");
+    }
+  }
+  // grouped receive fed by eager sends that were posted first (all-eager group, mixed tags)
+  if (props.maxRecvs >= 4 && !eager_off) {
+    const int n = 4;
+    std::vector<std::vector<uint8_t>> sbuf(n, std::vector<uint8_t>(512)), rbuf(n, std::vector<uint8_t>(512));
+    std::vector<void*> sreqs;
+    void* mh[4];
+    if (g_rank == 0) {
+      for (int k = 0; k < n; ++k) {
+        fill(sbuf[k], 900 + k);
+        void* req;
+        OK(net->regMr(p.s, sbuf[k].data(), 512, NCCL_PTR_HOST, &mh[k]));
+        if (post_send(p.s, sbuf[k].data(), 512, 20 + (k % 2), mh[k], &req)) return 1;
+        sreqs.push_back(req);
+      }
+    }
+    if (barrier(sock)) FAIL("barrier");
+    if (g_rank == 1) {
+      void* data[4];
+      size_t sizes[4];
+      int tags[4] = {20, 21, 20, 21};
+      void* rmh[4];
+      for (int k = 0; k < n; ++k) {
+        data[k] = rbuf[k].data();
+        sizes[k] = 512;
+        OK(net->regMr(p.r, rbuf[k].data(), 512, NCCL_PTR_HOST, &rmh[k]));
+      }
+      void* req;
+      if (post_recv(p.r, n, data, sizes, tags, rmh, &req)) return 1;
+      std::vector<void*> rr{req};
+      std::vector<int> got;
+      if (wait_all(rr, &got, n)) return 1;
+      // sends in order: tags 20,21,20,21 -> entries 0,1,2,3
+      for (int k = 0; k < n; ++k) {
+        std::vector<uint8_t> want(512);
+        fill(want, 900 + k);
+        if (got[k] != 512 || memcmp(want.data(), rbuf[k].data(), 512)) FAIL("eager group: sub %d wrong", k);
+        OK(net->deregMr(p.r, rmh[k]));
+      }
+    } else {
+      if (wait_all(sreqs)) return 1;
+      for (int k = 0; k < n; ++k) OK(net->deregMr(p.s, mh[k]));
+    }
+    if (barrier(sock)) FAIL("barrier");
+  }
+  return close_pair(&p);
+}
+
+static int scenario_reuse_listen(int sock) {
+  Pair base;
+  char mine[NCCL_NET_HANDLE_MAXSIZE] = {0}, theirs[NCCL_NET_HANDLE_MAXSIZE] = {0};
+  OK(net->listen(g_ctx, 0, mine, &base.l));
+  if (xchg(sock, mine, theirs, sizeof(mine))) FAIL("handle exchange");
+  for (int round = 0; round < 12; ++round) {
+    char h[NCCL_NET_HANDLE_MAXSIZE];
+    memcpy(h, theirs, sizeof(h));  // a fresh copy: connect keeps its progress inside the handle
+    void *s = nullptr, *r = nullptr;
+    auto t0 = Clock::now();
+    while (!s || !r) {
+      if (!s) OK(net->connect(g_ctx, 0, h, &s, nullptr));
+      if (!r) OK(net->accept(base.l, &r, nullptr));
+      if (expired(t0)) FAIL("round %d: connect/accept stuck", round);
+    }
+    uint64_t out = 0xabc000 + round + g_rank, in = 0;
+    void *smh, *rmh, *sreq, *rreq;
+    OK(net->regMr(s, &out, sizeof(out), NCCL_PTR_HOST, &smh));
+    OK(net->regMr(r, &in, sizeof(in), NCCL_PTR_HOST, &rmh));
+    void* d = &in;
+    size_t sz = sizeof(in);
+    int tag = 1;
+    if (post_recv(r, 1, &d, &sz, &tag, &rmh, &rreq)) return 1;
+    if (post_send(s, &out, sizeof(out), 1, smh, &sreq)) return 1;
+    std::vector<void*> reqs{rreq, sreq};
+    if (wait_all(reqs)) return 1;
+    if (in != 0xabc000u + round + (1 - g_rank)) FAIL("round %d: got %llx", round, (unsigned long long)in);
+    OK(net->deregMr(s, smh));
+    OK(net->deregMr(r, rmh));
+    if (barrier(sock)) FAIL("barrier");
+    OK(net->closeSend(s));
+    OK(net->closeRecv(r));
+  }
+  OK(net->closeListen(base.l));
+  return barrier(sock);
+}
+
+// Close communicators while 32 receives are still posted and unmatched: no crash, no hang, and a
+// fresh connection works afterwards (the aborted endpoint is replaced).
+static int scenario_inflight_close(int sock) {
+  for (int iter = 0; iter < 10; ++iter) {
+    Pair p;
+    if (connect_pair(0, sock, &p)) return 1;
+    const int N = 32;
+    std::vector<std::vector<uint8_t>> rbuf(N, std::vector<uint8_t>(1 << 16));
+    std::vector<void*> mhs(N);
+    for (int i = 0; i < N; ++i) {
+      OK(net->regMr(p.r, rbuf[i].data(), rbuf[i].size(), NCCL_PTR_HOST, &mhs[i]));
+      void* d = rbuf[i].data();
+      size_t s = rbuf[i].size();
+      int tag = 0;
+      void* req;
+      if (post_recv(p.r, 1, &d, &s, &tag, &mhs[i], &req)) return 1;
+    }
+    if (barrier(sock)) FAIL("barrier");
+    for (int i = 0; i < N; ++i) OK(net->deregMr(p.r, mhs[i]));
+    OK(net->closeRecv(p.r));
+    OK(net->closeSend(p.s));
+    p = Pair();
+    if (barrier(sock)) FAIL("barrier");
+  }
+  Pair q;
+  if (connect_pair(0, sock, &q)) return 1;
+  return close_pair(&q);
+}
+
+static int scenario_threads(int) {
+  // each thread gets its own endpoint: 4 threads connect to themselves (loopback) concurrently
+  std::vector<std::thread> th;
+  std::vector<int> rc(4, 1);
+  for (int t = 0; t < 4; ++t) {
+    th.emplace_back([&, t]() {
+      char h[NCCL_NET_HANDLE_MAXSIZE] = {0};
+      void *l = nullptr, *s = nullptr, *r = nullptr;
+      if (net->listen(g_ctx, 0, h, &l) != ncclSuccess) return;
+      auto t0 = Clock::now();
+      while ((!s || !r) && !expired(t0)) {
+        if (!s && net->connect(g_ctx, 0, h, &s, nullptr) != ncclSuccess) return;
+        if (!r && net->accept(l, &r, nullptr) != ncclSuccess) return;
+      }
+      if (!s || !r) return;
+      uint64_t out = 77 + t, in = 0;
+      void *smh, *rmh, *sreq = nullptr, *rreq = nullptr;
+      net->regMr(s, &out, 8, NCCL_PTR_HOST, &smh);
+      net->regMr(r, &in, 8, NCCL_PTR_HOST, &rmh);
+      void* d = &in;
+      size_t sz = 8;
+      int tag = 5;
+      while (!rreq && !expired(t0)) net->irecv(r, 1, &d, &sz, &tag, &rmh, nullptr, &rreq);
+      while (!sreq && !expired(t0)) net->isend(s, &out, 8, 5, smh, nullptr, &sreq);
+      int ds = 0, dr = 0;
+      while ((!ds || !dr) && !expired(t0)) {
+        if (!ds) net->test(sreq, &ds, nullptr);
+        if (!dr) net->test(rreq, &dr, nullptr);
+      }
+      net->deregMr(s, smh);
+      net->deregMr(r, rmh);
+      net->closeSend(s);
+      net->closeRecv(r);
+      net->closeListen(l);
+      if (ds && dr && in == 77u + t) rc[t] = 0;
+    });
+  }
+  for (auto& t : th) t.join();
+  for (int t = 0; t < 4; ++t)
+    if (rc[t]) FAIL("thread %d failed", t);
+  return 0;
+}
+
+struct Scenario {
+  const char* name;
+  int (*fn)(int);
+};
+static const Scenario kScenarios[] = {
+    {"connection", scenario_connection},     {"message_transfer", scenario_message_transfer},
+    {"pingpong", scenario_pingpong},         {"grouped_recv", scenario_grouped_recv},
+    {"eager", scenario_eager},               {"reuse_listen", scenario_reuse_listen},
+    {"inflight_close", scenario_inflight_close}, {"threads", scenario_threads},
+};
+
+static int run_rank(const char* so, const char* only, int sock) {
+  g_sock = sock;
+  void* h = dlopen(so, RTLD_NOW | RTLD_LOCAL);
+  if (!h) FAIL("dlopen(%s): %s", so, dlerror());
+  net = (ncclNet_v11_t*)dlsym(h, "ncclNetPlugin_v11");
+  if (!net) FAIL("ncclNetPlugin_v11 not exported");
+  OK(net->init(&g_ctx, 0x1234, nullptr, logger, nullptr));
+  int rc = 0;
+  for (const auto& s : kScenarios) {
+    if (only && strcmp(only, s.name)) continue;
+    const int r = s.fn(sock);
+    fprintf(stderr, "[rank %d] %-18s %s\n", g_rank, s.name, r ? "FAILED" : "ok");
+    if (r) {
+      rc = 1;
+      break;  // the peer will time out on its side; do not continue out of step
+    }
+  }
+  if (!rc) OK(net->finalize(g_ctx));
+  return rc;
+}
+
+int main(int argc, char** argv) {
+  const char* so = argc > 1 ? argv[1] : "./libnccl-net-ofi-b200.so";
+  const char* only = argc > 2 ? argv[2] : nullptr;
+  int sv[2];
+  if (socketpair(AF_UNIX, SOCK_STREAM, 0, sv) != 0) return 2;
+  const pid_t pid = fork();
+  if (pid < 0) return 2;
+  if (pid == 0) {
+    close(sv[0]);
+    g_rank = 1;
+    _exit(run_rank(so, only, sv[1]));
+  }
+  close(sv[1]);
+  g_rank = 0;
+  const int rc0 = run_rank(so, only, sv[0]);
+  close(sv[0]);  // a peer blocked in a barrier sees end-of-file instead of waiting forever
+  int status = 0;
+  waitpid(pid, &status, 0);
+  const int rc1 = WIFEXITED(status) ? WEXITSTATUS(status) : 3;
+  if (rc0 || rc1) {
+    fprintf(stderr, "FAILED: rank0=%d rank1=%d\n", rc0, rc1);
+    return 1;
+  }
+  printf("ok\n");
+  return 0;
+}

@@ -1,0 +1,358 @@
+#include "b200net/shm_fabric.h"
+
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <sys/uio.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <cerrno>
+#include <cstring>
+#include <stdexcept>
+
+#include "b200net/log.h"
+#include "b200net/math.h"
+#include "b200net/param.h"
+
+namespace b200net {
+
+static constexpr uint64_t EP_MAGIC = 0x42323030'4e455431ull;  // "B200NET1"
+static std::atomic<uint32_t> g_next_ep_id{0};
+
+// staged write fragment: [FragHdr][bytes]
+struct FragHdr {
+  uint64_t remote_addr;
+  uint32_t len;
+  uint32_t pad;
+};
+
+bool FabricEndpoint::cma_disabled_by_param() { return params().disable_cma.get(); }
+
+FabricEndpoint::FabricEndpoint() : id_(g_next_ep_id.fetch_add(1)) {
+  char buf[FAB_EP_NAME_LEN];
+  snprintf(buf, sizeof(buf), "/b200net.%d.%u", static_cast<int>(getpid()), id_);
+  name_ = buf;
+  const size_t small_bytes = MpscByteRing::footprint(FAB_SMALL_CELLS, FAB_SMALL_CELL + sizeof(DgramHdr));
+  const size_t large_bytes = MpscByteRing::footprint(FAB_LARGE_CELLS, FAB_LARGE_CELL + sizeof(DgramHdr));
+  const size_t hdr_bytes = round_up<size_t>(sizeof(EpSegmentHdr), 64);
+  const size_t small_off = hdr_bytes;
+  const size_t large_off = round_up<size_t>(small_off + small_bytes, 64);
+  const size_t mr_off = round_up<size_t>(large_off + large_bytes, 4096);
+  bytes_ = round_up<size_t>(mr_off + FAB_MR_TABLE_SLOTS * sizeof(MrTableEntry), 4096);
+  shm_unlink(name_.c_str());  // a stale segment of a dead process with the same pid
+  fd_ = shm_open(name_.c_str(), O_CREAT | O_EXCL | O_RDWR, 0600);
+  if (fd_ < 0) throw std::runtime_error("shm_open(" + name_ + ") failed: " + strerror(errno));
+  if (ftruncate(fd_, static_cast<off_t>(bytes_)) != 0) {
+    const int e = errno;
+    close(fd_);
+    shm_unlink(name_.c_str());
+    throw std::runtime_error(std::string("ftruncate failed: ") + strerror(e));
+  }
+  base_ = mmap(nullptr, bytes_, PROT_READ | PROT_WRITE, MAP_SHARED, fd_, 0);
+  if (base_ == MAP_FAILED) {
+    const int e = errno;
+    close(fd_);
+    shm_unlink(name_.c_str());
+    throw std::runtime_error(std::string("mmap failed: ") + strerror(e));
+  }
+  hdr_ = new (base_) EpSegmentHdr();
+  hdr_->pid = static_cast<uint32_t>(getpid());
+  hdr_->ep_id = id_;
+  hdr_->small_off = small_off;
+  hdr_->large_off = large_off;
+  hdr_->mr_table_off = mr_off;
+  hdr_->total_bytes = bytes_;
+  hdr_->closed.store(0);
+  char* b = static_cast<char*>(base_);
+  small_ = MpscByteRing::create(b + small_off, FAB_SMALL_CELLS, FAB_SMALL_CELL + sizeof(DgramHdr));
+  large_ = MpscByteRing::create(b + large_off, FAB_LARGE_CELLS, FAB_LARGE_CELL + sizeof(DgramHdr));
+  mr_table_ = reinterpret_cast<MrTableEntry*>(b + mr_off);
+  std::atomic_thread_fence(std::memory_order_release);
+  hdr_->magic = EP_MAGIC;  // published last: a peer that sees the magic sees initialised rings
+}
+
+FabricEndpoint::~FabricEndpoint() {
+  if (hdr_) hdr_->closed.store(1, std::memory_order_release);
+  {
+    std::lock_guard<std::mutex> g(av_mu_);
+    for (auto& [n, m] : av_)
+      if (m->base && m->base != base_) munmap(m->base, m->bytes);
+    av_.clear();
+  }
+  if (base_) munmap(base_, bytes_);
+  if (fd_ >= 0) close(fd_);
+  shm_unlink(name_.c_str());
+}
+
+PeerMapping* FabricEndpoint::av_insert(const std::string& name) {
+  std::lock_guard<std::mutex> g(av_mu_);
+  auto it = av_.find(name);
+  if (it != av_.end()) return it->second.get();
+  auto m = std::make_unique<PeerMapping>();
+  m->name = name;
+  if (name == name_) {
+    m->base = base_;
+    m->bytes = bytes_;
+  } else {
+    const int fd = shm_open(name.c_str(), O_RDWR, 0600);
+    if (fd < 0) return nullptr;
+    struct stat st;
+    if (fstat(fd, &st) != 0 || static_cast<size_t>(st.st_size) < sizeof(EpSegmentHdr)) {
+      close(fd);
+      return nullptr;
+    }
+    m->bytes = static_cast<size_t>(st.st_size);
+    m->base = mmap(nullptr, m->bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+    close(fd);
+    if (m->base == MAP_FAILED) return nullptr;
+  }
+  m->hdr = static_cast<EpSegmentHdr*>(m->base);
+  if (m->hdr->magic != EP_MAGIC || m->hdr->total_bytes > m->bytes) {
+    if (m->base != base_) munmap(m->base, m->bytes);
+    return nullptr;
+  }
+  char* b = static_cast<char*>(m->base);
+  m->pid = m->hdr->pid;
+  m->small = MpscByteRing::attach(b + m->hdr->small_off);
+  m->large = MpscByteRing::attach(b + m->hdr->large_off);
+  m->mr_table = reinterpret_cast<MrTableEntry*>(b + m->hdr->mr_table_off);
+  PeerMapping* raw = m.get();
+  av_[name] = std::move(m);
+  return raw;
+}
+
+void FabricEndpoint::av_remove(const std::string& name) {
+  std::lock_guard<std::mutex> g(av_mu_);
+  auto it = av_.find(name);
+  if (it == av_.end()) return;
+  if (it->second->base && it->second->base != base_) munmap(it->second->base, it->second->bytes);
+  av_.erase(it);
+}
+
+void FabricEndpoint::inject_drop(DgramType type, int count) { drop_[static_cast<int>(type)] = count; }
+
+int FabricEndpoint::send(PeerMapping* dst, DgramType type, uint16_t flags, const void* a, size_t alen, const void* b,
+                         size_t blen) {
+  if (!dst) return -EINVAL;
+  if (dst->hdr->closed.load(std::memory_order_acquire)) return -ENOTCONN;
+  const size_t len = alen + blen;
+  if (len > FAB_LARGE_CELL) return -EMSGSIZE;
+  if (!drop_.empty()) {
+    auto it = drop_.find(static_cast<int>(type));
+    if (it != drop_.end() && it->second > 0) {
+      --it->second;
+      ++dropped_;
+      return 0;  // the sender believes it went out
+    }
+  }
+  // header + first fragment are gathered into one contiguous prefix; small on-stack copy
+  DgramHdr h{static_cast<uint16_t>(type), flags, id_, static_cast<uint32_t>(getpid()), static_cast<uint32_t>(len)};
+  MpscByteRing& ring = (len <= FAB_SMALL_CELL && !(flags & DGRAM_FLAG_ORDER_AFTER_FRAGS)) ? dst->small : dst->large;
+  bool ok;
+  if (blen == 0) {
+    ok = ring.push(&h, sizeof(h), a, alen);
+  } else {
+    // three fragments: copy header + a into a scratch prefix
+    char prefix[sizeof(DgramHdr) + 256];
+    if (alen > 256) return -EMSGSIZE;
+    memcpy(prefix, &h, sizeof(h));
+    memcpy(prefix + sizeof(h), a, alen);
+    ok = ring.push(prefix, sizeof(h) + alen, b, blen);
+  }
+  if (!ok) {
+    ++eagain_;
+    return -EAGAIN;
+  }
+  ++sent_;
+  return 0;
+}
+
+// Cross-memory attach is assumed to work until the kernel refuses it (ptrace policy); the first
+// refusal switches this peer to staged writes for good.
+bool FabricEndpoint::probe_cma(PeerMapping* dst) {
+  if (!dst->cma_probed) {
+    dst->cma_probed = true;
+    dst->cma_ok = !cma_disabled_by_param();
+  }
+  return dst->cma_ok;
+}
+
+bool FabricEndpoint::writes_are_staged(PeerMapping* dst) {
+  if (dst->pid == static_cast<uint32_t>(getpid()) && !cma_disabled_by_param()) return false;
+  return !probe_cma(dst);
+}
+
+int FabricEndpoint::write_host(PeerMapping* dst, uint64_t remote_addr, const void* local, size_t len, size_t* done) {
+  if (!dst || !done) return -EINVAL;
+  if (*done >= len) return 0;
+  if (dst->hdr->closed.load(std::memory_order_acquire)) return -ENOTCONN;
+  if (dst->pid == static_cast<uint32_t>(getpid()) && !cma_disabled_by_param()) {
+    memcpy(reinterpret_cast<char*>(remote_addr) + *done, static_cast<const char*>(local) + *done, len - *done);
+    *done = len;
+    return 0;
+  }
+  if (probe_cma(dst)) {
+    while (*done < len) {
+      iovec l{const_cast<char*>(static_cast<const char*>(local)) + *done, len - *done};
+      iovec r{reinterpret_cast<void*>(remote_addr + *done), len - *done};
+      const ssize_t n = process_vm_writev(static_cast<pid_t>(dst->pid), &l, 1, &r, 1, 0);
+      if (n < 0) {
+        if (*done == 0 && (errno == EPERM || errno == ENOSYS)) {
+          NET_INFO(NCCL_NET, "cross-memory attach to pid %u refused (%s): using staged writes", dst->pid,
+                   strerror(errno));
+          dst->cma_ok = false;
+          break;
+        }
+        return errno == ESRCH ? -ENOTCONN : -EFAULT;
+      }
+      *done += static_cast<size_t>(n);
+    }
+    if (*done >= len) return 0;
+  }
+  // staged path: fragments that the target applies when it polls; stop at the first full ring
+  const size_t chunk = FAB_LARGE_CELL - sizeof(FragHdr);
+  while (*done < len) {
+    const size_t n = std::min(chunk, len - *done);
+    FragHdr fh{remote_addr + *done, static_cast<uint32_t>(n), 0};
+    const int rc = send(dst, DgramType::WRITE_FRAG, 0, &fh, sizeof(fh), static_cast<const char*>(local) + *done, n);
+    if (rc != 0) return rc;  // -EAGAIN: caller retries later from *done
+    *done += n;
+  }
+  return 0;
+}
+
+int FabricEndpoint::read_host(PeerMapping* dst, uint64_t remote_addr, void* local, size_t len) {
+  if (!dst) return -EINVAL;
+  if (len == 0) return 0;
+  if (dst->pid == static_cast<uint32_t>(getpid())) {
+    memcpy(local, reinterpret_cast<const void*>(remote_addr), len);
+    return 0;
+  }
+  if (!probe_cma(dst)) return -ENOTSUP;
+  size_t done = 0;
+  while (done < len) {
+    iovec l{static_cast<char*>(local) + done, len - done};
+    iovec r{reinterpret_cast<void*>(remote_addr + done), len - done};
+    const ssize_t n = process_vm_readv(static_cast<pid_t>(dst->pid), &l, 1, &r, 1, 0);
+    if (n < 0) {
+      if (done == 0 && (errno == EPERM || errno == ENOSYS)) {
+        dst->cma_ok = false;
+        return -ENOTSUP;
+      }
+      return -EFAULT;
+    }
+    done += static_cast<size_t>(n);
+  }
+  return 0;
+}
+
+int FabricEndpoint::poll(int budget, const DgramHandler& handler) {
+  int n = 0;
+  for (MpscByteRing* ring : {&small_, &large_}) {
+    while (n < budget) {
+      size_t len = 0;
+      const void* p = ring->peek(&len);
+      if (!p) break;
+      const DgramHdr* h = static_cast<const DgramHdr*>(p);
+      const char* payload = static_cast<const char*>(p) + sizeof(DgramHdr);
+      if (h->type == static_cast<uint16_t>(DgramType::WRITE_FRAG)) {
+        const FragHdr* fh = reinterpret_cast<const FragHdr*>(payload);
+        memcpy(reinterpret_cast<void*>(fh->remote_addr), payload + sizeof(FragHdr), fh->len);
+      } else {
+        handler(*h, payload);
+      }
+      ring->release_front();
+      ++n;
+    }
+  }
+  return n;
+}
+
+int FabricEndpoint::mr_publish(const MrTableEntry& e) {
+  std::lock_guard<std::mutex> g(mr_mu_);
+  for (size_t i = 0; i < FAB_MR_TABLE_SLOTS; ++i) {
+    const size_t slot = (e.key + i) % FAB_MR_TABLE_SLOTS;
+    if (mr_table_[slot].key == 0) {
+      MrTableEntry tmp = e;
+      tmp.key = 0;
+      mr_table_[slot] = tmp;
+      std::atomic_thread_fence(std::memory_order_release);
+      reinterpret_cast<std::atomic<uint64_t>*>(&mr_table_[slot].key)->store(e.key, std::memory_order_release);
+      return 0;
+    }
+  }
+  return -ENOSPC;
+}
+
+void FabricEndpoint::mr_unpublish(uint64_t key) {
+  std::lock_guard<std::mutex> g(mr_mu_);
+  for (size_t i = 0; i < FAB_MR_TABLE_SLOTS; ++i) {
+    const size_t slot = (key + i) % FAB_MR_TABLE_SLOTS;
+    if (mr_table_[slot].key == key) {
+      reinterpret_cast<std::atomic<uint64_t>*>(&mr_table_[slot].key)->store(0, std::memory_order_release);
+      return;
+    }
+  }
+}
+
+const MrTableEntry* FabricEndpoint::mr_lookup(const PeerMapping* peer, uint64_t key) {
+  if (!peer || key == 0) return nullptr;
+  for (size_t i = 0; i < FAB_MR_TABLE_SLOTS; ++i) {
+    const size_t slot = (key + i) % FAB_MR_TABLE_SLOTS;
+    const uint64_t k = reinterpret_cast<const std::atomic<uint64_t>*>(&peer->mr_table[slot].key)->load(std::memory_order_acquire);
+    if (k == key) return &peer->mr_table[slot];
+  }
+  return nullptr;
+}
+
+// ---------------------------------------------------------------- ShmWindow
+std::unique_ptr<ShmWindow> ShmWindow::create(const std::string& name, size_t bytes) {
+  shm_unlink(name.c_str());
+  const int fd = shm_open(name.c_str(), O_CREAT | O_EXCL | O_RDWR, 0600);
+  if (fd < 0) return nullptr;
+  bytes = round_up<size_t>(bytes, 4096);
+  if (ftruncate(fd, static_cast<off_t>(bytes)) != 0) {
+    close(fd);
+    shm_unlink(name.c_str());
+    return nullptr;
+  }
+  void* p = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (p == MAP_FAILED) {
+    shm_unlink(name.c_str());
+    return nullptr;
+  }
+  memset(p, 0, bytes);
+  std::unique_ptr<ShmWindow> w(new ShmWindow());
+  w->name_ = name;
+  w->base_ = p;
+  w->bytes_ = bytes;
+  w->owner_ = true;
+  return w;
+}
+
+std::unique_ptr<ShmWindow> ShmWindow::open(const std::string& name) {
+  const int fd = shm_open(name.c_str(), O_RDWR, 0600);
+  if (fd < 0) return nullptr;
+  struct stat st;
+  if (fstat(fd, &st) != 0 || st.st_size <= 0) {
+    close(fd);
+    return nullptr;
+  }
+  void* p = mmap(nullptr, static_cast<size_t>(st.st_size), PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (p == MAP_FAILED) return nullptr;
+  std::unique_ptr<ShmWindow> w(new ShmWindow());
+  w->name_ = name;
+  w->base_ = p;
+  w->bytes_ = static_cast<size_t>(st.st_size);
+  return w;
+}
+
+ShmWindow::~ShmWindow() {
+  if (base_) munmap(base_, bytes_);
+  if (owner_) shm_unlink(name_.c_str());
+}
+
+}  // namespace b200net

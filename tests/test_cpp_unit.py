@@ -5,7 +5,7 @@ from pathlib import Path
 import pytest
 
 CSRC_TESTS = Path(__file__).resolve().parent.parent / "aws-ofi-nccl_b200" / "csrc" / "tests"
-NAMES = sorted(p.stem for p in list(CSRC_TESTS.glob("*.cpp")) + list(CSRC_TESTS.glob("*.c")))
+NAMES = sorted(p.stem for p in CSRC_TESTS.glob("unit_*.cpp"))
 
 
 @pytest.mark.parametrize("name", NAMES)

@@ -1,0 +1,61 @@
+"""Functional tests of the net plugin through its exported ABI (two host processes, no GPU)."""
+import ctypes
+import os
+import subprocess
+
+import pytest
+
+
+def _run(built, env_extra, scenario=None, timeout=400):
+    env = dict(os.environ)
+    env.update(env_extra)
+    cmd = [str(built / "tests" / "func_net"), str(built / "libnccl-net-ofi-b200.so")]
+    if scenario:
+        cmd.append(scenario)
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=built)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+
+
+@pytest.mark.parametrize("env", [
+    {"B200NET_PROTOCOL": "SENDRECV"},
+    {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4"},
+    {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "1"},
+    {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4", "B200NET_DISABLE_CMA": "1"},
+    {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4", "B200NET_EAGER_MAX_SIZE": "0"},
+    {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "3", "B200NET_MIN_STRIPE_SIZE": "4096",
+     "B200NET_MR_CACHE_DISABLE": "1"},
+], ids=["sendrecv", "rdma4", "rdma1", "rdma4-staged-writes", "rdma4-no-eager", "rdma3-small-stripes-nocache"])
+def test_two_process_scenarios(built, env):
+    _run(built, env)
+
+
+def test_compat_env_prefix_is_honoured(built):
+    # the reference's variable names keep working
+    _run(built, {"OFI_NCCL_PROTOCOL": "RDMA", "OFI_NCCL_FORCE_NUM_RAILS": "2"}, "pingpong")
+
+
+def test_exported_symbols_and_names(built):
+    lib = ctypes.CDLL(str(built / "libnccl-net-ofi-b200.so"))
+    for v in range(6, 13):
+        assert hasattr(lib, f"ncclNetPlugin_v{v}")
+    for alias in ("libnccl-net.so", "libnccl-net-b200.so"):
+        assert (built / alias).exists()
+
+
+def test_c_program_can_dlopen_plugin(built):
+    res = subprocess.run([str(built / "tests" / "dlopen_c_test"), str(built / "libnccl-net-ofi-b200.so")],
+                         capture_output=True, text=True, timeout=60, cwd=built)
+    assert res.returncode == 0 and res.stdout.startswith("ok"), res.stdout + res.stderr
+
+
+def test_plugin_name_follows_nccl_net(built):
+    code = ("import ctypes,sys;l=ctypes.CDLL(sys.argv[1]);"
+            "p=ctypes.c_char_p.in_dll(l,'ncclNetPlugin_v11');print(p.value.decode())")
+    import sys
+    so = str(built / "libnccl-net-ofi-b200.so")
+    out = subprocess.run([sys.executable, "-c", code, so], capture_output=True, text=True,
+                         env={**os.environ, "NCCL_NET": "MyFabric"}).stdout.strip()
+    assert out == "MyFabric"
+    out = subprocess.run([sys.executable, "-c", code, so], capture_output=True, text=True,
+                         env={k: v for k, v in os.environ.items() if k != "NCCL_NET"}).stdout.strip()
+    assert out == "B200NVL"
