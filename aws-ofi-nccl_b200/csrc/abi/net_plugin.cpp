@@ -1,6 +1,10 @@
 // Exported ncclNet tables, ABI versions 6 to 12. NCCL dlsym()s the newest "ncclNetPlugin_vN" it
 // knows; each table adapts that generation's signatures and property struct to the validated API
 // (reference: src/nccl_ofi_interface_nvidia.cpp:661-858).
+#include <execinfo.h>
+#include <signal.h>
+#include <unistd.h>
+
 #include <atomic>
 #include <climits>
 #include <cstdlib>
@@ -25,6 +29,26 @@ __attribute__((constructor)) void adopt_requested_name() {
   const char* want = getenv("NCCL_NET");
   if (want && *want && strcasecmp(want, "IB") != 0 && strcasecmp(want, "Socket") != 0)
     snprintf(g_name, sizeof(g_name), "%s", want);
+}
+
+// Debug aid: with B200NET_SEGV_BACKTRACE=1 a crash inside the process prints raw return addresses
+// (resolve them against the .so with addr2line) before the default action runs.
+void segv_backtrace(int sig) {
+  void* frames[64];
+  const int n = backtrace(frames, 64);
+  const char msg[] = "\n[b200net] fatal signal, backtrace:\n";
+  if (write(2, msg, sizeof(msg) - 1) < 0) {}
+  backtrace_symbols_fd(frames, n, 2);
+  signal(sig, SIG_DFL);
+  raise(sig);
+}
+__attribute__((constructor)) void install_segv_backtrace() {
+  const char* e = getenv("B200NET_SEGV_BACKTRACE");
+  if (e && *e == '1') {
+    signal(SIGSEGV, segv_backtrace);
+    signal(SIGBUS, segv_backtrace);
+    signal(SIGABRT, segv_backtrace);
+  }
 }
 
 // The strings returned in property structs must outlive the call: keep one copy per device.
@@ -225,10 +249,10 @@ ncclResult_t irecv_v6(void* r, int n, void** d, int* sizes, int* tags, void** mh
 ncclResult_t irecv_v9(void* r, int n, void** d, size_t* sizes, int* tags, void** mh, void** req) {
   return api::irecv(r, n, d, sizes, tags, mh, req);
 }
-// v10+: a non-null phandles[0] value of NCCL_NET_OPTIONAL_RECV_COMPLETION marks LL/LL128 receives
-// that may complete before their data has landed.
-ncclResult_t irecv_v10(void* r, int n, void** d, size_t* sizes, int* tags, void** mh, void** ph, void** req) {
-  const bool optional = ph && reinterpret_cast<uintptr_t>(ph[0]) == NCCL_NET_OPTIONAL_RECV_COMPLETION;
+// v10+: NCCL marks LL/LL128 receives, which may complete before their data has landed, by
+// presetting *request to NCCL_NET_OPTIONAL_RECV_COMPLETION.
+ncclResult_t irecv_v10(void* r, int n, void** d, size_t* sizes, int* tags, void** mh, void**, void** req) {
+  const bool optional = req && reinterpret_cast<uintptr_t>(*req) == NCCL_NET_OPTIONAL_RECV_COMPLETION;
   return api::irecv(r, n, d, sizes, tags, mh, req, optional);
 }
 ncclResult_t iflush(void* r, int n, void** d, int* sizes, void** mh, void** req) { return api::iflush(r, n, d, sizes, mh, req); }

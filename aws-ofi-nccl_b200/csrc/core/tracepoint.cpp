@@ -4,7 +4,7 @@
 
 #include <chrono>
 #include <mutex>
-#include <sstream>
+#include <cstdio>
 
 #include "b200net/param.h"
 
@@ -92,17 +92,19 @@ std::vector<Record> snapshot_ring() {
 }
 
 std::string to_chrome_json(const std::vector<Record>& recs) {
-  std::ostringstream o;
-  o << "{\"traceEvents\":[";
+  std::string o = "{\"traceEvents\":[";
+  char buf[384];
   for (size_t i = 0; i < recs.size(); ++i) {
     const Record& r = recs[i];
-    if (i) o << ",";
-    o << "{\"name\":\"" << event_name(r.ev) << "\",\"ph\":\"i\",\"s\":\"t\",\"ts\":" << (r.ts_ns / 1000.0)
-      << ",\"pid\":" << r.dev << ",\"tid\":" << r.comm_id << ",\"args\":{\"seq\":" << r.seq << ",\"size\":" << r.size
-      << ",\"req\":\"" << r.req << "\"}}";
+    snprintf(buf, sizeof(buf),
+             "%s{\"name\":\"%s\",\"ph\":\"i\",\"s\":\"t\",\"ts\":%.3f,\"pid\":%u,\"tid\":%u,"
+             "\"args\":{\"seq\":%u,\"size\":%llu,\"req\":\"%p\"}}",
+             i ? "," : "", event_name(r.ev), r.ts_ns / 1000.0, static_cast<unsigned>(r.dev), r.comm_id, r.seq,
+             static_cast<unsigned long long>(r.size), r.req);
+    o += buf;
   }
-  o << "]}";
-  return o.str();
+  o += "]}";
+  return o;
 }
 
 }  // namespace b200net::trace

@@ -1,0 +1,128 @@
+// Tuner: chooses (algorithm, protocol, channel count) per collective call for NCCL's tuner plugin
+// interface. Three back-ends share one context:
+//   REGION   : polygons in (log2 bytes, log2 ranks) space, first match wins
+//   MODEL    : Hockney cost model  latency * pipeline_ops + bytes / bandwidth
+//   MEASURED : a table of measured times per (collective, algorithm, protocol, channels, size),
+//              produced by a calibration run on the machine itself; active on a single node too
+// (reference: src/tuner/nccl_ofi_tuner.cpp, nccl_ofi_regions.cpp, nccl_ofi_model.cpp,
+//  include/tuner/nccl_ofi_tuner_region.h).
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "nccl_abi.h"
+
+namespace b200net::tuner {
+
+constexpr size_t TUNER_MAX_RANKS = 1024 * 1024;
+constexpr size_t TUNER_MAX_SIZE = 100ull * 1024 * 1024 * 1024;
+constexpr int TUNER_MAX_VERTICES = 20;
+
+enum class PlatformKind { UNKNOWN, P5_P5E, P5EN, P6_B200, P6_B300, B200_NVSWITCH };
+PlatformKind platform_from_product_name(const std::string& product, bool local_nvswitch_b200);
+const char* platform_name(PlatformKind k);
+
+// ---------------------------------------------------------------- geometry
+struct Point {
+  double x, y;  // log2(bytes), log2(ranks)
+};
+struct Region {
+  int algorithm, protocol;
+  std::vector<Point> vertices;  // polygon, any orientation, at most TUNER_MAX_VERTICES
+};
+// 1 strictly inside, 0 on the boundary, -1 outside.
+int is_inside_region(Point p, const Region& r);
+// Push the far edges of a polygon out to the limits of the space, so that sizes / rank counts
+// beyond the measured range keep the decision of the nearest measured edge.
+Region extend_region(const Region& r, Point lo, Point hi);
+double distance_to_segment(Point p, Point a, Point b);
+bool segments_intersect(Point a, Point b, Point c, Point d);
+
+struct Decision {
+  int algorithm = NCCL_ALGO_UNDEF;
+  int protocol = NCCL_PROTO_UNDEF;
+  int n_channels = 0;  // 0 = leave to NCCL
+};
+
+// ---------------------------------------------------------------- back-ends
+class RegionTuner {
+ public:
+  RegionTuner(PlatformKind platform, size_t n_ranks, size_t n_nodes);
+  bool supported() const { return !regions_[ncclFuncAllReduce].empty(); }
+  Decision decide(ncclFunc_t coll, size_t bytes) const;
+  const std::vector<Region>& regions(ncclFunc_t coll) const { return regions_[coll]; }
+
+ private:
+  PlatformKind platform_;
+  size_t n_ranks_, n_nodes_;
+  std::vector<Region> regions_[ncclNumFuncs];
+};
+
+struct ModelParams {
+  double net_lat_us;              // inter-node latency
+  double internode_bw_GiBs;       // per rail
+  int rails;
+  double intranode_bw_GiBs;       // per channel
+  double nvlink_lat_us[NCCL_NUM_ALGORITHMS][NCCL_NUM_PROTOCOLS];
+  int channels;
+};
+class ModelTuner {
+ public:
+  ModelTuner(PlatformKind platform, size_t n_ranks, size_t n_nodes);
+  bool supported() const { return supported_; }
+  // microseconds, or <0 when the combination is not modelled
+  double cost_us(ncclFunc_t coll, int algo, int proto, int pipe_ops, size_t bytes) const;
+  Decision decide(ncclFunc_t coll, size_t bytes, int pipe_ops) const;
+  const ModelParams& params() const { return p_; }
+
+ private:
+  ModelParams p_{};
+  size_t n_ranks_, n_nodes_;
+  bool supported_ = false;
+};
+
+struct MeasuredRow {
+  int coll, algo, proto, n_channels;
+  size_t bytes;
+  double time_us;
+};
+class MeasuredTuner {
+ public:
+  // Parses the calibration JSON ({"world":N,"rows":[{"coll":..,"algo":..,"proto":..,"nchannels":..,
+  // "bytes":..,"time_us":..},...]}). Returns false (and stays unsupported) on a malformed file.
+  bool load(const std::string& path);
+  bool load_from_string(const std::string& json);
+  bool supported() const { return !rows_.empty(); }
+  size_t world() const { return world_; }
+  // Best measured combination at the nearest measured size (log scale) for this collective.
+  Decision decide(ncclFunc_t coll, size_t bytes) const;
+  size_t num_rows() const { return rows_.size(); }
+
+ private:
+  std::vector<MeasuredRow> rows_;
+  size_t world_ = 0;
+};
+
+// ---------------------------------------------------------------- context used by the ABI shims
+enum class TunerType { INTERNAL, REGION, MODEL, MEASURED };
+struct TunerContext {
+  TunerType type = TunerType::INTERNAL;
+  PlatformKind platform = PlatformKind::UNKNOWN;
+  size_t n_ranks = 0, n_nodes = 0;
+  RegionTuner* region = nullptr;
+  ModelTuner* model = nullptr;
+  MeasuredTuner* measured = nullptr;
+  ~TunerContext();
+};
+// nullptr means "fall back to NCCL's internal tuner" (unknown platform, TUNER_TYPE=Internal, ...).
+TunerContext* create_context(size_t n_ranks, size_t n_nodes);
+// Apply a decision to NCCL's cost table: the chosen entry gets cost 0 unless NCCL marked it
+// NCCL_ALGO_PROTO_IGNORE. Returns true when the table was changed.
+bool apply_decision(const Decision& d, float** cost_table, int num_algo, int num_proto, int* n_channels);
+Decision get_decision(const TunerContext* ctx, ncclFunc_t coll, size_t bytes, int pipe_ops);
+// Chunk size hint (v6 getChunkSize); 0 = no opinion.
+size_t get_chunk_size(const TunerContext* ctx, ncclFunc_t coll, size_t bytes, int algo, int proto, int n_channels);
+
+}  // namespace b200net::tuner

@@ -8,7 +8,8 @@
 
 #include <cstdlib>
 #include <cstring>
-#include <fstream>
+#include <cstdio>
+#include <string>
 
 namespace b200net {
 
@@ -49,11 +50,15 @@ uint32_t system_node_id() {
 std::string system_product_name() {
   if (const char* f = getenv("OFI_NCCL_FORCE_PRODUCT_NAME")) return f;
   if (const char* f = getenv("B200NET_FORCE_PRODUCT_NAME")) return f;
-  std::ifstream in("/sys/devices/virtual/dmi/id/product_name");
-  std::string s;
-  if (in && std::getline(in, s)) {
-    while (!s.empty() && (s.back() == '\n' || s.back() == ' ')) s.pop_back();
-    return s;
+  char buf[256] = {0};
+  if (FILE* f = fopen("/sys/devices/virtual/dmi/id/product_name", "r")) {
+    const bool got = fgets(buf, sizeof(buf), f) != nullptr;
+    fclose(f);
+    if (got) {
+      std::string s(buf);
+      while (!s.empty() && (s.back() == '\n' || s.back() == ' ')) s.pop_back();
+      return s;
+    }
   }
   return "";
 }
@@ -63,9 +68,11 @@ uint64_t system_host_hash() {
   char host[256] = {0};
   gethostname(host, sizeof(host) - 1);
   uint64_t h = fnv1a(host, strlen(host));
-  std::ifstream in("/proc/sys/kernel/random/boot_id");
-  std::string boot;
-  if (in && std::getline(in, boot)) h = fnv1a(boot.data(), boot.size(), h);
+  char boot[128] = {0};
+  if (FILE* f = fopen("/proc/sys/kernel/random/boot_id", "r")) {
+    if (fgets(boot, sizeof(boot), f)) h = fnv1a(boot, strlen(boot), h);
+    fclose(f);
+  }
   return h;
 }
 

@@ -6,8 +6,7 @@
 #include <algorithm>
 #include <cctype>
 #include <cstring>
-#include <fstream>
-#include <sstream>
+#include <cstdio>
 
 #include "b200net/cuda_shim.h"
 #include "b200net/log.h"
@@ -18,9 +17,11 @@ namespace b200net {
 static int read_numa_node(const std::string& bus_id) {
   std::string id = bus_id;
   std::transform(id.begin(), id.end(), id.begin(), [](unsigned char c) { return std::tolower(c); });
-  std::ifstream in("/sys/bus/pci/devices/" + id + "/numa_node");
   int n = -1;
-  if (in) in >> n;
+  if (FILE* f = fopen(("/sys/bus/pci/devices/" + id + "/numa_node").c_str(), "r")) {
+    if (fscanf(f, "%d", &n) != 1) n = -1;
+    fclose(f);
+  }
   return n;
 }
 
@@ -98,8 +99,8 @@ std::vector<TopoGroup> Topology::group(int rails_per_gpu, int rail_speed_mbps) c
 // </pci></cpu></system> — the GPU and its virtual NIC share a (virtual) switch, so NCCL's search
 // pairs them with the shortest path.
 std::string Topology::to_nccl_xml(const std::vector<TopoGroup>& groups) const {
-  std::ostringstream o;
-  o << "<system version=\"1\">\n";
+  std::string o = "<system version=\"1\">\n";
+  char line[512];
   std::vector<int> numas;
   for (const auto& g : gpus_) {
     const int n = g.numa_node < 0 ? 0 : g.numa_node;
@@ -108,27 +109,35 @@ std::string Topology::to_nccl_xml(const std::vector<TopoGroup>& groups) const {
   std::sort(numas.begin(), numas.end());
   if (numas.empty()) numas.push_back(0);
   for (int numa : numas) {
-    o << "  <cpu numaid=\"" << numa << "\" affinity=\"\" arch=\"x86_64\" vendor=\"\" familyid=\"0\" modelid=\"0\">\n";
+    snprintf(line, sizeof(line),
+             "  <cpu numaid=\"%d\" affinity=\"\" arch=\"x86_64\" vendor=\"\" familyid=\"0\" modelid=\"0\">\n", numa);
+    o += line;
     for (const auto& grp : groups) {
       const TopoGpu& g = gpus_[grp.gpu];
       if ((g.numa_node < 0 ? 0 : g.numa_node) != numa) continue;
-      char sw[32], nic[32];
-      snprintf(sw, sizeof(sw), "ffff:%02x:00.0", g.ordinal);
-      snprintf(nic, sizeof(nic), "ffff:%02x:01.0", g.ordinal);
-      o << "    <pci busid=\"" << sw << "\" class=\"0x060400\" link_speed=\"32.0 GT/s PCIe\" link_width=\"16\">\n";
-      o << "      <pci busid=\"" << (g.pci_bus_id.empty() ? "0000:00:00.0" : g.pci_bus_id)
-        << "\" class=\"0x030200\" link_speed=\"32.0 GT/s PCIe\" link_width=\"16\"/>\n";
-      o << "      <pci busid=\"" << nic << "\" class=\"0x020000\" link_speed=\"32.0 GT/s PCIe\" link_width=\"16\">\n";
-      o << "        <nic>\n";
-      o << "          <net name=\"nvl" << g.ordinal << "\" dev=\"" << g.ordinal << "\" speed=\"" << grp.speed_mbps
-        << "\" port=\"0\" guid=\"0x" << std::hex << (0xb200000000ull | static_cast<unsigned>(g.ordinal)) << std::dec
-        << "\" maxconn=\"32768\" gdr=\"1\"/>\n";
-      o << "        </nic>\n      </pci>\n    </pci>\n";
+      snprintf(line, sizeof(line),
+               "    <pci busid=\"ffff:%02x:00.0\" class=\"0x060400\" link_speed=\"32.0 GT/s PCIe\" link_width=\"16\">\n",
+               g.ordinal);
+      o += line;
+      snprintf(line, sizeof(line),
+               "      <pci busid=\"%s\" class=\"0x030200\" link_speed=\"32.0 GT/s PCIe\" link_width=\"16\"/>\n",
+               g.pci_bus_id.empty() ? "0000:00:00.0" : g.pci_bus_id.c_str());
+      o += line;
+      snprintf(line, sizeof(line),
+               "      <pci busid=\"ffff:%02x:01.0\" class=\"0x020000\" link_speed=\"32.0 GT/s PCIe\" link_width=\"16\">\n",
+               g.ordinal);
+      o += line;
+      o += "        <nic>\n";
+      snprintf(line, sizeof(line),
+               "          <net name=\"nvl%d\" dev=\"%d\" speed=\"%d\" port=\"0\" guid=\"0x%llx\" maxconn=\"32768\" gdr=\"1\"/>\n",
+               g.ordinal, g.ordinal, grp.speed_mbps, 0xb200000000ull | static_cast<unsigned>(g.ordinal));
+      o += line;
+      o += "        </nic>\n      </pci>\n    </pci>\n";
     }
-    o << "  </cpu>\n";
+    o += "  </cpu>\n";
   }
-  o << "</system>\n";
-  return o.str();
+  o += "</system>\n";
+  return o;
 }
 
 std::string Topology::write_topo_memfd(const std::string& xml) {

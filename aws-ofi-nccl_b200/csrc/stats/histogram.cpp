@@ -2,7 +2,8 @@
 
 #include <cstdlib>
 #include <cstring>
-#include <sstream>
+#include <cmath>
+#include <cstdio>
 
 namespace b200net::stats {
 
@@ -34,48 +35,58 @@ PrintFormat print_format_from_env() {
   return PrintFormat::TEXT;
 }
 
+static std::string num(double v) {
+  char b[64];
+  if (v == static_cast<double>(static_cast<long long>(v)) && std::fabs(v) < 1e15)
+    snprintf(b, sizeof(b), "%lld", static_cast<long long>(v));
+  else
+    snprintf(b, sizeof(b), "%g", v);
+  return b;
+}
+
 std::string format_histogram(const HistogramSnapshot& s, PrintFormat f, bool skip_empty) {
-  std::ostringstream o;
+  std::string o;
   const double mean = s.samples ? s.sum / static_cast<double>(s.samples) : 0.0;
+  const std::string samples = std::to_string(s.samples);
   switch (f) {
     case PrintFormat::TEXT:
-      o << "histogram " << s.name << " (" << s.unit << "): samples=" << s.samples << " min=" << s.min
-        << " max=" << s.max << " mean=" << mean << "\n";
+      o += "histogram " + s.name + " (" + s.unit + "): samples=" + samples + " min=" + num(s.min) + " max=" + num(s.max) +
+           " mean=" + num(mean) + "\n";
       for (size_t i = 0; i < s.counts.size(); ++i) {
         if (skip_empty && !s.counts[i]) continue;
-        o << "  >= " << s.lower_bounds[i] << " : " << s.counts[i] << "\n";
+        o += "  >= " + num(s.lower_bounds[i]) + " : " + std::to_string(s.counts[i]) + "\n";
       }
       break;
     case PrintFormat::TABLE:
-      o << "| " << s.name << " | lower bound (" << s.unit << ") | count |\n|---|---|---|\n";
+      o += "| " + s.name + " | lower bound (" + s.unit + ") | count |\n|---|---|---|\n";
       for (size_t i = 0; i < s.counts.size(); ++i) {
         if (skip_empty && !s.counts[i]) continue;
-        o << "| | " << s.lower_bounds[i] << " | " << s.counts[i] << " |\n";
+        o += "| | " + num(s.lower_bounds[i]) + " | " + std::to_string(s.counts[i]) + " |\n";
       }
-      o << "| total | | " << s.samples << " |\n";
+      o += "| total | | " + samples + " |\n";
       break;
     case PrintFormat::CSV:
-      o << "name,unit,lower_bound,count\n";
+      o += "name,unit,lower_bound,count\n";
       for (size_t i = 0; i < s.counts.size(); ++i) {
         if (skip_empty && !s.counts[i]) continue;
-        o << s.name << "," << s.unit << "," << s.lower_bounds[i] << "," << s.counts[i] << "\n";
+        o += s.name + "," + s.unit + "," + num(s.lower_bounds[i]) + "," + std::to_string(s.counts[i]) + "\n";
       }
       break;
     case PrintFormat::JSON: {
-      o << "{\"name\":\"" << s.name << "\",\"unit\":\"" << s.unit << "\",\"samples\":" << s.samples
-        << ",\"min\":" << s.min << ",\"max\":" << s.max << ",\"mean\":" << mean << ",\"bins\":[";
+      o += "{\"name\":\"" + s.name + "\",\"unit\":\"" + s.unit + "\",\"samples\":" + samples + ",\"min\":" + num(s.min) +
+           ",\"max\":" + num(s.max) + ",\"mean\":" + num(mean) + ",\"bins\":[";
       bool first = true;
       for (size_t i = 0; i < s.counts.size(); ++i) {
         if (skip_empty && !s.counts[i]) continue;
-        if (!first) o << ",";
+        if (!first) o += ",";
         first = false;
-        o << "{\"ge\":" << s.lower_bounds[i] << ",\"count\":" << s.counts[i] << "}";
+        o += "{\"ge\":" + num(s.lower_bounds[i]) + ",\"count\":" + std::to_string(s.counts[i]) + "}";
       }
-      o << "]}\n";
+      o += "]}\n";
       break;
     }
   }
-  return o.str();
+  return o;
 }
 
 size_t print_all_histograms(FILE* out) {

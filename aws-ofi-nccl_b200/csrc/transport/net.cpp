@@ -5,7 +5,7 @@
 
 #include <cerrno>
 #include <cstring>
-#include <fstream>
+#include <cstdio>
 
 #include "b200net/cuda_shim.h"
 #include "b200net/environ.h"
@@ -71,8 +71,17 @@ static std::string pci_path_of_gpu(const std::string& bus_id) {
   for (auto& c : id) c = static_cast<char>(tolower(c));
   const std::string link = "/sys/bus/pci/devices/" + id;
   char buf[512];
-  if (realpath(link.c_str(), buf)) return buf;
-  return "";
+  if (!realpath(link.c_str(), buf)) return "";
+  // Report the bridge above the GPU: NCCL then places the virtual NIC as a sibling of the GPU
+  // under the same switch. Without a bridge above (GPU directly on a root port) report nothing and
+  // let NCCL attach the NIC to the CPU.
+  std::string path(buf);
+  const size_t slash = path.rfind('/');
+  if (slash == std::string::npos) return "";
+  const std::string parent = path.substr(0, slash);
+  const std::string leaf = parent.substr(parent.rfind('/') + 1);
+  if (leaf.find(':') == std::string::npos || leaf.find('.') == std::string::npos) return "";
+  return parent;
 }
 
 int fill_common_properties(Device* d, Properties* p, int rails) {
@@ -154,8 +163,10 @@ int net_create_plugin(Plugin** out) {
       EnvManager::instance().insert_envvar("NCCL_TOPO_FILE", path, false);
     const std::string copy = params().topo_file_write.get();
     if (!copy.empty()) {
-      std::ofstream f(copy);
-      f << xml;
+      if (FILE* f = fopen(copy.c_str(), "w")) {
+        fputs(xml.c_str(), f);
+        fclose(f);
+      }
     }
   }
   // without device-memory support NCCL must not use the LL128 protocol through host bounce buffers

@@ -48,3 +48,20 @@ def test_device_collectives_p2p_only():
 def test_data_parallel_gradients_and_replicas():
     out = _run("dp_worker.py", min(_ngpus(), 4))
     assert "dp worker OK" in out
+
+
+@pytest.mark.skipif(_ngpus() < 2, reason="needs at least 2 GPUs")
+def test_unmodified_nccl_runs_over_the_net_plugin(tmp_path):
+    """NCCL loads the plugin through NCCL_NET_PLUGIN; P2P and SHM transports are off, so every byte
+    between the two GPUs crosses isend/irecv/test of this repository's plugin."""
+    lib = ROOT / "aws-ofi-nccl_b200" / "lib"
+    log = tmp_path / "nccl.log"
+    env = {
+        "NCCL_NET_PLUGIN": "ofi-b200", "LD_LIBRARY_PATH": f"{lib}:" + os.environ.get("LD_LIBRARY_PATH", ""),
+        "NCCL_P2P_DISABLE": "1", "NCCL_SHM_DISABLE": "1", "NCCL_DEBUG": "INFO", "NCCL_DEBUG_SUBSYS": "INIT,NET",
+        "NCCL_DEBUG_FILE": str(log) + ".%p", "NCCL_NVLS_ENABLE": "0", "NCCL_CUMEM_ENABLE": "0",
+    }
+    out = _run("nccl_plugin_worker.py", 2, env, timeout=900)
+    assert "nccl plugin worker OK" in out
+    text = "".join(p.read_text() for p in tmp_path.glob("nccl.log.*"))
+    assert "B200NVL" in text, text[-3000:]
