@@ -40,6 +40,9 @@ struct Api {
   CUresult (*EventRecord)(CUevent, CUstream) = nullptr;
   CUresult (*EventQuery)(CUevent) = nullptr;
   CUresult (*MemcpyAsync)(CUdeviceptr, CUdeviceptr, size_t, CUstream) = nullptr;
+  CUresult (*MemAlloc)(CUdeviceptr*, size_t) = nullptr;
+  CUresult (*MemFree)(CUdeviceptr) = nullptr;
+  CUresult (*MemsetD8)(CUdeviceptr, unsigned char, size_t) = nullptr;
   CUresult (*MemCreate)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long) = nullptr;
   CUresult (*MemRelease)(CUmemGenericAllocationHandle) = nullptr;
   CUresult (*MemGetAllocationGranularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags) = nullptr;
@@ -100,6 +103,9 @@ void do_init() {
   ok &= sym(g.EventRecord, "cuEventRecord");
   ok &= sym(g.EventQuery, "cuEventQuery");
   ok &= sym(g.MemcpyAsync, "cuMemcpyAsync");
+  ok &= sym(g.MemAlloc, "cuMemAlloc");
+  ok &= sym(g.MemFree, "cuMemFree");
+  ok &= sym(g.MemsetD8, "cuMemsetD8");
   ok &= sym(g.MemCreate, "cuMemCreate");
   ok &= sym(g.MemRelease, "cuMemRelease");
   ok &= sym(g.MemGetAllocationGranularity, "cuMemGetAllocationGranularity");
@@ -229,6 +235,21 @@ int memcpy_async(void* dst, const void* src, size_t n, Stream s) {
   if (!available()) return -ENOSYS;
   return rc_of(g.MemcpyAsync(reinterpret_cast<CUdeviceptr>(dst), reinterpret_cast<CUdeviceptr>(src), n, static_cast<CUstream>(s)));
 }
+
+int mem_alloc(void** ptr, size_t bytes) {
+  if (!available()) return -ENOSYS;
+  CUdeviceptr p = 0;
+  CUresult r = g.MemAlloc(&p, bytes);
+  if (r != CUDA_SUCCESS) return rc_of(r);
+  r = g.MemsetD8(p, 0, bytes);
+  if (r != CUDA_SUCCESS) {
+    g.MemFree(p);
+    return rc_of(r);
+  }
+  *ptr = reinterpret_cast<void*>(p);
+  return 0;
+}
+int mem_free(void* ptr) { return available() ? rc_of(g.MemFree(reinterpret_cast<CUdeviceptr>(ptr))) : -ENOSYS; }
 
 int vmm_alloc(int device, size_t bytes, void** ptr, size_t* rounded, uint64_t* handle_out) {
   if (!available()) return -ENOSYS;

@@ -1,0 +1,597 @@
+#include "b200net/gin.h"
+
+#include <unistd.h>
+
+#include <cerrno>
+#include <chrono>
+#include <cstring>
+
+#include "b200net/api.h"
+#include "b200net/log.h"
+#include "b200net/param.h"
+#include "b200net/tracepoint.h"
+
+namespace b200net::gin {
+
+using Clock = std::chrono::steady_clock;
+static bool expired(Clock::time_point t0, int seconds = 30) { return Clock::now() - t0 > std::chrono::seconds(seconds); }
+static std::atomic<uint32_t> g_next_comm_id{1};
+
+// ------------------------------------------------------------------------------------------ device signal worker
+DeviceSignalWorker& DeviceSignalWorker::instance() {
+  static DeviceSignalWorker* w = new DeviceSignalWorker();
+  return *w;
+}
+DeviceSignalWorker::DeviceSignalWorker() { thread_ = std::thread([this] { run(); }); }
+DeviceSignalWorker::~DeviceSignalWorker() {
+  stop_.store(true);
+  if (thread_.joinable()) thread_.join();
+}
+bool DeviceSignalWorker::submit(const SignalWork& w) {
+  if (!ring_.push(w)) return false;
+  submitted_.fetch_add(1);
+  return true;
+}
+void DeviceSignalWorker::drain() {
+  const uint64_t target = submitted_.load();
+  while (completed_.load() < target) std::this_thread::yield();
+}
+void DeviceSignalWorker::run() {
+  int idle = 0;
+  while (!stop_.load(std::memory_order_relaxed)) {
+    // take a batch, fold additions to the same word, apply each word once
+    std::map<uint64_t, uint64_t> batch;
+    int n = 0;
+    SignalWork w;
+    while (n < 512 && ring_.pop(w)) {
+      batch[w.addr] += w.value;
+      ++n;
+    }
+    if (!n) {
+      if (++idle > 1000) std::this_thread::sleep_for(std::chrono::microseconds(50));
+      continue;
+    }
+    idle = 0;
+    if (!stream_) {
+      cuda::ensure_primary_ctx(0);
+      cuda::stream_create(&stream_);
+    }
+    for (auto& [addr, add] : batch) {
+      auto it = shadow_.find(addr);
+      if (it == shadow_.end()) {
+        uint64_t cur = 0;  // first touch: read the word once; afterwards the shadow is authoritative
+        cuda::memcpy_async(&cur, reinterpret_cast<void*>(addr), 8, stream_);
+        cuda::stream_synchronize(stream_);
+        it = shadow_.emplace(addr, cur).first;
+      }
+      it->second += add;
+      cuda::memcpy_async(reinterpret_cast<void*>(addr), &it->second, 8, stream_);
+    }
+    cuda::stream_synchronize(stream_);
+    completed_.fetch_add(static_cast<uint64_t>(n));
+  }
+}
+
+// ------------------------------------------------------------------------------------------ requests
+class StatusRequest : public GinRequest {
+ public:
+  StatusRequest(CollComm* c, std::shared_ptr<std::atomic<int>> s) : comm(c), status(std::move(s)) {}
+  int test(int* done) override {
+    comm->progress();
+    const int v = status->load();
+    *done = v != 0;
+    if (v < 0) {
+      delete this;
+      return v;
+    }
+    if (v) delete this;
+    return 0;
+  }
+  CollComm* comm;
+  std::shared_ptr<std::atomic<int>> status;
+};
+
+// ------------------------------------------------------------------------------------------ CollComm
+CollComm::CollComm(int dev_, int nranks_, int rank_) : dev(dev_), nranks(nranks_), rank(rank_) {
+  comm_id = g_next_comm_id.fetch_add(1);
+  peers_.resize(static_cast<size_t>(nranks));
+}
+
+CollComm::~CollComm() {
+  for (SymmMr* m : mrs_) delete m;
+  for (GinContext* c : contexts_) delete c;
+}
+
+// Blocking helpers over the net transport's own API (used only during collective set-up).
+static int net_send_recv(void* scomm, void* rcomm, const void* sbuf, void* rbuf, size_t n) {
+  void *smh = nullptr, *rmh = nullptr;
+  if (api::reg_mr(scomm, const_cast<void*>(sbuf), n, NCCL_PTR_HOST, &smh) != ncclSuccess) return -EIO;
+  if (api::reg_mr(rcomm, rbuf, n, NCCL_PTR_HOST, &rmh) != ncclSuccess) return -EIO;
+  void *sreq = nullptr, *rreq = nullptr;
+  size_t sz = n;
+  int tag = 0x61;
+  const auto t0 = Clock::now();
+  int sdone = 0, rdone = 0;
+  while (!sdone || !rdone) {
+    if (!rreq && api::irecv(rcomm, 1, &rbuf, &sz, &tag, &rmh, &rreq) != ncclSuccess) return -EIO;
+    if (!sreq && api::isend(scomm, const_cast<void*>(sbuf), n, tag, smh, &sreq) != ncclSuccess) return -EIO;
+    if (sreq && !sdone && api::test(sreq, &sdone, nullptr) != ncclSuccess) return -EIO;
+    if (rreq && !rdone && api::test(rreq, &rdone, nullptr) != ncclSuccess) return -EIO;
+    if (expired(t0)) return -ETIMEDOUT;
+  }
+  api::dereg_mr(scomm, smh);
+  api::dereg_mr(rcomm, rmh);
+  return 0;
+}
+
+int CollComm::all_gather(void* buf, size_t bytes) {
+  if (nranks == 1) return 0;
+  char* b = static_cast<char*>(buf);
+  // step s: pass on the block received in step s-1 (own block first); n-1 steps
+  for (int s = 0; s < nranks - 1; ++s) {
+    const int send_idx = (rank - s + nranks) % nranks;
+    const int recv_idx = (rank - s - 1 + nranks) % nranks;
+    const int rc = net_send_recv(ring_send_, ring_recv_, b + send_idx * bytes, b + recv_idx * bytes, bytes);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+int CollComm::connect(void* handles[], ListenComm* lcomm) {
+  std::lock_guard<std::recursive_mutex> g(lock);
+  if (nranks > 1) {
+    const int next = (rank + 1) % nranks;
+    const auto t0 = Clock::now();
+    char handle_copy[NCCL_NET_HANDLE_MAXSIZE];
+    memcpy(handle_copy, handles[next], sizeof(handle_copy));
+    while (!ring_send_ || !ring_recv_) {
+      if (!ring_send_ && api::connect(dev, handle_copy, &ring_send_, -1) != ncclSuccess) return -EHOSTUNREACH;
+      if (!ring_recv_ && api::accept(lcomm->net_listen, &ring_recv_) != ncclSuccess) return -EHOSTUNREACH;
+      if (expired(t0)) return -ETIMEDOUT;
+    }
+  }
+  std::vector<PeerRecord> recs(static_cast<size_t>(nranks));
+  memset(recs.data(), 0, recs.size() * sizeof(PeerRecord));
+  strncpy(recs[rank].ep_name, fab_.name().c_str(), FAB_EP_NAME_LEN - 1);
+  recs[rank].pid = static_cast<uint32_t>(getpid());
+  recs[rank].comm_id = comm_id;
+  const int rc = all_gather(recs.data(), sizeof(PeerRecord));
+  if (rc) return rc;
+  for (int r = 0; r < nranks; ++r) {
+    peers_[r].map = fab_.av_insert(std::string(recs[r].ep_name, strnlen(recs[r].ep_name, FAB_EP_NAME_LEN)));
+    peers_[r].comm_id = recs[r].comm_id;
+    if (!peers_[r].map) return -EHOSTUNREACH;
+  }
+  B200NET_TRACE_EVENT(GinConnect, dev, comm_id, 0, static_cast<uint64_t>(nranks), this);
+  return 0;
+}
+
+int CollComm::reg_mr_sym(void* data, size_t size, int type, uint64_t flags, SymmMr** out) {
+  std::lock_guard<std::recursive_mutex> g(lock);
+  for (SymmMr* m : mrs_) {  // the same buffer registered again: share the registration
+    if (m->base == data && m->size == size) {
+      ++m->refcnt;
+      *out = m;
+      return 0;
+    }
+  }
+  auto* m = new SymmMr();
+  m->base = data;
+  m->size = size;
+  m->type = type;
+  m->flags = flags;
+  m->remote.resize(static_cast<size_t>(nranks));
+  RemoteMr mine;
+  memset(&mine, 0, sizeof(mine));
+  mine.addr = reinterpret_cast<uint64_t>(data);
+  mine.size = size;
+  mine.kind = static_cast<uint32_t>(MrKind::HOST);
+  if (type == NCCL_PTR_CUDA) {
+    void* base = nullptr;
+    size_t sz = 0;
+    int d = 0;
+    bool vmm = false;
+    if (!cuda::available() || cuda::pointer_info(data, &d, &base, &sz, &vmm) != 0) {
+      delete m;
+      return -EINVAL;
+    }
+    mine.device = static_cast<uint32_t>(d);
+    mine.kind = static_cast<uint32_t>(MrKind::CUDA_STAGED);
+    if (!vmm && cuda::ipc_get_handle(base, mine.ipc_handle) == 0) {
+      mine.kind = static_cast<uint32_t>(MrKind::CUDA_IPC);
+      mine.key = reinterpret_cast<uint64_t>(base);  // allocation base: offsets are taken from it
+    }
+  }
+  m->remote[rank] = mine;
+  const int rc = all_gather(m->remote.data(), sizeof(RemoteMr));
+  if (rc) {
+    delete m;
+    return rc;
+  }
+  m->mapped.assign(static_cast<size_t>(nranks), nullptr);
+  if (type == NCCL_PTR_CUDA) {
+    for (int r = 0; r < nranks; ++r) {
+      if (r == rank) {
+        m->mapped[r] = data;
+      } else if (m->remote[r].kind == static_cast<uint32_t>(MrKind::CUDA_IPC)) {
+        void* p = nullptr;
+        if (cuda::ipc_open(m->remote[r].ipc_handle, &p) == 0)
+          m->mapped[r] = static_cast<char*>(p) + (m->remote[r].addr - m->remote[r].key);
+      }
+    }
+  }
+  mrs_.push_back(m);
+  B200NET_TRACE_EVENT(GinRegMr, dev, comm_id, 0, size, m);
+  *out = m;
+  return 0;
+}
+
+int CollComm::dereg_mr_sym(SymmMr* mr) {
+  std::lock_guard<std::recursive_mutex> g(lock);
+  if (!mr) return 0;
+  if (--mr->refcnt > 0) return 0;
+  for (auto it = mrs_.begin(); it != mrs_.end(); ++it)
+    if (*it == mr) {
+      mrs_.erase(it);
+      break;
+    }
+  if (mr->type == NCCL_PTR_CUDA)
+    for (int r = 0; r < nranks; ++r)
+      if (r != rank && mr->mapped[r])
+        cuda::ipc_close(static_cast<char*>(mr->mapped[r]) - (mr->remote[r].addr - mr->remote[r].key));
+  if (mr->gpu_handle_block) cuda::mem_free(mr->gpu_handle_block);
+  B200NET_TRACE_EVENT(GinDeregMr, dev, comm_id, 0, mr->size, mr);
+  delete mr;
+  return 0;
+}
+
+int CollComm::send_ack(uint32_t peer_rank) {
+  PeerState& p = peers_[peer_rank];
+  AckMsg a{p.comm_id, static_cast<uint32_t>(rank), p.rx_applied};
+  const int rc = fab_.send(p.map, DgramType::GIN_ACK, 0, &a, sizeof(a));
+  if (rc == 0) {
+    p.rx_acked = p.rx_applied;
+    B200NET_TRACE_EVENT(GinAckSend, dev, comm_id, static_cast<uint32_t>(a.acked_seq), 0, this);
+  }
+  return rc;
+}
+
+int CollComm::apply_signal(const MetadataMsg& m) {
+  if (m.signal_op != NCCL_NET_SIGNAL_OP_INC && m.signal_op != NCCL_NET_SIGNAL_OP_ADD) return -EINVAL;
+  // bounds: the word must lie inside one of this rank's registrations
+  bool inside = false;
+  for (SymmMr* mr : mrs_) {
+    const uint64_t b = reinterpret_cast<uint64_t>(mr->base);
+    if (m.signal_addr >= b && m.signal_addr + 8 <= b + mr->size) inside = true;
+  }
+  if (!inside) {
+    NET_WARN("signal address %llx outside every registration: dropped", static_cast<unsigned long long>(m.signal_addr));
+    error_ = true;
+    return -EFAULT;
+  }
+  const uint64_t add = m.signal_op == NCCL_NET_SIGNAL_OP_INC ? 1 : m.signal_value;
+  if (m.signal_is_device) {
+    if (!DeviceSignalWorker::instance().submit(SignalWork{m.signal_addr, add, m.src_rank, 0})) return -EAGAIN;
+  } else {
+    __atomic_fetch_add(reinterpret_cast<uint64_t*>(m.signal_addr), add, __ATOMIC_RELEASE);
+  }
+  B200NET_TRACE_EVENT(GinSignalDeliver, dev, comm_id, static_cast<uint32_t>(m.seq), add, this);
+  return 0;
+}
+
+void CollComm::handle_dgram(const DgramHdr& h, const void* payload) {
+  if (h.type == static_cast<uint16_t>(DgramType::GIN_METADATA)) {
+    const auto* m = static_cast<const MetadataMsg*>(payload);
+    if (m->comm_id != comm_id || m->src_rank >= static_cast<uint32_t>(nranks)) return;
+    B200NET_TRACE_EVENT(GinMetadataRecv, dev, comm_id, static_cast<uint32_t>(m->seq), 0, this);
+    PeerState& p = peers_[m->src_rank];
+    if (m->signal_addr) {
+      if (apply_signal(*m) == -EAGAIN) deferred_signals_.push_back(*m);
+    }
+    if (m->seq > p.rx_applied) p.rx_applied = m->seq;
+    const uint32_t interval = static_cast<uint32_t>(params().gin_ack_interval.get());
+    if (p.rx_applied - p.rx_acked >= interval) send_ack(m->src_rank);
+  } else if (h.type == static_cast<uint16_t>(DgramType::GIN_ACK)) {
+    const auto* a = static_cast<const AckMsg*>(payload);
+    if (a->comm_id != comm_id || a->src_rank >= static_cast<uint32_t>(nranks)) return;
+    PeerState& p = peers_[a->src_rank];
+    if (a->acked_seq > p.tx_acked) p.tx_acked = a->acked_seq;
+    B200NET_TRACE_EVENT(GinAckRecv, dev, comm_id, static_cast<uint32_t>(a->acked_seq), 0, this);
+  }
+}
+
+// Retire the operations towards one peer strictly in order: an operation's metadata (which carries
+// its signal, and advances the peer's applied count) goes out only after its data has landed and
+// after every earlier operation's metadata.
+int CollComm::retire(PeerState& p, uint32_t peer_rank) {
+  while (!p.ops.empty()) {
+    PendingOp& op = p.ops.front();
+    if (!op.data_done) {
+      if (op.event) {
+        const int q = cuda::event_query(op.event);
+        if (q < 0) {
+          op.status->store(-EIO);
+          error_ = true;
+          p.ops.pop_front();
+          continue;
+        }
+        if (q == 1) return 0;
+        cuda::event_destroy(op.event);
+        op.event = nullptr;
+        op.data_done = true;
+      } else if (op.len) {
+        const int rc = fab_.write_host(p.map, op.remote_addr, op.local, op.len, &op.done);
+        if (rc == -EAGAIN) return 0;
+        if (rc != 0) {
+          op.status->store(rc);
+          error_ = true;
+          p.ops.pop_front();
+          continue;
+        }
+        op.staged = fab_.writes_are_staged(p.map);
+        op.data_done = true;
+      } else {
+        op.data_done = true;
+      }
+    }
+    if (!op.signal_sent) {
+      const int rc = fab_.send(p.map, DgramType::GIN_METADATA, op.staged ? DGRAM_FLAG_ORDER_AFTER_FRAGS : 0, &op.meta,
+                               sizeof(op.meta));
+      if (rc == -EAGAIN) return 0;
+      if (rc != 0) {
+        op.status->store(rc);
+        error_ = true;
+        p.ops.pop_front();
+        continue;
+      }
+      op.signal_sent = true;
+      B200NET_TRACE_EVENT(GinMetadataSend, dev, comm_id, static_cast<uint32_t>(op.seq), 0, this);
+    }
+    op.status->store(1);
+    p.ops.pop_front();
+    (void)peer_rank;
+  }
+  return 0;
+}
+
+int CollComm::progress() {
+  std::lock_guard<std::recursive_mutex> g(lock);
+  B200NET_TRACE_EVENT(GinProgress, dev, comm_id, 0, 0, this);
+  fab_.poll(256, [this](const DgramHdr& h, const void* p) { handle_dgram(h, p); });
+  while (!deferred_signals_.empty()) {
+    if (apply_signal(deferred_signals_.front()) == -EAGAIN) break;
+    deferred_signals_.pop_front();
+  }
+  for (int r = 0; r < nranks; ++r) retire(peers_[r], static_cast<uint32_t>(r));
+  return 0;
+}
+
+int CollComm::iput(uint64_t src_off, SymmMr* src, size_t size, uint64_t dst_off, SymmMr* dst, uint32_t peer_rank,
+                   bool with_signal, uint64_t sig_off, SymmMr* sig, uint64_t sig_value, uint32_t sig_op,
+                   GinRequest** req) {
+  std::lock_guard<std::recursive_mutex> g(lock);
+  *req = nullptr;
+  if (closing_) return -ESHUTDOWN;
+  if (peer_rank >= static_cast<uint32_t>(nranks)) return -EINVAL;
+  if (size && (!src || !dst || src_off + size > src->size || dst_off + size > dst->remote[peer_rank].size)) return -EINVAL;
+  if (with_signal && (!sig || sig_off + 8 > sig->remote[peer_rank].size)) return -EINVAL;
+  progress();
+  PeerState& p = peers_[peer_rank];
+  if (p.tx_head - p.tx_acked >= GIN_ACK_REQ_THRESHOLD) return 0;  // window full: no request, call again
+  PendingOp op;
+  op.seq = ++p.tx_head;
+  op.len = size;
+  op.status = std::make_shared<std::atomic<int>>(0);
+  op.has_signal = with_signal;
+  memset(&op.meta, 0, sizeof(op.meta));
+  op.meta.comm_id = p.comm_id;
+  op.meta.src_rank = static_cast<uint32_t>(rank);
+  op.meta.seq = op.seq;
+  if (with_signal) {
+    op.meta.signal_addr = sig->remote[peer_rank].addr + sig_off;
+    op.meta.signal_value = sig_value;
+    op.meta.signal_op = sig_op;
+    op.meta.signal_is_device = sig->remote[peer_rank].kind != static_cast<uint32_t>(MrKind::HOST);
+  }
+  B200NET_TRACE_EVENT(GinPutSignalBegin, dev, comm_id, static_cast<uint32_t>(op.seq), size, nullptr);
+  if (size) {
+    const char* lsrc = static_cast<const char*>(src->base) + src_off;
+    const RemoteMr& rm = dst->remote[peer_rank];
+    if (rm.kind == static_cast<uint32_t>(MrKind::HOST)) {
+      op.local = lsrc;
+      op.remote_addr = rm.addr + dst_off;
+    } else if (dst->mapped[peer_rank]) {
+      // device window mapped here: copy-engine transfer on a stream, completion through an event
+      static thread_local cuda::Stream st = nullptr;
+      if (!st && cuda::stream_create(&st) != 0) return -EIO;
+      if (cuda::event_create(&op.event) != 0) return -EIO;
+      if (cuda::memcpy_async(static_cast<char*>(dst->mapped[peer_rank]) + dst_off, lsrc, size, st) != 0 ||
+          cuda::event_record(op.event, st) != 0)
+        return -EIO;
+    } else {
+      return -ENOTSUP;  // a device window that cannot be mapped into this process
+    }
+  }
+  auto status = op.status;
+  p.ops.push_back(std::move(op));
+  retire(p, peer_rank);
+  *req = new StatusRequest(this, status);
+  return 0;
+}
+
+int CollComm::iget(uint64_t remote_off, SymmMr* remote, size_t size, uint64_t local_off, SymmMr* local,
+                   uint32_t peer_rank, GinRequest** req) {
+  std::lock_guard<std::recursive_mutex> g(lock);
+  *req = nullptr;
+  if (peer_rank >= static_cast<uint32_t>(nranks) || !remote || !local) return -EINVAL;
+  if (remote_off + size > remote->remote[peer_rank].size || local_off + size > local->size) return -EINVAL;
+  progress();
+  B200NET_TRACE_EVENT(GinGetBegin, dev, comm_id, 0, size, nullptr);
+  auto status = std::make_shared<std::atomic<int>>(0);
+  char* ldst = static_cast<char*>(local->base) + local_off;
+  const RemoteMr& rm = remote->remote[peer_rank];
+  int rc = 0;
+  if (rm.kind == static_cast<uint32_t>(MrKind::HOST)) {
+    rc = fab_.read_host(peers_[peer_rank].map, rm.addr + remote_off, ldst, size);
+  } else if (remote->mapped[peer_rank]) {
+    static thread_local cuda::Stream st = nullptr;
+    if (!st && cuda::stream_create(&st) != 0) return -EIO;
+    rc = cuda::memcpy_async(ldst, static_cast<char*>(remote->mapped[peer_rank]) + remote_off, size, st);
+    if (rc == 0) rc = cuda::stream_synchronize(st);
+  } else {
+    rc = -ENOTSUP;
+  }
+  if (rc != 0) return rc;
+  status->store(1);
+  B200NET_TRACE_EVENT(GinGetEnd, dev, comm_id, 0, size, nullptr);
+  *req = new StatusRequest(this, status);
+  return 0;
+}
+
+// Everything this rank received so far is visible to its GPU: data arrived through coherent
+// NVLink / host writes and signals are applied after the data, so a fence plus the drain of the
+// device-signal worker is all a flush has to do.
+int CollComm::iflush(GinRequest** req) {
+  std::lock_guard<std::recursive_mutex> g(lock);
+  progress();
+  B200NET_TRACE_EVENT(GinFlushBegin, dev, comm_id, 0, 0, nullptr);
+  std::atomic_thread_fence(std::memory_order_acq_rel);
+  if (cuda::available()) DeviceSignalWorker::instance().drain();
+  auto status = std::make_shared<std::atomic<int>>(1);
+  B200NET_TRACE_EVENT(GinFlushEnd, dev, comm_id, 0, 0, nullptr);
+  *req = new StatusRequest(this, status);
+  return 0;
+}
+
+int CollComm::create_context(int n_signals, int n_counters, int n_contexts, bool kernel_initiated, GinContext** out) {
+  std::lock_guard<std::recursive_mutex> g(lock);
+  if (n_signals < 0 || n_counters < 0 || n_contexts < 1 || n_contexts > GIN_MAX_CONTEXTS ||
+      n_signals > GIN_MAX_SIGNALS_PER_CONTEXT || n_counters > GIN_MAX_SIGNALS_PER_CONTEXT)
+    return -EINVAL;
+  auto* c = new GinContext();
+  c->comm = this;
+  c->n_signals = n_signals;
+  c->n_counters = n_counters;
+  c->n_contexts = n_contexts;
+  c->kernel_initiated = kernel_initiated;
+  c->net_dev_handle.netDeviceType = kernel_initiated ? NCCL_NET_DEVICE_GIN_GDAKI : NCCL_NET_DEVICE_GIN_PROXY;
+  c->net_dev_handle.netDeviceVersion = 1;
+  c->net_dev_handle.needsProxyProgress = kernel_initiated ? 0 : 1;
+  if (kernel_initiated) {
+    // Ranks may ask for different counts: size the pad for the maximum so every rank's layout agrees.
+    std::vector<int32_t> counts(static_cast<size_t>(2 * nranks), 0);
+    counts[2 * rank] = n_signals;
+    counts[2 * rank + 1] = n_counters;
+    int rc = all_gather(counts.data(), 2 * sizeof(int32_t));
+    if (rc) {
+      delete c;
+      return rc;
+    }
+    int max_sig = 0, max_cnt = 0;
+    for (int r = 0; r < nranks; ++r) {
+      max_sig = std::max(max_sig, counts[2 * r]);
+      max_cnt = std::max(max_cnt, counts[2 * r + 1]);
+    }
+    const size_t pad_bytes = static_cast<size_t>(n_contexts) * (2 * max_sig + max_cnt + 16) * 8;
+    if (!cuda::available() || cuda::mem_alloc(&c->dev_pad, pad_bytes) != 0) {
+      delete c;
+      return -ENOMEM;
+    }
+    // exchange the pads' IPC handles in ONE all-gather and map every peer's pad
+    struct PadRec { uint8_t ipc[64]; uint64_t bytes; };
+    std::vector<PadRec> pads(static_cast<size_t>(nranks));
+    memset(pads.data(), 0, pads.size() * sizeof(PadRec));
+    pads[rank].bytes = pad_bytes;
+    rc = cuda::ipc_get_handle(c->dev_pad, pads[rank].ipc);
+    if (rc == 0) rc = all_gather(pads.data(), sizeof(PadRec));
+    if (rc) {
+      cuda::mem_free(c->dev_pad);
+      delete c;
+      return rc;
+    }
+    c->peer_pads.assign(static_cast<size_t>(nranks), nullptr);
+    for (int r = 0; r < nranks; ++r) {
+      if (r == rank) c->peer_pads[r] = c->dev_pad;
+      else if (cuda::ipc_open(pads[r].ipc, &c->peer_pads[r]) != 0) c->has_error = true;
+    }
+    // the device-visible block: {rank, nranks, signals per context, counters per context, pad[nranks]}
+    std::vector<uint64_t> block(static_cast<size_t>(4 + nranks));
+    block[0] = static_cast<uint64_t>(rank);
+    block[1] = static_cast<uint64_t>(nranks);
+    block[2] = static_cast<uint64_t>(max_sig);
+    block[3] = static_cast<uint64_t>(max_cnt);
+    for (int r = 0; r < nranks; ++r) block[4 + r] = reinterpret_cast<uint64_t>(c->peer_pads[r]);
+    if (cuda::mem_alloc(&c->dev_handle_gpu, block.size() * 8) != 0) {
+      cuda::mem_free(c->dev_pad);
+      delete c;
+      return -ENOMEM;
+    }
+    cuda::Stream st = nullptr;
+    cuda::stream_create(&st);
+    cuda::memcpy_async(c->dev_handle_gpu, block.data(), block.size() * 8, st);
+    cuda::stream_synchronize(st);
+    cuda::stream_destroy(st);
+    c->net_dev_handle.handle = c->dev_handle_gpu;
+    c->net_dev_handle.size = block.size() * 8;
+    NET_INFO(NCCL_INIT | NCCL_NET, "GIN context ready: %d ranks, %d signals, %d counters, %d contexts (kernel-initiated)",
+             nranks, max_sig, max_cnt, n_contexts);
+  }
+  contexts_.push_back(c);
+  *out = c;
+  return 0;
+}
+
+int CollComm::destroy_context(GinContext* ctx) {
+  std::lock_guard<std::recursive_mutex> g(lock);
+  for (auto it = contexts_.begin(); it != contexts_.end(); ++it) {
+    if (*it != ctx) continue;
+    contexts_.erase(it);
+    if (ctx->kernel_initiated) {
+      for (int r = 0; r < nranks; ++r)
+        if (r != rank && ctx->peer_pads[r]) cuda::ipc_close(ctx->peer_pads[r]);
+      if (ctx->dev_handle_gpu) cuda::mem_free(ctx->dev_handle_gpu);
+      if (ctx->dev_pad) cuda::mem_free(ctx->dev_pad);
+    }
+    delete ctx;
+    return 0;
+  }
+  return -ENOENT;
+}
+
+int CollComm::close() {
+  {
+    std::lock_guard<std::recursive_mutex> g(lock);
+    closing_ = true;
+  }
+  // phase 1: everything issued must retire, and every peer must learn how far we applied its ops
+  const auto t0 = Clock::now();
+  for (;;) {
+    progress();
+    std::lock_guard<std::recursive_mutex> g(lock);
+    bool busy = false;
+    for (int r = 0; r < nranks; ++r) {
+      if (!peers_[r].ops.empty()) busy = true;
+      if (peers_[r].map && peers_[r].rx_applied != peers_[r].rx_acked) send_ack(static_cast<uint32_t>(r));
+    }
+    if (!busy && deferred_signals_.empty()) break;
+    if (expired(t0)) {
+      NET_WARN("GIN close: operations still pending after the deadline");
+      break;
+    }
+  }
+  // phase 2: a ring barrier so that no rank tears its endpoint down while a peer may still write
+  if (nranks > 1 && ring_send_ && ring_recv_) {
+    std::vector<uint8_t> tok(static_cast<size_t>(nranks), 0);
+    all_gather(tok.data(), 1);
+  }
+  std::lock_guard<std::recursive_mutex> g(lock);
+  // contexts NCCL never destroyed are swept here
+  while (!contexts_.empty()) destroy_context(contexts_.back());
+  if (ring_send_) api::close_send(ring_send_);
+  if (ring_recv_) api::close_recv(ring_recv_);
+  ring_send_ = ring_recv_ = nullptr;
+  B200NET_TRACE_EVENT(GinClose, dev, comm_id, 0, 0, this);
+  return 0;
+}
+
+}  // namespace b200net::gin

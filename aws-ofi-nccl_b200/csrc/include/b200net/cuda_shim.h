@@ -41,6 +41,10 @@ int event_query(Event e);  // 0 done, 1 not yet, <0 error
 int memcpy_async(void* dst, const void* src, size_t n, Stream s);  // unified addressing: any direction
 int stream_synchronize(Stream s);
 
+// Plain device allocation (IPC-exportable with ipc_get_handle), zero-filled.
+int mem_alloc(void** ptr, size_t bytes);
+int mem_free(void* ptr);
+
 // VMM allocation that can be exported to peers as a POSIX fd (granularity rounded).
 int vmm_alloc(int device, size_t bytes, void** ptr, size_t* rounded, uint64_t* handle_out);
 int vmm_free(void* ptr, size_t rounded, uint64_t handle);

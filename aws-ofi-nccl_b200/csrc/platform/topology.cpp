@@ -51,8 +51,8 @@ Topology Topology::discover() {
         continue;
       }
       int access = 0, atomics = 0;
-      cuda::p2p_attribute(1 /* ACCESS_SUPPORTED */, a, b, &access);
-      cuda::p2p_attribute(2 /* NATIVE_ATOMIC_SUPPORTED */, a, b, &atomics);
+      cuda::p2p_attribute(2 /* ACCESS_SUPPORTED */, a, b, &access);
+      cuda::p2p_attribute(3 /* NATIVE_ATOMIC_SUPPORTED */, a, b, &atomics);
       // native atomics between peers exist over NVLink, not over PCIe
       t.links_[a][b] = !access ? LinkType::NONE : atomics ? LinkType::NVLINK : LinkType::PCIE;
     }

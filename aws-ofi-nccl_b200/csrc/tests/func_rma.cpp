@@ -1,0 +1,243 @@
+// Functional test of the RMA / GIN tables through the public ABI (dlopen + ncclRmaPlugin_v15,
+// ncclGinPlugin_v13, ncclGinPlugin_v14), N processes on one host, host buffers:
+//   * collective connect over the plugin's own ring bootstrap
+//   * 64 iput + 64 iputSignal(INC) + iputSignal(ADD) to every peer; the target polls the signal
+//     word while calling rmaProgress; payload verified
+//   * iget from the next rank, iflush as a fence
+//   * the same buffer registered twice shares one registration; dereg keeps it alive
+//   * createContext of the kernel-initiated table rejects a null config and out-of-range backend
+//     versions before it looks at the communicator (a dummy pointer is passed)
+// usage: func_rma [plugin.so] [nranks]
+#include <dlfcn.h>
+#include <sys/mman.h>
+#include <sys/wait.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "nccl_abi.h"
+
+static int g_rank = 0, g_n = 3;
+#define FAIL(...)                                                     \
+  do {                                                                \
+    fprintf(stderr, "[rank %d] %s:%d: ", g_rank, __FILE__, __LINE__); \
+    fprintf(stderr, __VA_ARGS__);                                     \
+    fprintf(stderr, "\n");                                            \
+    return 1;                                                         \
+  } while (0)
+#define OK(call)                                                   \
+  do {                                                             \
+    ncclResult_t _r = (call);                                      \
+    if (_r != ncclSuccess) FAIL("%s returned %d", #call, (int)_r); \
+  } while (0)
+
+using Clock = std::chrono::steady_clock;
+static bool expired(Clock::time_point t0, int s = 30) { return Clock::now() - t0 > std::chrono::seconds(s); }
+
+// out-of-band exchange through memory shared by all forked ranks
+struct Oob {
+  char handles[16][NCCL_NET_HANDLE_MAXSIZE];
+  std::atomic<int> arrived[64];
+  std::atomic<int> failed;
+};
+static Oob* oob = nullptr;
+static int g_barrier_idx = 0;
+static int oob_barrier() {
+  const int idx = g_barrier_idx++;
+  oob->arrived[idx].fetch_add(1);
+  const auto t0 = Clock::now();
+  while (oob->arrived[idx].load() < g_n) {
+    if (oob->failed.load() || expired(t0, 60)) return 1;
+    usleep(100);
+  }
+  return 0;
+}
+
+static void logger(ncclDebugLogLevel level, unsigned long, const char* file, int line, const char* fmt, ...) {
+  if (level > NCCL_LOG_WARN && !getenv("FUNC_NET_VERBOSE")) return;
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  fprintf(stderr, "[rank %d] %s (%s:%d)\n", g_rank, buf, file, line);
+}
+
+static int wait_req(ncclRma_v15_t* rma, void* coll, void* ctx, void* req) {
+  const auto t0 = Clock::now();
+  int done = 0;
+  while (!done) {
+    OK(rma->test(coll, req, &done));
+    OK(rma->rmaProgress(ctx));
+    if (expired(t0)) FAIL("request did not complete");
+  }
+  return 0;
+}
+
+static int run_rank(const char* so) {
+  void* h = dlopen(so, RTLD_NOW | RTLD_LOCAL);
+  if (!h) FAIL("dlopen: %s", dlerror());
+  for (const char* s : {"ncclGinPlugin_v11", "ncclGinPlugin_v13", "ncclGinPlugin_v14", "ncclRmaPlugin_v14", "ncclRmaPlugin_v15"})
+    if (!dlsym(h, s)) FAIL("symbol %s not exported", s);
+  auto* rma = static_cast<ncclRma_v15_t*>(dlsym(h, "ncclRmaPlugin_v15"));
+  auto* gin14 = static_cast<ncclGin_v14_t*>(dlsym(h, "ncclGinPlugin_v14"));
+
+  // ---- reject paths of the kernel-initiated table: nothing is initialised, the comm is a dummy
+  {
+    void* dummy = reinterpret_cast<void*>(0x1000);
+    void* ctx = nullptr;
+    ncclNetDeviceHandle_t* dh = nullptr;
+    if (gin14->createContext(dummy, nullptr, &ctx, &dh) != ncclInvalidArgument) FAIL("null config accepted");
+    ncclGinConfig_v14_t cfg = {4, 4, 1, 0, -1, -1, 0};
+    if (gin14->createContext(dummy, &cfg, &ctx, &dh) != ncclInvalidArgument) FAIL("backend version -1 accepted");
+    cfg.backendVersion = 2;
+    if (gin14->createContext(dummy, &cfg, &ctx, &dh) != ncclInvalidArgument) FAIL("backend version beyond the maximum accepted");
+    ncclGinProperties_v14_t gp = {true, true};
+    OK(gin14->getGinProperties(&gp));
+    if (gp.supportsStrongSignals || gp.supportsVASignals) FAIL("unexpected GIN properties");
+  }
+
+  void* pctx = nullptr;
+  OK(rma->init(&pctx, 77, logger));
+  int ndev = 0;
+  OK(rma->devices(&ndev));
+  ncclNetProperties_v12_t props;
+  OK(rma->getProperties(0, &props));
+  if (props.netDeviceType != NCCL_NET_DEVICE_GIN_PROXY) FAIL("device type %d", (int)props.netDeviceType);
+  void* lcomm = nullptr;
+  OK(rma->listen(pctx, 0, oob->handles[g_rank], &lcomm));
+  if (oob_barrier()) FAIL("barrier");
+  void* handles[16];
+  for (int r = 0; r < g_n; ++r) handles[r] = oob->handles[r];
+  void* coll = nullptr;
+  OK(rma->connect(pctx, handles, g_n, g_rank, lcomm, &coll));
+  ncclRmaConfig_t cfg = {1, -1, 0};
+  void* ctx = nullptr;
+  OK(rma->createContext(coll, &cfg, &ctx));
+
+  // ---- buffers: data window (slot per source rank), signal words, source payload
+  const size_t SLOT = 4096;
+  std::vector<uint8_t> window(SLOT * g_n, 0), src(SLOT), got(SLOT, 0);
+  std::vector<uint64_t> signals(16, 0);
+  for (size_t i = 0; i < SLOT; ++i) src[i] = static_cast<uint8_t>(i * 7 + g_rank);
+  void *win_mh, *src_mh, *sig_mh, *got_mh;
+  OK(rma->regMrSym(coll, window.data(), window.size(), NCCL_PTR_HOST, 0, &win_mh));
+  OK(rma->regMrSym(coll, src.data(), src.size(), NCCL_PTR_HOST, 0, &src_mh));
+  OK(rma->regMrSym(coll, signals.data(), signals.size() * 8, NCCL_PTR_HOST, NCCL_NET_MR_FLAG_SIGNAL_NEVER_RESET, &sig_mh));
+  OK(rma->regMrSym(coll, got.data(), got.size(), NCCL_PTR_HOST, 0, &got_mh));
+
+  // duplicate registration: same handle, and it survives one dereg
+  void* dup = nullptr;
+  OK(rma->regMrSym(coll, window.data(), window.size(), NCCL_PTR_HOST, 0, &dup));
+  if (dup != win_mh) FAIL("a second registration of the same buffer got a different handle");
+  OK(rma->deregMrSym(coll, dup));
+
+  // ---- puts: 64 plain + 64 with INC to every peer, then one ADD of 1000
+  for (int p = 0; p < g_n; ++p) {
+    if (p == g_rank) continue;
+    for (int i = 0; i < 128; ++i) {
+      void* req = nullptr;
+      const auto t0 = Clock::now();
+      while (!req) {
+        if (i % 2 == 0)
+          OK(rma->iput(ctx, 0, (i % 16) * 256, src_mh, 256, g_rank * SLOT + (i % 16) * 256, win_mh, p, 0, &req));
+        else
+          OK(rma->iputSignal(ctx, 0, (i % 16) * 256, src_mh, 256, g_rank * SLOT + (i % 16) * 256, win_mh, p, g_rank * 8,
+                             sig_mh, 1, NCCL_NET_SIGNAL_OP_INC, false, 0, &req));
+        OK(rma->rmaProgress(ctx));
+        if (expired(t0)) FAIL("iput kept returning no request");
+      }
+      if (wait_req(rma, coll, ctx, req)) return 1;
+    }
+    void* req = nullptr;
+    OK(rma->iputSignal(ctx, 0, 0, src_mh, 0, 0, win_mh, p, g_rank * 8, sig_mh, 1000, NCCL_NET_SIGNAL_OP_ADD, true,
+                       ncclRmaOptFlagsAggregateRequests, &req));
+    if (!req) FAIL("signal-only put returned no request");
+    if (wait_req(rma, coll, ctx, req)) return 1;
+  }
+  // ---- targets: wait for 64 + 1000 from every peer, then check the payload
+  {
+    const auto t0 = Clock::now();
+    for (;;) {
+      OK(rma->rmaProgress(ctx));
+      bool all = true;
+      for (int p = 0; p < g_n; ++p)
+        if (p != g_rank && __atomic_load_n(&signals[p], __ATOMIC_ACQUIRE) != 1064) all = false;
+      if (all) break;
+      if (expired(t0)) FAIL("signals did not reach 1064: %llu %llu %llu", (unsigned long long)signals[0],
+                            (unsigned long long)signals[1], (unsigned long long)signals[2]);
+    }
+    for (int p = 0; p < g_n; ++p) {
+      if (p == g_rank) continue;
+      for (size_t i = 0; i < SLOT; ++i)
+        if (window[p * SLOT + i] != static_cast<uint8_t>(i * 7 + p)) FAIL("payload from rank %d differs at byte %zu", p, i);
+    }
+  }
+  if (oob_barrier()) FAIL("barrier");
+  // ---- get from the next rank's source buffer, fenced by a flush
+  {
+    const int peer = (g_rank + 1) % g_n;
+    void* req = nullptr;
+    OK(rma->iget(ctx, 0, 0, src_mh, SLOT, 0, got_mh, peer, 0, &req));
+    if (!req) FAIL("iget returned no request");
+    if (wait_req(rma, coll, ctx, req)) return 1;
+    OK(rma->iflush(ctx, 0, got_mh, peer, &req));
+    if (req && wait_req(rma, coll, ctx, req)) return 1;
+    for (size_t i = 0; i < SLOT; ++i)
+      if (got[i] != static_cast<uint8_t>(i * 7 + peer)) FAIL("iget payload differs at byte %zu", i);
+  }
+  bool err = true;
+  OK(rma->queryLastError(ctx, &err));
+  if (err) FAIL("queryLastError reports an error");
+  if (oob_barrier()) FAIL("barrier");
+  OK(rma->deregMrSym(coll, got_mh));
+  OK(rma->deregMrSym(coll, sig_mh));
+  OK(rma->deregMrSym(coll, src_mh));
+  OK(rma->deregMrSym(coll, win_mh));
+  OK(rma->destroyContext(ctx));
+  OK(rma->closeColl(coll));
+  OK(rma->closeListen(lcomm));
+  OK(rma->finalize(pctx));
+  return 0;
+}
+
+int main(int argc, char** argv) {
+  const char* so = argc > 1 ? argv[1] : "./libnccl-net-ofi-b200.so";
+  g_n = argc > 2 ? atoi(argv[2]) : 3;
+  if (g_n < 1 || g_n > 16) return 2;
+  oob = static_cast<Oob*>(mmap(nullptr, sizeof(Oob), PROT_READ | PROT_WRITE, MAP_SHARED | MAP_ANONYMOUS, -1, 0));
+  if (oob == MAP_FAILED) return 2;
+  memset(static_cast<void*>(oob), 0, sizeof(Oob));
+  std::vector<pid_t> kids;
+  for (int r = 1; r < g_n; ++r) {
+    const pid_t pid = fork();
+    if (pid < 0) return 2;
+    if (pid == 0) {
+      g_rank = r;
+      const int rc = run_rank(so);
+      if (rc) oob->failed.store(1);
+      _exit(rc);
+    }
+    kids.push_back(pid);
+  }
+  g_rank = 0;
+  int rc = run_rank(so);
+  if (rc) oob->failed.store(1);
+  for (pid_t k : kids) {
+    int st = 0;
+    waitpid(k, &st, 0);
+    if (!WIFEXITED(st) || WEXITSTATUS(st)) rc = 1;
+  }
+  if (rc) {
+    fprintf(stderr, "FAILED\n");
+    return 1;
+  }
+  printf("ok\n");
+  return 0;
+}

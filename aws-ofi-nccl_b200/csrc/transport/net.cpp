@@ -1,6 +1,7 @@
 // Plugin bring-up: parameters, CUDA driver, topology, platform selection, protocol selection,
 // device creation, environment publication; plus the domain and endpoint caches
 // (reference: src/nccl_ofi_net.cpp — create_plugin :179-421, properties :504-639, caches :706-940).
+#include <limits.h>
 #include <unistd.h>
 
 #include <cerrno>
@@ -70,7 +71,7 @@ static std::string pci_path_of_gpu(const std::string& bus_id) {
   std::string id = bus_id;
   for (auto& c : id) c = static_cast<char>(tolower(c));
   const std::string link = "/sys/bus/pci/devices/" + id;
-  char buf[512];
+  char buf[PATH_MAX];  // realpath() requires a PATH_MAX buffer
   if (!realpath(link.c_str(), buf)) return "";
   // Report the bridge above the GPU: NCCL then places the virtual NIC as a sibling of the GPU
   // under the same switch. Without a bridge above (GPU directly on a root port) report nothing and

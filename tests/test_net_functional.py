@@ -59,3 +59,25 @@ def test_plugin_name_follows_nccl_net(built):
     out = subprocess.run([sys.executable, "-c", code, so], capture_output=True, text=True,
                          env={k: v for k, v in os.environ.items() if k != "NCCL_NET"}).stdout.strip()
     assert out == "B200NVL"
+
+
+@pytest.mark.parametrize("nranks,env", [
+    (2, {"B200NET_PROTOCOL": "SENDRECV"}),
+    (3, {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4"}),
+    (4, {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "2", "B200NET_DISABLE_CMA": "1"}),
+], ids=["2-sendrecv", "3-rdma", "4-rdma-staged"])
+def test_rma_gin_tables_n_processes(built, nranks, env):
+    e = dict(os.environ)
+    e.update(env)
+    res = subprocess.run([str(built / "tests" / "func_rma"), str(built / "libnccl-net-ofi-b200.so"), str(nranks)],
+                         capture_output=True, text=True, timeout=300, env=e, cwd=built)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+
+
+def test_gin_rma_tuner_symbols_exported(built):
+    lib = ctypes.CDLL(str(built / "libnccl-net-ofi-b200.so"))
+    for sym in ("ncclGinPlugin_v11", "ncclGinPlugin_v13", "ncclGinPlugin_v14", "ncclRmaPlugin_v14", "ncclRmaPlugin_v15",
+                "ncclTunerPlugin_v2", "ncclTunerPlugin_v3", "ncclTunerPlugin_v4", "ncclTunerPlugin_v5",
+                "ncclTunerPlugin_v6"):
+        assert hasattr(lib, sym), sym
+    assert (built / "libnccl-tuner-ofi-b200.so").exists()
