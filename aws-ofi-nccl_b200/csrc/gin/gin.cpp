@@ -297,7 +297,46 @@ void CollComm::handle_dgram(const DgramHdr& h, const void* payload) {
     PeerState& p = peers_[a->src_rank];
     if (a->acked_seq > p.tx_acked) p.tx_acked = a->acked_seq;
     B200NET_TRACE_EVENT(GinAckRecv, dev, comm_id, static_cast<uint32_t>(a->acked_seq), 0, this);
+  } else if (h.type == static_cast<uint16_t>(DgramType::READ_REQ)) {
+    const auto* r = static_cast<const ReadReqMsg*>(payload);
+    if (r->comm_id != comm_id || r->src_rank >= static_cast<uint32_t>(nranks)) return;
+    read_services_.push_back(ReadService{*r, 0, false});
+  } else if (h.type == static_cast<uint16_t>(DgramType::READ_RESP)) {
+    const auto* r = static_cast<const ReadRespMsg*>(payload);
+    auto it = reads_in_flight_.find(r->req_id);
+    if (it != reads_in_flight_.end()) {
+      it->second->store(r->status == 0 ? 1 : r->status);
+      reads_in_flight_.erase(it);
+    }
   }
+}
+
+// Serve reads requested by peers that cannot reach this rank's memory directly: write the bytes
+// into the requester's buffer, then confirm (ordered behind the fragments).
+int CollComm::serve_reads() {
+  while (!read_services_.empty()) {
+    ReadService& sv = read_services_.front();
+    PeerState& p = peers_[sv.req.src_rank];
+    int status = 0;
+    bool inside = false;
+    for (SymmMr* mr : mrs_) {
+      const uint64_t b = reinterpret_cast<uint64_t>(mr->base);
+      if (sv.req.addr >= b && sv.req.addr + sv.req.len <= b + mr->size && mr->type == NCCL_PTR_HOST) inside = true;
+    }
+    if (!inside) status = -EFAULT;
+    if (!status && !sv.data_done) {
+      const int rc = fab_.write_host(p.map, sv.req.reply_addr, reinterpret_cast<const void*>(sv.req.addr), sv.req.len, &sv.done);
+      if (rc == -EAGAIN) return 0;
+      if (rc != 0) status = rc;
+      sv.data_done = true;
+    }
+    ReadRespMsg resp{p.comm_id, static_cast<uint32_t>(rank), sv.req.req_id, status, 0};
+    const int rc = fab_.send(p.map, DgramType::READ_RESP, fab_.writes_are_staged(p.map) ? DGRAM_FLAG_ORDER_AFTER_FRAGS : 0,
+                             &resp, sizeof(resp));
+    if (rc == -EAGAIN) return 0;
+    read_services_.pop_front();
+  }
+  return 0;
 }
 
 // Retire the operations towards one peer strictly in order: an operation's metadata (which carries
@@ -363,6 +402,7 @@ int CollComm::progress() {
     deferred_signals_.pop_front();
   }
   for (int r = 0; r < nranks; ++r) retire(peers_[r], static_cast<uint32_t>(r));
+  serve_reads();
   return 0;
 }
 
@@ -433,6 +473,18 @@ int CollComm::iget(uint64_t remote_off, SymmMr* remote, size_t size, uint64_t lo
   int rc = 0;
   if (rm.kind == static_cast<uint32_t>(MrKind::HOST)) {
     rc = fab_.read_host(peers_[peer_rank].map, rm.addr + remote_off, ldst, size);
+    if (rc == -ENOTSUP) {
+      // no direct access to the peer's memory: ask it to write the bytes here
+      PeerState& p = peers_[peer_rank];
+      ReadReqMsg rq{p.comm_id, static_cast<uint32_t>(rank), next_read_id_++, rm.addr + remote_off, size,
+                    reinterpret_cast<uint64_t>(ldst)};
+      rc = fab_.send(p.map, DgramType::READ_REQ, 0, &rq, sizeof(rq));
+      if (rc == -EAGAIN) return 0;  // no request: call again
+      if (rc != 0) return rc;
+      reads_in_flight_[rq.req_id] = status;
+      *req = new StatusRequest(this, status);
+      return 0;
+    }
   } else if (remote->mapped[peer_rank]) {
     static thread_local cuda::Stream st = nullptr;
     if (!st && cuda::stream_create(&st) != 0) return -EIO;

@@ -54,6 +54,20 @@ struct AckMsg {
   uint64_t acked_seq;         // every operation up to and including this one has been applied
 };
 
+struct ReadReqMsg {           // "write [addr, addr+len) of your memory to my address reply_addr"
+  uint32_t comm_id;
+  uint32_t src_rank;
+  uint64_t req_id;
+  uint64_t addr, len, reply_addr;
+};
+struct ReadRespMsg {
+  uint32_t comm_id;
+  uint32_t src_rank;
+  uint64_t req_id;
+  int32_t status;
+  uint32_t pad;
+};
+
 class CollComm;
 
 struct SymmMr {
@@ -183,6 +197,11 @@ class CollComm {
   std::vector<SymmMr*> mrs_;
   std::vector<GinContext*> contexts_;
   std::deque<MetadataMsg> deferred_signals_;  // device signals the worker ring had no room for
+  struct ReadService { ReadReqMsg req; size_t done; bool data_done; };
+  std::deque<ReadService> read_services_;     // reads this rank is serving for peers without direct access
+  std::map<uint64_t, std::shared_ptr<std::atomic<int>>> reads_in_flight_;
+  uint64_t next_read_id_ = 1;
+  int serve_reads();
   bool error_ = false, closing_ = false;
 };
 

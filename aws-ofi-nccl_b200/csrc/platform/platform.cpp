@@ -22,8 +22,8 @@ int PlatformB200::init(std::string*) {
 }
 
 std::vector<std::pair<std::string, std::string>> PlatformB200::nccl_env() const {
-  // chunk sizes sized for copy-engine / SM-copy stripes over NVLink rather than NIC MTUs
-  return {{"NCCL_BUFFSIZE", "8388608"}, {"NCCL_P2P_NET_CHUNKSIZE", "524288"}, {"NCCL_NVLS_CHUNKSIZE", "524288"},
+  // chunks sized for copy-engine stripes over NVLink (MiB-sized copies) rather than for NIC MTUs
+  return {{"NCCL_BUFFSIZE", "33554432"}, {"NCCL_P2P_NET_CHUNKSIZE", "4194304"}, {"NCCL_NVLS_CHUNKSIZE", "524288"},
           {"NCCL_NET_FORCE_FLUSH", "0"}};
 }
 

@@ -48,12 +48,17 @@ struct Oob {
 };
 static Oob* oob = nullptr;
 static int g_barrier_idx = 0;
+static ncclRma_v15_t* g_rma = nullptr;
+static void* g_progress_ctx = nullptr;
+// While waiting, keep the progress engine turning (as NCCL's proxy thread would): a peer may be
+// reading from this rank through the request/response path.
 static int oob_barrier() {
   const int idx = g_barrier_idx++;
   oob->arrived[idx].fetch_add(1);
   const auto t0 = Clock::now();
   while (oob->arrived[idx].load() < g_n) {
     if (oob->failed.load() || expired(t0, 60)) return 1;
+    if (g_rma && g_progress_ctx) g_rma->rmaProgress(g_progress_ctx);
     usleep(100);
   }
   return 0;
@@ -120,6 +125,8 @@ static int run_rank(const char* so) {
   ncclRmaConfig_t cfg = {1, -1, 0};
   void* ctx = nullptr;
   OK(rma->createContext(coll, &cfg, &ctx));
+  g_rma = rma;
+  g_progress_ctx = ctx;
 
   // ---- buffers: data window (slot per source rank), signal words, source payload
   const size_t SLOT = 4096;
@@ -196,6 +203,7 @@ static int run_rank(const char* so) {
   OK(rma->queryLastError(ctx, &err));
   if (err) FAIL("queryLastError reports an error");
   if (oob_barrier()) FAIL("barrier");
+  g_progress_ctx = nullptr;
   OK(rma->deregMrSym(coll, got_mh));
   OK(rma->deregMrSym(coll, sig_mh));
   OK(rma->deregMrSym(coll, src_mh));
