@@ -1,0 +1,411 @@
+// Tensor-parallel GEMMs fused with their collectives, each as ONE kernel:
+//
+//  ag_gemm  : all-gather(A over ranks, along M or B along N) -> tcgen05 GEMM (-> SwiGLU). A few
+//             "mover" CTAs pull the peers' shards over NVLink into this GPU's copy of the
+//             gathered operand and publish one flag per 128-row chunk; the GEMM CTAs walk the tiles
+//             in the order the chunks arrive (own shard first) and their TMA producer waits on the
+//             flag of the chunk it is about to load. Remote data crosses NVLink exactly once and
+//             is always TMA-loaded from local memory.
+//  gemm_rs  : tcgen05 GEMM -> reduce-scatter. The epilogue stores each finished tile straight
+//             into the owning rank's staging slot (peer stores) and sets its per-tile arrival
+//             flag there (release-ordered remote store); "reducer" CTAs on the owner wait for
+//             all contributions of a tile and sum them in fp32. Ranks walk the shards in rotated
+//             order so that no GPU's NVLink ingress is hit by everyone at once.
+//
+// Every wait is bounded (status word + early exit), none of the loads uses cluster multicast.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "gemm_epilogues.cuh"
+#include "gemm_tcgen05.cuh"
+#include "gin_device.cuh"
+#include "host_util.h"
+
+namespace b200 {
+
+const GinDevHandle* comm_handle(int id);  // collectives.cu
+
+// Scratch words inside the control pad used by these kernels (u32 each).
+// Every flag holds the number of the call (per communicator, counted on the host) that last set
+// it, so nothing is ever reset and calls of different shapes can follow one another.
+constexpr size_t TP_READY_OFF = GIN_PAD_SCRATCH_OFF;                    // [4096] chunk-ready flags (ag_gemm)
+constexpr size_t TP_ARRIVED_OFF = GIN_PAD_SCRATCH_OFF + 4096 * 4;       // [16384][src rank] tile arrival flags (gemm_rs)
+constexpr int TP_MAX_CHUNKS = 4096;
+constexpr int TP_MAX_TILES = 16384;
+static_assert(TP_ARRIVED_OFF + size_t(TP_MAX_TILES) * GIN_MAX_RANKS * 4 <= GIN_PAD_BYTES, "pad too small");
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+// ------------------------------------------------------------------------------------------ ag_gemm
+// Gate on the gathered operand: chunk index = tile index along the gathered dimension.
+struct ChunkGate {
+  const uint32_t* ready;   // local flags
+  uint32_t target;         // value a flag reaches when its chunk has landed in this call
+  int chunks_per_shard;
+  int my_shard;
+  int on_b;                // 0: A rows are gathered (gate on tm), 1: B rows are gathered (gate on tn)
+  uint64_t limit_ns;
+  __device__ __forceinline__ bool wait_tile(int tm, int tn, volatile int* abort_flag, int* err_word) {
+    const int chunk = on_b ? tn : tm;
+    if (chunk / chunks_per_shard == my_shard) return true;
+    const uint32_t* f = ready + chunk;
+    if (static_cast<int32_t>(ld_acquire_gpu_u32(f) - target) >= 0) {
+      fence_proxy_async_global();
+      return true;
+    }
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t spins = 1;; ++spins) {
+      if (static_cast<int32_t>(ld_acquire_gpu_u32(f) - target) >= 0) {
+        fence_proxy_async_global();  // the chunk was written with ordinary stores; TMA reads it next
+        return true;
+      }
+      if ((spins & 0xFF) == 0) {
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > limit_ns) {
+          *abort_flag = 1;
+          if (err_word) atomicCAS(err_word, 0, DEV_ERR_SIGNAL_TIMEOUT);
+          return false;
+        }
+      }
+    }
+  }
+};
+
+struct AgGemmArgs {
+  GinDevHandle h;
+  size_t gathered_off;      // byte offset of the gathered operand inside the window
+  size_t shard_bytes;       // bytes of one rank's shard (contiguous rows)
+  size_t chunk_bytes;       // bytes of one gate chunk (tile rows x row bytes)
+  int chunks_per_shard;
+  int n_movers;
+  int channel;
+  uint32_t epoch;
+};
+
+// Mover CTAs: fetch the peers' shards, nearest rank first, chunk by chunk.
+__device__ __forceinline__ void ag_mover(const AgGemmArgs& a) {
+  const GinDevHandle& h = a.h;
+  if (!gin_barrier(h, a.channel, blockIdx.x)) return;  // every rank's shard is in place
+  uint32_t* ready = reinterpret_cast<uint32_t*>(h.pad[h.rank] + TP_READY_OFF);
+  for (int s = 1; s < h.nranks; ++s) {
+    const int peer = (h.rank + s) % h.nranks;
+    for (int c = blockIdx.x; c < a.chunks_per_shard; c += a.n_movers) {
+      const size_t off = a.gathered_off + peer * a.shard_bytes + c * a.chunk_bytes;
+      const uint4* src = reinterpret_cast<const uint4*>(h.window[peer] + off);
+      uint4* dst = reinterpret_cast<uint4*>(h.window[h.rank] + off);
+      const size_t nvec = a.chunk_bytes >> 4;
+      constexpr int U = 4;
+      for (size_t v = threadIdx.x; v < nvec; v += static_cast<size_t>(blockDim.x) * U) {
+        uint4 val[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (v + u * blockDim.x < nvec) val[u] = src[v + u * blockDim.x];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (v + u * blockDim.x < nvec) dst[v + u * blockDim.x] = val[u];
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence();
+        st_release_gpu_u32(ready + peer * a.chunks_per_shard + c, a.epoch);
+      }
+    }
+  }
+  gin_barrier(h, a.channel, blockIdx.x);  // nobody overwrites a shard that a peer is still reading
+}
+
+template <int BN, bool B_MN, class Epi>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmShape shape,
+                   AgGemmArgs args, Epi epi, int gate_on_b) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if (static_cast<int>(blockIdx.x) < args.n_movers) {
+    ag_mover(args);
+    return;
+  }
+  ChunkGate gate{reinterpret_cast<const uint32_t*>(args.h.pad[args.h.rank] + TP_READY_OFF), args.epoch,
+                 args.chunks_per_shard, args.h.rank, gate_on_b, args.h.wait_limit_ns};
+  gemm_mainloop<BN, false, B_MN>(&tmA, &tmB, shape, epi, gate, args.h.status, smem_raw);
+}
+
+// ------------------------------------------------------------------------------------------ gemm_rs
+struct RsArgs {
+  GinDevHandle h;
+  size_t staging_off;       // window offset of the staging area: [src rank][rows_per_shard][N] bf16
+  int rows_per_shard;       // M / nranks
+  int tiles_per_shard_m;
+  int n_reducers;
+  int channel;
+  uint32_t epoch;
+  __nv_bfloat16* out;       // [rows_per_shard][N] on this rank
+  int64_t ld_out;
+  float scale;
+};
+
+template <int BN>
+struct PushEpilogue {
+  static constexpr bool kPair = false;
+  GinDevHandle h;
+  size_t staging_off;
+  int rows_per_shard, tiles_per_shard_m, N;
+  int owner, row_base;
+  // Shared-memory counters of epilogue warps that finished a tile, indexed by (tile sequence & 3):
+  // with two accumulator buffers a warp can run at most two tiles ahead of the slowest one, so
+  // four counters never mix tiles.
+  unsigned int* warp_count;
+  unsigned int seq;
+  uint32_t epoch;
+  __device__ __forceinline__ void tile_begin(int tm, int) {
+    owner = tm / tiles_per_shard_m;
+    row_base = owner * rows_per_shard;
+  }
+  __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&acc)[32], const GemmShape& s) {
+    if (row >= s.M || col0 >= s.N) return;
+    // my contribution goes to slot `rank` of the owner's staging area
+    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(h.window[owner] + staging_off) +
+                          (static_cast<size_t>(h.rank) * rows_per_shard + (row - row_base)) * N + col0;
+    uint4* out = reinterpret_cast<uint4*>(base);
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+      out[v] = make_uint4(pack_bf16x2(__uint_as_float(acc[8 * v]), __uint_as_float(acc[8 * v + 1])),
+                          pack_bf16x2(__uint_as_float(acc[8 * v + 2]), __uint_as_float(acc[8 * v + 3])),
+                          pack_bf16x2(__uint_as_float(acc[8 * v + 4]), __uint_as_float(acc[8 * v + 5])),
+                          pack_bf16x2(__uint_as_float(acc[8 * v + 6]), __uint_as_float(acc[8 * v + 7])));
+  }
+  // Called by every epilogue thread. The warp that arrives last (no warp ever waits for another,
+  // so a warp that gave up on a timeout cannot block the rest) tells the owner that this rank's
+  // contribution to the tile is complete.
+  __device__ __forceinline__ void tile_end(int tm, int tn) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) {
+      fence_acq_rel_sys();  // this warp's peer stores are performed before the count moves
+      const unsigned int prev = atomicAdd(warp_count + (seq & 3u), 1u);
+      if ((prev & 3u) == 3u) {
+        const int tiles_n = (N + BN - 1) / BN;
+        const int t = (tm - owner * tiles_per_shard_m) * tiles_n + tn;
+        uint32_t* flag = reinterpret_cast<uint32_t*>(h.pad[owner] + TP_ARRIVED_OFF) + t * GIN_MAX_RANKS + h.rank;
+        st_release_sys_u32(flag, epoch);
+      }
+    }
+    ++seq;
+  }
+};
+
+template <int BN>
+__device__ __forceinline__ void rs_reducer(const RsArgs& a, int N) {
+  const GinDevHandle& h = a.h;
+  if (!gin_barrier(h, a.channel, blockIdx.x)) return;  // staging areas are free, counters consistent
+  const int tiles_n = (N + BN - 1) / BN;
+  const int ntiles = a.tiles_per_shard_m * tiles_n;
+  const uint32_t* arrived = reinterpret_cast<const uint32_t*>(h.pad[h.rank] + TP_ARRIVED_OFF);
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  for (int t = blockIdx.x; t < ntiles; t += a.n_reducers) {
+    // one thread per source rank waits for that rank's contribution to the tile
+    if (static_cast<int>(threadIdx.x) < h.nranks &&
+        !gin_spin_u32_ge(h, arrived + t * GIN_MAX_RANKS + threadIdx.x, a.epoch, DEV_ERR_SIGNAL_TIMEOUT))
+      ok = 0;
+    __syncthreads();
+    if (!ok) break;
+    const int tm = t / tiles_n, tn = t % tiles_n;
+    const int rows = min(GEMM_BM, a.rows_per_shard - tm * GEMM_BM);
+    const int cols = min(BN, N - tn * BN);
+    const int vec_per_row = cols / 8;
+    const __nv_bfloat16* st = reinterpret_cast<const __nv_bfloat16*>(h.window[h.rank] + a.staging_off);
+    for (int i = threadIdx.x; i < rows * vec_per_row; i += blockDim.x) {
+      const int r = i / vec_per_row, c = (i % vec_per_row) * 8;
+      const size_t row = static_cast<size_t>(tm) * GEMM_BM + r;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int src = 0; src < h.nranks; ++src) {
+        const uint4 v = *reinterpret_cast<const uint4*>(st + (static_cast<size_t>(src) * a.rows_per_shard + row) * N + tn * BN + c);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[2 * j] += __low2float(p[j]);
+          acc[2 * j + 1] += __high2float(p[j]);
+        }
+      }
+      uint4 o = make_uint4(pack_bf16x2(acc[0] * a.scale, acc[1] * a.scale), pack_bf16x2(acc[2] * a.scale, acc[3] * a.scale),
+                           pack_bf16x2(acc[4] * a.scale, acc[5] * a.scale), pack_bf16x2(acc[6] * a.scale, acc[7] * a.scale));
+      *reinterpret_cast<uint4*>(a.out + row * a.ld_out + tn * BN + c) = o;
+    }
+    __syncthreads();
+  }
+  gin_barrier(h, a.channel, blockIdx.x);  // every rank has consumed its staging area
+}
+
+template <int BN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmShape shape,
+                   RsArgs args) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if (static_cast<int>(blockIdx.x) < args.n_reducers) {
+    rs_reducer<BN>(args, shape.N);
+    return;
+  }
+  __shared__ unsigned int epi_warp_count[4];
+  if (threadIdx.x < 4) epi_warp_count[threadIdx.x] = 0;
+  __syncthreads();
+  PushEpilogue<BN> epi{args.h, args.staging_off, args.rows_per_shard, args.tiles_per_shard_m, shape.N, 0, 0, epi_warp_count, 0, args.epoch};
+  NoGate gate;
+  gemm_mainloop<BN, false, B_MN>(&tmA, &tmB, shape, epi, gate, args.h.status, smem_raw);
+}
+
+// per-communicator call counters (flags and counters only ever grow; the expected value is
+// derived from the number of calls made so far)
+static uint32_t g_ag_epoch[64] = {0};
+static uint32_t g_rs_epoch[64] = {0};
+
+template <typename K>
+static int set_smem(K kern, int bytes) {
+  return static_cast<int>(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+}
+
+}  // namespace b200
+
+extern "C" {
+using namespace b200;
+
+// C[M,N] = gather(A)[M,K] * B^T, A gathered along M from all ranks' shards (rows rank*M/n ...),
+// which live at `gathered_off` in every rank's window (own shard already in place); the local
+// operand B is passed in `other`.
+//   b_mn     : B stored [K][N] instead of [N][K]
+//   epilogue : 0 = store C (bf16, ldc), 1 = SwiGLU on interleaved gate|up columns -> act [M][N/2]
+//              (ld_act), also storing the raw gate|up into C when C is non-null
+// M must be a multiple of 128 * nranks.
+// gather_b = 1 gathers B instead (FSDP: the weight [N][K] is sharded over ranks along N, the
+// activation A [M][K] is local and passed in `other`); then N must be a multiple of 256 * nranks
+// and b_mn must be 0.
+int b200_ag_gemm(int comm, size_t gathered_off, int gather_b, int M, int N, int K, const void* other, long long ld_other,
+                 int b_mn, void* C, long long ldc, void* act, long long ld_act, int epilogue, int n_movers, int channel,
+                 void* stream) {
+  ensure_context();
+  const GinDevHandle* hp = comm_handle(comm);
+  if (!hp || comm < 0 || comm >= 64 || !other) return B200_ERR_BAD_ARG;
+  GinDevHandle h = *hp;
+  constexpr int BN = 256;
+  if (K % 8 || N % 64 || (epilogue == 1 && !act) || (epilogue == 0 && !C)) return B200_ERR_BAD_ARG;
+  if (!gather_b && M % (GEMM_BM * h.nranks)) return B200_ERR_BAD_ARG;
+  if (gather_b && (N % (BN * h.nranks) || b_mn)) return B200_ERR_BAD_ARG;
+  const size_t shard_bytes = static_cast<size_t>((gather_b ? N : M) / h.nranks) * K * 2;
+  if (gathered_off % 1024 || gathered_off + shard_bytes * h.nranks > h.window_bytes) return B200_ERR_BAD_ARG;
+  GemmShape shape{M, N, K, (M + GEMM_BM - 1) / GEMM_BM, (N + BN - 1) / BN};
+  const int chunks_total = gather_b ? shape.tiles_n : shape.tiles_m;
+  const int chunks_per_shard = chunks_total / h.nranks;
+  if (chunks_total > TP_MAX_CHUNKS) return B200_ERR_TOO_LARGE;
+  if (n_movers <= 0) n_movers = 16;
+  if (n_movers > chunks_per_shard) n_movers = chunks_per_shard;
+  const int sms = sm_count();
+  shape.cta_first = n_movers;
+  shape.num_ctas = sms - n_movers;
+  if (shape.num_ctas > shape.tiles_m * shape.tiles_n) shape.num_ctas = shape.tiles_m * shape.tiles_n;
+  // own shard first, then rank+1, rank+2, ... along the gathered dimension
+  if (gather_b) {
+    shape.n_rot = h.rank * chunks_per_shard;
+    shape.m_major = 0;
+  } else {
+    shape.m_rot = h.rank * chunks_per_shard;
+    shape.m_major = 1;
+  }
+  CUtensorMap tmA, tmB;
+  int rc;
+  const void* gathered = h.window[h.rank] + gathered_off;
+  if (gather_b) {
+    rc = make_tmap_2d(&tmA, other, M, K, ld_other, GEMM_BM, GEMM_BK, 2, true);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tmB, gathered, N, K, K, BN, GEMM_BK, 2, true);
+  } else {
+    rc = make_tmap_2d(&tmA, gathered, M, K, K, GEMM_BM, GEMM_BK, 2, true);
+    if (rc) return rc;
+    rc = b_mn ? make_tmap_2d(&tmB, other, K, N, ld_other, GEMM_BK, 64, 2, true)
+              : make_tmap_2d(&tmB, other, N, K, ld_other, BN, GEMM_BK, 2, true);
+  }
+  if (rc) return rc;
+  AgGemmArgs args{h, gathered_off, shard_bytes, static_cast<size_t>(gather_b ? BN : GEMM_BM) * K * 2, chunks_per_shard,
+                  n_movers, channel, ++g_ag_epoch[comm]};
+  const int grid = n_movers + shape.num_ctas;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int smem = GemmSmem<BN>::TOTAL;
+  if (epilogue == 1) {
+    SwiGluEpilogue epi{static_cast<__nv_bfloat16*>(act), ld_act, static_cast<__nv_bfloat16*>(C), ldc};
+    if (b_mn) {
+      auto k = ag_gemm_kernel<BN, true, SwiGluEpilogue>;
+      if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
+      k<<<grid, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args, epi, gather_b);
+    } else {
+      auto k = ag_gemm_kernel<BN, false, SwiGluEpilogue>;
+      if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
+      k<<<grid, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args, epi, gather_b);
+    }
+  } else {
+    StoreEpilogue<__nv_bfloat16> epi{static_cast<__nv_bfloat16*>(C), ldc, 0};
+    if (b_mn) {
+      auto k = ag_gemm_kernel<BN, true, StoreEpilogue<__nv_bfloat16>>;
+      if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
+      k<<<grid, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args, epi, gather_b);
+    } else {
+      auto k = ag_gemm_kernel<BN, false, StoreEpilogue<__nv_bfloat16>>;
+      if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
+      k<<<grid, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args, epi, gather_b);
+    }
+  }
+  B200_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// out[M/n, N] (this rank's rows) = scale * sum over ranks of (A_r[M,K] * B_r^T)[rows of this rank].
+// staging_off: window offset of nranks * (M/n) * N bf16 of staging space on every rank.
+int b200_gemm_rs(int comm, const void* A, long long lda, const void* B, long long ldb, int b_mn, int M, int N, int K,
+                 size_t staging_off, void* out, long long ld_out, float scale, int n_reducers, int channel,
+                 void* stream) {
+  ensure_context();
+  const GinDevHandle* hp = comm_handle(comm);
+  if (!hp || comm < 0 || comm >= 64) return B200_ERR_BAD_ARG;
+  GinDevHandle h = *hp;
+  constexpr int BN = 256;
+  if (M % (GEMM_BM * h.nranks) || K % 8 || N % 32 || !A || !B || !out) return B200_ERR_BAD_ARG;
+  const size_t staging_bytes = static_cast<size_t>(M) * N * 2;
+  if (staging_off % 16 || staging_off + staging_bytes > h.window_bytes) return B200_ERR_BAD_ARG;
+  GemmShape shape{M, N, K, M / GEMM_BM, (N + BN - 1) / BN};
+  const int tiles_per_shard_m = shape.tiles_m / h.nranks;
+  if (tiles_per_shard_m * shape.tiles_n > TP_MAX_TILES) return B200_ERR_TOO_LARGE;
+  if (n_reducers <= 0) n_reducers = 16;
+  const int sms = sm_count();
+  shape.cta_first = n_reducers;
+  shape.num_ctas = sms - n_reducers;
+  if (shape.num_ctas > shape.tiles_m * shape.tiles_n) shape.num_ctas = shape.tiles_m * shape.tiles_n;
+  shape.m_rot = ((h.rank + 1) % h.nranks) * tiles_per_shard_m;  // next rank's rows first, own rows last
+  shape.m_major = 1;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, A, M, K, lda, GEMM_BM, GEMM_BK, 2, true);
+  if (rc) return rc;
+  rc = b_mn ? make_tmap_2d(&tmB, B, K, N, ldb, GEMM_BK, 64, 2, true) : make_tmap_2d(&tmB, B, N, K, ldb, BN, GEMM_BK, 2, true);
+  if (rc) return rc;
+  RsArgs args{h, staging_off, M / h.nranks, tiles_per_shard_m, n_reducers, channel, ++g_rs_epoch[comm],
+              static_cast<__nv_bfloat16*>(out), ld_out, scale};
+  const int grid = n_reducers + shape.num_ctas;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int smem = GemmSmem<BN>::TOTAL;
+  if (b_mn) {
+    auto k = gemm_rs_kernel<BN, true>;
+    if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
+    k<<<grid, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args);
+  } else {
+    auto k = gemm_rs_kernel<BN, false>;
+    if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
+    k<<<grid, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args);
+  }
+  B200_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

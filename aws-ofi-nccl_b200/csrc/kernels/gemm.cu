@@ -7,6 +7,7 @@
 //   b_mn = 0 : B stored [N][K] (K contiguous)      b_mn = 1 : B stored [K][N] (N contiguous)
 // so a linear layer's forward (x W^T), input gradient (dy W) and weight gradient (dy^T x) all run
 // on the same kernel without materialising a transpose.
+#include "gemm_epilogues.cuh"
 #include "gemm_tcgen05.cuh"
 #include "host_util.h"
 
@@ -23,69 +24,6 @@ int* device_status_word() {
   }
   return words[dev];
 }
-
-template <typename OutT>
-struct StoreEpilogue {
-  OutT* C;
-  int64_t ldc;
-  int accumulate;
-  __device__ __forceinline__ void tile_begin(int, int) {}
-  __device__ __forceinline__ void tile_end(int, int) {}
-  __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&acc)[32], const GemmShape& s) {
-    if (row >= s.M || col0 >= s.N) return;
-    OutT* dst = C + static_cast<int64_t>(row) * ldc + col0;
-    const int ncols = min(32, s.N - col0);
-    if constexpr (sizeof(OutT) == 2) {
-      if (ncols == 32) {
-        uint32_t packed[16];
-        if (accumulate) {
-          const uint4* old = reinterpret_cast<const uint4*>(dst);
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 o = old[v];
-            const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const __nv_bfloat162 ob = *reinterpret_cast<const __nv_bfloat162*>(&ow[j]);
-              packed[v * 4 + j] = pack_bf16x2(__uint_as_float(acc[v * 8 + 2 * j]) + __low2float(ob),
-                                              __uint_as_float(acc[v * 8 + 2 * j + 1]) + __high2float(ob));
-            }
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            packed[j] = pack_bf16x2(__uint_as_float(acc[2 * j]), __uint_as_float(acc[2 * j + 1]));
-        }
-        uint4* out = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-        for (int v = 0; v < 4; ++v)
-          out[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-      } else {
-        for (int j = 0; j < ncols; ++j) {
-          float v = __uint_as_float(acc[j]);
-          if (accumulate) v += __bfloat162float(reinterpret_cast<__nv_bfloat16*>(dst)[j]);
-          reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16(v);
-        }
-      }
-    } else {
-      if (ncols == 32) {
-        float4* out = reinterpret_cast<float4*>(dst);
-#pragma unroll
-        for (int v = 0; v < 8; ++v) {
-          float4 o = accumulate ? out[v] : make_float4(0.f, 0.f, 0.f, 0.f);
-          out[v] = make_float4(o.x + __uint_as_float(acc[4 * v]), o.y + __uint_as_float(acc[4 * v + 1]),
-                               o.z + __uint_as_float(acc[4 * v + 2]), o.w + __uint_as_float(acc[4 * v + 3]));
-        }
-      } else {
-        for (int j = 0; j < ncols; ++j) {
-          float v = __uint_as_float(acc[j]);
-          if (accumulate) v += reinterpret_cast<float*>(dst)[j];
-          reinterpret_cast<float*>(dst)[j] = v;
-        }
-      }
-    }
-  }
-};
 
 template <int BN, bool A_MN, bool B_MN, typename OutT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)

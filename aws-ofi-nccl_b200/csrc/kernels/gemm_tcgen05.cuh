@@ -28,13 +28,29 @@ struct GemmSmem {
 struct GemmShape {
   int M, N, K;
   int tiles_m, tiles_n;
+  // Fused kernels run the GEMM on a subset of the grid and may want a rotated M order:
+  int cta_first = 0;   // first CTA (blockIdx.x) that takes part in the GEMM
+  int num_ctas = 0;    // number of GEMM CTAs (0 = the whole grid)
+  int m_rot = 0;       // tile_m = (raw + m_rot) % tiles_m
+  int m_major = 0;     // 1: walk all N tiles of an M tile before the next M tile
+  int n_rot = 0;       // tile_n = (raw + n_rot) % tiles_n
 };
 
-// The tile id -> (tile_m, tile_n) map: M fastest inside a band of 8 N-tiles... kept simple and
-// L2-friendly: consecutive CTAs share the same B (weight) tile.
+// The tile id -> (tile_m, tile_n) map. Default: M fastest, so consecutive CTAs share the same B
+// (weight) tile. m_major: N fastest, so that M tiles finish (or are needed) one after another.
 __device__ __forceinline__ void tile_coords(const GemmShape& s, int tile, int& tm, int& tn) {
-  tm = tile % s.tiles_m;
-  tn = tile / s.tiles_m;
+  int raw_m;
+  if (s.m_major) {
+    raw_m = tile / s.tiles_n;
+    tn = tile % s.tiles_n;
+  } else {
+    raw_m = tile % s.tiles_m;
+    tn = tile / s.tiles_m;
+  }
+  tm = raw_m + s.m_rot;
+  if (tm >= s.tiles_m) tm -= s.tiles_m;
+  tn += s.n_rot;
+  if (tn >= s.tiles_n) tn -= s.tiles_n;
 }
 
 // Epilogue functor contract:
@@ -86,6 +102,8 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
 
   const int num_tiles = shape.tiles_m * shape.tiles_n;
   const int num_kb = (shape.K + GEMM_BK - 1) / GEMM_BK;
+  const int cta_id = static_cast<int>(blockIdx.x) - shape.cta_first;
+  const int cta_stride = shape.num_ctas > 0 ? shape.num_ctas : static_cast<int>(gridDim.x);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -93,10 +111,10 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = cta_id; tile < num_tiles && ok; tile += cta_stride) {
         int tm, tn;
         tile_coords(shape, tile, tm, tn);
-        if (!gate.wait_rows(tm, abort_flag, err_word)) break;
+        if (!gate.wait_tile(tm, tn, abort_flag, err_word)) break;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1, abort_flag, err_word, DEV_ERR_EMPTY_BAR_TIMEOUT,
                                  GEMM_WAIT_LIMIT_NS)) {
@@ -136,7 +154,7 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
       int acc_buf = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = cta_id; tile < num_tiles && ok; tile += cta_stride) {
         if (!mbar_wait_bounded(tempty_bar(acc_buf), acc_phase ^ 1, abort_flag, err_word, DEV_ERR_TMEM_EMPTY_TIMEOUT,
                                GEMM_WAIT_LIMIT_NS))
           break;
@@ -175,7 +193,7 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
     const int quarter = warp & 3;
     int acc_buf = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    for (int tile = cta_id; tile < num_tiles; tile += cta_stride) {
       int tm, tn;
       tile_coords(shape, tile, tm, tn);
       if (!mbar_wait_bounded(tfull_bar(acc_buf), acc_phase, abort_flag, err_word, DEV_ERR_TMEM_FULL_TIMEOUT,
@@ -185,12 +203,23 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
       epi.tile_begin(tm, tn);
       const int row = tm * GEMM_BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc_buf * BN;
+      if constexpr (Epilogue::kPair) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t acc[32];
-        tmem_ld_32x32(taddr + c * 32, acc);
-        tmem_ld_wait();
-        epi(row, tn * BN + c * 32, acc, shape);
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t acc0[32], acc1[32];
+          tmem_ld_32x32(taddr + c * 64, acc0);
+          tmem_ld_32x32(taddr + c * 64 + 32, acc1);
+          tmem_ld_wait();
+          epi(row, tn * BN + c * 64, acc0, acc1, shape);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t acc[32];
+          tmem_ld_32x32(taddr + c * 32, acc);
+          tmem_ld_wait();
+          epi(row, tn * BN + c * 32, acc, shape);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -217,7 +246,7 @@ __device__ __forceinline__ void gemm_mainloop(const CUtensorMap* tmA, const CUte
 
 // Gate that never waits (all operand rows are local and ready).
 struct NoGate {
-  __device__ __forceinline__ bool wait_rows(int, volatile int*, int*) { return true; }
+  __device__ __forceinline__ bool wait_tile(int, int, volatile int*, int*) { return true; }
 };
 
 }  // namespace b200

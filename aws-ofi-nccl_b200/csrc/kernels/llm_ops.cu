@@ -219,7 +219,9 @@ __global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict_
     reinterpret_cast<Bf16x8*>(out + t * F)[c] = pack8(o);
   }
 }
-// dgu[T,2F] from dout[T,F] and the saved gate|up.
+// dgu[T,2F] from dout[T,F] and the saved gate|up. INTERLEAVED: gate and up alternate in blocks of
+// 32 columns (the layout the fused GEMM+SwiGLU epilogue produces) instead of two halves.
+template <bool INTERLEAVED>
 __global__ void swiglu_bwd_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ gu, bf16* __restrict__ dgu,
                                   int64_t T, int F) {
   const int64_t nvec = T * F / 8;
@@ -228,10 +230,12 @@ __global__ void swiglu_bwd_kernel(const bf16* __restrict__ dout, const bf16* __r
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t t = i / fv;
     const int c = static_cast<int>(i - t * fv);
+    const int gi = INTERLEAVED ? (c >> 2) * 8 + (c & 3) : c;       // in 8-element vectors
+    const int ui = INTERLEAVED ? gi + 4 : fv + c;
     const Bf16x8* row = reinterpret_cast<const Bf16x8*>(gu + t * 2 * F);
     float g[8], u[8], d[8], dg[8], du[8];
-    unpack8(row[c], g);
-    unpack8(row[fv + c], u);
+    unpack8(row[gi], g);
+    unpack8(row[ui], u);
     unpack8(reinterpret_cast<const Bf16x8*>(dout + t * F)[c], d);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -241,8 +245,8 @@ __global__ void swiglu_bwd_kernel(const bf16* __restrict__ dout, const bf16* __r
       dg[j] = d[j] * u[j] * (s + silu * (1.f - s));
     }
     Bf16x8* orow = reinterpret_cast<Bf16x8*>(dgu + t * 2 * F);
-    orow[c] = pack8(dg);
-    orow[fv + c] = pack8(du);
+    orow[gi] = pack8(dg);
+    orow[ui] = pack8(du);
   }
 }
 
@@ -494,7 +498,15 @@ int b200_swiglu_fwd(const void* gu, void* out, long long T, int F, void* stream)
 int b200_swiglu_bwd(const void* dout, const void* gu, void* dgu, long long T, int F, void* stream) {
   b200::ensure_context();
   if (F % 8) return B200_ERR_BAD_ARG;
-  swiglu_bwd_kernel<<<grid_for(T * F / 8, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  swiglu_bwd_kernel<false><<<grid_for(T * F / 8, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const bf16*>(dout), static_cast<const bf16*>(gu), static_cast<bf16*>(dgu), T, F);
+  B200_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+int b200_swiglu_bwd_interleaved(const void* dout, const void* gu, void* dgu, long long T, int F, void* stream) {
+  b200::ensure_context();
+  if (F % 32) return B200_ERR_BAD_ARG;
+  swiglu_bwd_kernel<true><<<grid_for(T * F / 8, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const bf16*>(dout), static_cast<const bf16*>(gu), static_cast<bf16*>(dgu), T, F);
   B200_CUDA_OK(cudaGetLastError());
   return 0;

@@ -22,6 +22,7 @@ _SIGNATURES = {
     "b200_rmsnorm_bwd": ([_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
     "b200_swiglu_fwd": ([_vp, _vp, _ll, _i, _vp], _i),
     "b200_swiglu_bwd": ([_vp, _vp, _vp, _ll, _i, _vp], _i),
+    "b200_swiglu_bwd_interleaved": ([_vp, _vp, _vp, _ll, _i, _vp], _i),
     "b200_rope": ([_vp, _vp, _vp, _ll, _i, _i, _ll, _i, _i, _vp], _i),
     "b200_cross_entropy": ([_vp, _vp, _vp, _i, _i, _ll, _f, _vp], _i),
     "b200_embedding_fwd": ([_vp, _vp, _vp, _ll, _i, _vp], _i),

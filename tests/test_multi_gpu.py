@@ -65,3 +65,16 @@ def test_unmodified_nccl_runs_over_the_net_plugin(tmp_path):
     assert "nccl plugin worker OK" in out
     text = "".join(p.read_text() for p in tmp_path.glob("nccl.log.*"))
     assert "B200NVL" in text, text[-3000:]
+
+
+@pytest.mark.skipif(_ngpus() < 1, reason="needs a GPU")
+def test_fused_tp_kernels_single_rank():
+    """World size 1: the fused kernels degenerate to a gated GEMM and a local reduction."""
+    out = _run("tp_worker.py", 1)
+    assert "TP_WORKER_OK" in out
+
+
+@pytest.mark.skipif(_ngpus() < 2, reason="needs at least 2 GPUs")
+def test_fused_tp_kernels_all_gpus():
+    out = _run("tp_worker.py", min(_ngpus(), 8))
+    assert "TP_WORKER_OK" in out
