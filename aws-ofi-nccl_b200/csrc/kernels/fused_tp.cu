@@ -90,34 +90,83 @@ struct AgGemmArgs {
   uint32_t epoch;
 };
 
-// Mover CTAs: fetch the peers' shards, nearest rank first, chunk by chunk.
-__device__ __forceinline__ void ag_mover(const AgGemmArgs& a) {
+// Untiled bulk copies (no multicast): global -> shared with an mbarrier, shared -> global in a bulk group.
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes)
+               : "memory");
+}
+
+constexpr uint32_t MOVER_PIECE = 32768;
+constexpr int MOVER_STAGES = 5;   // 160 KiB of the CTA's shared memory; four loads in flight
+static_assert(MOVER_STAGES * MOVER_PIECE + 1024 + 64 <= GemmSmem<256>::TOTAL, "mover buffers exceed the kernel's smem");
+
+// Mover CTAs: fetch the peers' shards, nearest rank first, chunk by chunk. One thread drives the
+// copy engine: pieces of 32 KiB travel peer memory -> shared memory -> this GPU's copy of the
+// gathered operand, several loads in flight, and the chunk's flag is published once its last
+// store has completed.
+__device__ __forceinline__ void ag_mover(const AgGemmArgs& a, uint8_t* smem_raw) {
   const GinDevHandle& h = a.h;
   if (!gin_barrier(h, a.channel, blockIdx.x)) return;  // every rank's shard is in place
-  uint32_t* ready = reinterpret_cast<uint32_t*>(h.pad[h.rank] + TP_READY_OFF);
-  for (int s = 1; s < h.nranks; ++s) {
-    const int peer = (h.rank + s) % h.nranks;
-    for (int c = blockIdx.x; c < a.chunks_per_shard; c += a.n_movers) {
-      const size_t off = a.gathered_off + peer * a.shard_bytes + c * a.chunk_bytes;
-      const uint4* src = reinterpret_cast<const uint4*>(h.window[peer] + off);
-      uint4* dst = reinterpret_cast<uint4*>(h.window[h.rank] + off);
-      const size_t nvec = a.chunk_bytes >> 4;
-      constexpr int U = 4;
-      for (size_t v = threadIdx.x; v < nvec; v += static_cast<size_t>(blockDim.x) * U) {
-        uint4 val[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (v + u * blockDim.x < nvec) val[u] = src[v + u * blockDim.x];
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (v + u * blockDim.x < nvec) dst[v + u * blockDim.x] = val[u];
+  if (threadIdx.x == 0 && h.nranks > 1) {
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = base + MOVER_STAGES * MOVER_PIECE;
+    for (int s = 0; s < MOVER_STAGES; ++s) mbar_init(bars + 8u * s, 1);
+    fence_barrier_init();
+    uint32_t* ready = reinterpret_cast<uint32_t*>(h.pad[h.rank] + TP_READY_OFF);
+    const uint32_t pieces_per_chunk = static_cast<uint32_t>((a.chunk_bytes + MOVER_PIECE - 1) / MOVER_PIECE);
+    const int my_chunks = (a.chunks_per_shard - static_cast<int>(blockIdx.x) + a.n_movers - 1) / a.n_movers;
+    const uint32_t total = static_cast<uint32_t>(h.nranks - 1) * my_chunks * pieces_per_chunk;
+    // piece index -> (peer, chunk, offset in chunk, bytes)
+    auto locate = [&](uint32_t i, int& peer, int& chunk, size_t& off, uint32_t& bytes) {
+      const uint32_t pc = i / pieces_per_chunk, pi = i - pc * pieces_per_chunk;
+      const int s = 1 + static_cast<int>(pc) / my_chunks;
+      peer = (h.rank + s) % h.nranks;
+      chunk = static_cast<int>(blockIdx.x) + (static_cast<int>(pc) % my_chunks) * a.n_movers;
+      const size_t in_chunk = static_cast<size_t>(pi) * MOVER_PIECE;
+      off = a.gathered_off + peer * a.shard_bytes + chunk * a.chunk_bytes + in_chunk;
+      const size_t left = a.chunk_bytes - in_chunk;
+      bytes = left < MOVER_PIECE ? static_cast<uint32_t>(left) : MOVER_PIECE;
+    };
+    auto issue = [&](uint32_t i) {
+      int peer, chunk;
+      size_t off;
+      uint32_t bytes;
+      locate(i, peer, chunk, off, bytes);
+      const uint32_t st = i % MOVER_STAGES;
+      mbar_expect_tx(bars + 8u * st, bytes);
+      bulk_load(base + st * MOVER_PIECE, h.window[peer] + off, bytes, bars + 8u * st);
+    };
+    int abort_local = 0;
+    for (uint32_t i = 0; i < total && i < MOVER_STAGES - 1; ++i) issue(i);
+    for (uint32_t i = 0; i < total; ++i) {
+      const uint32_t st = i % MOVER_STAGES;
+      if (!mbar_wait_bounded(bars + 8u * st, (i / MOVER_STAGES) & 1u, &abort_local, h.status, DEV_ERR_SIGNAL_TIMEOUT,
+                             h.wait_limit_ns))
+        break;
+      int peer, chunk;
+      size_t off;
+      uint32_t bytes;
+      locate(i, peer, chunk, off, bytes);
+      bulk_store(h.window[h.rank] + off, base + st * MOVER_PIECE, bytes);
+      tma_store_commit();
+      if (i + MOVER_STAGES - 1 < total) {
+        // the stage about to be refilled was read by the store issued one step ago
+        tma_store_wait_read<1>();
+        issue(i + MOVER_STAGES - 1);
       }
-      __syncthreads();
-      if (threadIdx.x == 0) {
+      if ((i + 1) % pieces_per_chunk == 0) {
+        tma_store_wait<0>();           // the chunk is complete in this GPU's memory
+        fence_proxy_async_global();
         __threadfence();
-        st_release_gpu_u32(ready + peer * a.chunks_per_shard + c, a.epoch);
+        st_release_gpu_u32(ready + peer * a.chunks_per_shard + chunk, a.epoch);
       }
     }
+    tma_store_wait<0>();
   }
   gin_barrier(h, a.channel, blockIdx.x);  // nobody overwrites a shard that a peer is still reading
 }
@@ -128,7 +177,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                    AgGemmArgs args, Epi epi, int gate_on_b) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   if (static_cast<int>(blockIdx.x) < args.n_movers) {
-    ag_mover(args);
+    ag_mover(args, smem_raw);
     return;
   }
   ChunkGate gate{reinterpret_cast<const uint32_t*>(args.h.pad[args.h.rank] + TP_READY_OFF), args.epoch,
@@ -152,7 +201,7 @@ struct RsArgs {
 
 template <int BN>
 struct PushEpilogue {
-  static constexpr bool kPair = false;
+  static constexpr bool kPair = true;   // called with 64 consecutive columns per row
   GinDevHandle h;
   size_t staging_off;
   int rows_per_shard, tiles_per_shard_m, N;
@@ -163,22 +212,48 @@ struct PushEpilogue {
   unsigned int* warp_count;
   unsigned int seq;
   uint32_t epoch;
+  uint8_t* stage;  // 4 KiB of shared memory per epilogue warp: 32 rows x 128 B, 16-byte chunks XOR-swizzled by row
   __device__ __forceinline__ void tile_begin(int tm, int) {
     owner = tm / tiles_per_shard_m;
     row_base = owner * rows_per_shard;
   }
-  __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&acc)[32], const GemmShape& s) {
-    if (row >= s.M || col0 >= s.N) return;
-    // my contribution goes to slot `rank` of the owner's staging area
-    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(h.window[owner] + staging_off) +
-                          (static_cast<size_t>(h.rank) * rows_per_shard + (row - row_base)) * N + col0;
-    uint4* out = reinterpret_cast<uint4*>(base);
+  // Each lane arrives with one accumulator row. The warp transposes through shared memory so that
+  // every store instruction writes four complete 128-byte row segments: stores that cross NVLink
+  // as full lines instead of 32 scattered 16-byte pieces.
+  __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&a0)[32], const uint32_t (&a1)[32],
+                                             const GemmShape& s) {
+    if (col0 >= s.N) return;  // uniform over the warp
+    const int lane = threadIdx.x & 31;
+    uint8_t* buf = stage + ((threadIdx.x >> 5) - 2) * 4096;
 #pragma unroll
-    for (int v = 0; v < 4; ++v)
-      out[v] = make_uint4(pack_bf16x2(__uint_as_float(acc[8 * v]), __uint_as_float(acc[8 * v + 1])),
-                          pack_bf16x2(__uint_as_float(acc[8 * v + 2]), __uint_as_float(acc[8 * v + 3])),
-                          pack_bf16x2(__uint_as_float(acc[8 * v + 4]), __uint_as_float(acc[8 * v + 5])),
-                          pack_bf16x2(__uint_as_float(acc[8 * v + 6]), __uint_as_float(acc[8 * v + 7])));
+    for (int j = 0; j < 4; ++j) {
+      const uint4 v = make_uint4(pack_bf16x2(__uint_as_float(a0[8 * j]), __uint_as_float(a0[8 * j + 1])),
+                                 pack_bf16x2(__uint_as_float(a0[8 * j + 2]), __uint_as_float(a0[8 * j + 3])),
+                                 pack_bf16x2(__uint_as_float(a0[8 * j + 4]), __uint_as_float(a0[8 * j + 5])),
+                                 pack_bf16x2(__uint_as_float(a0[8 * j + 6]), __uint_as_float(a0[8 * j + 7])));
+      *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 v = make_uint4(pack_bf16x2(__uint_as_float(a1[8 * j]), __uint_as_float(a1[8 * j + 1])),
+                                 pack_bf16x2(__uint_as_float(a1[8 * j + 2]), __uint_as_float(a1[8 * j + 3])),
+                                 pack_bf16x2(__uint_as_float(a1[8 * j + 4]), __uint_as_float(a1[8 * j + 5])),
+                                 pack_bf16x2(__uint_as_float(a1[8 * j + 6]), __uint_as_float(a1[8 * j + 7])));
+      *reinterpret_cast<uint4*>(buf + lane * 128 + (((j + 4) ^ (lane & 7)) << 4)) = v;
+    }
+    __syncwarp();
+    // my contribution goes to slot `rank` of the owner's staging area
+    const int row0 = row - lane;  // first row of this warp's 32-row slab
+    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(h.window[owner] + staging_off) +
+                          (static_cast<size_t>(h.rank) * rows_per_shard + (row0 - row_base)) * N + col0;
+    const int c = lane & 7;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = 4 * i + (lane >> 3);
+      const uint4 v = *reinterpret_cast<const uint4*>(buf + r * 128 + ((c ^ (r & 7)) << 4));
+      *reinterpret_cast<uint4*>(base + static_cast<size_t>(r) * N + c * 8) = v;
+    }
+    __syncwarp();
   }
   // Called by every epilogue thread. The warp that arrives last (no warp ever waits for another,
   // so a warp that gave up on a timeout cannot block the rest) tells the owner that this rank's
@@ -221,22 +296,47 @@ __device__ __forceinline__ void rs_reducer(const RsArgs& a, int N) {
     const int cols = min(BN, N - tn * BN);
     const int vec_per_row = cols / 8;
     const __nv_bfloat16* st = reinterpret_cast<const __nv_bfloat16*>(h.window[h.rank] + a.staging_off);
-    for (int i = threadIdx.x; i < rows * vec_per_row; i += blockDim.x) {
-      const int r = i / vec_per_row, c = (i % vec_per_row) * 8;
-      const size_t row = static_cast<size_t>(tm) * GEMM_BM + r;
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int src = 0; src < h.nranks; ++src) {
-        const uint4 v = *reinterpret_cast<const uint4*>(st + (static_cast<size_t>(src) * a.rows_per_shard + row) * N + tn * BN + c);
-        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+    constexpr int U = 8;  // independent 16-byte loads in flight per thread and source
+    const int nvec = rows * vec_per_row;
+    for (int i0 = threadIdx.x; i0 < nvec; i0 += blockDim.x * U) {
+      float acc[U][8];
+      size_t off[U];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          acc[2 * j] += __low2float(p[j]);
-          acc[2 * j + 1] += __high2float(p[j]);
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + u * blockDim.x;
+        const int r = i / vec_per_row, c = (i - r * vec_per_row) * 8;
+        off[u] = (static_cast<size_t>(tm) * GEMM_BM + r) * N + tn * BN + c;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+      }
+      for (int src = 0; src < h.nranks; ++src) {
+        const __nv_bfloat16* sp = st + static_cast<size_t>(src) * a.rows_per_shard * N;
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * blockDim.x < nvec) v[u] = *reinterpret_cast<const uint4*>(sp + off[u]);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[u][2 * j] += __low2float(p[j]);
+            acc[u][2 * j + 1] += __high2float(p[j]);
+          }
         }
       }
-      uint4 o = make_uint4(pack_bf16x2(acc[0] * a.scale, acc[1] * a.scale), pack_bf16x2(acc[2] * a.scale, acc[3] * a.scale),
-                           pack_bf16x2(acc[4] * a.scale, acc[5] * a.scale), pack_bf16x2(acc[6] * a.scale, acc[7] * a.scale));
-      *reinterpret_cast<uint4*>(a.out + row * a.ld_out + tn * BN + c) = o;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i >= nvec) continue;
+        const int r = i / vec_per_row, c = (i - r * vec_per_row) * 8;
+        const size_t row = static_cast<size_t>(tm) * GEMM_BM + r;
+        const uint4 o = make_uint4(pack_bf16x2(acc[u][0] * a.scale, acc[u][1] * a.scale),
+                                   pack_bf16x2(acc[u][2] * a.scale, acc[u][3] * a.scale),
+                                   pack_bf16x2(acc[u][4] * a.scale, acc[u][5] * a.scale),
+                                   pack_bf16x2(acc[u][6] * a.scale, acc[u][7] * a.scale));
+        *reinterpret_cast<uint4*>(a.out + row * a.ld_out + tn * BN + c) = o;
+      }
     }
     __syncthreads();
   }
@@ -255,7 +355,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   __shared__ unsigned int epi_warp_count[4];
   if (threadIdx.x < 4) epi_warp_count[threadIdx.x] = 0;
   __syncthreads();
-  PushEpilogue<BN> epi{args.h, args.staging_off, args.rows_per_shard, args.tiles_per_shard_m, shape.N, 0, 0, epi_warp_count, 0, args.epoch};
+  PushEpilogue<BN> epi{args.h, args.staging_off, args.rows_per_shard, args.tiles_per_shard_m, shape.N, 0, 0,
+                       epi_warp_count, 0, args.epoch, smem_raw + GemmSmem<BN>::TOTAL};
   NoGate gate;
   gemm_mainloop<BN, false, B_MN>(&tmA, &tmB, shape, epi, gate, args.h.status, smem_raw);
 }
@@ -372,7 +473,7 @@ int b200_gemm_rs(int comm, const void* A, long long lda, const void* B, long lon
   if (!hp || comm < 0 || comm >= 64) return B200_ERR_BAD_ARG;
   GinDevHandle h = *hp;
   constexpr int BN = 256;
-  if (M % (GEMM_BM * h.nranks) || K % 8 || N % 32 || !A || !B || !out) return B200_ERR_BAD_ARG;
+  if (M % (GEMM_BM * h.nranks) || K % 8 || N % 64 || !A || !B || !out) return B200_ERR_BAD_ARG;
   const size_t staging_bytes = static_cast<size_t>(M) * N * 2;
   if (staging_off % 16 || staging_off + staging_bytes > h.window_bytes) return B200_ERR_BAD_ARG;
   GemmShape shape{M, N, K, M / GEMM_BM, (N + BN - 1) / BN};
@@ -394,7 +495,7 @@ int b200_gemm_rs(int comm, const void* A, long long lda, const void* B, long lon
               static_cast<__nv_bfloat16*>(out), ld_out, scale};
   const int grid = n_reducers + shape.num_ctas;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int smem = GemmSmem<BN>::TOTAL;
+  const int smem = GemmSmem<BN>::TOTAL + 4 * 4096;  // + one transpose buffer per epilogue warp
   if (b_mn) {
     auto k = gemm_rs_kernel<BN, true>;
     if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
