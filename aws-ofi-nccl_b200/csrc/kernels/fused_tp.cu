@@ -6,11 +6,11 @@
 //             in the order the chunks arrive (own shard first) and their TMA producer waits on the
 //             flag of the chunk it is about to load. Remote data crosses NVLink exactly once and
 //             is always TMA-loaded from local memory.
-//  gemm_rs  : tcgen05 GEMM -> reduce-scatter. The epilogue stores each finished tile straight
-//             into the owning rank's staging slot (peer stores) and sets its per-tile arrival
-//             flag there (release-ordered remote store); "reducer" CTAs on the owner wait for
-//             all contributions of a tile and sum them in fp32. Ranks walk the shards in rotated
-//             order so that no GPU's NVLink ingress is hit by everyone at once.
+//  gemm_rs  : tcgen05 GEMM -> reduce-scatter as a ring inside the epilogue: every finished tile is
+//             added to the running sum received from the next rank and stored straight into the
+//             previous rank's staging slot (peer stores + a release-ordered flag); the last hop
+//             writes the result. All SMs run the GEMM, the traffic is spread over the whole
+//             kernel, and no GPU's NVLink ingress is hit by everyone at once.
 //
 // Every wait is bounded (status word + early exit), none of the loads uses cluster multicast.
 #include <cuda_bf16.h>
@@ -29,7 +29,7 @@ const GinDevHandle* comm_handle(int id);  // collectives.cu
 // Every flag holds the number of the call (per communicator, counted on the host) that last set
 // it, so nothing is ever reset and calls of different shapes can follow one another.
 constexpr size_t TP_READY_OFF = GIN_PAD_SCRATCH_OFF;                    // [4096] chunk-ready flags (ag_gemm)
-constexpr size_t TP_ARRIVED_OFF = GIN_PAD_SCRATCH_OFF + 4096 * 4;       // [16384][src rank] tile arrival flags (gemm_rs)
+constexpr size_t TP_ARRIVED_OFF = GIN_PAD_SCRATCH_OFF + 4096 * 4;       // [ring step][tile of a shard] arrival flags (gemm_rs)
 constexpr int TP_MAX_CHUNKS = 4096;
 constexpr int TP_MAX_TILES = 16384;
 static_assert(TP_ARRIVED_OFF + size_t(TP_MAX_TILES) * GIN_MAX_RANKS * 4 <= GIN_PAD_BYTES, "pad too small");
@@ -186,13 +186,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 }
 
 // ------------------------------------------------------------------------------------------ gemm_rs
+// Ring reduce-scatter carried by the GEMM epilogue. Rank r walks the shards r+1, r+2, ..., r
+// (its own last). At step k it computes its partial tile of shard r+1+k, adds the running sum that
+// rank r+1 pushed for the same tile one step earlier, and either pushes the new sum to rank r-1
+// (peer stores + a release-ordered flag) or, at the last step, scales and writes the result.
+// Neighbours run one step apart, so an incoming tile has normally landed long before it is
+// needed; the wait on its flag is bounded all the same. The staging area is double-buffered by
+// call parity, which makes the kernel free of cross-GPU barriers: a rank can run at most one call
+// ahead of its ring neighbour.
 struct RsArgs {
   GinDevHandle h;
-  size_t staging_off;       // window offset of the staging area: [src rank][rows_per_shard][N] bf16
+  size_t staging_off;       // window offset: [parity 2][step n-1][rows_per_shard][N] bf16
   int rows_per_shard;       // M / nranks
   int tiles_per_shard_m;
-  int n_reducers;
-  int channel;
   uint32_t epoch;
   __nv_bfloat16* out;       // [rows_per_shard][N] on this rank
   int64_t ld_out;
@@ -200,163 +206,132 @@ struct RsArgs {
 };
 
 template <int BN>
-struct PushEpilogue {
+struct RingEpilogue {
   static constexpr bool kPair = true;   // called with 64 consecutive columns per row
-  GinDevHandle h;
-  size_t staging_off;
-  int rows_per_shard, tiles_per_shard_m, N;
-  int owner, row_base;
+  RsArgs a;
+  int N, tiles_n;
   // Shared-memory counters of epilogue warps that finished a tile, indexed by (tile sequence & 3):
   // with two accumulator buffers a warp can run at most two tiles ahead of the slowest one, so
   // four counters never mix tiles.
   unsigned int* warp_count;
-  unsigned int seq;
-  uint32_t epoch;
   uint8_t* stage;  // 4 KiB of shared memory per epilogue warp: 32 rows x 128 B, 16-byte chunks XOR-swizzled by row
-  __device__ __forceinline__ void tile_begin(int tm, int) {
-    owner = tm / tiles_per_shard_m;
-    row_base = owner * rows_per_shard;
+  unsigned int seq;
+  int step, row_base, tile_in_shard;
+  bool have_in;
+
+  __device__ __forceinline__ size_t slot_elems() const { return static_cast<size_t>(a.rows_per_shard) * N; }
+  __device__ __forceinline__ __nv_bfloat16* staging(int rank, int slot) const {
+    const size_t parity_elems = static_cast<size_t>(a.h.nranks - 1) * slot_elems();
+    return reinterpret_cast<__nv_bfloat16*>(a.h.window[rank] + a.staging_off) + (a.epoch & 1u) * parity_elems +
+           static_cast<size_t>(slot) * slot_elems();
   }
-  // Each lane arrives with one accumulator row. The warp transposes through shared memory so that
-  // every store instruction writes four complete 128-byte row segments: stores that cross NVLink
-  // as full lines instead of 32 scattered 16-byte pieces.
-  __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&a0)[32], const uint32_t (&a1)[32],
-                                             const GemmShape& s) {
+  __device__ __forceinline__ uint32_t* flag(int rank, int slot) const {
+    return reinterpret_cast<uint32_t*>(a.h.pad[rank] + TP_ARRIVED_OFF) +
+           static_cast<size_t>(slot) * a.tiles_per_shard_m * tiles_n + tile_in_shard;
+  }
+
+  __device__ __forceinline__ void tile_begin(int tm, int tn) {
+    const int n = a.h.nranks;
+    const int shard = tm / a.tiles_per_shard_m;
+    step = (shard - a.h.rank - 1 + 2 * n) % n;
+    row_base = shard * a.rows_per_shard;
+    tile_in_shard = (tm - shard * a.tiles_per_shard_m) * tiles_n + tn;
+    have_in = false;
+    if (step > 0) {
+      int ok = 1;
+      if ((threadIdx.x & 31) == 0) ok = gin_spin_u32_ge(a.h, flag(a.h.rank, step - 1), a.epoch, DEV_ERR_SIGNAL_TIMEOUT) ? 1 : 0;
+      have_in = __shfl_sync(0xffffffffu, ok, 0) != 0;  // on a timeout the tile goes on without the missing sum
+    }
+  }
+
+  __device__ __forceinline__ void operator()(int row, int col0, uint32_t (&a0)[32], uint32_t (&a1)[32], const GemmShape& s) {
     if (col0 >= s.N) return;  // uniform over the warp
     const int lane = threadIdx.x & 31;
     uint8_t* buf = stage + ((threadIdx.x >> 5) - 2) * 4096;
+    const int row0 = row - lane;  // first row of this warp's 32-row slab
+    const size_t slab = static_cast<size_t>(row0 - row_base) * N + col0;
+    const int c = lane & 7;
+    if (have_in) {
+      // coalesced read of the incoming 32 x 64 slab (four full 128-byte row segments per load)
+      const __nv_bfloat16* in = staging(a.h.rank, step - 1) + slab;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint4 v = make_uint4(pack_bf16x2(__uint_as_float(a0[8 * j]), __uint_as_float(a0[8 * j + 1])),
-                                 pack_bf16x2(__uint_as_float(a0[8 * j + 2]), __uint_as_float(a0[8 * j + 3])),
-                                 pack_bf16x2(__uint_as_float(a0[8 * j + 4]), __uint_as_float(a0[8 * j + 5])),
-                                 pack_bf16x2(__uint_as_float(a0[8 * j + 6]), __uint_as_float(a0[8 * j + 7])));
+      for (int i = 0; i < 8; ++i) {
+        const int r = 4 * i + (lane >> 3);
+        const uint4 v = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * N + c * 8);
+        *reinterpret_cast<uint4*>(buf + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+      }
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint4 v = *reinterpret_cast<const uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4));
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+        uint32_t* acc = j < 4 ? &a0[8 * j] : &a1[8 * (j - 4)];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          acc[2 * q] = __float_as_uint(__uint_as_float(acc[2 * q]) + __low2float(p[q]));
+          acc[2 * q + 1] = __float_as_uint(__uint_as_float(acc[2 * q + 1]) + __high2float(p[q]));
+        }
+      }
+      __syncwarp();
+    }
+    const bool last = step == a.h.nranks - 1;
+    const float sc = last ? a.scale : 1.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t* acc = j < 4 ? &a0[8 * j] : &a1[8 * (j - 4)];
+      const uint4 v = make_uint4(pack_bf16x2(__uint_as_float(acc[0]) * sc, __uint_as_float(acc[1]) * sc),
+                                 pack_bf16x2(__uint_as_float(acc[2]) * sc, __uint_as_float(acc[3]) * sc),
+                                 pack_bf16x2(__uint_as_float(acc[4]) * sc, __uint_as_float(acc[5]) * sc),
+                                 pack_bf16x2(__uint_as_float(acc[6]) * sc, __uint_as_float(acc[7]) * sc));
       *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
     }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint4 v = make_uint4(pack_bf16x2(__uint_as_float(a1[8 * j]), __uint_as_float(a1[8 * j + 1])),
-                                 pack_bf16x2(__uint_as_float(a1[8 * j + 2]), __uint_as_float(a1[8 * j + 3])),
-                                 pack_bf16x2(__uint_as_float(a1[8 * j + 4]), __uint_as_float(a1[8 * j + 5])),
-                                 pack_bf16x2(__uint_as_float(a1[8 * j + 6]), __uint_as_float(a1[8 * j + 7])));
-      *reinterpret_cast<uint4*>(buf + lane * 128 + (((j + 4) ^ (lane & 7)) << 4)) = v;
-    }
     __syncwarp();
-    // my contribution goes to slot `rank` of the owner's staging area
-    const int row0 = row - lane;  // first row of this warp's 32-row slab
-    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(h.window[owner] + staging_off) +
-                          (static_cast<size_t>(h.rank) * rows_per_shard + (row0 - row_base)) * N + col0;
-    const int c = lane & 7;
+    __nv_bfloat16* dst;
+    int64_t ld;
+    if (last) {
+      dst = a.out + static_cast<int64_t>(row0 - row_base) * a.ld_out + col0;
+      ld = a.ld_out;
+    } else {
+      const int prev = (a.h.rank + a.h.nranks - 1) % a.h.nranks;
+      dst = staging(prev, step) + slab;
+      ld = N;
+    }
+    // every store instruction writes four complete 128-byte row segments
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int r = 4 * i + (lane >> 3);
       const uint4 v = *reinterpret_cast<const uint4*>(buf + r * 128 + ((c ^ (r & 7)) << 4));
-      *reinterpret_cast<uint4*>(base + static_cast<size_t>(r) * N + c * 8) = v;
+      *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(r) * ld + c * 8) = v;
     }
     __syncwarp();
   }
+
   // Called by every epilogue thread. The warp that arrives last (no warp ever waits for another,
-  // so a warp that gave up on a timeout cannot block the rest) tells the owner that this rank's
-  // contribution to the tile is complete.
-  __device__ __forceinline__ void tile_end(int tm, int tn) {
+  // so a warp that gave up on a timeout cannot block the rest) tells the previous rank that the
+  // running sum of this tile is complete in its staging slot.
+  __device__ __forceinline__ void tile_end(int, int) {
     __syncwarp();
-    if ((threadIdx.x & 31) == 0) {
+    if (step != a.h.nranks - 1 && (threadIdx.x & 31) == 0) {
       fence_acq_rel_sys();  // this warp's peer stores are performed before the count moves
-      const unsigned int prev = atomicAdd(warp_count + (seq & 3u), 1u);
-      if ((prev & 3u) == 3u) {
-        const int tiles_n = (N + BN - 1) / BN;
-        const int t = (tm - owner * tiles_per_shard_m) * tiles_n + tn;
-        uint32_t* flag = reinterpret_cast<uint32_t*>(h.pad[owner] + TP_ARRIVED_OFF) + t * GIN_MAX_RANKS + h.rank;
-        st_release_sys_u32(flag, epoch);
+      const unsigned int prev_count = atomicAdd(warp_count + (seq & 3u), 1u);
+      if ((prev_count & 3u) == 3u) {
+        const int prev = (a.h.rank + a.h.nranks - 1) % a.h.nranks;
+        st_release_sys_u32(flag(prev, step), a.epoch);
       }
     }
     ++seq;
   }
 };
 
-template <int BN>
-__device__ __forceinline__ void rs_reducer(const RsArgs& a, int N) {
-  const GinDevHandle& h = a.h;
-  if (!gin_barrier(h, a.channel, blockIdx.x)) return;  // staging areas are free, counters consistent
-  const int tiles_n = (N + BN - 1) / BN;
-  const int ntiles = a.tiles_per_shard_m * tiles_n;
-  const uint32_t* arrived = reinterpret_cast<const uint32_t*>(h.pad[h.rank] + TP_ARRIVED_OFF);
-  __shared__ int ok;
-  if (threadIdx.x == 0) ok = 1;
-  __syncthreads();
-  for (int t = blockIdx.x; t < ntiles; t += a.n_reducers) {
-    // one thread per source rank waits for that rank's contribution to the tile
-    if (static_cast<int>(threadIdx.x) < h.nranks &&
-        !gin_spin_u32_ge(h, arrived + t * GIN_MAX_RANKS + threadIdx.x, a.epoch, DEV_ERR_SIGNAL_TIMEOUT))
-      ok = 0;
-    __syncthreads();
-    if (!ok) break;
-    const int tm = t / tiles_n, tn = t % tiles_n;
-    const int rows = min(GEMM_BM, a.rows_per_shard - tm * GEMM_BM);
-    const int cols = min(BN, N - tn * BN);
-    const int vec_per_row = cols / 8;
-    const __nv_bfloat16* st = reinterpret_cast<const __nv_bfloat16*>(h.window[h.rank] + a.staging_off);
-    constexpr int U = 8;  // independent 16-byte loads in flight per thread and source
-    const int nvec = rows * vec_per_row;
-    for (int i0 = threadIdx.x; i0 < nvec; i0 += blockDim.x * U) {
-      float acc[U][8];
-      size_t off[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int i = i0 + u * blockDim.x;
-        const int r = i / vec_per_row, c = (i - r * vec_per_row) * 8;
-        off[u] = (static_cast<size_t>(tm) * GEMM_BM + r) * N + tn * BN + c;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
-      }
-      for (int src = 0; src < h.nranks; ++src) {
-        const __nv_bfloat16* sp = st + static_cast<size_t>(src) * a.rows_per_shard * N;
-        uint4 v[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (i0 + u * blockDim.x < nvec) v[u] = *reinterpret_cast<const uint4*>(sp + off[u]);
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            acc[u][2 * j] += __low2float(p[j]);
-            acc[u][2 * j + 1] += __high2float(p[j]);
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int i = i0 + u * blockDim.x;
-        if (i >= nvec) continue;
-        const int r = i / vec_per_row, c = (i - r * vec_per_row) * 8;
-        const size_t row = static_cast<size_t>(tm) * GEMM_BM + r;
-        const uint4 o = make_uint4(pack_bf16x2(acc[u][0] * a.scale, acc[u][1] * a.scale),
-                                   pack_bf16x2(acc[u][2] * a.scale, acc[u][3] * a.scale),
-                                   pack_bf16x2(acc[u][4] * a.scale, acc[u][5] * a.scale),
-                                   pack_bf16x2(acc[u][6] * a.scale, acc[u][7] * a.scale));
-        *reinterpret_cast<uint4*>(a.out + row * a.ld_out + tn * BN + c) = o;
-      }
-    }
-    __syncthreads();
-  }
-  gin_barrier(h, a.channel, blockIdx.x);  // every rank has consumed its staging area
-}
-
 template <int BN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmShape shape,
                    RsArgs args) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  if (static_cast<int>(blockIdx.x) < args.n_reducers) {
-    rs_reducer<BN>(args, shape.N);
-    return;
-  }
   __shared__ unsigned int epi_warp_count[4];
   if (threadIdx.x < 4) epi_warp_count[threadIdx.x] = 0;
   __syncthreads();
-  PushEpilogue<BN> epi{args.h, args.staging_off, args.rows_per_shard, args.tiles_per_shard_m, shape.N, 0, 0,
-                       epi_warp_count, 0, args.epoch, smem_raw + GemmSmem<BN>::TOTAL};
+  RingEpilogue<BN> epi{args, shape.N, shape.tiles_n, epi_warp_count, smem_raw + GemmSmem<BN>::TOTAL, 0, 0, 0, 0, false};
   NoGate gate;
   gemm_mainloop<BN, false, B_MN>(&tmA, &tmB, shape, epi, gate, args.h.status, smem_raw);
 }
@@ -464,26 +439,27 @@ int b200_ag_gemm(int comm, size_t gathered_off, int gather_b, int M, int N, int 
 }
 
 // out[M/n, N] (this rank's rows) = scale * sum over ranks of (A_r[M,K] * B_r^T)[rows of this rank].
-// staging_off: window offset of nranks * (M/n) * N bf16 of staging space on every rank.
+// staging_off: window offset of 2 * (nranks-1) * (M/nranks) * N bf16 of staging space on every rank
+// (b200_gemm_rs_staging_bytes). The running sums are rounded to bf16 at every hop of the ring.
+size_t b200_gemm_rs_staging_bytes(int nranks, int M, int N) {
+  return nranks <= 1 ? 0 : 2ull * (nranks - 1) * (static_cast<size_t>(M) / nranks) * N * 2;
+}
+
 int b200_gemm_rs(int comm, const void* A, long long lda, const void* B, long long ldb, int b_mn, int M, int N, int K,
-                 size_t staging_off, void* out, long long ld_out, float scale, int n_reducers, int channel,
-                 void* stream) {
+                 size_t staging_off, void* out, long long ld_out, float scale, void* stream) {
   ensure_context();
   const GinDevHandle* hp = comm_handle(comm);
   if (!hp || comm < 0 || comm >= 64) return B200_ERR_BAD_ARG;
   GinDevHandle h = *hp;
   constexpr int BN = 256;
-  if (M % (GEMM_BM * h.nranks) || K % 8 || N % 64 || !A || !B || !out) return B200_ERR_BAD_ARG;
-  const size_t staging_bytes = static_cast<size_t>(M) * N * 2;
-  if (staging_off % 16 || staging_off + staging_bytes > h.window_bytes) return B200_ERR_BAD_ARG;
+  if (M % (GEMM_BM * h.nranks) || K % 8 || N % 64 || !A || !B || !out || ld_out % 8) return B200_ERR_BAD_ARG;
+  if (staging_off % 16 || staging_off + b200_gemm_rs_staging_bytes(h.nranks, M, N) > h.window_bytes) return B200_ERR_BAD_ARG;
   GemmShape shape{M, N, K, M / GEMM_BM, (N + BN - 1) / BN};
   const int tiles_per_shard_m = shape.tiles_m / h.nranks;
-  if (tiles_per_shard_m * shape.tiles_n > TP_MAX_TILES) return B200_ERR_TOO_LARGE;
-  if (n_reducers <= 0) n_reducers = 16;
+  if (static_cast<size_t>(h.nranks - 1) * tiles_per_shard_m * shape.tiles_n > static_cast<size_t>(TP_MAX_TILES) * GIN_MAX_RANKS)
+    return B200_ERR_TOO_LARGE;
   const int sms = sm_count();
-  shape.cta_first = n_reducers;
-  shape.num_ctas = sms - n_reducers;
-  if (shape.num_ctas > shape.tiles_m * shape.tiles_n) shape.num_ctas = shape.tiles_m * shape.tiles_n;
+  shape.num_ctas = sms < shape.tiles_m * shape.tiles_n ? sms : shape.tiles_m * shape.tiles_n;
   shape.m_rot = ((h.rank + 1) % h.nranks) * tiles_per_shard_m;  // next rank's rows first, own rows last
   shape.m_major = 1;
   CUtensorMap tmA, tmB;
@@ -491,19 +467,18 @@ int b200_gemm_rs(int comm, const void* A, long long lda, const void* B, long lon
   if (rc) return rc;
   rc = b_mn ? make_tmap_2d(&tmB, B, K, N, ldb, GEMM_BK, 64, 2, true) : make_tmap_2d(&tmB, B, N, K, ldb, BN, GEMM_BK, 2, true);
   if (rc) return rc;
-  RsArgs args{h, staging_off, M / h.nranks, tiles_per_shard_m, n_reducers, channel, ++g_rs_epoch[comm],
-              static_cast<__nv_bfloat16*>(out), ld_out, scale};
-  const int grid = n_reducers + shape.num_ctas;
+  RsArgs args{h, staging_off, M / h.nranks, tiles_per_shard_m, ++g_rs_epoch[comm], static_cast<__nv_bfloat16*>(out), ld_out,
+              scale};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int smem = GemmSmem<BN>::TOTAL + 4 * 4096;  // + one transpose buffer per epilogue warp
   if (b_mn) {
     auto k = gemm_rs_kernel<BN, true>;
     if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
-    k<<<grid, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args);
+    k<<<shape.num_ctas, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args);
   } else {
     auto k = gemm_rs_kernel<BN, false>;
     if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
-    k<<<grid, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args);
+    k<<<shape.num_ctas, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args);
   }
   B200_CUDA_OK(cudaGetLastError());
   return 0;

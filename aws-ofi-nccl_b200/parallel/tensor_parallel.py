@@ -23,7 +23,9 @@ from .symm import Communicator
 
 _vp, _i, _sz, _f, _ll = C.c_void_p, C.c_int, C.c_size_t, C.c_float, C.c_longlong
 _lib.register("b200_ag_gemm", [_i, _sz, _i, _i, _i, _i, _vp, _ll, _i, _vp, _ll, _vp, _ll, _i, _i, _i, _vp], _i)
-_lib.register("b200_gemm_rs", [_i, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _sz, _vp, _ll, _f, _i, _i, _vp], _i)
+_lib.register("b200_gemm_rs", [_i, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _sz, _vp, _ll, _f, _vp], _i)
+_lib.register("b200_gemm_rs_staging_bytes", [_i, _i, _i], _sz)
+_lib.set_kernels_per_call("b200_gemm_rs_staging_bytes", 0)
 
 TP_CHANNEL = 2  # barrier slots used by the fused kernels (0: default collectives, 1: gradient reducer)
 
@@ -71,19 +73,24 @@ def ag_gemm(comm: Communicator, gathered_off: int, rows: int, k: int, other: tor
     _lib.check(rc, "b200_ag_gemm")
 
 
+def gemm_rs_staging_bytes(world: int, m: int, n: int) -> int:
+    """Window bytes ``gemm_rs`` needs at ``staging_off`` on every rank (two call parities of the
+    world-1 ring hops)."""
+    return 0 if world <= 1 else 2 * (world - 1) * (m // world) * n * 2
+
+
 def gemm_rs(comm: Communicator, a: torch.Tensor, b: torch.Tensor, staging_off: int, out: torch.Tensor, *,
-            b_mn: bool = False, scale: float = 1.0, n_reducers: int = 0, channel: int = TP_CHANNEL) -> None:
-    """One kernel: partial = a[M,K] @ op(b), reduce-scatter over ranks along M;
-    out[M/world, N] = scale * sum_r partial_r[rows of this rank].  ``staging_off`` names M*N bf16
-    of window space on every rank."""
+            b_mn: bool = False, scale: float = 1.0) -> None:
+    """One kernel: partial = a[M,K] @ op(b), ring reduce-scatter over ranks along M inside the GEMM
+    epilogue; out[M/world, N] = scale * sum_r partial_r[rows of this rank].  ``staging_off`` names
+    ``gemm_rs_staging_bytes`` of window space on every rank."""
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.stride(1) == 1 and b.stride(1) == 1
     M, K = a.shape
     N = b.shape[1] if b_mn else b.shape[0]
     assert (b.shape[0] if b_mn else b.shape[1]) == K
     assert out.shape == (M // comm.world, N) and out.dtype == torch.bfloat16 and out.stride(1) == 1
     rc = _lib.load().b200_gemm_rs(comm.id, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), int(b_mn), M, N, K,
-                                  staging_off, out.data_ptr(), out.stride(0), scale, n_reducers, channel,
-                                  _lib.stream_ptr())
+                                  staging_off, out.data_ptr(), out.stride(0), scale, _lib.stream_ptr())
     _lib.check(rc, "b200_gemm_rs")
 
 
@@ -102,7 +109,7 @@ class _TPMlpFn(torch.autograd.Function):
         act = torch.empty((T, Fl), device=x_shard.device, dtype=torch.bfloat16)
         ag_gemm(comm, mlp.x_off, T, H, w_gu, out=gu, act=act, swiglu=True, n_movers=mlp.n_helpers)
         y_shard = torch.empty((Ts, H), device=x_shard.device, dtype=torch.bfloat16)
-        gemm_rs(comm, act, w_down, mlp.stage_off, y_shard, n_reducers=mlp.n_helpers)
+        gemm_rs(comm, act, w_down, mlp.stage_off, y_shard)
         ctx.mlp = mlp
         ctx.save_for_backward(gu, act, w_gu, w_down)
         return y_shard
@@ -124,7 +131,7 @@ class _TPMlpFn(torch.autograd.Function):
                                                            _lib.stream_ptr()), "swiglu_bwd_interleaved")
         # dx[T/n,H] = reduce_scatter(dgu[T,2Fl] @ w_gu[2Fl,H])   (w_gu is stored [K=2Fl][N=H])
         dx_shard = torch.empty((Ts, H), device=dy_shard.device, dtype=torch.bfloat16)
-        gemm_rs(comm, dgu, w_gu, mlp.stage_off, dx_shard, b_mn=True, n_reducers=mlp.n_helpers)
+        gemm_rs(comm, dgu, w_gu, mlp.stage_off, dx_shard, b_mn=True)
         # dW_gu[2Fl,H] = dgu^T @ x_full
         _accumulate_wgrad(w_gu, dgu, mlp.x_full)
         return dx_shard, None, None, None
@@ -162,7 +169,7 @@ class TensorParallelMLP(torch.nn.Module):
         self.x_off = _align(window_offset)
         self.dy_off = _align(self.x_off + act_bytes)
         self.stage_off = _align(self.dy_off + act_bytes)
-        self.window_end = self.stage_off + act_bytes
+        self.window_end = self.stage_off + gemm_rs_staging_bytes(comm.world, tokens, hidden)
         assert self.window_end <= comm.window.chunk, "communicator window too small for this layer"
         self.x_full = comm.view(self.x_off, tokens * hidden, torch.bfloat16).view(tokens, hidden)
         self.dy_full = comm.view(self.dy_off, tokens * hidden, torch.bfloat16).view(tokens, hidden)
@@ -178,7 +185,7 @@ class TensorParallelMLP(torch.nn.Module):
 
     @staticmethod
     def window_bytes(tokens: int, hidden: int) -> int:
-        return 3 * _align(tokens * hidden * 2) + 1024
+        return 4 * _align(tokens * hidden * 2) + 1024
 
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
         return _TPMlpFn.apply(x_shard, self.w_gate_up, self.w_down, self)

@@ -68,7 +68,7 @@ def main() -> None:
     ap.add_argument("--ffn", type=int, default=14336)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--helpers", type=int, default=16, help="mover / reducer CTAs per fused kernel")
+    ap.add_argument("--helpers", type=int, default=16, help="mover CTAs of the all-gather kernels")
     ap.add_argument("--json")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -119,7 +119,7 @@ def main() -> None:
 
     # ---- GEMM -> reduce-scatter
     def fused_down():
-        tp.gemm_rs(comm, act, w_down, mlp.stage_off, y_shard, n_reducers=args.helpers)
+        tp.gemm_rs(comm, act, w_down, mlp.stage_off, y_shard)
 
     def base_down():
         torch.matmul(act, w_down.t(), out=y_full)

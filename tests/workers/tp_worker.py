@@ -84,11 +84,11 @@ def main():
         dist.all_reduce(ref_full)
         for rep in range(2):
             o = torch.empty(Ts, N, device=dev, dtype=torch.bfloat16)
-            tp.gemm_rs(comm, a, w, stage_off, o, n_reducers=4)
+            tp.gemm_rs(comm, a, w, stage_off, o)
             torch.cuda.synchronize()
             check(f"gemm_rs {M}x{N}x{K} rep{rep}", o, ref_full[rank * Ts:(rank + 1) * Ts])
         o = torch.empty(Ts, N, device=dev, dtype=torch.bfloat16)
-        tp.gemm_rs(comm, a, wt, stage_off, o, b_mn=True, scale=0.5, n_reducers=4)
+        tp.gemm_rs(comm, a, wt, stage_off, o, b_mn=True, scale=0.5)
         torch.cuda.synchronize()
         check(f"gemm_rs b_mn {M}x{N}x{K}", o, 0.5 * ref_full[rank * Ts:(rank + 1) * Ts])
         dist.barrier()
