@@ -35,6 +35,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   gemm_mainloop<BN, A_MN, B_MN>(&tmA, &tmB, shape, epi, gate, err_word, smem_raw);
 }
 
+// M tiles per raster group: the CTAs of one wave (one per SM) then cover a patch of about
+// group_m x (SMs / group_m) tiles, which is close to square in elements for the default value.
+// B200_GEMM_GROUP_M overrides it (0 = plain column-major walk).
+static int gemm_group_m(int bn) {
+  static int override_value = -2;
+  if (override_value == -2) {
+    const char* e = getenv("B200_GEMM_GROUP_M");
+    override_value = e ? atoi(e) : -1;
+  }
+  if (override_value >= 0) return override_value;
+  return bn == 256 ? 16 : 12;
+}
+
 template <int BN, bool A_MN, bool B_MN, typename OutT>
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
                        int64_t ldc, int accumulate, int max_ctas, cudaStream_t stream) {
@@ -51,6 +64,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
     rc = make_tmap_2d(&tmB, B, K, N, ldb, GEMM_BK, 64, 2, true);
   if (rc) return rc;
   GemmShape shape{M, N, K, (M + GEMM_BM - 1) / GEMM_BM, (N + BN - 1) / BN};
+  shape.group_m = gemm_group_m(BN);
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OutT>;
   static bool attr_set = false;
   if (!attr_set) {

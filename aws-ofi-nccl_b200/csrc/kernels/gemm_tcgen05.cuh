@@ -34,15 +34,25 @@ struct GemmShape {
   int m_rot = 0;       // tile_m = (raw + m_rot) % tiles_m
   int m_major = 0;     // 1: walk all N tiles of an M tile before the next M tile
   int n_rot = 0;       // tile_n = (raw + n_rot) % tiles_n
+  int group_m = 0;     // default order only: M tiles are walked in groups of this many (0 = all)
 };
 
-// The tile id -> (tile_m, tile_n) map. Default: M fastest, so consecutive CTAs share the same B
-// (weight) tile. m_major: N fastest, so that M tiles finish (or are needed) one after another.
+// The tile id -> (tile_m, tile_n) map. Default: M fastest inside a group of group_m M tiles, so
+// the CTAs that run together cover a roughly square patch of C and share both their A and their B
+// tiles in L2. m_major: N fastest, so that M tiles finish (or are needed) one after another.
 __device__ __forceinline__ void tile_coords(const GemmShape& s, int tile, int& tm, int& tn) {
   int raw_m;
   if (s.m_major) {
     raw_m = tile / s.tiles_n;
     tn = tile % s.tiles_n;
+  } else if (s.group_m > 0 && s.group_m < s.tiles_m) {
+    const int per_group = s.group_m * s.tiles_n;
+    const int g = tile / per_group;
+    const int first_m = g * s.group_m;
+    const int gsize = min(s.group_m, s.tiles_m - first_m);
+    const int in = tile - g * per_group;
+    tn = in / gsize;
+    raw_m = first_m + (in - tn * gsize);
   } else {
     raw_m = tile % s.tiles_m;
     tn = tile / s.tiles_m;

@@ -1,6 +1,6 @@
 """GEMM micro-benchmark: the tcgen05 kernel vs torch.matmul (cuBLAS) on the Llama-3-8B shapes.
 
-    python -m aws_ofi_nccl_b200.utils.bench_gemm [--json out.json] [--small]
+    python -m aws_ofi_nccl_b200.utils.bench_gemm [--json out.json] [--small] [--shape M N K]
 
 Times each shape with CUDA events (warm-up, L2 flushed between iterations) and reports TFLOP/s and
 the fraction of the measured cuBLAS peak from MEASURED_PEAKS.json when that file is present.
@@ -69,8 +69,13 @@ def main() -> None:
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), help="time this one shape only")
     args = ap.parse_args()
-    rows = run(SMALL_SHAPES if args.small else LLAMA_SHAPES, iters=args.iters, bn=args.bn)
+    if args.shape:
+        shapes = [("custom", *args.shape, False, False)]
+    else:
+        shapes = SMALL_SHAPES if args.small else LLAMA_SHAPES
+    rows = run(shapes, iters=args.iters, bn=args.bn)
     if args.json:
         with open(args.json, "w") as f:
             json.dump(rows, f, indent=1)
