@@ -78,3 +78,15 @@ def test_fused_tp_kernels_single_rank():
 def test_fused_tp_kernels_all_gpus():
     out = _run("tp_worker.py", min(_ngpus(), 8))
     assert "TP_WORKER_OK" in out
+
+
+@pytest.mark.skipif(_ngpus() < 1, reason="needs a GPU")
+def test_moe_dispatch_combine_single_rank():
+    out = _run("moe_worker.py", 1)
+    assert "MOE_WORKER_OK" in out
+
+
+@pytest.mark.skipif(_ngpus() < 2, reason="needs at least 2 GPUs")
+def test_moe_dispatch_combine_all_gpus():
+    out = _run("moe_worker.py", min(_ngpus(), 8))
+    assert "MOE_WORKER_OK" in out
