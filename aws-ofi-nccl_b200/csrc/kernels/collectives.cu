@@ -240,8 +240,8 @@ __global__ void __launch_bounds__(256) gin_pingpong_kernel(GinDevHandle h, size_
     ok = 1;
     gin_reset_signal(h, sig);
   }
-  if (!gin_barrier(h, GIN_NUM_CHANNELS - 1, 0)) return;
   const int peer = h.rank ^ 1;
+  if (!gin_barrier_pair(h, GIN_NUM_CHANNELS - 1, GIN_MAX_BLOCKS - 1, peer)) return;  // ranks 0 and 1 only
   const uint64_t t0 = globaltimer_ns();
   for (int i = 1; i <= iters && ok; ++i) {
     if (h.rank == 0) {

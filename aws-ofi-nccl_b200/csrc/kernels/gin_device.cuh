@@ -151,6 +151,26 @@ __device__ __forceinline__ bool gin_barrier(const GinDevHandle& h, int ch, int s
   return ok;
 }
 
+// Two-rank form: only this rank and `peer` meet (both must use the same channel and slot, and that
+// slot must not be used for full barriers).
+__device__ __forceinline__ bool gin_barrier_pair(const GinDevHandle& h, int ch, int slot, int peer) {
+  __shared__ int ok_pair;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const size_t idx = (static_cast<size_t>(ch) * GIN_MAX_BLOCKS + slot);
+    uint32_t* epoch = reinterpret_cast<uint32_t*>(h.pad[h.rank] + GIN_PAD_EPOCH_OFF) + idx;
+    const uint32_t target = *epoch + 1;
+    uint32_t* remote = reinterpret_cast<uint32_t*>(h.pad[peer] + GIN_PAD_FLAGS_OFF) + idx * GIN_MAX_RANKS + h.rank;
+    fence_acq_rel_sys();
+    red_release_sys_add_u32(remote, 1);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(h.pad[h.rank] + GIN_PAD_FLAGS_OFF) + idx * GIN_MAX_RANKS + peer;
+    ok_pair = gin_spin_u32_ge(h, mine, target, DEV_ERR_BARRIER_TIMEOUT) ? 1 : 0;
+    *epoch = target;
+  }
+  __syncthreads();
+  return ok_pair != 0;
+}
+
 // ---------------------------------------------------------------- put
 // Copy `bytes` from local `src` into peer's window at dst_off; all `nthreads` threads with index
 // `tid` take part (a warp: 32/lane, a CTA: blockDim/threadIdx). 16-byte vectors when both sides
