@@ -389,8 +389,13 @@ int b200_ag_gemm(int comm, size_t gathered_off, int gather_b, int M, int N, int 
     shape.n_rot = h.rank * chunks_per_shard;
     shape.m_major = 0;
   } else {
+    // groups of M tiles that never straddle a shard, M fastest inside a group: the CTAs of a wave
+    // share their weight tiles in L2 and still consume the shards in arrival order
     shape.m_rot = h.rank * chunks_per_shard;
-    shape.m_major = 1;
+    int gm = chunks_per_shard < 16 ? chunks_per_shard : 16;
+    while (chunks_per_shard % gm) --gm;
+    shape.group_m = gm;
+    if (gm >= shape.tiles_m) shape.m_major = 1;  // a single group: walk the N tiles of each M tile instead
   }
   CUtensorMap tmA, tmB;
   int rc;
