@@ -90,6 +90,24 @@ def _host_sources() -> list[Path]:
     return sorted(p for p in CSRC.rglob("*.cpp") if "tests" not in p.parts and "kernels" not in p.parts)
 
 
+def _embed_net_kernels(force: bool = False) -> Path:
+    """csrc/device/net_kernels.cu -> sm_100a cubin -> a byte list the plugin compiles in
+    (the plugin loads it with cuModuleLoadData; it links no CUDA library)."""
+    gen = OBJ / "gen"
+    gen.mkdir(parents=True, exist_ok=True)
+    src = CSRC / "device" / "net_kernels.cu"
+    cubin, inc = gen / "net_kernels.cubin", gen / "net_kernels_cubin.inc"
+    if force or _stale(inc, [src]):
+        try:
+            _run([NVCC, "-cubin", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
+                  str(src), "-o", str(cubin)])
+            data = cubin.read_bytes()
+        except (RuntimeError, OSError):
+            data = b"\0"   # no nvcc: the plugin then reports the kernels as unavailable and uses the copy engine
+        inc.write_text(",".join(str(b) for b in data) + "\n")
+    return gen
+
+
 def build_host(force: bool = False, sanitize: str | None = None) -> Path | None:
     """Compile the host plugin (C++20) and link the NCCL-loadable shared objects."""
     srcs = _host_sources()
@@ -99,7 +117,7 @@ def build_host(force: bool = False, sanitize: str | None = None) -> Path | None:
     tag = f"host-{sanitize}" if sanitize else "host"
     (OBJ / tag).mkdir(parents=True, exist_ok=True)
     hdrs = _headers()
-    flags = list(CXX_FLAGS)
+    flags = list(CXX_FLAGS) + ["-I", str(_embed_net_kernels(force))]
     if sanitize:
         flags += [f"-fsanitize={sanitize}", "-fno-omit-frame-pointer"]
     objs, jobs = [], []

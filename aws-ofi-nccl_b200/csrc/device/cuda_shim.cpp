@@ -40,6 +40,13 @@ struct Api {
   CUresult (*EventRecord)(CUevent, CUstream) = nullptr;
   CUresult (*EventQuery)(CUevent) = nullptr;
   CUresult (*MemcpyAsync)(CUdeviceptr, CUdeviceptr, size_t, CUstream) = nullptr;
+  CUresult (*ModuleLoadData)(CUmodule*, const void*) = nullptr;
+  CUresult (*ModuleUnload)(CUmodule) = nullptr;
+  CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+  CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
+                           void**, void**) = nullptr;
+  CUresult (*MemHostAlloc)(void**, size_t, unsigned) = nullptr;
+  CUresult (*MemFreeHost)(void*) = nullptr;
   CUresult (*MemAlloc)(CUdeviceptr*, size_t) = nullptr;
   CUresult (*MemFree)(CUdeviceptr) = nullptr;
   CUresult (*MemsetD8)(CUdeviceptr, unsigned char, size_t) = nullptr;
@@ -103,6 +110,12 @@ void do_init() {
   ok &= sym(g.EventRecord, "cuEventRecord");
   ok &= sym(g.EventQuery, "cuEventQuery");
   ok &= sym(g.MemcpyAsync, "cuMemcpyAsync");
+  sym(g.ModuleLoadData, "cuModuleLoadData", false);
+  sym(g.ModuleUnload, "cuModuleUnload", false);
+  sym(g.ModuleGetFunction, "cuModuleGetFunction", false);
+  sym(g.LaunchKernel, "cuLaunchKernel", false);
+  sym(g.MemHostAlloc, "cuMemHostAlloc", false);
+  sym(g.MemFreeHost, "cuMemFreeHost", false);
   ok &= sym(g.MemAlloc, "cuMemAlloc");
   ok &= sym(g.MemFree, "cuMemFree");
   ok &= sym(g.MemsetD8, "cuMemsetD8");
@@ -231,6 +244,34 @@ int event_query(Event e) {
   if (r == CUDA_ERROR_NOT_READY) return 1;
   return rc_of(r);
 }
+int module_load_data(const void* image, void** module) {
+  if (!available() || !g.ModuleLoadData) return -ENOSYS;
+  CUmodule m = nullptr;
+  const int rc = rc_of(g.ModuleLoadData(&m, image));
+  *module = m;
+  return rc;
+}
+int module_unload(void* module) {
+  return (available() && g.ModuleUnload) ? rc_of(g.ModuleUnload(static_cast<CUmodule>(module))) : -ENOSYS;
+}
+int module_get_function(void* module, const char* name, void** fn) {
+  if (!available() || !g.ModuleGetFunction) return -ENOSYS;
+  CUfunction f = nullptr;
+  const int rc = rc_of(g.ModuleGetFunction(&f, static_cast<CUmodule>(module), name));
+  *fn = f;
+  return rc;
+}
+int launch_kernel(void* fn, unsigned grid, unsigned block, unsigned smem_bytes, Stream s, void** args) {
+  if (!available() || !g.LaunchKernel) return -ENOSYS;
+  return rc_of(g.LaunchKernel(static_cast<CUfunction>(fn), grid, 1, 1, block, 1, 1, smem_bytes, static_cast<CUstream>(s), args,
+                              nullptr));
+}
+int host_alloc(void** ptr, size_t bytes) {
+  if (!available() || !g.MemHostAlloc) return -ENOSYS;
+  return rc_of(g.MemHostAlloc(ptr, bytes, CU_MEMHOSTALLOC_PORTABLE | CU_MEMHOSTALLOC_DEVICEMAP));
+}
+int host_free(void* ptr) { return (available() && g.MemFreeHost) ? rc_of(g.MemFreeHost(ptr)) : -ENOSYS; }
+
 int memcpy_async(void* dst, const void* src, size_t n, Stream s) {
   if (!available()) return -ENOSYS;
   return rc_of(g.MemcpyAsync(reinterpret_cast<CUdeviceptr>(dst), reinterpret_cast<CUdeviceptr>(src), n, static_cast<CUstream>(s)));

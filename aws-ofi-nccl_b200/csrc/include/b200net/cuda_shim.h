@@ -41,6 +41,15 @@ int event_query(Event e);  // 0 done, 1 not yet, <0 error
 int memcpy_async(void* dst, const void* src, size_t n, Stream s);  // unified addressing: any direction
 int stream_synchronize(Stream s);
 
+// Kernels from an embedded image: load into the current context, look up, launch.
+int module_load_data(const void* image, void** module);
+int module_unload(void* module);
+int module_get_function(void* module, const char* name, void** fn);
+int launch_kernel(void* fn, unsigned grid, unsigned block, unsigned smem_bytes, Stream s, void** args);
+// Page-locked host memory that the GPU can write (portable, mapped).
+int host_alloc(void** ptr, size_t bytes);
+int host_free(void* ptr);
+
 // Plain device allocation (IPC-exportable with ipc_get_handle), zero-filled.
 int mem_alloc(void** ptr, size_t bytes);
 int mem_free(void* ptr);

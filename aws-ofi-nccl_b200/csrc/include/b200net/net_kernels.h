@@ -1,0 +1,59 @@
+// Host side of the plugin's own device kernels (copy with completion flag, eager pack): loads the
+// embedded sm_100a image into the current CUDA context through the driver shim and hands out
+// completion slots in pinned host memory
+// (reference: the NIC performs these transfers, src/rdma/nccl_ofi_rdma.cpp post_rdma_write;
+//  completions arrive through the CQ, src/rdma/nccl_ofi_rdma.cpp process_completions).
+#pragma once
+#include <atomic>
+#include <cstddef>
+#include <cstdint>
+#include <mutex>
+#include <vector>
+
+#include "b200net/cuda_shim.h"
+#include "b200net/idpool.h"
+
+namespace b200net {
+
+class NetKernels {
+ public:
+  static constexpr int NUM_FLAGS = 1024;
+  static constexpr int NUM_EAGER_SLOTS = 64;
+  static constexpr size_t EAGER_PAYLOAD_MAX = 8192;
+  static constexpr size_t EAGER_SLOT_BYTES = 16 + EAGER_PAYLOAD_MAX + 8 + 8;  // header, payload, pad, flag
+
+  // The instance of the calling thread's current CUDA context; nullptr when there is no GPU, no
+  // context, the image does not load (not an sm_100a device) or B200NET_COPY_KERNEL=0.
+  static NetKernels* get();
+
+  // dst[0,n) = src[0,n) on stream `st` with `ctas` CTAs (0 = size based); *slot receives the
+  // completion slot to poll with done() and to give back with release(). -EAGAIN: no slot free.
+  int copy_flag(void* dst, const void* src, size_t n, cuda::Stream st, int ctas, int* slot);
+  bool done(int slot) const;
+  void release(int slot);
+
+  // Packs a device payload (n <= EAGER_PAYLOAD_MAX) and a 16-byte header into a pinned slot.
+  int eager_pack(const void* dev_src, size_t n, uint64_t hdr0, uint64_t hdr1, cuda::Stream st, int* slot);
+  bool eager_done(int slot) const;
+  const uint8_t* eager_slot(int slot) const { return eager_ + static_cast<size_t>(slot) * EAGER_SLOT_BYTES; }
+  void eager_release(int slot);
+
+  uint64_t launches() const { return launches_.load(); }
+
+ private:
+  NetKernels() = default;
+  int init();
+  void* module_ = nullptr;
+  void* fn_copy_ = nullptr;
+  void* fn_pack_ = nullptr;
+  volatile uint64_t* flags_ = nullptr;   // pinned host, NUM_FLAGS words
+  uint32_t* counters_ = nullptr;         // device, NUM_FLAGS words, zero when idle
+  uint8_t* eager_ = nullptr;             // pinned host, NUM_EAGER_SLOTS slots
+  std::vector<uint64_t> expect_, eager_expect_;
+  std::vector<int> free_flags_, free_eager_;
+  std::mutex lock_;
+  uint64_t next_value_ = 1;
+  std::atomic<uint64_t> launches_{0};
+};
+
+}  // namespace b200net

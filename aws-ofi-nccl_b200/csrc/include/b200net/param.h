@@ -119,6 +119,9 @@ class EnumParam : public Param<std::string> {
 struct Params {
   EnumParam protocol{"PROTOCOL", "", {"", "RDMA", "SENDRECV"}, "transport protocol; empty = choose by rail count"};
   Param<uint64_t> eager_max_size{"EAGER_MAX_SIZE", 8192, "largest message sent eagerly (bytes); 0 disables eager"};
+  Param<bool> copy_kernel{"COPY_KERNEL", true,
+                          "move device payloads with the plugin's own copy / eager-pack kernels (0: copy engine only)"};
+  Param<uint64_t> copy_kernel_ctas{"COPY_KERNEL_CTAS", 0, "CTAs per copy-kernel launch (0: chosen from the size)"};
   Param<uint64_t> min_stripe_size{"MIN_STRIPE_SIZE", 128 * 1024, "smallest stripe when a message is split over rails"};
   Param<uint64_t> sched_max_small_rr_size{"SCHED_MAX_SMALL_RR_SIZE", 64, "messages below this go to one rail round-robin"};
   Param<int> cq_read_count{"CQ_READ_COUNT", 4, "completions drained per poll of one rail"};

@@ -25,6 +25,7 @@
 #include "b200net/msgbuff.h"
 #include "b200net/net.h"
 #include "b200net/param.h"
+#include "b200net/net_kernels.h"
 #include "b200net/rdma_proto.h"
 #include "b200net/scheduler.h"
 #include "b200net/shm_fabric.h"
@@ -47,8 +48,9 @@ struct DeviceFragHdr {
 struct Stripe {
   int rail;
   size_t offset, len, done;
-  cuda::Event event;   // non-null while a device copy is in flight
+  cuda::Event event;   // non-null while a copy-engine transfer is in flight
   bool posted, complete, notified;
+  int kslot = -1;      // completion slot of a copy-kernel transfer in flight
 };
 
 class RdmaSendReq : public Request {
@@ -118,6 +120,20 @@ class RdmaEndpoint : public Endpoint {
   int ensure_published(MrHandle* mh);
   cuda::Stream rail_stream(int rail);
   void* map_peer_cuda(PeerMapping* peer, const MrTableEntry* e);
+  // Loads the plugin's device kernels into the current context. Only called from set-up paths
+  // (registration, connect, listen): loading a module or a function while a collective kernel
+  // that waits for this very transport is running can block forever.
+  void prepare_kernels() {
+    if (!kernels_tried && cuda::available()) {
+      cuda::Context ctx = nullptr;
+      if (cuda::ctx_get_current(&ctx) == 0 && ctx) {
+        kernels = NetKernels::get();
+        kernels_tried = true;
+      }
+    }
+  }
+  NetKernels* kernels = nullptr;   // null: copy engine only
+  bool kernels_tried = false;
 
   FabricEndpoint fab;
   ConnectionManager cm;
@@ -256,6 +272,7 @@ int RdmaEndpoint::ensure_published(MrHandle* mh) {
 
 int RdmaEndpoint::reg_mr(void* data, size_t size, int type, MrHandle** out) {
   std::lock_guard<std::recursive_mutex> g(ep_lock);
+  if (type != NCCL_PTR_HOST) prepare_kernels();
   MrCache* cache = domain->mr_cache.get();
   const MrCacheKey key = MrCacheKey::from_iovec(data, size);
   if (cache) {
@@ -372,6 +389,7 @@ int RdmaEndpoint::progress() {
 // ------------------------------------------------------------------------------------------ listen / connect / accept
 int RdmaEndpoint::listen(ConnHandle* handle, ListenComm** lcomm) {
   std::lock_guard<std::recursive_mutex> g(ep_lock);
+  prepare_kernels();
   auto l = std::make_unique<RdmaListenComm>();
   l->ep = this;
   l->dev_id = domain->device->dev_id;
@@ -386,6 +404,7 @@ int RdmaEndpoint::listen(ConnHandle* handle, ListenComm** lcomm) {
 
 int RdmaEndpoint::connect(ConnHandle* handle, SendComm** scomm, int) {
   std::lock_guard<std::recursive_mutex> g(ep_lock);
+  prepare_kernels();
   *scomm = nullptr;
   auto* sc = static_cast<RdmaSendComm*>(handle->state.comm);
   if (!sc) {
@@ -568,17 +587,37 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
           cuda::Stream st = e->rail_stream(s.rail);
           if (!mapped || !st || cuda::event_create(&s.event) != 0) return -EIO;
           char* dst = static_cast<char*>(mapped) + (r->target.buff_addr - mr->base) + s.offset;
-          if (cuda::memcpy_async(dst, src + s.offset, s.len, st) != 0 || cuda::event_record(s.event, st) != 0) return -EIO;
+          // device source: the plugin's own copy kernel moves the stripe over NVLink and sets a
+          // completion word in pinned memory; anything else goes through the copy engine
+          NetKernels* nk = src_dev ? e->kernels : nullptr;
+          if (nk && nk->copy_flag(dst, src + s.offset, s.len, st, 0, &s.kslot) == 0) {
+            cuda::event_destroy(s.event);
+            s.event = nullptr;
+          } else {
+            s.kslot = -1;
+            if (cuda::memcpy_async(dst, src + s.offset, s.len, st) != 0 || cuda::event_record(s.event, st) != 0) return -EIO;
+          }
           s.posted = true;
           B200NET_TRACE_EVENT(SendWriteSegmentStart, dev_id, local_comm_id, r->seq, s.len, r);
         }
-        const int q = cuda::event_query(s.event);
-        if (q < 0) return -EIO;
-        if (q == 0) {
-          cuda::event_destroy(s.event);
-          s.event = nullptr;
-          s.done = s.len;
-          s.complete = true;
+        if (s.kslot >= 0) {
+          NetKernels* nk = e->kernels;
+          if (!nk) return -EIO;
+          if (nk->done(s.kslot)) {
+            nk->release(s.kslot);
+            s.kslot = -1;
+            s.done = s.len;
+            s.complete = true;
+          }
+        } else {
+          const int q = cuda::event_query(s.event);
+          if (q < 0) return -EIO;
+          if (q == 0) {
+            cuda::event_destroy(s.event);
+            s.event = nullptr;
+            s.done = s.len;
+            s.complete = true;
+          }
         }
       } else if (kind == static_cast<uint32_t>(MrKind::CUDA_STAGED)) {
         // the target cannot be mapped here: ship fragments that the receiver copies to the device
@@ -701,8 +740,28 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
   }
   // no control message yet: eager if allowed
   const size_t eager_max = params().eager_max_size.get();
-  if (idx == -1 && eager_max > 0 && size <= eager_max && size + sizeof(EagerHdr) <= FAB_LARGE_CELL &&
-      static_cast<int>(eager_queue.size()) < MAX_EAGER_PENDING && cuda::is_host_pointer(data)) {
+  const bool eager_size_ok = idx == -1 && eager_max > 0 && size <= eager_max && size + sizeof(EagerHdr) <= FAB_LARGE_CELL &&
+                             static_cast<int>(eager_queue.size()) < MAX_EAGER_PENDING;
+  const void* eager_src = data;
+  int eager_slot = -1;
+  NetKernels* nk = nullptr;
+  if (eager_size_ok && size > 0 && !cuda::is_host_pointer(data)) {
+    // device payload: the pack kernel writes header + payload + flag into a pinned slot and the
+    // datagram is sent from there; without the kernels a device payload waits for the rendezvous
+    nk = size <= NetKernels::EAGER_PAYLOAD_MAX ? e->kernels : nullptr;
+    cuda::Stream st = nk ? e->rail_stream(0) : nullptr;
+    if (!nk || !st || nk->eager_pack(data, size, next_eager_seq, size, st, &eager_slot) != 0) return 0;
+    const auto t0 = std::chrono::steady_clock::now();
+    while (!nk->eager_done(eager_slot)) {
+      if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(2)) {
+        // the slot stays reserved: the kernel may still write it
+        NET_WARN("eager pack kernel did not complete within 2 s");
+        return -EIO;
+      }
+    }
+    eager_src = nk->eager_slot(eager_slot) + 16;
+  }
+  if (eager_size_ok && (eager_slot >= 0 || cuda::is_host_pointer(data))) {
     EagerHdr h;
     memset(&h, 0, sizeof(h));
     h.remote_comm_id = remote_comm_id;
@@ -711,7 +770,8 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
     h.base_mask = consumed_mask;
     h.tag = tag;
     h.size = size;
-    const int rc = e->fab.send(peer, DgramType::EAGER, 0, &h, sizeof(h), data, size);
+    const int rc = e->fab.send(peer, DgramType::EAGER, 0, &h, sizeof(h), eager_src, size);
+    if (eager_slot >= 0) nk->eager_release(eager_slot);  // the datagram holds a copy
     if (rc == -EAGAIN) return 0;  // ring full: NCCL calls again
     if (rc != 0) return rc;
     auto* r = new RdmaSendReq();
