@@ -27,6 +27,8 @@ OBJ = ROOT / "build"
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 CXX = os.environ.get("CXX", "g++")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+# Sanitizer builds need a compiler that ships the sanitizer runtimes (the default one may not).
+SAN_CXX = os.environ.get("SAN_CXX", "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else CXX)
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -125,12 +127,12 @@ def build_host(force: bool = False, sanitize: str | None = None) -> Path | None:
         o = OBJ / tag / ("_".join(s.relative_to(CSRC).with_suffix("").parts) + ".o")
         objs.append(o)
         if force or _stale(o, [s] + hdrs):
-            jobs.append(([CXX, *flags, "-c", str(s), "-o", str(o)], o))
+            jobs.append(([SAN_CXX if sanitize else CXX, *flags, "-c", str(s), "-o", str(o)], o))
     _compile_many(jobs)
     name = "libnccl-net-ofi-b200.so" if not sanitize else f"libnccl-net-ofi-b200-{sanitize}.so"
     out = LIB / name
     if force or jobs or not out.exists():
-        link = [CXX, "-shared", "-o", str(out), *map(str, objs), "-pthread", "-ldl", "-lrt",
+        link = [SAN_CXX if sanitize else CXX, "-shared", "-o", str(out), *map(str, objs), "-pthread", "-ldl", "-lrt",
                 "-Wl,-Bsymbolic", "-Wl,--no-undefined"]
         if sanitize:
             link = [x for x in link if x != "-Wl,--no-undefined"] + [f"-fsanitize={sanitize}"]
@@ -168,7 +170,7 @@ def build_tests(force: bool = False, sanitize: str | None = None) -> list[Path]:
             flags = list(CXX_FLAGS)
             if sanitize:
                 flags += [f"-fsanitize={sanitize}", "-fno-omit-frame-pointer"]
-            jobs.append(([CXX, *flags, str(s), str(ar), "-o", str(o), "-pthread", "-ldl", "-lrt"], o))
+            jobs.append(([SAN_CXX if sanitize else CXX, *flags, str(s), str(ar), "-o", str(o), "-pthread", "-ldl", "-lrt"], o))
     _compile_many(jobs)
     return outs
 

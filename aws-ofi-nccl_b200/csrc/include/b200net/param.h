@@ -119,6 +119,8 @@ class EnumParam : public Param<std::string> {
 struct Params {
   EnumParam protocol{"PROTOCOL", "", {"", "RDMA", "SENDRECV"}, "transport protocol; empty = choose by rail count"};
   Param<uint64_t> eager_max_size{"EAGER_MAX_SIZE", 8192, "largest message sent eagerly (bytes); 0 disables eager"};
+  Param<std::string> fault_drop{"FAULT_DROP", "",
+                                "testing: drop datagrams on send, 'type:count[,type:count]' with the numeric datagram type"};
   Param<bool> copy_kernel{"COPY_KERNEL", true,
                           "move device payloads with the plugin's own copy / eager-pack kernels (0: copy engine only)"};
   Param<uint64_t> copy_kernel_ctas{"COPY_KERNEL_CTAS", 0, "CTAs per copy-kernel launch (0: chosen from the size)"};

@@ -53,7 +53,7 @@ class SrRecvReq : public Request {
   size_t cap, received = 0, total = ~size_t{0};
   int tag;
   uint32_t msg_seq;
-  MrHandle* mh;
+  int mem_type = NCCL_PTR_HOST;  // copied at post time: the registration may be released before the data lands
   bool complete = false;
 };
 class SrFlushReq : public Request {
@@ -319,7 +319,7 @@ void SrRecvComm::apply(SrRecvReq* r, const FragHdr& h, const void* data, size_t 
   r->total = h.total;
   if (h.offset < r->cap) {
     const size_t n = std::min(len, r->cap - static_cast<size_t>(h.offset));
-    if (r->mh && r->mh->type == NCCL_PTR_CUDA) {
+    if (r->mem_type == NCCL_PTR_CUDA) {
       cuda::Stream st = nullptr;
       if (cuda::stream_create(&st) == 0) {
         cuda::memcpy_async(r->buf + h.offset, data, n, st);
@@ -327,7 +327,7 @@ void SrRecvComm::apply(SrRecvReq* r, const FragHdr& h, const void* data, size_t 
         cuda::stream_destroy(st);
       }
     } else {
-      memcpy(r->buf + h.offset, data, n);
+      if (n) memcpy(r->buf + h.offset, data, n);
     }
   }
   r->received += len;
@@ -360,7 +360,7 @@ int SrRecvComm::recv(int n, void** data, size_t* sizes, int* tags, MrHandle** mh
   r->buf = static_cast<char*>(data[0]);
   r->cap = sizes[0];
   r->tag = tags[0];
-  r->mh = mh ? mh[0] : nullptr;
+  r->mem_type = (mh && mh[0]) ? mh[0]->type : NCCL_PTR_HOST;
   r->msg_seq = next_msg++;
   posted.push_back(r);
   ++inflight;

@@ -70,6 +70,16 @@ FabricEndpoint::FabricEndpoint() : id_(g_next_ep_id.fetch_add(1)) {
   mr_table_ = reinterpret_cast<MrTableEntry*>(b + mr_off);
   std::atomic_thread_fence(std::memory_order_release);
   hdr_->magic = EP_MAGIC;  // published last: a peer that sees the magic sees initialised rings
+  // host-side fault injection requested through the environment ("type:count,type:count")
+  const std::string spec = params().fault_drop.get();
+  for (size_t pos = 0; pos < spec.size();) {
+    size_t end = spec.find(',', pos);
+    if (end == std::string::npos) end = spec.size();
+    int type = 0, count = 0;
+    if (sscanf(spec.substr(pos, end - pos).c_str(), "%d:%d", &type, &count) == 2 && count > 0)
+      inject_drop(static_cast<DgramType>(type), count);
+    pos = end + 1;
+  }
 }
 
 FabricEndpoint::~FabricEndpoint() {

@@ -1,0 +1,14 @@
+"""Failure handling of the net plugin with faults made on the host: a dropped connect request, a
+dropped write completion, a peer process that exits. No GPU is involved and nothing is made to
+hang: every plugin call has to return promptly with a status."""
+import subprocess
+
+import pytest
+
+
+@pytest.mark.parametrize("scenario", ["drop_conn", "drop_completion", "peer_exit"])
+def test_host_fault_scenarios(built, scenario):
+    cmd = [str(built / "tests" / "func_fault"), str(built / "libnccl-net-ofi-b200.so"), scenario]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=120, cwd=built)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    assert "ok" in res.stdout

@@ -1,0 +1,54 @@
+"""The host code under ASAN + UBSAN and under TSAN: every C++ unit test, the two-process functional
+test of both protocols and the multi-threaded connection scenario run against sanitizer builds of
+the plugin.  Skipped when the toolchain has no sanitizer runtimes (B200NET_SKIP_SANITIZERS=1 skips
+it by hand)."""
+import os
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+LIB = ROOT / "aws-ofi-nccl_b200" / "lib"
+
+pytestmark = pytest.mark.skipif(os.environ.get("B200NET_SKIP_SANITIZERS") == "1", reason="disabled by environment")
+
+
+def _build(kind: str):
+    from aws_ofi_nccl_b200 import build
+    try:
+        build.build_host(sanitize=kind)
+        build.build_tests(sanitize=kind)
+    except RuntimeError as e:
+        pytest.skip(f"no {kind} sanitizer build on this toolchain: {e}")
+    return LIB / f"tests-{kind}", LIB / f"libnccl-net-ofi-b200-{kind}.so"
+
+
+def _run(cmd, env_extra=None, timeout=600):
+    env = dict(os.environ)
+    env.update(env_extra or {})
+    res = subprocess.run([str(c) for c in cmd], capture_output=True, text=True, timeout=timeout, env=env, cwd=LIB)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-6000:]
+    assert "runtime error" not in res.stderr, res.stderr[-6000:]
+
+
+def test_address_and_undefined_behaviour():
+    tests, so = _build("address,undefined")
+    for exe in sorted(tests.glob("unit_*")):
+        _run([exe])
+    scenarios = ["connection", "message_transfer", "pingpong", "grouped_recv", "eager", "reuse_listen", "threads"]
+    for proto in ("SENDRECV", "RDMA"):
+        for sc in scenarios:
+            _run([tests / "func_net", so, sc], {"B200NET_PROTOCOL": proto, "B200NET_FORCE_NUM_RAILS": "2"})
+        # a communicator closed with requests in flight abandons those requests by design
+        _run([tests / "func_net", so, "inflight_close"],
+             {"B200NET_PROTOCOL": proto, "ASAN_OPTIONS": "detect_leaks=0"})
+    for sc in ("drop_conn", "peer_exit"):
+        _run([tests / "func_fault", so, sc], {"ASAN_OPTIONS": "detect_leaks=0"})
+
+
+def test_thread_sanitizer():
+    tests, so = _build("thread")
+    for exe in sorted(tests.glob("unit_*")):
+        _run([exe])
+    _run([tests / "func_net", so, "threads"], {"B200NET_PROTOCOL": "RDMA"})
