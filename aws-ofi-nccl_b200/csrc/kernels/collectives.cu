@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(512) all_reduce_kernel(GinDevHandle h, size_t 
   const size_t per = (nvec + h.nranks - 1) / h.nranks;
   const size_t v0 = min(nvec, per * h.rank);
   const size_t v1 = min(nvec, v0 + per);
-  reduce_range<BF16, NVLS, NVLS ? 4 : 2>(h, off, v0, v1, scale, [&](size_t idx, const float(&acc)[8]) {
+  reduce_range<BF16, NVLS, NVLS ? 8 : 2>(h, off, v0, v1, scale, [&](size_t idx, const float(&acc)[8]) {
     broadcast_vec<NVLS>(h, off + (idx << 4), pack_vec<BF16>(acc));
   });
   gin_barrier(h, ch, blockIdx.x);
@@ -147,7 +147,7 @@ template <bool BF16, bool NVLS>
 __global__ void __launch_bounds__(512) all_reduce_oneshot_kernel(GinDevHandle h, size_t off, size_t nvec, float scale,
                                                                 void* out, int ch) {
   if (!gin_barrier(h, ch, blockIdx.x)) return;
-  reduce_range<BF16, NVLS, NVLS ? 4 : 2>(h, off, 0, nvec, scale, [&](size_t idx, const float(&acc)[8]) {
+  reduce_range<BF16, NVLS, NVLS ? 8 : 2>(h, off, 0, nvec, scale, [&](size_t idx, const float(&acc)[8]) {
     reinterpret_cast<uint4*>(out)[idx] = pack_vec<BF16>(acc);
   });
   gin_barrier(h, ch, blockIdx.x);
@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(512) reduce_scatter_kernel(GinDevHandle h, siz
                                                             float scale, void* out, int ch) {
   if (!gin_barrier(h, ch, blockIdx.x)) return;
   const size_t base = off + ((nvec_per_rank * h.rank) << 4);
-  reduce_range<BF16, NVLS, NVLS ? 4 : 2>(h, base, 0, nvec_per_rank, scale, [&](size_t idx, const float(&acc)[8]) {
+  reduce_range<BF16, NVLS, NVLS ? 8 : 2>(h, base, 0, nvec_per_rank, scale, [&](size_t idx, const float(&acc)[8]) {
     if constexpr (OUT_MODE == 1 && BF16) {
       float4* o = reinterpret_cast<float4*>(out) + 2 * idx;
       o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);

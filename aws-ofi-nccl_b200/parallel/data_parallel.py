@@ -23,7 +23,7 @@ class GradReducer:
         self.group, self.device = group, device
         self.world = dist.get_world_size(group)
         self.bucket_bytes = bucket_bytes or int(os.environ.get("B200NET_DP_BUCKET_MB", "512")) << 20
-        self.nblocks = nblocks or int(os.environ.get("B200NET_DP_BLOCKS", "24"))
+        self.nblocks = nblocks or int(os.environ.get("B200NET_DP_BLOCKS", "48"))
         self.nvls = nvls
         self.channel = channel
         self.comm: Communicator | None = None

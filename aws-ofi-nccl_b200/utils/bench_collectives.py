@@ -21,17 +21,25 @@ from ..parallel.symm import Communicator
 
 
 def _time(fn, warmup: int, iters: int, dev) -> float:
+    """ms per call: the iterations are timed in five batches and the median batch is reported, so a
+    single stall (another tenant, a clock change) does not distort a whole size; max over ranks."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize(dev)
-    dist.barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(iters):
-        fn()
-    b.record()
-    b.synchronize()
-    t = torch.tensor([a.elapsed_time(b) / iters], device=dev, dtype=torch.float64)
+    batches = 5 if iters >= 10 else 1
+    per = max(1, iters // batches)
+    means = []
+    for _ in range(batches):
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(per):
+            fn()
+        b.record()
+        b.synchronize()
+        means.append(a.elapsed_time(b) / per)
+    means.sort()
+    t = torch.tensor([means[len(means) // 2]], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
 
