@@ -16,8 +16,11 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "gemm_epilogues.cuh"
 #include "gemm_tcgen05.cuh"
+#include "gemm_tcgen05_2cta.cuh"
 #include "gin_device.cuh"
 #include "host_util.h"
 
@@ -185,6 +188,32 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   gemm_mainloop<BN, false, B_MN>(&tmA, &tmB, shape, epi, gate, args.h.status, smem_raw);
 }
 
+// The same kernel on CTA pairs (256-row cluster tiles, tcgen05.mma.cta_group::2). Movers come in
+// pairs too (n_movers is even), so every cluster is either two movers or two GEMM CTAs.
+template <bool B_MN, class Epi>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+    ag_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmShape shape,
+                        AgGemmArgs args, Epi epi, int gate_on_b) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if (static_cast<int>(blockIdx.x) < args.n_movers) {
+    ag_mover(args, smem_raw);
+    return;
+  }
+  ChunkGate gate{reinterpret_cast<const uint32_t*>(args.h.pad[args.h.rank] + TP_READY_OFF), args.epoch,
+                 args.chunks_per_shard, args.h.rank, gate_on_b, args.h.wait_limit_ns};
+  gemm_mainloop_2cta<256, false, B_MN>(&tmA, &tmB, shape, epi, gate, args.h.status, smem_raw);
+}
+
+// B200_TP_2CTA=0 keeps the fused kernels on single CTAs.
+static bool tp_pairs_enabled() {
+  static int mode = -2;
+  if (mode == -2) {
+    const char* e = getenv("B200_TP_2CTA");
+    mode = e ? atoi(e) : 1;
+  }
+  return mode != 0;
+}
+
 // ------------------------------------------------------------------------------------------ gemm_rs
 // Ring reduce-scatter carried by the GEMM epilogue. Rank r walks the shards r+1, r+2, ..., r
 // (its own last). At step k it computes its partial tile of shard r+1+k, adds the running sum that
@@ -336,6 +365,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   gemm_mainloop<BN, false, B_MN>(&tmA, &tmB, shape, epi, gate, args.h.status, smem_raw);
 }
 
+template <bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+    gemm_rs_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmShape shape,
+                        RsArgs args) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ unsigned int epi_warp_count[4];
+  if (threadIdx.x < 4) epi_warp_count[threadIdx.x] = 0;
+  __syncthreads();
+  RingEpilogue<256> epi{args, shape.N, shape.tiles_n, epi_warp_count, smem_raw + Gemm2Smem<256>::TOTAL, 0, 0, 0, 0, false};
+  NoGate gate;
+  gemm_mainloop_2cta<256, false, B_MN>(&tmA, &tmB, shape, epi, gate, args.h.status, smem_raw);
+}
+
 // per-communicator call counters (flags and counters only ever grow; the expected value is
 // derived from the number of calls made so far)
 static uint32_t g_ag_epoch[64] = {0};
@@ -397,48 +439,73 @@ int b200_ag_gemm(int comm, size_t gathered_off, int gather_b, int M, int N, int 
     shape.group_m = gm;
     if (gm >= shape.tiles_m) shape.m_major = 1;  // a single group: walk the N tiles of each M tile instead
   }
+  // CTA pairs when every 256-row (A gathered) cluster tile lies inside one shard and the B tile is full width
+  const bool pairs = tp_pairs_enabled() && M >= 256 && N >= 256 && (gather_b || chunks_per_shard % 2 == 0) && sms >= 4;
+  if (pairs) {
+    n_movers = (n_movers + 1) & ~1;
+    shape.tiles_m = (M + GEMM2_BM - 1) / GEMM2_BM;
+    shape.cta_first = n_movers;
+    shape.num_ctas = (sms - n_movers) & ~1;
+    if (shape.num_ctas > 2 * shape.tiles_m * shape.tiles_n) shape.num_ctas = 2 * shape.tiles_m * shape.tiles_n;
+    if (gather_b) {
+      shape.n_rot = h.rank * chunks_per_shard;
+      shape.m_major = 0;
+      shape.group_m = 0;
+    } else {
+      const int cps2 = chunks_per_shard / 2;   // 256-row tiles per shard
+      shape.m_rot = h.rank * cps2;
+      int gm = cps2 < 8 ? cps2 : 8;
+      while (cps2 % gm) --gm;
+      shape.group_m = gm;
+      shape.m_major = gm >= shape.tiles_m ? 1 : 0;
+    }
+  }
   CUtensorMap tmA, tmB;
   int rc;
   const void* gathered = h.window[h.rank] + gathered_off;
+  const int b_box_rows = pairs ? BN / 2 : BN;
   if (gather_b) {
     rc = make_tmap_2d(&tmA, other, M, K, ld_other, GEMM_BM, GEMM_BK, 2, true);
     if (rc) return rc;
-    rc = make_tmap_2d(&tmB, gathered, N, K, K, BN, GEMM_BK, 2, true);
+    rc = make_tmap_2d(&tmB, gathered, N, K, K, b_box_rows, GEMM_BK, 2, true);
   } else {
     rc = make_tmap_2d(&tmA, gathered, M, K, K, GEMM_BM, GEMM_BK, 2, true);
     if (rc) return rc;
     rc = b_mn ? make_tmap_2d(&tmB, other, K, N, ld_other, GEMM_BK, 64, 2, true)
-              : make_tmap_2d(&tmB, other, N, K, ld_other, BN, GEMM_BK, 2, true);
+              : make_tmap_2d(&tmB, other, N, K, ld_other, b_box_rows, GEMM_BK, 2, true);
   }
   if (rc) return rc;
   AgGemmArgs args{h, gathered_off, shard_bytes, static_cast<size_t>(gather_b ? BN : GEMM_BM) * K * 2, chunks_per_shard,
                   n_movers, channel, ++g_ag_epoch[comm]};
   const int grid = n_movers + shape.num_ctas;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int smem = GemmSmem<BN>::TOTAL;
+  const int smem = pairs ? Gemm2Smem<BN>::TOTAL : GemmSmem<BN>::TOTAL;
+#define B200_AG_LAUNCH(KERNEL, EPI)                                             \
+  do {                                                                          \
+    auto k = KERNEL;                                                            \
+    if (set_smem(k, smem)) return B200_ERR_BAD_ARG;                             \
+    k<<<grid, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args, EPI, gather_b);   \
+  } while (0)
   if (epilogue == 1) {
     SwiGluEpilogue epi{static_cast<__nv_bfloat16*>(act), ld_act, static_cast<__nv_bfloat16*>(C), ldc};
-    if (b_mn) {
-      auto k = ag_gemm_kernel<BN, true, SwiGluEpilogue>;
-      if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
-      k<<<grid, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args, epi, gather_b);
+    if (pairs) {
+      if (b_mn) B200_AG_LAUNCH((ag_gemm_pair_kernel<true, SwiGluEpilogue>), epi);
+      else B200_AG_LAUNCH((ag_gemm_pair_kernel<false, SwiGluEpilogue>), epi);
     } else {
-      auto k = ag_gemm_kernel<BN, false, SwiGluEpilogue>;
-      if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
-      k<<<grid, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args, epi, gather_b);
+      if (b_mn) B200_AG_LAUNCH((ag_gemm_kernel<BN, true, SwiGluEpilogue>), epi);
+      else B200_AG_LAUNCH((ag_gemm_kernel<BN, false, SwiGluEpilogue>), epi);
     }
   } else {
     StoreEpilogue<__nv_bfloat16> epi{static_cast<__nv_bfloat16*>(C), ldc, 0};
-    if (b_mn) {
-      auto k = ag_gemm_kernel<BN, true, StoreEpilogue<__nv_bfloat16>>;
-      if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
-      k<<<grid, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args, epi, gather_b);
+    if (pairs) {
+      if (b_mn) B200_AG_LAUNCH((ag_gemm_pair_kernel<true, StoreEpilogue<__nv_bfloat16>>), epi);
+      else B200_AG_LAUNCH((ag_gemm_pair_kernel<false, StoreEpilogue<__nv_bfloat16>>), epi);
     } else {
-      auto k = ag_gemm_kernel<BN, false, StoreEpilogue<__nv_bfloat16>>;
-      if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
-      k<<<grid, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args, epi, gather_b);
+      if (b_mn) B200_AG_LAUNCH((ag_gemm_kernel<BN, true, StoreEpilogue<__nv_bfloat16>>), epi);
+      else B200_AG_LAUNCH((ag_gemm_kernel<BN, false, StoreEpilogue<__nv_bfloat16>>), epi);
     }
   }
+#undef B200_AG_LAUNCH
   B200_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -464,27 +531,41 @@ int b200_gemm_rs(int comm, const void* A, long long lda, const void* B, long lon
   if (static_cast<size_t>(h.nranks - 1) * tiles_per_shard_m * shape.tiles_n > static_cast<size_t>(TP_MAX_TILES) * GIN_MAX_RANKS)
     return B200_ERR_TOO_LARGE;
   const int sms = sm_count();
-  shape.num_ctas = sms < shape.tiles_m * shape.tiles_n ? sms : shape.tiles_m * shape.tiles_n;
-  shape.m_rot = ((h.rank + 1) % h.nranks) * tiles_per_shard_m;  // next rank's rows first, own rows last
+  const bool pairs = tp_pairs_enabled() && tiles_per_shard_m % 2 == 0 && N >= 256 && sms >= 2;
+  if (pairs) {
+    shape.tiles_m = M / GEMM2_BM;
+    shape.num_ctas = (sms & ~1) < 2 * shape.tiles_m * shape.tiles_n ? (sms & ~1) : 2 * shape.tiles_m * shape.tiles_n;
+    shape.m_rot = ((h.rank + 1) % h.nranks) * (tiles_per_shard_m / 2);
+  } else {
+    shape.num_ctas = sms < shape.tiles_m * shape.tiles_n ? sms : shape.tiles_m * shape.tiles_n;
+    shape.m_rot = ((h.rank + 1) % h.nranks) * tiles_per_shard_m;  // next rank's rows first, own rows last
+  }
   shape.m_major = 1;
   CUtensorMap tmA, tmB;
   int rc = make_tmap_2d(&tmA, A, M, K, lda, GEMM_BM, GEMM_BK, 2, true);
   if (rc) return rc;
-  rc = b_mn ? make_tmap_2d(&tmB, B, K, N, ldb, GEMM_BK, 64, 2, true) : make_tmap_2d(&tmB, B, N, K, ldb, BN, GEMM_BK, 2, true);
+  rc = b_mn ? make_tmap_2d(&tmB, B, K, N, ldb, GEMM_BK, 64, 2, true)
+            : make_tmap_2d(&tmB, B, N, K, ldb, pairs ? BN / 2 : BN, GEMM_BK, 2, true);
   if (rc) return rc;
   RsArgs args{h, staging_off, M / h.nranks, tiles_per_shard_m, ++g_rs_epoch[comm], static_cast<__nv_bfloat16*>(out), ld_out,
               scale};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int smem = GemmSmem<BN>::TOTAL + 4 * 4096;  // + one transpose buffer per epilogue warp
-  if (b_mn) {
-    auto k = gemm_rs_kernel<BN, true>;
-    if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
-    k<<<shape.num_ctas, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args);
+  // + one transpose buffer per epilogue warp
+  const int smem = (pairs ? Gemm2Smem<BN>::TOTAL : GemmSmem<BN>::TOTAL) + 4 * 4096;
+#define B200_RS_LAUNCH(KERNEL)                                                  \
+  do {                                                                          \
+    auto k = KERNEL;                                                            \
+    if (set_smem(k, smem)) return B200_ERR_BAD_ARG;                             \
+    k<<<shape.num_ctas, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args);        \
+  } while (0)
+  if (pairs) {
+    if (b_mn) B200_RS_LAUNCH((gemm_rs_pair_kernel<true>));
+    else B200_RS_LAUNCH((gemm_rs_pair_kernel<false>));
   } else {
-    auto k = gemm_rs_kernel<BN, false>;
-    if (set_smem(k, smem)) return B200_ERR_BAD_ARG;
-    k<<<shape.num_ctas, GEMM_THREADS, smem, s>>>(tmA, tmB, shape, args);
+    if (b_mn) B200_RS_LAUNCH((gemm_rs_kernel<BN, true>));
+    else B200_RS_LAUNCH((gemm_rs_kernel<BN, false>));
   }
+#undef B200_RS_LAUNCH
   B200_CUDA_OK(cudaGetLastError());
   return 0;
 }

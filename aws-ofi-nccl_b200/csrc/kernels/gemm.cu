@@ -90,7 +90,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                           int64_t ldc, GemmShape shape, int accumulate, int* err_word) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   StoreEpilogue<OutT> epi{C, ldc, accumulate};
-  gemm_mainloop_2cta<BN, A_MN, B_MN>(&tmA, &tmB, shape, epi, err_word, smem_raw);
+  NoGate gate;
+  gemm_mainloop_2cta<BN, A_MN, B_MN>(&tmA, &tmB, shape, epi, gate, err_word, smem_raw);
 }
 
 template <int BN, bool A_MN, bool B_MN, typename OutT>

@@ -87,9 +87,13 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 
 // Launch with cluster dimension (2,1,1), 192 threads, Gemm2Smem<BN>::TOTAL (+ epilogue extras)
 // bytes of dynamic shared memory and an even grid. shape.tiles_m counts 256-row tiles here.
-template <int BN, bool A_MN, bool B_MN, class Epilogue>
+// The gate and the epilogue hooks (tile_begin / tile_end) are called with the index of this CTA's
+// 128-row tile (2 * pair tile + rank in the pair), so gates and epilogues written for the one-CTA
+// mainloop work unchanged. shape.cta_first / num_ctas (both even) restrict the GEMM to a part of
+// the grid.
+template <int BN, bool A_MN, bool B_MN, class Epilogue, class LoadGate>
 __device__ __forceinline__ void gemm_mainloop_2cta(const CUtensorMap* tmA, const CUtensorMap* tmB, GemmShape shape,
-                                                   Epilogue& epi, int* err_word, uint8_t* smem_raw) {
+                                                   Epilogue& epi, LoadGate& gate, int* err_word, uint8_t* smem_raw) {
   using S = Gemm2Smem<BN>;
   static_assert(BN == 128 || BN == 256, "cluster tile is 256 x 128 or 256 x 256");
   constexpr int HALF_N = BN / 2;
@@ -135,8 +139,8 @@ __device__ __forceinline__ void gemm_mainloop_2cta(const CUtensorMap* tmA, const
 
   const int num_tiles = shape.tiles_m * shape.tiles_n;
   const int num_kb = (shape.K + GEMM_BK - 1) / GEMM_BK;
-  const int pair_id = static_cast<int>(blockIdx.x) >> 1;
-  const int pair_stride = static_cast<int>(gridDim.x) >> 1;
+  const int pair_id = (static_cast<int>(blockIdx.x) - shape.cta_first) >> 1;
+  const int pair_stride = (shape.num_ctas > 0 ? shape.num_ctas : static_cast<int>(gridDim.x)) >> 1;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -149,6 +153,7 @@ __device__ __forceinline__ void gemm_mainloop_2cta(const CUtensorMap* tmA, const
         tile_coords(shape, tile, tm, tn);
         const int row0 = tm * GEMM2_BM + static_cast<int>(rank) * 128;   // this CTA's rows of A
         const int col0 = tn * BN + static_cast<int>(rank) * HALF_N;   // this CTA's half of B
+        if (!gate.wait_tile(2 * tm + static_cast<int>(rank), tn, abort_flag, err_word)) break;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1, abort_flag, err_word, DEV_ERR_EMPTY_BAR_TIMEOUT,
                                  GEMM_WAIT_LIMIT_NS)) {
@@ -233,7 +238,7 @@ __device__ __forceinline__ void gemm_mainloop_2cta(const CUtensorMap* tmA, const
                              GEMM_WAIT_LIMIT_NS))
         break;
       tc_fence_after();
-      epi.tile_begin(tm, tn);
+      epi.tile_begin(2 * tm + static_cast<int>(rank), tn);
       const int row = tm * GEMM2_BM + static_cast<int>(rank) * 128 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc_buf * BN;
       if constexpr (Epilogue::kPair) {
@@ -257,7 +262,7 @@ __device__ __forceinline__ void gemm_mainloop_2cta(const CUtensorMap* tmA, const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(map_to_cta(tempty_bar(acc_buf), 0));
-      epi.tile_end(tm, tn);
+      epi.tile_end(2 * tm + static_cast<int>(rank), tn);
       acc_buf ^= 1;
       if (acc_buf == 0) acc_phase ^= 1;
     }
