@@ -74,6 +74,9 @@ def build_kernels(force: bool = False, extra_flags: list[str] | None = None) -> 
     (OBJ / "kernels").mkdir(parents=True, exist_ok=True)
     hdrs = _headers()
     srcs = sorted((CSRC / "kernels").glob("*.cu"))
+    out = LIB / "libb200ops.so"
+    if not force and not extra_flags and not _stale(out, srcs + hdrs):
+        return out   # the library is newer than every source: nothing to do, even without the object files
     objs, jobs = [], []
     for s in srcs:
         o = OBJ / "kernels" / (s.stem + ".o")
@@ -81,7 +84,6 @@ def build_kernels(force: bool = False, extra_flags: list[str] | None = None) -> 
         if force or _stale(o, [s] + hdrs):
             jobs.append(([NVCC, *NVCC_FLAGS, *(extra_flags or []), "-c", str(s), "-o", str(o)], o))
     _compile_many(jobs)
-    out = LIB / "libb200ops.so"
     if force or jobs or not out.exists():
         _run([NVCC, "-shared", "-o", str(out), *map(str, objs), "-cudart", "static",
               "-gencode", "arch=compute_100a,code=sm_100a"])
@@ -119,6 +121,12 @@ def build_host(force: bool = False, sanitize: str | None = None) -> Path | None:
     tag = f"host-{sanitize}" if sanitize else "host"
     (OBJ / tag).mkdir(parents=True, exist_ok=True)
     hdrs = _headers()
+    if not sanitize and not force:
+        fresh = LIB / "libnccl-net-ofi-b200.so"
+        deps = srcs + hdrs + [CSRC / "device" / "net_kernels.cu"]
+        if not _stale(fresh, deps) and not _stale(LIB / "libinternal_plugin.a", deps) and all(
+                (LIB / a).exists() for a in ("libnccl-net.so", "libnccl-tuner-ofi-b200.so", "libnccl-net-b200.so")):
+            return fresh   # newer than every source: nothing to do, even without the object files
     flags = list(CXX_FLAGS) + ["-I", str(_embed_net_kernels(force))]
     if sanitize:
         flags += [f"-fsanitize={sanitize}", "-fno-omit-frame-pointer"]
@@ -129,8 +137,11 @@ def build_host(force: bool = False, sanitize: str | None = None) -> Path | None:
         if force or _stale(o, [s] + hdrs):
             jobs.append(([SAN_CXX if sanitize else CXX, *flags, "-c", str(s), "-o", str(o)], o))
     _compile_many(jobs)
+    # sanitizer builds stay under build/ (large, and of no use on a GPU box)
+    outdir = LIB if not sanitize else OBJ / "san"
+    outdir.mkdir(parents=True, exist_ok=True)
     name = "libnccl-net-ofi-b200.so" if not sanitize else f"libnccl-net-ofi-b200-{sanitize}.so"
-    out = LIB / name
+    out = outdir / name
     if force or jobs or not out.exists():
         link = [SAN_CXX if sanitize else CXX, "-shared", "-o", str(out), *map(str, objs), "-pthread", "-ldl", "-lrt",
                 "-Wl,-Bsymbolic", "-Wl,--no-undefined"]
@@ -141,7 +152,7 @@ def build_host(force: bool = False, sanitize: str | None = None) -> Path | None:
             for alias in ("libnccl-net.so", "libnccl-tuner-ofi-b200.so", "libnccl-net-b200.so"):
                 shutil.copyfile(out, LIB / alias)
     # static archive for unit tests that reach internals
-    ar = LIB / ("libinternal_plugin.a" if not sanitize else f"libinternal_plugin-{sanitize}.a")
+    ar = outdir / ("libinternal_plugin.a" if not sanitize else f"libinternal_plugin-{sanitize}.a")
     if force or jobs or not ar.exists():
         if ar.exists():
             ar.unlink()
@@ -154,9 +165,10 @@ def build_tests(force: bool = False, sanitize: str | None = None) -> list[Path]:
     tdir = CSRC / "tests"
     if not tdir.exists():
         return []
-    outdir = LIB / ("tests" if not sanitize else f"tests-{sanitize}")
+    base = LIB if not sanitize else OBJ / "san"
+    outdir = base / ("tests" if not sanitize else f"tests-{sanitize}")
     outdir.mkdir(parents=True, exist_ok=True)
-    ar = LIB / ("libinternal_plugin.a" if not sanitize else f"libinternal_plugin-{sanitize}.a")
+    ar = base / ("libinternal_plugin.a" if not sanitize else f"libinternal_plugin-{sanitize}.a")
     hdrs = _headers()
     jobs, outs = [], []
     for s in sorted(list(tdir.glob("*.cpp")) + list(tdir.glob("*.c"))):

@@ -9,7 +9,7 @@ from pathlib import Path
 import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
-LIB = ROOT / "aws-ofi-nccl_b200" / "lib"
+LIB = ROOT / "aws-ofi-nccl_b200" / "build" / "san"
 
 pytestmark = pytest.mark.skipif(os.environ.get("B200NET_SKIP_SANITIZERS") == "1", reason="disabled by environment")
 
