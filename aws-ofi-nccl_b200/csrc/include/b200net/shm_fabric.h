@@ -124,6 +124,8 @@ class FabricEndpoint {
   // True when write_host() towards this peer goes through fragments rather than direct writes.
   bool writes_are_staged(PeerMapping* dst);
   static bool cma_disabled_by_param();
+  // Unlinks segments left in /dev/shm by processes that no longer exist; returns how many.
+  static int collect_stale_segments();
   // Fault injection for tests: drop the next n datagrams of a type on send (host side only).
   void inject_drop(DgramType type, int count);
   uint64_t dropped() const { return dropped_; }

@@ -14,6 +14,7 @@
 #include "b200net/net.h"
 #include "b200net/param.h"
 #include "b200net/scheduler.h"
+#include "b200net/shm_fabric.h"
 #include "b200net/platform.h"
 #include "b200net/system.h"
 #include "b200net/topology.h"
@@ -118,6 +119,8 @@ int net_create_plugin(Plugin** out) {
     return 0;
   }
   if (parameters_init() != 0) return -EINVAL;
+  const int stale = FabricEndpoint::collect_stale_segments();
+  if (stale) NET_INFO(NCCL_INIT, "removed %d shared-memory segment(s) of processes that no longer exist", stale);
   cuda::init();  // optional: without a driver only host buffers are served
   auto* topo = new Topology(Topology::discover());
   PlatformManager& pm = PlatformManager::instance();

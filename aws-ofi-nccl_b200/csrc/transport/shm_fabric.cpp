@@ -1,6 +1,8 @@
 #include "b200net/shm_fabric.h"
 
+#include <dirent.h>
 #include <fcntl.h>
+#include <signal.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
 #include <sys/uio.h>
@@ -28,6 +30,25 @@ struct FragHdr {
 };
 
 bool FabricEndpoint::cma_disabled_by_param() { return params().disable_cma.get(); }
+
+// Segments are named b200net.<pid>.<n> (endpoints) and b200net.mb.<pid>.<n>.<m> (mailboxes); a
+// process that dies without running its destructors leaves them behind. Unlink those whose owner
+// no longer exists.
+int FabricEndpoint::collect_stale_segments() {
+  DIR* d = opendir("/dev/shm");
+  if (!d) return 0;
+  int removed = 0;
+  while (dirent* e = readdir(d)) {
+    int pid = 0;
+    if (sscanf(e->d_name, "b200net.mb.%d.", &pid) != 1 && sscanf(e->d_name, "b200net.%d.", &pid) != 1) continue;
+    if (pid <= 0 || pid == static_cast<int>(getpid())) continue;
+    if (kill(pid, 0) == 0 || errno != ESRCH) continue;   // alive, or not ours to judge
+    const std::string name = std::string("/") + e->d_name;
+    if (shm_unlink(name.c_str()) == 0) ++removed;
+  }
+  closedir(d);
+  return removed;
+}
 
 FabricEndpoint::FabricEndpoint() : id_(g_next_ep_id.fetch_add(1)) {
   char buf[FAB_EP_NAME_LEN];
