@@ -103,6 +103,10 @@ __device__ __forceinline__ void broadcast_vec(const GinDevHandle& h, size_t off,
   }
 }
 
+// Register budget: with U = 4 the NVLS all-reduce needs 68 registers, so a 512-thread CTA of it and
+// a 192-thread GEMM CTA (90 registers) fit one SM together and the gradient all-reduce really does
+// overlap the backward GEMMs; U = 8 (96 registers) pushed the pair over the 64 K register file and
+// the collective then waited for whole SMs.
 // Walk vectors [v0, v1) of the window range starting at byte `off` with the whole grid, U vectors
 // per thread per trip: the U reductions (multimem loads, or nranks peer loads each) are issued
 // before any result is consumed, which keeps enough bytes in flight to cover the NVLink latency.
@@ -135,7 +139,7 @@ __global__ void __launch_bounds__(512) all_reduce_kernel(GinDevHandle h, size_t 
   const size_t per = (nvec + h.nranks - 1) / h.nranks;
   const size_t v0 = min(nvec, per * h.rank);
   const size_t v1 = min(nvec, v0 + per);
-  reduce_range<BF16, NVLS, NVLS ? 8 : 2>(h, off, v0, v1, scale, [&](size_t idx, const float(&acc)[8]) {
+  reduce_range<BF16, NVLS, NVLS ? 4 : 2>(h, off, v0, v1, scale, [&](size_t idx, const float(&acc)[8]) {
     broadcast_vec<NVLS>(h, off + (idx << 4), pack_vec<BF16>(acc));
   });
   gin_barrier(h, ch, blockIdx.x);
@@ -147,7 +151,7 @@ template <bool BF16, bool NVLS>
 __global__ void __launch_bounds__(512) all_reduce_oneshot_kernel(GinDevHandle h, size_t off, size_t nvec, float scale,
                                                                 void* out, int ch) {
   if (!gin_barrier(h, ch, blockIdx.x)) return;
-  reduce_range<BF16, NVLS, NVLS ? 8 : 2>(h, off, 0, nvec, scale, [&](size_t idx, const float(&acc)[8]) {
+  reduce_range<BF16, NVLS, NVLS ? 4 : 2>(h, off, 0, nvec, scale, [&](size_t idx, const float(&acc)[8]) {
     reinterpret_cast<uint4*>(out)[idx] = pack_vec<BF16>(acc);
   });
   gin_barrier(h, ch, blockIdx.x);
@@ -160,7 +164,7 @@ __global__ void __launch_bounds__(512) reduce_scatter_kernel(GinDevHandle h, siz
                                                             float scale, void* out, int ch) {
   if (!gin_barrier(h, ch, blockIdx.x)) return;
   const size_t base = off + ((nvec_per_rank * h.rank) << 4);
-  reduce_range<BF16, NVLS, NVLS ? 8 : 2>(h, base, 0, nvec_per_rank, scale, [&](size_t idx, const float(&acc)[8]) {
+  reduce_range<BF16, NVLS, NVLS ? 4 : 2>(h, base, 0, nvec_per_rank, scale, [&](size_t idx, const float(&acc)[8]) {
     if constexpr (OUT_MODE == 1 && BF16) {
       float4* o = reinterpret_cast<float4*>(out) + 2 * idx;
       o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
