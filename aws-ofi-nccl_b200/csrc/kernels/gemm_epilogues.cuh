@@ -70,6 +70,39 @@ struct StoreEpilogue {
 };
 
 
+// bf16 store of acc * row_scale[row] * col_scale[col]: the dequantisation of an fp8 product whose
+// operands were quantised per row (activations: one scale per token, weights: one per output
+// channel).
+struct ScaledStoreEpilogue {
+  static constexpr bool kPair = false;
+  __nv_bfloat16* C;
+  int64_t ldc;
+  const float* row_scale;   // [M]
+  const float* col_scale;   // [N]
+  __device__ __forceinline__ void tile_begin(int, int) {}
+  __device__ __forceinline__ void tile_end(int, int) {}
+  __device__ __forceinline__ void operator()(int row, int col0, const uint32_t (&acc)[32], const GemmShape& s) {
+    if (row >= s.M || col0 >= s.N) return;
+    const float rs = row_scale[row];
+    __nv_bfloat16* dst = C + static_cast<int64_t>(row) * ldc + col0;
+    const int ncols = min(32, s.N - col0);
+    if (ncols == 32) {
+      uint32_t packed[16];
+#pragma unroll
+      for (int v = 0; v < 8; ++v) {
+        const float4 cs = *reinterpret_cast<const float4*>(col_scale + col0 + 4 * v);
+        packed[2 * v] = pack_bf16x2(__uint_as_float(acc[4 * v]) * rs * cs.x, __uint_as_float(acc[4 * v + 1]) * rs * cs.y);
+        packed[2 * v + 1] = pack_bf16x2(__uint_as_float(acc[4 * v + 2]) * rs * cs.z, __uint_as_float(acc[4 * v + 3]) * rs * cs.w);
+      }
+      uint4* out = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+      for (int v = 0; v < 4; ++v) out[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+    } else {
+      for (int j = 0; j < ncols; ++j) dst[j] = __float2bfloat16(__uint_as_float(acc[j]) * rs * col_scale[col0 + j]);
+    }
+  }
+};
+
 // SwiGLU fused into the up/gate GEMM. The weight rows are interleaved in blocks of 64 output
 // columns: 32 gate columns followed by their 32 up columns, so one call sees a gate chunk and the
 // matching up chunk and writes act = silu(gate) * up (and, optionally, the raw gate|up pair that

@@ -77,6 +77,18 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, u
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// fp8 (e4m3 / e5m2) operands: kind::f8f6f4, K = 32 per instruction.
+__device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on `bar` (same offset) in both CTAs of the pair once every MMA issued so far has finished.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
   const uint16_t mask = 3;
@@ -91,11 +103,15 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 // 128-row tile (2 * pair tile + rank in the pair), so gates and epilogues written for the one-CTA
 // mainloop work unchanged. shape.cta_first / num_ctas (both even) restrict the GEMM to a part of
 // the grid.
-template <int BN, bool A_MN, bool B_MN, class Epilogue, class LoadGate>
+// FP8: both operands are 1-byte e4m3, K-major only; a k-block is then 128 elements (the same 128
+// bytes per row, so stages, swizzle and descriptors do not change) and one MMA covers K = 32.
+template <int BN, bool A_MN, bool B_MN, class Epilogue, class LoadGate, bool FP8 = false>
 __device__ __forceinline__ void gemm_mainloop_2cta(const CUtensorMap* tmA, const CUtensorMap* tmB, GemmShape shape,
                                                    Epilogue& epi, LoadGate& gate, int* err_word, uint8_t* smem_raw) {
   using S = Gemm2Smem<BN>;
   static_assert(BN == 128 || BN == 256, "cluster tile is 256 x 128 or 256 x 256");
+  static_assert(!FP8 || (!A_MN && !B_MN), "fp8 operands are K-major");
+  constexpr int BK_ELEMS = FP8 ? 2 * GEMM_BK : GEMM_BK;   // elements per 128-byte row of a stage
   constexpr int HALF_N = BN / 2;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -138,7 +154,7 @@ __device__ __forceinline__ void gemm_mainloop_2cta(const CUtensorMap* tmA, const
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
   const int num_tiles = shape.tiles_m * shape.tiles_n;
-  const int num_kb = (shape.K + GEMM_BK - 1) / GEMM_BK;
+  const int num_kb = (shape.K + BK_ELEMS - 1) / BK_ELEMS;
   const int pair_id = (static_cast<int>(blockIdx.x) - shape.cta_first) >> 1;
   const int pair_stride = (shape.num_ctas > 0 ? shape.num_ctas : static_cast<int>(gridDim.x)) >> 1;
 
@@ -165,13 +181,13 @@ __device__ __forceinline__ void gemm_mainloop_2cta(const CUtensorMap* tmA, const
           const uint32_t bar = map_to_cta(full_bar(stage), 0);
           if (leader) mbar_expect_tx(full_bar(stage), 2 * S::STAGE_BYTES);  // both CTAs' bytes
           if constexpr (!A_MN) {
-            tma_load_2d_pair(a_dst, tmA, kb * GEMM_BK, row0, bar);
+            tma_load_2d_pair(a_dst, tmA, kb * BK_ELEMS, row0, bar);
           } else {
 #pragma unroll
             for (int j = 0; j < 2; ++j) tma_load_2d_pair(a_dst + j * 8192, tmA, row0 + j * 64, kb * GEMM_BK, bar);
           }
           if constexpr (!B_MN) {
-            tma_load_2d_pair(b_dst, tmB, kb * GEMM_BK, col0, bar);
+            tma_load_2d_pair(b_dst, tmB, kb * BK_ELEMS, col0, bar);
           } else {
 #pragma unroll
             for (int j = 0; j < HALF_N / 64; ++j) tma_load_2d_pair(b_dst + j * 8192, tmB, col0 + j * 64, kb * GEMM_BK, bar);
@@ -186,7 +202,8 @@ __device__ __forceinline__ void gemm_mainloop_2cta(const CUtensorMap* tmA, const
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (leader && elect_one_sync()) {
-      constexpr uint32_t idesc = make_instr_desc(1, 1, GEMM2_BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      // operand format field: 1 = bf16 for kind::f16, 0 = e4m3 for kind::f8f6f4
+      constexpr uint32_t idesc = make_instr_desc(FP8 ? 0 : 1, FP8 ? 0 : 1, GEMM2_BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int acc_buf = 0;
@@ -213,7 +230,10 @@ __device__ __forceinline__ void gemm_mainloop_2cta(const CUtensorMap* tmA, const
                                         : make_smem_desc_sw128(a_src + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc_sw128(b_src + k * 2048, 8192, 1024)
                                         : make_smem_desc_sw128(b_src + k * 32, 16, 1024);
-            umma_f16_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (FP8)
+              umma_f8_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              umma_f16_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit_pair(empty_bar(stage));  // frees the stage in both CTAs once these MMAs have read it
           if (++stage == S::STAGES) {

@@ -73,7 +73,8 @@ struct SubRecv {
   void* buf;
   size_t cap;
   int tag;
-  MrHandle* mh;
+  MrHandle* mh;             // only dereferenced while the receive is being posted
+  int mem_type = NCCL_PTR_HOST;  // copied then: the registration may be released before an eager payload lands
   size_t received = 0;
   int segs_done = 0, segs_expected = -1;
   bool done = false;
@@ -918,7 +919,7 @@ void RdmaRecvComm::match_eager() {
     SubRecv& s = target->subs[target_idx];
     const size_t nbytes = std::min<size_t>(rx.hdr.size, s.cap);
     if (nbytes) {
-      if (s.mh && s.mh->type == NCCL_PTR_CUDA) {
+      if (s.mem_type == NCCL_PTR_CUDA) {
         cuda::Stream st = rep()->rail_stream(0);
         if (st) {
           cuda::memcpy_async(s.buf, rx.data.data(), nbytes, st);
@@ -960,7 +961,7 @@ int RdmaRecvComm::recv(int n, void** data, size_t* sizes, int* tags, MrHandle** 
   CtrlMsg& slot = box[seq % MAILBOX_SLOTS];
   B200NET_TRACE_EVENT(WriteCtrlStart, dev_id, local_comm_id, seq, n, r);
   for (int i = 0; i < n; ++i) {
-    r->subs[i] = SubRecv{data[i], sizes[i], tags[i], mh ? mh[i] : nullptr};
+    r->subs[i] = SubRecv{data[i], sizes[i], tags[i], mh ? mh[i] : nullptr, (mh && mh[i]) ? mh[i]->type : NCCL_PTR_HOST};
     if (mh && mh[i]) {
       const int rc = e->ensure_published(mh[i]);
       if (rc != 0) {

@@ -20,6 +20,8 @@ _SIGNATURES = {
     "b200_rmsnorm_fwd": ([_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp], _i),
     "b200_rmsnorm_bwd_partial_rows": ([], _i),
     "b200_rmsnorm_bwd": ([_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
+    "b200_gemm_fp8": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp], _i),
+    "b200_quant_rows_fp8": ([_vp, _vp, _vp, _i, _i, _ll, _ll, _vp], _i),
     "b200_swiglu_fwd": ([_vp, _vp, _ll, _i, _vp], _i),
     "b200_swiglu_bwd": ([_vp, _vp, _vp, _ll, _i, _vp], _i),
     "b200_swiglu_bwd_interleaved": ([_vp, _vp, _vp, _ll, _i, _vp], _i),

@@ -41,6 +41,35 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+def quantize_rows_fp8(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [R, K] -> (e4m3 [R, K], fp32 scale [R]) with one scale per row: x ~= q * scale[:, None]."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    R, K = x.shape
+    q = torch.empty((R, K), device=x.device, dtype=torch.float8_e4m3fn)
+    scale = torch.empty(R, device=x.device, dtype=torch.float32)
+    _lib.check(_lib.load().b200_quant_rows_fp8(x.data_ptr(), q.data_ptr(), scale.data_ptr(), R, K, x.stride(0), q.stride(0),
+                                               _lib.stream_ptr()), "b200_quant_rows_fp8")
+    return q, scale
+
+
+def gemm_fp8(a8: torch.Tensor, b8: torch.Tensor, a_scale: torch.Tensor, b_scale: torch.Tensor,
+             out: torch.Tensor | None = None) -> torch.Tensor:
+    """C[M,N] (bf16) = (a8[M,K] @ b8[N,K]^T) * a_scale[:, None] * b_scale[None, :] with e4m3 operands,
+    fp32 accumulation in TMEM and the dequantisation fused into the epilogue (M >= 256, N >= 128)."""
+    assert a8.dtype == torch.float8_e4m3fn and b8.dtype == torch.float8_e4m3fn
+    assert a8.stride(1) == 1 and b8.stride(1) == 1 and a8.shape[1] == b8.shape[1]
+    M, K = a8.shape
+    N = b8.shape[0]
+    assert a_scale.shape == (M,) and b_scale.shape == (N,) and a_scale.dtype == b_scale.dtype == torch.float32
+    if out is None:
+        out = torch.empty((M, N), device=a8.device, dtype=torch.bfloat16)
+    assert out.shape == (M, N) and out.dtype == torch.bfloat16 and out.stride(1) == 1
+    _lib.check(_lib.load().b200_gemm_fp8(a8.data_ptr(), b8.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(),
+                                         out.data_ptr(), M, N, K, a8.stride(0), b8.stride(0), out.stride(0),
+                                         _lib.stream_ptr()), "b200_gemm_fp8")
+    return out
+
+
 class _Linear(torch.autograd.Function):
     """y = x W^T.  The weight gradient is written straight into ``weight.main_grad`` when the
     parameter has one (a view of the flat gradient buffer), and the ``grad_ready`` hook of the

@@ -63,6 +63,31 @@ def run(shapes, iters: int = 10, bn: int = 0) -> list[dict]:
     return rows
 
 
+def run_fp8(shapes, iters: int = 10) -> list[dict]:
+    """e4m3 x e4m3 -> bf16 with per-row scales; torch._scaled_mm (cuBLASLt) is the library reference."""
+    from ..ops.gemm import gemm_fp8, quantize_rows_fp8
+
+    rows = []
+    for name, M, N, K, _, _ in shapes:
+        x = torch.randn(M, K, device="cuda").bfloat16()
+        w = (torch.randn(N, K, device="cuda") * K ** -0.5).bfloat16()
+        xq, xs = quantize_rows_fp8(x)
+        wq, ws = quantize_rows_fp8(w)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = time_cuda(lambda: gemm_fp8(xq, wq, xs, ws, out=out), iters=iters)
+        row = {"shape": name + "_fp8", "M": M, "N": N, "K": K, "ms": ms, "tflops": 2.0 * M * N * K / ms / 1e9}
+        try:
+            sa, sb = xs[:, None].contiguous(), ws[None, :].contiguous()
+            ms_lib = time_cuda(lambda: torch._scaled_mm(xq, wq.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16),
+                               iters=iters)
+            row.update(cublaslt_ms=ms_lib, cublaslt_tflops=2.0 * M * N * K / ms_lib / 1e9, vs_cublaslt=ms_lib / ms)
+        except (RuntimeError, TypeError, AttributeError) as e:   # not offered by this torch build for these scales
+            row["cublaslt"] = f"unavailable: {type(e).__name__}"
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+    return rows
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--json")
@@ -70,12 +95,15 @@ def main() -> None:
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), help="time this one shape only")
+    ap.add_argument("--fp8", action="store_true", help="also time the e4m3 kernel (row / column scales) on the forward shapes")
     args = ap.parse_args()
     if args.shape:
         shapes = [("custom", *args.shape, False, False)]
     else:
         shapes = SMALL_SHAPES if args.small else LLAMA_SHAPES
     rows = run(shapes, iters=args.iters, bn=args.bn)
+    if args.fp8:
+        rows += run_fp8([s for s in shapes if not s[4] and not s[5]], iters=args.iters)
     if args.json:
         with open(args.json, "w") as f:
             json.dump(rows, f, indent=1)

@@ -70,3 +70,27 @@ def test_linear_autograd_matches_torch():
     yr.backward(dy.float())
     for got, ref in ((y, yr), (x.grad, xr.grad), (w.grad, wr.grad)):
         assert (got.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 128, 128), (512, 1024, 4096), (4096, 4096, 4096), (384, 640, 2064), (8192, 14336, 4096)])
+def test_fp8_gemm_matches_the_dequantised_product(M, N, K):
+    """Same quantised operands on both sides: the kernel's fp32 accumulation of e4m3 products must
+    agree with an fp32 matmul of the dequantised matrices up to the bf16 rounding of the output."""
+    from aws_ofi_nccl_b200.ops.gemm import gemm_fp8, quantize_rows_fp8
+
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * K ** -0.5).bfloat16()
+    xq, xs = quantize_rows_fp8(x)
+    wq, ws = quantize_rows_fp8(w)
+    # the quantiser itself: one scale per row, at most one e4m3 step of error
+    x_dq = xq.float() * xs[:, None]
+    assert torch.allclose(xs, x.float().abs().amax(1).clamp_min(1e-12) / 448, rtol=1e-6)
+    assert ((x_dq - x.float()).abs() <= x.float().abs() * 0.0625 + xs[:, None] * 2 ** -9 + 1e-6).all()
+    out = gemm_fp8(xq, wq, xs, ws)
+    ref = (xq.float() @ wq.float().t()) * xs[:, None] * ws[None, :]
+    err = (out.float() - ref).norm() / ref.norm()
+    assert err < 5e-3, err
+    # and against the unquantised product, within fp8 accuracy
+    full = x.float() @ w.float().t()
+    assert (out.float() - full).norm() / full.norm() < 6e-2
