@@ -151,7 +151,9 @@ struct Params {
                                true,
 #endif
                                "use error-checking mutexes"};
-  Param<bool> disable_dmabuf{"DISABLE_DMABUF", false, ""};
+  Param<bool> disable_dmabuf{"DISABLE_DMABUF", true,
+                             "do not advertise dma-buf registration (default: peers are reached through IPC / VMM "
+                             "mappings, a dma-buf descriptor adds nothing, and NCCL's export of its own buffers can fail)"};
   Param<bool> cuda_flush_enable{"CUDA_FLUSH_ENABLE", false, "flush with the driver instead of a fence"};
   Param<bool> disable_cma{"DISABLE_CMA", false, "never use cross-memory attach for host rendezvous writes"};
   Param<bool> nvls_enable{"NVLS_ENABLE", true, "use NVSwitch multicast where available"};

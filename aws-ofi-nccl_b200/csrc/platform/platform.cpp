@@ -23,6 +23,10 @@ int PlatformB200::init(std::string*) {
 
 std::vector<std::pair<std::string, std::string>> PlatformB200::nccl_env() const {
   // chunks sized for copy-engine stripes over NVLink (MiB-sized copies) rather than for NIC MTUs
+  // NCCL_NET_GDR_LEVEL is left alone on purpose: with NCCL's default the topology distance to this
+  // transport's virtual NIC keeps NCCL's own chunks in host memory. Forcing device buffers through
+  // (NCCL_NET_GDR_LEVEL=SYS) stalled NCCL's first collective: the peer buffer is mapped on first use,
+  // from the proxy thread, while NCCL's kernel is already waiting for that very transfer.
   return {{"NCCL_BUFFSIZE", "33554432"}, {"NCCL_P2P_NET_CHUNKSIZE", "4194304"}, {"NCCL_NVLS_CHUNKSIZE", "524288"},
           {"NCCL_NET_FORCE_FLUSH", "0"}};
 }

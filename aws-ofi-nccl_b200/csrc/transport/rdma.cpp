@@ -135,6 +135,8 @@ class RdmaEndpoint : public Endpoint {
   }
   NetKernels* kernels = nullptr;   // null: copy engine only
   bool kernels_tried = false;
+  // payload bytes by the path they took (reported when the endpoint goes away)
+  uint64_t bytes_kernel = 0, bytes_copy_engine = 0, bytes_staged = 0, bytes_host = 0, bytes_eager = 0;
 
   FabricEndpoint fab;
   ConnectionManager cm;
@@ -213,6 +215,11 @@ class RdmaRecvComm : public RecvComm {
 RdmaEndpoint::RdmaEndpoint(Domain* d, int rails) : Endpoint(d), cm(&fab), num_rails(rails) {}
 
 RdmaEndpoint::~RdmaEndpoint() {
+  if (bytes_kernel | bytes_copy_engine | bytes_staged | bytes_host | bytes_eager)
+    NET_INFO(NCCL_NET, "endpoint payload bytes: copy kernel %llu, copy engine %llu, staged through host %llu, host writes %llu, eager %llu",
+             static_cast<unsigned long long>(bytes_kernel), static_cast<unsigned long long>(bytes_copy_engine),
+             static_cast<unsigned long long>(bytes_staged), static_cast<unsigned long long>(bytes_host),
+             static_cast<unsigned long long>(bytes_eager));
   for (auto& [k, p] : ipc_maps)
     if (k.first != static_cast<uint32_t>(getpid())) cuda::ipc_close(p);
   for (auto s : streams)
@@ -586,17 +593,19 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
         if (!s.posted) {
           void* mapped = e->map_peer_cuda(peer, mr);
           cuda::Stream st = e->rail_stream(s.rail);
-          if (!mapped || !st || cuda::event_create(&s.event) != 0) return -EIO;
+          if (!mapped || !st) return -EIO;
           char* dst = static_cast<char*>(mapped) + (r->target.buff_addr - mr->base) + s.offset;
           // device source: the plugin's own copy kernel moves the stripe over NVLink and sets a
           // completion word in pinned memory; anything else goes through the copy engine
           NetKernels* nk = src_dev ? e->kernels : nullptr;
           if (nk && nk->copy_flag(dst, src + s.offset, s.len, st, 0, &s.kslot) == 0) {
-            cuda::event_destroy(s.event);
-            s.event = nullptr;
+            e->bytes_kernel += s.len;
           } else {
+            e->bytes_copy_engine += s.len;
             s.kslot = -1;
-            if (cuda::memcpy_async(dst, src + s.offset, s.len, st) != 0 || cuda::event_record(s.event, st) != 0) return -EIO;
+            if (cuda::event_create(&s.event) != 0 || cuda::memcpy_async(dst, src + s.offset, s.len, st) != 0 ||
+                cuda::event_record(s.event, st) != 0)
+              return -EIO;
           }
           s.posted = true;
           B200NET_TRACE_EVENT(SendWriteSegmentStart, dev_id, local_comm_id, r->seq, s.len, r);
@@ -631,6 +640,7 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
           if (rc == -EAGAIN) break;
           if (rc != 0) return rc;
           s.done += nbytes;
+          e->bytes_staged += nbytes;
         }
         s.complete = s.done >= s.len;
       } else {
@@ -638,7 +648,9 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
           s.posted = true;
           B200NET_TRACE_EVENT(SendWriteSegmentStart, dev_id, local_comm_id, r->seq, s.len, r);
         }
+        const size_t before = s.done;
         const int rc = e->fab.write_host(peer, r->target.buff_addr + s.offset, src + s.offset, s.len, &s.done);
+        e->bytes_host += s.done - before;
         if (rc != 0 && rc != -EAGAIN) return rc;
         s.complete = (rc == 0);
       }
@@ -773,6 +785,7 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
     h.size = size;
     const int rc = e->fab.send(peer, DgramType::EAGER, 0, &h, sizeof(h), eager_src, size);
     if (eager_slot >= 0) nk->eager_release(eager_slot);  // the datagram holds a copy
+    if (rc == 0) e->bytes_eager += size;
     if (rc == -EAGAIN) return 0;  // ring full: NCCL calls again
     if (rc != 0) return rc;
     auto* r = new RdmaSendReq();
