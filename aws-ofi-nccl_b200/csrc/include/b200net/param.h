@@ -121,6 +121,9 @@ struct Params {
   Param<uint64_t> eager_max_size{"EAGER_MAX_SIZE", 8192, "largest message sent eagerly (bytes); 0 disables eager"};
   Param<std::string> fault_drop{"FAULT_DROP", "",
                                 "testing: drop datagrams on send, 'type:count[,type:count]' with the numeric datagram type"};
+  Param<uint64_t> host_copy_threads{"HOST_COPY_THREADS", 4,
+                                    "worker threads for large host-to-host stripes (0: the calling thread copies)"};
+  Param<uint64_t> host_copy_min_size{"HOST_COPY_MIN_SIZE", 262144, "smallest stripe handed to a copy worker (bytes)"};
   Param<bool> copy_kernel{"COPY_KERNEL", true,
                           "move device payloads with the plugin's own copy / eager-pack kernels (0: copy engine only)"};
   Param<uint64_t> copy_kernel_ctas{"COPY_KERNEL_CTAS", 0, "CTAs per copy-kernel launch (0: chosen from the size)"};

@@ -12,6 +12,9 @@
 #include <sys/types.h>
 
 #include <cstdint>
+#include <condition_variable>
+#include <deque>
+#include <thread>
 #include <functional>
 #include <memory>
 #include <mutex>
@@ -147,6 +150,36 @@ class FabricEndpoint {
   std::mutex mr_mu_;
   std::unordered_map<int, int> drop_;  // DgramType -> remaining drops
   uint64_t dropped_ = 0, sent_ = 0, eagain_ = 0;
+};
+
+// Worker threads for large cross-memory writes: one proxy thread copying at memcpy speed is the
+// ceiling of the host path, several stripes copied at once are not. Jobs carry a shared status
+// word (0 pending, 1 done, negative errno) that the poster polls.
+class HostCopyPool {
+ public:
+  static HostCopyPool& instance();
+  // False when the pool is disabled (B200NET_HOST_COPY_THREADS=0) or could not start.
+  bool submit(uint32_t pid, uint64_t remote_addr, const void* local, size_t len, std::shared_ptr<std::atomic<int>> status);
+  int threads() const { return static_cast<int>(workers_.size()); }
+  void shutdown();   // joins the workers; the pool restarts on the next submit
+  uint64_t jobs_done() const { return done_.load(); }
+
+ private:
+  struct Job {
+    uint32_t pid;
+    uint64_t remote_addr;
+    const void* local;
+    size_t len;
+    std::shared_ptr<std::atomic<int>> status;
+  };
+  void run();
+  bool start_locked();
+  std::mutex mu_;
+  std::condition_variable cv_;
+  std::deque<Job> jobs_;
+  std::vector<std::thread> workers_;
+  bool stop_ = false;
+  std::atomic<uint64_t> done_{0};
 };
 
 // A named shared-memory window (ctrl mailboxes, GIN signal pages): created by its owner, mapped by

@@ -389,6 +389,47 @@ static int scenario_inflight_close(int sock) {
   return close_pair(&q);
 }
 
+// Large rendezvous messages, eight in flight: reports the one-way bandwidth of the host path.
+static int scenario_bandwidth(int sock) {
+  Pair p;
+  if (connect_pair(0, sock, &p)) return 1;
+  const size_t n = 16u << 20;
+  const int rounds = 6, window = 8;
+  std::vector<std::vector<uint8_t>> bufs(window, std::vector<uint8_t>(n));
+  for (int i = 0; i < window; ++i) fill(bufs[i], 100 + i + 50 * g_rank);
+  std::vector<void*> mhs(window);
+  void* comm = g_rank == 0 ? p.s : p.r;
+  for (int i = 0; i < window; ++i) OK(net->regMr(comm, bufs[i].data(), n, NCCL_PTR_HOST, &mhs[i]));
+  if (barrier(sock)) FAIL("barrier");
+  const auto t0 = Clock::now();
+  for (int r = 0; r < rounds; ++r) {
+    std::vector<void*> reqs(window);
+    for (int i = 0; i < window; ++i) {
+      if (g_rank == 0) {
+        if (post_send(p.s, bufs[i].data(), n, 9, mhs[i], &reqs[i])) return 1;
+      } else {
+        void* d = bufs[i].data();
+        size_t sz = n;
+        int tag = 9;
+        if (post_recv(p.r, 1, &d, &sz, &tag, &mhs[i], &reqs[i])) return 1;
+      }
+    }
+    if (wait_all(reqs)) return 1;
+  }
+  const double secs = std::chrono::duration<double>(Clock::now() - t0).count();
+  if (g_rank == 1) {
+    for (int i = 0; i < window; ++i) {
+      std::vector<uint8_t> want(n);
+      fill(want, 100 + i);
+      if (bufs[i] != want) FAIL("payload %d differs after the bandwidth run", i);
+    }
+    fprintf(stderr, "[rank 1] bandwidth: %.2f GB/s one way (%d x %d x %zu MiB in %.3f s)\n",
+            rounds * window * static_cast<double>(n) / secs / 1e9, rounds, window, n >> 20, secs);
+  }
+  for (int i = 0; i < window; ++i) OK(net->deregMr(comm, mhs[i]));
+  return close_pair(&p);
+}
+
 static int scenario_threads(int) {
   // each thread gets its own endpoint: 4 threads connect to themselves (loopback) concurrently
   std::vector<std::thread> th;
@@ -441,6 +482,7 @@ static const Scenario kScenarios[] = {
     {"pingpong", scenario_pingpong},         {"grouped_recv", scenario_grouped_recv},
     {"eager", scenario_eager},               {"reuse_listen", scenario_reuse_listen},
     {"inflight_close", scenario_inflight_close}, {"threads", scenario_threads},
+    {"bandwidth", scenario_bandwidth},
 };
 
 static int run_rank(const char* so, const char* only, int sock) {

@@ -186,6 +186,7 @@ int net_create_plugin(Plugin** out) {
 void net_destroy_plugin() {
   std::lock_guard<std::mutex> g(g_plugin_mu);
   if (!g_plugin || --g_plugin_refs > 0) return;
+  HostCopyPool::instance().shutdown();   // no thread of this library outlives the plugin
   delete g_plugin;
   g_plugin = nullptr;
   delete g_topo;

@@ -6,14 +6,17 @@
 //
 // The "wire" is the shared-memory fabric for host buffers and CUDA IPC mappings + copy-engine
 // copies on per-rail streams for device buffers; the protocol state machine is independent of it.
+#include <sched.h>
 #include <unistd.h>
 
+#include <atomic>
 #include <cerrno>
 #include <chrono>
 #include <cstring>
 #include <deque>
 #include <functional>
 #include <list>
+#include <memory>
 #include <set>
 
 #include "b200net/assert.h"
@@ -51,11 +54,17 @@ struct Stripe {
   cuda::Event event;   // non-null while a copy-engine transfer is in flight
   bool posted, complete, notified;
   int kslot = -1;      // completion slot of a copy-kernel transfer in flight
+  std::shared_ptr<std::atomic<int>> job;  // status of a stripe handed to a host copy worker
 };
 
 class RdmaSendReq : public Request {
  public:
   int test(int* done, int* sizes) override;
+  // A stripe still held by a copy worker reads this request's source buffer: wait for it.
+  ~RdmaSendReq() override {
+    for (Stripe& s : stripes)
+      while (s.job && s.job->load(std::memory_order_acquire) == 0) sched_yield();
+  }
   RdmaSendComm* comm = nullptr;
   void* data = nullptr;
   size_t size = 0;
@@ -648,11 +657,31 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
           s.posted = true;
           B200NET_TRACE_EVENT(SendWriteSegmentStart, dev_id, local_comm_id, r->seq, s.len, r);
         }
-        const size_t before = s.done;
-        const int rc = e->fab.write_host(peer, r->target.buff_addr + s.offset, src + s.offset, s.len, &s.done);
-        e->bytes_host += s.done - before;
-        if (rc != 0 && rc != -EAGAIN) return rc;
-        s.complete = (rc == 0);
+        if (s.job) {
+          // a copy worker has this stripe
+          const int st = s.job->load(std::memory_order_acquire);
+          if (st < 0) return st == -ESRCH ? -ENOTCONN : -EFAULT;
+          if (st == 1) {
+            s.done = s.len;
+            s.complete = true;
+            s.job.reset();
+          }
+        } else if (s.done == 0 && s.len >= params().host_copy_min_size.get() && peer->pid != static_cast<uint32_t>(getpid()) &&
+                   !e->fab.writes_are_staged(peer) && [&] {
+                     auto status = std::make_shared<std::atomic<int>>(0);
+                     if (!HostCopyPool::instance().submit(peer->pid, r->target.buff_addr + s.offset, src + s.offset, s.len, status))
+                       return false;
+                     s.job = std::move(status);
+                     return true;
+                   }()) {
+          e->bytes_host += s.len;
+        } else {
+          const size_t before = s.done;
+          const int rc = e->fab.write_host(peer, r->target.buff_addr + s.offset, src + s.offset, s.len, &s.done);
+          e->bytes_host += s.done - before;
+          if (rc != 0 && rc != -EAGAIN) return rc;
+          s.complete = (rc == 0);
+        }
       }
     }
     if (s.complete && !s.notified) {

@@ -253,6 +253,76 @@ int FabricEndpoint::write_host(PeerMapping* dst, uint64_t remote_addr, const voi
   return 0;
 }
 
+// ------------------------------------------------------------------------------------------ copy workers
+HostCopyPool& HostCopyPool::instance() {
+  static HostCopyPool* pool = new HostCopyPool();   // never destroyed: workers are joined by shutdown()
+  return *pool;
+}
+
+bool HostCopyPool::start_locked() {
+  if (!workers_.empty()) return true;
+  const int n = static_cast<int>(params().host_copy_threads.get());
+  if (n <= 0) return false;
+  stop_ = false;
+  try {
+    for (int i = 0; i < n; ++i) workers_.emplace_back([this] { run(); });
+  } catch (const std::exception&) {
+    return !workers_.empty();
+  }
+  return true;
+}
+
+bool HostCopyPool::submit(uint32_t pid, uint64_t remote_addr, const void* local, size_t len,
+                          std::shared_ptr<std::atomic<int>> status) {
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    if (!start_locked()) return false;
+    status->store(0, std::memory_order_relaxed);
+    jobs_.push_back(Job{pid, remote_addr, local, len, std::move(status)});
+  }
+  cv_.notify_one();
+  return true;
+}
+
+void HostCopyPool::run() {
+  for (;;) {
+    Job j;
+    {
+      std::unique_lock<std::mutex> lk(mu_);
+      cv_.wait(lk, [this] { return stop_ || !jobs_.empty(); });
+      if (jobs_.empty()) return;   // stop requested and nothing left
+      j = std::move(jobs_.front());
+      jobs_.pop_front();
+    }
+    int result = 1;
+    size_t done = 0;
+    while (done < j.len) {
+      iovec l{const_cast<char*>(static_cast<const char*>(j.local)) + done, j.len - done};
+      iovec r{reinterpret_cast<void*>(j.remote_addr + done), j.len - done};
+      const ssize_t n = process_vm_writev(static_cast<pid_t>(j.pid), &l, 1, &r, 1, 0);
+      if (n <= 0) {
+        result = n < 0 ? -errno : -EFAULT;
+        break;
+      }
+      done += static_cast<size_t>(n);
+    }
+    done_.fetch_add(1, std::memory_order_relaxed);
+    j.status->store(result, std::memory_order_release);
+  }
+}
+
+void HostCopyPool::shutdown() {
+  std::vector<std::thread> ws;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    stop_ = true;
+    ws.swap(workers_);
+  }
+  cv_.notify_all();
+  for (auto& t : ws)
+    if (t.joinable()) t.join();
+}
+
 int FabricEndpoint::read_host(PeerMapping* dst, uint64_t remote_addr, void* local, size_t len) {
   if (!dst) return -EINVAL;
   if (len == 0) return 0;
