@@ -121,8 +121,8 @@ struct Params {
   Param<uint64_t> eager_max_size{"EAGER_MAX_SIZE", 8192, "largest message sent eagerly (bytes); 0 disables eager"};
   Param<std::string> fault_drop{"FAULT_DROP", "",
                                 "testing: drop datagrams on send, 'type:count[,type:count]' with the numeric datagram type"};
-  Param<uint64_t> host_copy_threads{"HOST_COPY_THREADS", 4,
-                                    "worker threads for large host-to-host stripes (0: the calling thread copies)"};
+  Param<uint64_t> host_copy_threads{"HOST_COPY_THREADS", 0,
+                                    "worker threads for large host-to-host stripes (0, the default: the calling thread copies)"};
   Param<uint64_t> host_copy_min_size{"HOST_COPY_MIN_SIZE", 262144, "smallest stripe handed to a copy worker (bytes)"};
   Param<bool> copy_kernel{"COPY_KERNEL", true,
                           "move device payloads with the plugin's own copy / eager-pack kernels (0: copy engine only)"};
@@ -154,9 +154,10 @@ struct Params {
                                true,
 #endif
                                "use error-checking mutexes"};
-  Param<bool> disable_dmabuf{"DISABLE_DMABUF", true,
-                             "do not advertise dma-buf registration (default: peers are reached through IPC / VMM "
-                             "mappings, a dma-buf descriptor adds nothing, and NCCL's export of its own buffers can fail)"};
+  Param<bool> disable_dmabuf{"DISABLE_DMABUF", false,
+                             "do not advertise dma-buf registration (peers are reached through IPC / VMM mappings, a "
+                             "dma-buf descriptor adds nothing; NCCL's export of its own buffers failed with it when "
+                             "NCCL_NET_GDR_LEVEL=SYS forced device buffers through)"};
   Param<bool> cuda_flush_enable{"CUDA_FLUSH_ENABLE", false, "flush with the driver instead of a fence"};
   Param<bool> disable_cma{"DISABLE_CMA", false, "never use cross-memory attach for host rendezvous writes"};
   Param<bool> nvls_enable{"NVLS_ENABLE", true, "use NVSwitch multicast where available"};
