@@ -389,6 +389,117 @@ static int scenario_inflight_close(int sock) {
   return close_pair(&q);
 }
 
+// The access pattern of NCCL's proxy thread: several channels, each a connection in both
+// directions, every channel keeps up to eight receives posted and eight chunk-sized sends in
+// flight, and ONE thread per process drives all of them round-robin with isend / irecv / test,
+// never blocking on any single request. Every chunk carries its channel and step in its first
+// bytes and is checked on arrival.
+static int scenario_proxy_pattern(int sock) {
+  const int channels = getenv("FUNC_NET_PROXY_CHANNELS") ? atoi(getenv("FUNC_NET_PROXY_CHANNELS")) : 8;
+  const int steps = 8, chunks_per_channel = 48;
+  const size_t chunk = getenv("FUNC_NET_PROXY_CHUNK") ? strtoul(getenv("FUNC_NET_PROXY_CHUNK"), nullptr, 0) : (1u << 20);
+  struct Chan {
+    Pair p;
+    std::vector<std::vector<uint8_t>> sbuf, rbuf;
+    std::vector<void*> smh, rmh, sreq, rreq;
+    std::vector<int> rreq_chunk, sreq_chunk;
+    int sent = 0, send_done = 0, posted = 0, recv_done = 0;
+  };
+  std::vector<Chan> ch(channels);
+  for (int c = 0; c < channels; ++c) {
+    if (connect_pair(0, sock, &ch[c].p)) return 1;
+    ch[c].sbuf.assign(steps, std::vector<uint8_t>(chunk));
+    ch[c].rbuf.assign(steps, std::vector<uint8_t>(chunk));
+    ch[c].smh.assign(steps, nullptr);
+    ch[c].rmh.assign(steps, nullptr);
+    ch[c].sreq.assign(steps, nullptr);
+    ch[c].rreq.assign(steps, nullptr);
+    ch[c].rreq_chunk.assign(steps, -1);
+    ch[c].sreq_chunk.assign(steps, -1);
+    for (int s = 0; s < steps; ++s) {
+      OK(net->regMr(ch[c].p.s, ch[c].sbuf[s].data(), chunk, NCCL_PTR_HOST, &ch[c].smh[s]));
+      OK(net->regMr(ch[c].p.r, ch[c].rbuf[s].data(), chunk, NCCL_PTR_HOST, &ch[c].rmh[s]));
+    }
+  }
+  if (barrier(sock)) FAIL("barrier");
+  auto stamp = [&](std::vector<uint8_t>& b, int c, int k) {
+    uint32_t hdr[4] = {0xC0FFEEu, static_cast<uint32_t>(g_rank), static_cast<uint32_t>(c), static_cast<uint32_t>(k)};
+    memcpy(b.data(), hdr, sizeof(hdr));
+    b[chunk - 1] = static_cast<uint8_t>(c * 31 + k);
+  };
+  auto t0 = Clock::now();
+  long done_total = 0;
+  const long want_total = 2L * channels * chunks_per_channel;
+  while (done_total < want_total) {
+    for (int c = 0; c < channels; ++c) {
+      Chan& x = ch[c];
+      // keep receives posted ahead
+      while (x.posted < chunks_per_channel && x.posted - x.recv_done < steps) {
+        const int slot = x.posted % steps;
+        void* d = x.rbuf[slot].data();
+        size_t sz = chunk;
+        int tag = c;
+        void* req = nullptr;
+        OK(net->irecv(x.p.r, 1, &d, &sz, &tag, &x.rmh[slot], nullptr, &req));
+        if (!req) break;
+        x.rreq[slot] = req;
+        x.rreq_chunk[slot] = x.posted++;
+      }
+      // keep sends in flight
+      while (x.sent < chunks_per_channel && x.sent - x.send_done < steps) {
+        const int slot = x.sent % steps;
+        stamp(x.sbuf[slot], c, x.sent);
+        void* req = nullptr;
+        OK(net->isend(x.p.s, x.sbuf[slot].data(), chunk, c, x.smh[slot], nullptr, &req));
+        if (!req) break;
+        x.sreq[slot] = req;
+        x.sreq_chunk[slot] = x.sent++;
+      }
+      // poll the oldest outstanding request of each kind (NCCL completes them in order)
+      if (x.send_done < x.sent) {
+        const int slot = x.send_done % steps;
+        int d = 0;
+        OK(net->test(x.sreq[slot], &d, nullptr));
+        if (d) {
+          ++x.send_done;
+          ++done_total;
+        }
+      }
+      if (x.recv_done < x.posted) {
+        const int slot = x.recv_done % steps;
+        int d = 0, sz = 0;
+        OK(net->test(x.rreq[slot], &d, &sz));
+        if (d) {
+          uint32_t hdr[4];
+          memcpy(hdr, x.rbuf[slot].data(), sizeof(hdr));
+          const int k = x.rreq_chunk[slot];
+          if (sz != static_cast<int>(chunk) || hdr[0] != 0xC0FFEEu || hdr[1] != static_cast<uint32_t>(1 - g_rank) ||
+              hdr[2] != static_cast<uint32_t>(c) || hdr[3] != static_cast<uint32_t>(k) ||
+              x.rbuf[slot][chunk - 1] != static_cast<uint8_t>(c * 31 + k))
+            FAIL("channel %d chunk %d arrived wrong (size %d, hdr %x %u %u %u)", c, k, sz, hdr[0], hdr[1], hdr[2], hdr[3]);
+          ++x.recv_done;
+          ++done_total;
+        }
+      }
+    }
+    if (expired(t0, 60)) {
+      for (int c = 0; c < channels; ++c)
+        fprintf(stderr, "[rank %d] channel %d: sent %d/%d done, posted %d recv done %d\n", g_rank, c, ch[c].sent, ch[c].send_done,
+                ch[c].posted, ch[c].recv_done);
+      FAIL("proxy pattern stalled at %ld of %ld completions", done_total, want_total);
+    }
+  }
+  if (barrier(sock)) FAIL("barrier");
+  for (int c = 0; c < channels; ++c) {
+    for (int s = 0; s < steps; ++s) {
+      OK(net->deregMr(ch[c].p.s, ch[c].smh[s]));
+      OK(net->deregMr(ch[c].p.r, ch[c].rmh[s]));
+    }
+    if (close_pair(&ch[c].p)) return 1;
+  }
+  return 0;
+}
+
 // Large rendezvous messages, eight in flight: reports the one-way bandwidth of the host path.
 static int scenario_bandwidth(int sock) {
   Pair p;
@@ -482,7 +593,7 @@ static const Scenario kScenarios[] = {
     {"pingpong", scenario_pingpong},         {"grouped_recv", scenario_grouped_recv},
     {"eager", scenario_eager},               {"reuse_listen", scenario_reuse_listen},
     {"inflight_close", scenario_inflight_close}, {"threads", scenario_threads},
-    {"bandwidth", scenario_bandwidth},
+    {"bandwidth", scenario_bandwidth},       {"proxy_pattern", scenario_proxy_pattern},
 };
 
 static int run_rank(const char* so, const char* only, int sock) {

@@ -76,6 +76,7 @@ class RdmaSendReq : public Request {
   CtrlEntry target{};       // copy of the control entry this send writes into
   std::vector<Stripe> stripes;
   std::vector<uint8_t> bounce;  // host copy of a device source that must travel through host memory
+  uint64_t serial = 0;          // unique per endpoint; queued retries name the request by it
 };
 
 struct SubRecv {
@@ -157,7 +158,10 @@ class RdmaEndpoint : public Endpoint {
   std::vector<cuda::Stream> streams;
   std::map<std::pair<uint32_t, uint64_t>, void*> ipc_maps;  // (peer pid, mr key) -> mapped base
   std::set<std::pair<MrHandle*, int>> published;
-  std::set<RdmaSendReq*> live_send_reqs;  // requests a queued retry may still touch
+  // Requests a queued retry may still touch, by serial number: a request's address can be handed
+  // out again (to another communicator's request) while an old retry for it is still queued.
+  std::map<uint64_t, RdmaSendReq*> live_send_reqs;
+  uint64_t next_req_serial = 1;
   bool in_progress = false;
 };
 
@@ -764,14 +768,16 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
     B200NET_TRACE_EVENT(Send, dev_id, local_comm_id, r->seq, r->size, r);
     consume_entry(idx, n);
     ++inflight;
-    e->live_send_reqs.insert(r);
+    r->serial = e->next_req_serial++;
+    e->live_send_reqs[r->serial] = r;
     const int prc = post_stripes(r);
     if (prc != 0 && prc != -EAGAIN) {
       r->state = ReqState::ERROR;
     } else if (prc == -EAGAIN) {
       B200NET_TRACE_EVENT(PendingQueueInsert, dev_id, local_comm_id, r->seq, r->size, r);
-      e->pending.push_back([this, e, r]() {
-        if (!e->live_send_reqs.count(r) || r->state != ReqState::PENDING) return 0;
+      e->pending.push_back([this, e, r, serial = r->serial]() {
+        auto live = e->live_send_reqs.find(serial);
+        if (live == e->live_send_reqs.end() || live->second != r || r->state != ReqState::PENDING) return 0;
         const int rc2 = post_stripes(r);
         if (rc2 != 0 && rc2 != -EAGAIN) r->state = ReqState::ERROR;
         return rc2 == -EAGAIN ? -EAGAIN : 0;
@@ -847,7 +853,7 @@ int RdmaSendReq::test(int* done, int* sizes) {
   }
   if (state == ReqState::ERROR) {
     --comm->inflight;
-    e->live_send_reqs.erase(this);
+    e->live_send_reqs.erase(serial);
     delete this;
     return -EIO;
   }
@@ -856,7 +862,7 @@ int RdmaSendReq::test(int* done, int* sizes) {
     if (sizes) sizes[0] = static_cast<int>(size);
     B200NET_TRACE_EVENT(SendEnd, comm->dev_id, comm->local_comm_id, seq, size, this);
     --comm->inflight;
-    e->live_send_reqs.erase(this);
+    e->live_send_reqs.erase(serial);
     delete this;
   }
   return 0;

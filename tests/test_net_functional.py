@@ -29,6 +29,17 @@ def test_two_process_scenarios(built, env):
     _run(built, env)
 
 
+@pytest.mark.parametrize("threads", ["0", "4"])
+def test_proxy_pattern_with_many_channels_in_flight(built, threads):
+    """Eight channels, eight chunk-sized sends in flight each, one driving thread per process (the
+    way NCCL's proxy uses a net plugin), with and without the host copy workers: this is the pattern
+    that exposed queued retries naming a recycled request address."""
+    env = {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4", "B200NET_HOST_COPY_THREADS": threads,
+           "FUNC_NET_PROXY_CHUNK": str(4 << 20)}
+    for _ in range(3):
+        _run(built, env, "proxy_pattern")
+
+
 def test_compat_env_prefix_is_honoured(built):
     # the reference's variable names keep working
     _run(built, {"OFI_NCCL_PROTOCOL": "RDMA", "OFI_NCCL_FORCE_NUM_RAILS": "2"}, "pingpong")
