@@ -36,7 +36,7 @@ def test_address_and_undefined_behaviour():
     tests, so = _build("address,undefined")
     for exe in sorted(tests.glob("unit_*")):
         _run([exe])
-    scenarios = ["connection", "message_transfer", "pingpong", "grouped_recv", "eager", "reuse_listen", "threads", "bandwidth"]
+    scenarios = ["connection", "message_transfer", "pingpong", "grouped_recv", "eager", "reuse_listen", "threads", "bandwidth", "proxy_pattern"]
     for proto in ("SENDRECV", "RDMA"):
         for sc in scenarios:
             # leak checking stays on for the single-process unit tests only: LeakSanitizer's report
@@ -56,4 +56,7 @@ def test_thread_sanitizer():
         _run([exe])
     _run([tests / "func_net", so, "threads"], {"B200NET_PROTOCOL": "RDMA"})
     # the copy workers and the proxy thread share stripes' status words
-    _run([tests / "func_net", so, "bandwidth"], {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4"})
+    _run([tests / "func_net", so, "bandwidth"], {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4",
+                                                  "B200NET_HOST_COPY_THREADS": "4"})
+    _run([tests / "func_net", so, "proxy_pattern"], {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4",
+                                                      "B200NET_HOST_COPY_THREADS": "4"})
