@@ -489,6 +489,11 @@ static int scenario_proxy_pattern(int sock) {
       FAIL("proxy pattern stalled at %ld of %ld completions", done_total, want_total);
     }
   }
+  if (g_rank == 0) {
+    const double secs = std::chrono::duration<double>(Clock::now() - t0).count();
+    fprintf(stderr, "[rank 0] proxy pattern: %.2f GB/s per direction (%d channels x %d chunks of %zu KiB in %.3f s)\n",
+            static_cast<double>(channels) * chunks_per_channel * chunk / secs / 1e9, channels, chunks_per_channel, chunk >> 10, secs);
+  }
   if (barrier(sock)) FAIL("barrier");
   for (int c = 0; c < channels; ++c) {
     for (int s = 0; s < steps; ++s) {
