@@ -124,6 +124,10 @@ struct Params {
   Param<uint64_t> host_copy_threads{"HOST_COPY_THREADS", 0,
                                     "worker threads for large host-to-host stripes (0, the default: the calling thread copies)"};
   Param<uint64_t> host_copy_min_size{"HOST_COPY_MIN_SIZE", 262144, "smallest stripe handed to a copy worker (bytes)"};
+  Param<bool> nccl_device_buffers{"NCCL_DEVICE_BUFFERS", false,
+                                  "make NCCL hand its device buffers to the plugin (sets NCCL_NET_GDR_LEVEL=SYS and "
+                                  "NCCL_NET_GDR_READ=1, stops advertising dma-buf): payloads then move with the copy "
+                                  "kernels over NVLink instead of through host memory"};
   Param<bool> copy_kernel{"COPY_KERNEL", true,
                           "move device payloads with the plugin's own copy / eager-pack kernels (0: copy engine only)"};
   Param<uint64_t> copy_kernel_ctas{"COPY_KERNEL_CTAS", 0, "CTAs per copy-kernel launch (0: chosen from the size)"};

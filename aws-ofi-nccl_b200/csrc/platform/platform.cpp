@@ -27,8 +27,15 @@ std::vector<std::pair<std::string, std::string>> PlatformB200::nccl_env() const 
   // transport's virtual NIC keeps NCCL's own chunks in host memory. Forcing device buffers through
   // (NCCL_NET_GDR_LEVEL=SYS) stalled NCCL's first collective: the peer buffer is mapped on first use,
   // from the proxy thread, while NCCL's kernel is already waiting for that very transfer.
-  return {{"NCCL_BUFFSIZE", "33554432"}, {"NCCL_P2P_NET_CHUNKSIZE", "4194304"}, {"NCCL_NVLS_CHUNKSIZE", "524288"},
-          {"NCCL_NET_FORCE_FLUSH", "0"}};
+  std::vector<std::pair<std::string, std::string>> env = {{"NCCL_BUFFSIZE", "33554432"},
+                                                          {"NCCL_P2P_NET_CHUNKSIZE", "4194304"},
+                                                          {"NCCL_NVLS_CHUNKSIZE", "524288"},
+                                                          {"NCCL_NET_FORCE_FLUSH", "0"}};
+  if (params().nccl_device_buffers.get()) {   // opt-in, see the comment above
+    env.emplace_back("NCCL_NET_GDR_LEVEL", "SYS");
+    env.emplace_back("NCCL_NET_GDR_READ", "1");
+  }
+  return env;
 }
 
 std::string PlatformB200::log_error_hint(int err) const {

@@ -102,7 +102,8 @@ int fill_common_properties(Device* d, Properties* p, int rails) {
   p->port_speed_mbps = HOST_PATH_MBPS;
   if (d->gpu_ordinal >= 0 && g_topo && d->gpu_ordinal < g_topo->num_gpus()) {
     p->ptr_support |= NCCL_PTR_CUDA;
-    if (!params().disable_dmabuf.get() && cuda::dmabuf_supported(d->gpu_ordinal)) p->ptr_support |= NCCL_PTR_DMABUF;
+    if (!params().disable_dmabuf.get() && !params().nccl_device_buffers.get() && cuda::dmabuf_supported(d->gpu_ordinal))
+      p->ptr_support |= NCCL_PTR_DMABUF;
     p->pci_path = pci_path_of_gpu(g_topo->gpu(d->gpu_ordinal).pci_bus_id);
     p->port_speed_mbps = g_topo->all_nvlink() ? NVLINK5_GPU_MBPS : 256000;  // PCIe gen5 x16 otherwise
   }
