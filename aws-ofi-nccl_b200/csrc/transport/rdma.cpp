@@ -154,7 +154,7 @@ class RdmaEndpoint : public Endpoint {
   IdPool comm_ids{NET_MAX_COMMS};
   std::map<uint32_t, RdmaSendComm*> send_comms;
   std::map<uint32_t, RdmaRecvComm*> recv_comms;
-  std::deque<std::function<int()>> pending;  // posts that hit -EAGAIN; retried in order
+  std::deque<std::function<int()>> pending;  // posts that met a full ring (-EAGAIN); retried in order
   std::vector<cuda::Stream> streams;
   std::map<std::pair<uint32_t, uint64_t>, void*> ipc_maps;  // (peer pid, mr key) -> mapped base
   std::set<std::pair<MrHandle*, int>> published;
@@ -600,6 +600,7 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
   const bool src_dev = !r->bounce.empty() ? false : !cuda::is_host_pointer(r->data);
   const char* src = r->bounce.empty() ? static_cast<const char*>(r->data) : reinterpret_cast<const char*>(r->bounce.data());
   bool all_done = true;
+  bool back_pressure = false;   // some ring was full: the post must be retried in order
   for (Stripe& s : r->stripes) {
     if (!s.complete) {
       if (kind == static_cast<uint32_t>(MrKind::CUDA_IPC)) {
@@ -650,7 +651,10 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
           DeviceFragHdr fh{r->target.buff_addr + s.offset + s.done, static_cast<uint32_t>(nbytes), 0};
           const int rc = e->fab.send(peer, static_cast<DgramType>(DGRAM_DEVICE_FRAG), 0, &fh, sizeof(fh),
                                      src + s.offset + s.done, nbytes);
-          if (rc == -EAGAIN) break;
+          if (rc == -EAGAIN) {
+            back_pressure = true;
+            break;
+          }
           if (rc != 0) return rc;
           s.done += nbytes;
           e->bytes_staged += nbytes;
@@ -684,6 +688,7 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
           const int rc = e->fab.write_host(peer, r->target.buff_addr + s.offset, src + s.offset, s.len, &s.done);
           e->bytes_host += s.done - before;
           if (rc != 0 && rc != -EAGAIN) return rc;
+          if (rc == -EAGAIN) back_pressure = true;
           s.complete = (rc == 0);
         }
       }
@@ -700,6 +705,8 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
         B200NET_TRACE_EVENT(SendWriteSegmentComplete, dev_id, local_comm_id, r->seq, s.len, r);
       } else if (rc != -EAGAIN) {
         return rc;
+      } else {
+        back_pressure = true;
       }
     }
     if (!s.notified) all_done = false;
@@ -709,7 +716,9 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
     r->state = ReqState::COMPLETED;
     return 0;
   }
-  return -EAGAIN;
+  // -EAGAIN: a ring was full, retry in order. -EINPROGRESS: only the request's own copies (kernel,
+  // copy engine, copy worker) are outstanding; test() polls them, nothing has to be queued.
+  return back_pressure ? -EAGAIN : -EINPROGRESS;
 }
 
 int RdmaSendComm::start_rendezvous(RdmaSendReq* r, const CtrlEntry& e) {
@@ -771,7 +780,7 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
     r->serial = e->next_req_serial++;
     e->live_send_reqs[r->serial] = r;
     const int prc = post_stripes(r);
-    if (prc != 0 && prc != -EAGAIN) {
+    if (prc != 0 && prc != -EAGAIN && prc != -EINPROGRESS) {
       r->state = ReqState::ERROR;
     } else if (prc == -EAGAIN) {
       B200NET_TRACE_EVENT(PendingQueueInsert, dev_id, local_comm_id, r->seq, r->size, r);
@@ -779,7 +788,7 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
         auto live = e->live_send_reqs.find(serial);
         if (live == e->live_send_reqs.end() || live->second != r || r->state != ReqState::PENDING) return 0;
         const int rc2 = post_stripes(r);
-        if (rc2 != 0 && rc2 != -EAGAIN) r->state = ReqState::ERROR;
+        if (rc2 != 0 && rc2 != -EAGAIN && rc2 != -EINPROGRESS) r->state = ReqState::ERROR;
         return rc2 == -EAGAIN ? -EAGAIN : 0;
       });
     }
@@ -849,7 +858,7 @@ int RdmaSendReq::test(int* done, int* sizes) {
   if (state == ReqState::PENDING && eager) comm->bind_eager_queue();
   if (state == ReqState::PENDING && !eager) {
     const int rc = comm->post_stripes(this);
-    if (rc != 0 && rc != -EAGAIN) state = ReqState::ERROR;
+    if (rc != 0 && rc != -EAGAIN && rc != -EINPROGRESS) state = ReqState::ERROR;
   }
   if (state == ReqState::ERROR) {
     --comm->inflight;
