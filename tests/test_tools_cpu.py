@@ -43,3 +43,51 @@ def test_plugin_links_no_cuda_library_and_imports_no_cuda_symbol(built):
     bad = [ln.split()[-1] for ln in undefined.splitlines() if ln.split() and ln.split()[-1].split("@")[0].startswith(("cu", "nccl"))
            and not ln.split()[-1].startswith("__cu")]
     assert not bad, bad
+
+
+def test_calibration_table_feeds_the_measured_tuner(built, tmp_path, monkeypatch):
+    """tuner_calibrate merges the per-(algorithm, protocol) jobs into the table format the plugin's
+    measured tuner parses; the jobs themselves (torchrun on GPUs) are replaced by canned timings in
+    which Ring/LL wins below 64 KiB and Ring/Simple above."""
+    from aws_ofi_nccl_b200.utils import tuner_calibrate as tc
+
+    def fake_run(cmd, capture_output, text, timeout, env):
+        algo, proto = env["NCCL_ALGO"], env["NCCL_PROTO"]
+
+        class R:
+            returncode = 0
+            stdout = ""
+            stderr = ""
+        r = R()
+        if algo != "Ring":
+            r.returncode = 1   # "not available here"
+            return r
+        rows = []
+        for size in (1 << 10, 1 << 14, 1 << 18, 1 << 22, 1 << 26):
+            if proto == "LL":
+                t = 10.0 + size / 20e3      # low latency, poor bandwidth (us)
+            elif proto == "Simple":
+                t = 30.0 + size / 300e3     # high latency, good bandwidth
+            else:
+                continue
+            rows.append({"coll": tc.COLLS["all_reduce"], "bytes": size, "time_us": t})
+        r.stdout = "noise\nCALIBRATION_ROWS " + json.dumps(rows) + "\n"
+        return r
+
+    monkeypatch.setattr(tc.subprocess, "run", fake_run)
+    table = tmp_path / "measured.json"
+    assert tc.main(["--gpus", "8", "--out", str(table), "--algos", "Ring", "Tree", "--protos", "LL", "Simple"]) == 0
+    doc = json.loads(table.read_text())
+    assert doc["world"] == 8 and len(doc["rows"]) == 10
+    assert {(r["algo"], r["proto"]) for r in doc["rows"]} == {(tc.ALGOS["Ring"], tc.PROTOS["LL"]), (tc.ALGOS["Ring"], tc.PROTOS["Simple"])}
+    monkeypatch.undo()
+    res = subprocess.run([sys.executable, "-m", "aws_ofi_nccl_b200.utils.tuner_cli", "--json", "--platform", "DGX B200",
+                          "--nodes", "1", "--tuner-type", "Measured", "--table", str(table), "--collectives", "all_reduce"],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-2000:]
+    (out,) = json.loads(res.stdout)
+    rows = out["collectives"]["all_reduce"]
+    assert rows[0]["decision"][:2] == ["Ring", "LL"] and rows[-1]["decision"][:2] == ["Ring", "Simple"]
+    # the crossover of the two canned cost lines is at 20 us * (1 / (1/20e3 - 1/300e3)) = 428 571 bytes
+    switch = next(r["from_bytes"] for r in rows if r["decision"][1] == "Simple")
+    assert 64 << 10 < switch < 4 << 20
