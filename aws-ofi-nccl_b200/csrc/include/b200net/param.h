@@ -123,7 +123,7 @@ struct Params {
                                 "testing: drop datagrams on send, 'type:count[,type:count]' with the numeric datagram type"};
   Param<uint64_t> host_copy_threads{"HOST_COPY_THREADS", 0,
                                     "worker threads for large host-to-host stripes (0, the default: the calling thread copies)"};
-  Param<uint64_t> host_copy_min_size{"HOST_COPY_MIN_SIZE", 262144, "smallest stripe handed to a copy worker (bytes)"};
+  Param<uint64_t> host_copy_min_size{"HOST_COPY_MIN_SIZE", 65536, "smallest stripe handed to a copy worker (bytes)"};
   Param<bool> nccl_device_buffers{"NCCL_DEVICE_BUFFERS", false,
                                   "make NCCL hand its device buffers to the plugin (sets NCCL_NET_GDR_LEVEL=SYS and "
                                   "NCCL_NET_GDR_READ=1, stops advertising dma-buf): payloads then move with the copy "

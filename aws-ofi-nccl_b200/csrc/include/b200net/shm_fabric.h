@@ -179,6 +179,8 @@ class HostCopyPool {
   std::deque<Job> jobs_;
   std::vector<std::thread> workers_;
   bool stop_ = false;
+  std::atomic<bool> stop_flag_{false};
+  std::atomic<int> queued_{0};
   std::atomic<uint64_t> done_{0};
 };
 

@@ -10,6 +10,7 @@
 
 #include <atomic>
 #include <cerrno>
+#include <chrono>
 #include <cstring>
 #include <stdexcept>
 
@@ -264,6 +265,7 @@ bool HostCopyPool::start_locked() {
   const int n = static_cast<int>(params().host_copy_threads.get());
   if (n <= 0) return false;
   stop_ = false;
+  stop_flag_.store(false);
   try {
     for (int i = 0; i < n; ++i) workers_.emplace_back([this] { run(); });
   } catch (const std::exception&) {
@@ -279,20 +281,43 @@ bool HostCopyPool::submit(uint32_t pid, uint64_t remote_addr, const void* local,
     if (!start_locked()) return false;
     status->store(0, std::memory_order_relaxed);
     jobs_.push_back(Job{pid, remote_addr, local, len, std::move(status)});
+    queued_.fetch_add(1, std::memory_order_release);
   }
   cv_.notify_one();
   return true;
 }
 
 void HostCopyPool::run() {
+  using clock = std::chrono::steady_clock;
   for (;;) {
     Job j;
-    {
+    bool have = false;
+    // Stripes arrive in bursts (one per rail of a chunk, a chunk per channel): poll for a short
+    // while before sleeping, so the next stripe does not pay a futex wake-up.
+    const auto spin_until = clock::now() + std::chrono::microseconds(100);
+    while (!have && clock::now() < spin_until) {
+      if (queued_.load(std::memory_order_acquire) > 0) {
+        std::lock_guard<std::mutex> g(mu_);
+        if (!jobs_.empty()) {
+          j = std::move(jobs_.front());
+          jobs_.pop_front();
+          queued_.fetch_sub(1, std::memory_order_relaxed);
+          have = true;
+        }
+      } else {
+#if defined(__x86_64__)
+        __builtin_ia32_pause();
+#endif
+      }
+      if (stop_flag_.load(std::memory_order_relaxed)) break;
+    }
+    if (!have) {
       std::unique_lock<std::mutex> lk(mu_);
       cv_.wait(lk, [this] { return stop_ || !jobs_.empty(); });
       if (jobs_.empty()) return;   // stop requested and nothing left
       j = std::move(jobs_.front());
       jobs_.pop_front();
+      queued_.fetch_sub(1, std::memory_order_relaxed);
     }
     int result = 1;
     size_t done = 0;
@@ -316,6 +341,7 @@ void HostCopyPool::shutdown() {
   {
     std::lock_guard<std::mutex> g(mu_);
     stop_ = true;
+    stop_flag_.store(true);
     ws.swap(workers_);
   }
   cv_.notify_all();
