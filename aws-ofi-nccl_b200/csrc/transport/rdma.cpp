@@ -710,7 +710,6 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
       }
     }
     if (!s.notified) all_done = false;
-    (void)src_dev;
   }
   if (all_done) {
     r->state = ReqState::COMPLETED;
