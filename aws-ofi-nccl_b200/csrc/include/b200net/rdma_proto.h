@@ -39,6 +39,28 @@ struct CtrlMsg {
 static_assert(sizeof(CtrlMsg) == 512, "a control message is 8 entries");
 constexpr size_t MAILBOX_BYTES = sizeof(CtrlMsg) * MAILBOX_SLOTS;
 
+// An entry is valid for sequence number `seq` when its ready word carries exactly that number:
+// a slot still holding the group of 256 sequence numbers ago does not match.
+inline bool entry_ready(const CtrlEntry& e, uint16_t seq) {
+  return e.ready.load(std::memory_order_acquire) == static_cast<uint16_t>(CTRL_READY | (seq & SEQ_MASK));
+}
+
+// The sender's matching rule for one receive group (mailbox slot): the whole group must have
+// arrived; among its entries not yet taken (`consumed` bit mask) the first with the send's tag
+// wins. Returns the entry index, -1 when the group is not (completely) there yet, -2 when it is
+// there but holds no free entry with this tag. *num_recvs receives the group size.
+inline int match_entry(const CtrlMsg& slot, uint16_t seq, uint8_t consumed, int tag, int* num_recvs) {
+  if (!entry_ready(slot.entries[0], seq)) return -1;
+  const int n = slot.entries[0].num_recvs;
+  if (n < 1 || n > MAX_RECVS) return -1;
+  for (int i = 1; i < n; ++i)
+    if (!entry_ready(slot.entries[i], seq)) return -1;
+  *num_recvs = n;
+  for (int i = 0; i < n; ++i)
+    if (!(consumed & (1u << i)) && slot.entries[i].tag == tag) return i;
+  return -2;
+}
+
 inline bool seq_before(uint16_t a, uint16_t b) {  // a strictly before b in the wrapping 10-bit space
   return a != b && (((b - a) & SEQ_MASK) < (1u << (SEQ_BITS - 1)));
 }

@@ -558,23 +558,6 @@ void RdmaSendComm::consume_entry(int idx, int num_recvs) {
   }
 }
 
-static bool entry_ready(const CtrlEntry& e, uint16_t seq) {
-  return e.ready.load(std::memory_order_acquire) == static_cast<uint16_t>(CTRL_READY | (seq & SEQ_MASK));
-}
-
-// Find the control entry of the current group that a send with `tag` goes to: the first entry not
-// yet taken whose tag matches. -1: the group is not (fully) posted yet or has no such entry.
-static int match_entry(const CtrlMsg& slot, uint16_t seq, uint8_t consumed, int tag, int* num_recvs) {
-  if (!entry_ready(slot.entries[0], seq)) return -1;
-  const int n = slot.entries[0].num_recvs;
-  if (n < 1 || n > MAX_RECVS) return -1;
-  for (int i = 1; i < n; ++i)
-    if (!entry_ready(slot.entries[i], seq)) return -1;
-  *num_recvs = n;
-  for (int i = 0; i < n; ++i)
-    if (!(consumed & (1u << i)) && slot.entries[i].tag == tag) return i;
-  return -2;
-}
 
 // Bind queued eager sends (head first, never skipping) to control entries that have arrived.
 void RdmaSendComm::bind_eager_queue() {
