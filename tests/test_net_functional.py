@@ -40,6 +40,15 @@ def test_proxy_pattern_with_many_channels_in_flight(built, threads):
         _run(built, env, "proxy_pattern")
 
 
+@pytest.mark.parametrize("proto,rails,ranks", [("RDMA", "4", 4), ("RDMA", "1", 3), ("SENDRECV", "1", 4)])
+def test_ring_of_processes(built, proto, rails, ranks):
+    """N ranks in a ring, 32 sends and 32 receives in flight per rank and round, flush, byte-exact."""
+    env = dict(os.environ, B200NET_PROTOCOL=proto, B200NET_FORCE_NUM_RAILS=rails)
+    cmd = [str(built / "tests" / "func_ring"), str(built / "libnccl-net-ofi-b200.so"), str(ranks)]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=built)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+
+
 def test_compat_env_prefix_is_honoured(built):
     # the reference's variable names keep working
     _run(built, {"OFI_NCCL_PROTOCOL": "RDMA", "OFI_NCCL_FORCE_NUM_RAILS": "2"}, "pingpong")
