@@ -187,10 +187,23 @@ def build_tests(force: bool = False, sanitize: str | None = None) -> list[Path]:
     return outs
 
 
+def build_fake_cuda(force: bool = False) -> Path:
+    """The stand-in driver for CPU tests of the device-buffer paths: lib/tests/fake_cuda/libcuda.so.1."""
+    src = CSRC / "tests" / "fake_cuda" / "fake_libcuda.cpp"
+    outdir = LIB / "tests" / "fake_cuda"
+    outdir.mkdir(parents=True, exist_ok=True)
+    out = outdir / "libcuda.so.1"
+    if force or _stale(out, [src]):
+        _run([CXX, "-std=c++20", "-O1", "-g", "-fPIC", "-shared", "-I", f"{CUDA_HOME}/include", str(src), "-o", str(out),
+              "-pthread", "-lrt"])
+    return out
+
+
 def build_all(force: bool = False) -> None:
     build_kernels(force)
     build_host(force)
     build_tests(force)
+    build_fake_cuda(force)
 
 
 if __name__ == "__main__":

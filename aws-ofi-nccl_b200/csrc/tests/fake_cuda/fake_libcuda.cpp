@@ -1,0 +1,368 @@
+// A stand-in for libcuda.so.1 for CPU tests of the plugin's device-buffer paths. "Device memory"
+// is POSIX shared memory, so legacy IPC handles really do map one process's buffer into another;
+// copies are memcpy; streams and events complete at once; the two kernels of the plugin's embedded
+// image are emulated by name (copy + completion flag, eager pack). Built as libcuda.so.1 into a
+// directory of its own and found through LD_LIBRARY_PATH by the tests only.
+//
+// Fault injection through the environment (read at cuInit):
+//   FAKE_CUDA_FAIL_IPC_OPEN=1   cuIpcOpenMemHandle fails (the plugin must fall back to staging)
+//   FAKE_CUDA_LAUNCH_DELAY_US=n kernels "finish" n microseconds after the launch call returns
+//                               (a helper thread performs them), so completions are asynchronous
+#include <cuda.h>
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <chrono>
+#include <condition_variable>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <deque>
+#include <functional>
+#include <map>
+#include <mutex>
+#include <string>
+#include <thread>
+
+namespace {
+
+struct Alloc {
+  size_t size;
+  std::string shm_name;   // empty: mapping of a peer's allocation
+  bool opened_from_peer;
+};
+std::mutex g_mu;
+std::map<uintptr_t, Alloc> g_allocs;   // base -> allocation ("device" address ranges of this process)
+std::atomic<int> g_next_alloc{0};
+bool g_fail_ipc_open = false;
+int g_launch_delay_us = 0;
+
+const Alloc* find_alloc(uintptr_t p, uintptr_t* base) {
+  auto it = g_allocs.upper_bound(p);
+  if (it == g_allocs.begin()) return nullptr;
+  --it;
+  if (p >= it->first && p < it->first + it->second.size) {
+    *base = it->first;
+    return &it->second;
+  }
+  return nullptr;
+}
+
+struct IpcHandlePayload {   // fits the 64 opaque bytes
+  char name[48];
+  uint64_t size;
+};
+static_assert(sizeof(IpcHandlePayload) <= sizeof(CUipcMemHandle), "handle payload too large");
+
+// ---- a worker that performs "kernels" after a delay. The queue state is allocated once and never
+// destroyed: the worker outlives main(), and destroying a condition variable that a thread still
+// waits on blocks the exiting process.
+using WorkQueue = std::deque<std::pair<std::chrono::steady_clock::time_point, std::function<void()>>>;
+std::mutex& g_wmu = *new std::mutex;
+std::condition_variable& g_wcv = *new std::condition_variable;
+WorkQueue& g_work = *new WorkQueue;
+std::thread* g_worker = nullptr;
+std::atomic<int> g_outstanding{0};   // queued or running
+void worker_main() {
+  for (;;) {
+    std::function<void()> fn;
+    {
+      std::unique_lock<std::mutex> lk(g_wmu);
+      g_wcv.wait(lk, [] { return !g_work.empty(); });
+      auto due = g_work.front().first;
+      if (std::chrono::steady_clock::now() < due) {
+        lk.unlock();
+        std::this_thread::sleep_until(due);
+        continue;
+      }
+      fn = std::move(g_work.front().second);
+      g_work.pop_front();
+    }
+    fn();
+    g_outstanding.fetch_sub(1);
+  }
+}
+void run_later(std::function<void()> fn) {
+  if (g_launch_delay_us <= 0) {
+    fn();
+    return;
+  }
+  std::lock_guard<std::mutex> g(g_wmu);
+  if (!g_worker) g_worker = new std::thread(worker_main);   // lives until the process exits
+  g_outstanding.fetch_add(1);
+  g_work.emplace_back(std::chrono::steady_clock::now() + std::chrono::microseconds(g_launch_delay_us), std::move(fn));
+  g_wcv.notify_one();
+}
+
+enum FakeFn : uintptr_t { FN_COPY_FLAG = 0x101, FN_EAGER_PACK = 0x102 };
+
+// ------------------------------------------------------------------------------------------ entry points
+CUresult fInit(unsigned) {
+  g_fail_ipc_open = getenv("FAKE_CUDA_FAIL_IPC_OPEN") && atoi(getenv("FAKE_CUDA_FAIL_IPC_OPEN"));
+  g_launch_delay_us = getenv("FAKE_CUDA_LAUNCH_DELAY_US") ? atoi(getenv("FAKE_CUDA_LAUNCH_DELAY_US")) : 0;
+  return CUDA_SUCCESS;
+}
+CUresult fDeviceGetCount(int* n) {
+  *n = getenv("FAKE_CUDA_DEVICES") ? atoi(getenv("FAKE_CUDA_DEVICES")) : 2;
+  return CUDA_SUCCESS;
+}
+CUresult fDeviceGet(CUdevice* d, int ord) {
+  *d = ord;
+  return CUDA_SUCCESS;
+}
+CUresult fDeviceGetAttribute(int* v, CUdevice_attribute a, CUdevice) {
+  switch (a) {
+    case CU_DEVICE_ATTRIBUTE_COMPUTE_CAPABILITY_MAJOR: *v = 10; break;
+    case CU_DEVICE_ATTRIBUTE_COMPUTE_CAPABILITY_MINOR: *v = 0; break;
+    case CU_DEVICE_ATTRIBUTE_MULTIPROCESSOR_COUNT: *v = 148; break;
+    case CU_DEVICE_ATTRIBUTE_UNIFIED_ADDRESSING: *v = 1; break;
+    default: *v = 0; break;   // no dma-buf, no multicast, no VMM handle types
+  }
+  return CUDA_SUCCESS;
+}
+CUresult fDeviceGetP2PAttribute(int* v, CUdevice_P2PAttribute, CUdevice, CUdevice) {
+  *v = 1;
+  return CUDA_SUCCESS;
+}
+CUresult fDeviceGetPCIBusId(char* out, int len, CUdevice d) {
+  snprintf(out, static_cast<size_t>(len), "0000:%02x:00.0", 0x10 + d);
+  return CUDA_SUCCESS;
+}
+CUresult fDeviceGetUuid(CUuuid* u, CUdevice d) {
+  memset(u, 0, sizeof(*u));
+  u->bytes[0] = static_cast<char>(0xFA);
+  u->bytes[15] = static_cast<char>(d);
+  return CUDA_SUCCESS;
+}
+CUresult fPointerGetAttribute(void* out, CUpointer_attribute a, CUdeviceptr p) {
+  std::lock_guard<std::mutex> g(g_mu);
+  uintptr_t base = 0;
+  const Alloc* al = find_alloc(static_cast<uintptr_t>(p), &base);
+  if (!al) return CUDA_ERROR_INVALID_VALUE;   // what the driver answers for plain host memory
+  switch (a) {
+    case CU_POINTER_ATTRIBUTE_MEMORY_TYPE: *static_cast<unsigned*>(out) = CU_MEMORYTYPE_DEVICE; break;
+    case CU_POINTER_ATTRIBUTE_DEVICE_ORDINAL: *static_cast<int*>(out) = 0; break;
+    case CU_POINTER_ATTRIBUTE_IS_LEGACY_CUDA_IPC_CAPABLE: *static_cast<int*>(out) = al->opened_from_peer ? 0 : 1; break;
+    default: return CUDA_ERROR_INVALID_VALUE;
+  }
+  return CUDA_SUCCESS;
+}
+CUresult fMemGetAddressRange(CUdeviceptr* base_out, size_t* size_out, CUdeviceptr p) {
+  std::lock_guard<std::mutex> g(g_mu);
+  uintptr_t base = 0;
+  const Alloc* al = find_alloc(static_cast<uintptr_t>(p), &base);
+  if (!al) return CUDA_ERROR_INVALID_VALUE;
+  if (base_out) *base_out = base;
+  if (size_out) *size_out = al->size;
+  return CUDA_SUCCESS;
+}
+CUresult fMemAlloc(CUdeviceptr* out, size_t bytes) {
+  char name[48];
+  snprintf(name, sizeof(name), "/fakecuda.%d.%d", static_cast<int>(getpid()), g_next_alloc.fetch_add(1));
+  shm_unlink(name);
+  const int fd = shm_open(name, O_CREAT | O_EXCL | O_RDWR, 0600);
+  if (fd < 0) return CUDA_ERROR_OUT_OF_MEMORY;
+  const size_t rounded = (bytes + 4095) & ~static_cast<size_t>(4095);
+  if (ftruncate(fd, static_cast<off_t>(rounded)) != 0) {
+    close(fd);
+    shm_unlink(name);
+    return CUDA_ERROR_OUT_OF_MEMORY;
+  }
+  void* p = mmap(nullptr, rounded, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (p == MAP_FAILED) {
+    shm_unlink(name);
+    return CUDA_ERROR_OUT_OF_MEMORY;
+  }
+  std::lock_guard<std::mutex> g(g_mu);
+  g_allocs[reinterpret_cast<uintptr_t>(p)] = Alloc{rounded, name, false};
+  *out = reinterpret_cast<CUdeviceptr>(p);
+  return CUDA_SUCCESS;
+}
+CUresult fMemFree(CUdeviceptr p) {
+  std::lock_guard<std::mutex> g(g_mu);
+  auto it = g_allocs.find(static_cast<uintptr_t>(p));
+  if (it == g_allocs.end()) return CUDA_ERROR_INVALID_VALUE;
+  munmap(reinterpret_cast<void*>(it->first), it->second.size);
+  if (!it->second.shm_name.empty()) shm_unlink(it->second.shm_name.c_str());
+  g_allocs.erase(it);
+  return CUDA_SUCCESS;
+}
+CUresult fMemsetD8(CUdeviceptr p, unsigned char v, size_t n) {
+  memset(reinterpret_cast<void*>(p), v, n);
+  return CUDA_SUCCESS;
+}
+CUresult fIpcGetMemHandle(CUipcMemHandle* h, CUdeviceptr p) {
+  std::lock_guard<std::mutex> g(g_mu);
+  auto it = g_allocs.find(static_cast<uintptr_t>(p));
+  if (it == g_allocs.end() || it->second.shm_name.empty()) return CUDA_ERROR_INVALID_VALUE;
+  IpcHandlePayload pl{};
+  snprintf(pl.name, sizeof(pl.name), "%s", it->second.shm_name.c_str());
+  pl.size = it->second.size;
+  memset(h, 0, sizeof(*h));
+  memcpy(h, &pl, sizeof(pl));
+  return CUDA_SUCCESS;
+}
+CUresult fIpcOpenMemHandle(CUdeviceptr* out, CUipcMemHandle h, unsigned) {
+  if (g_fail_ipc_open) return CUDA_ERROR_INVALID_DEVICE;
+  IpcHandlePayload pl;
+  memcpy(&pl, &h, sizeof(pl));
+  pl.name[sizeof(pl.name) - 1] = 0;
+  const int fd = shm_open(pl.name, O_RDWR, 0600);
+  if (fd < 0) return CUDA_ERROR_INVALID_VALUE;
+  void* p = mmap(nullptr, pl.size, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (p == MAP_FAILED) return CUDA_ERROR_OUT_OF_MEMORY;
+  std::lock_guard<std::mutex> g(g_mu);
+  g_allocs[reinterpret_cast<uintptr_t>(p)] = Alloc{pl.size, "", true};
+  *out = reinterpret_cast<CUdeviceptr>(p);
+  return CUDA_SUCCESS;
+}
+CUresult fIpcCloseMemHandle(CUdeviceptr p) {
+  std::lock_guard<std::mutex> g(g_mu);
+  auto it = g_allocs.find(static_cast<uintptr_t>(p));
+  if (it == g_allocs.end()) return CUDA_ERROR_INVALID_VALUE;
+  munmap(reinterpret_cast<void*>(it->first), it->second.size);
+  g_allocs.erase(it);
+  return CUDA_SUCCESS;
+}
+CUresult fCtxGetCurrent(CUcontext* c) {
+  *c = reinterpret_cast<CUcontext>(0x1);
+  return CUDA_SUCCESS;
+}
+CUresult fCtxSetCurrent(CUcontext) { return CUDA_SUCCESS; }
+CUresult fDevicePrimaryCtxRetain(CUcontext* c, CUdevice) {
+  *c = reinterpret_cast<CUcontext>(0x1);
+  return CUDA_SUCCESS;
+}
+CUresult fStreamCreate(CUstream* s, unsigned) {
+  static std::atomic<uintptr_t> next{0x1000};
+  *s = reinterpret_cast<CUstream>(next.fetch_add(16));
+  return CUDA_SUCCESS;
+}
+CUresult fStreamDestroy(CUstream) { return CUDA_SUCCESS; }
+CUresult fStreamSynchronize(CUstream) {
+  // delayed "kernels" are not tied to streams: wait until none is queued or running
+  while (g_outstanding.load() > 0) usleep(50);
+  return CUDA_SUCCESS;
+}
+CUresult fEventCreate(CUevent* e, unsigned) {
+  *e = reinterpret_cast<CUevent>(new int(0));
+  return CUDA_SUCCESS;
+}
+CUresult fEventDestroy(CUevent e) {
+  delete reinterpret_cast<int*>(e);
+  return CUDA_SUCCESS;
+}
+CUresult fEventRecord(CUevent, CUstream) { return CUDA_SUCCESS; }
+CUresult fEventQuery(CUevent) { return CUDA_SUCCESS; }
+CUresult fMemcpyAsync(CUdeviceptr d, CUdeviceptr s, size_t n, CUstream) {
+  memcpy(reinterpret_cast<void*>(d), reinterpret_cast<const void*>(s), n);
+  return CUDA_SUCCESS;
+}
+CUresult fModuleLoadData(CUmodule* m, const void* image) {
+  if (!image) return CUDA_ERROR_INVALID_IMAGE;
+  *m = reinterpret_cast<CUmodule>(0x2);
+  return CUDA_SUCCESS;
+}
+CUresult fModuleUnload(CUmodule) { return CUDA_SUCCESS; }
+CUresult fModuleGetFunction(CUfunction* f, CUmodule, const char* name) {
+  if (!strcmp(name, "b200net_copy_flag")) *f = reinterpret_cast<CUfunction>(FN_COPY_FLAG);
+  else if (!strcmp(name, "b200net_eager_pack")) *f = reinterpret_cast<CUfunction>(FN_EAGER_PACK);
+  else return CUDA_ERROR_NOT_FOUND;
+  return CUDA_SUCCESS;
+}
+CUresult fLaunchKernel(CUfunction f, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void** args,
+                       void**) {
+  const uintptr_t id = reinterpret_cast<uintptr_t>(f);
+  if (id == FN_COPY_FLAG) {
+    auto* dst = *static_cast<unsigned char**>(args[0]);
+    auto* src = *static_cast<const unsigned char**>(args[1]);
+    const unsigned long long bytes = *static_cast<unsigned long long*>(args[2]);
+    auto* flag = *static_cast<unsigned long long**>(args[4]);
+    const unsigned long long value = *static_cast<unsigned long long*>(args[5]);
+    run_later([=] {
+      memcpy(dst, src, bytes);
+      __atomic_store_n(flag, value, __ATOMIC_RELEASE);
+    });
+    return CUDA_SUCCESS;
+  }
+  if (id == FN_EAGER_PACK) {
+    auto* slot = *static_cast<unsigned char**>(args[0]);
+    auto* payload = *static_cast<const unsigned char**>(args[1]);
+    const unsigned bytes = *static_cast<unsigned*>(args[2]);
+    const unsigned long long h0 = *static_cast<unsigned long long*>(args[3]);
+    const unsigned long long h1 = *static_cast<unsigned long long*>(args[4]);
+    const unsigned flag_off = *static_cast<unsigned*>(args[5]);
+    const unsigned long long value = *static_cast<unsigned long long*>(args[6]);
+    run_later([=] {
+      memcpy(slot + 16, payload, bytes);
+      memcpy(slot, &h0, 8);
+      memcpy(slot + 8, &h1, 8);
+      __atomic_store_n(reinterpret_cast<unsigned long long*>(slot + flag_off), value, __ATOMIC_RELEASE);
+    });
+    return CUDA_SUCCESS;
+  }
+  return CUDA_ERROR_INVALID_HANDLE;
+}
+CUresult fMemHostAlloc(void** p, size_t bytes, unsigned) {
+  return posix_memalign(p, 4096, (bytes + 4095) & ~static_cast<size_t>(4095)) == 0 ? CUDA_SUCCESS : CUDA_ERROR_OUT_OF_MEMORY;
+}
+CUresult fMemFreeHost(void* p) {
+  free(p);
+  return CUDA_SUCCESS;
+}
+// VMM: not offered by the stand-in
+CUresult fNotSupported() { return CUDA_ERROR_NOT_SUPPORTED; }
+
+struct Entry {
+  const char* name;
+  void* fn;
+};
+#define E(n, f) {n, reinterpret_cast<void*>(f)}
+const Entry kTable[] = {
+    E("cuInit", fInit), E("cuDeviceGetCount", fDeviceGetCount), E("cuDeviceGet", fDeviceGet),
+    E("cuDeviceGetAttribute", fDeviceGetAttribute), E("cuDeviceGetP2PAttribute", fDeviceGetP2PAttribute),
+    E("cuDeviceGetPCIBusId", fDeviceGetPCIBusId), E("cuDeviceGetUuid", fDeviceGetUuid),
+    E("cuPointerGetAttribute", fPointerGetAttribute), E("cuMemGetAddressRange", fMemGetAddressRange),
+    E("cuIpcGetMemHandle", fIpcGetMemHandle), E("cuIpcOpenMemHandle", fIpcOpenMemHandle),
+    E("cuIpcCloseMemHandle", fIpcCloseMemHandle), E("cuCtxGetCurrent", fCtxGetCurrent), E("cuCtxSetCurrent", fCtxSetCurrent),
+    E("cuDevicePrimaryCtxRetain", fDevicePrimaryCtxRetain), E("cuStreamCreate", fStreamCreate),
+    E("cuStreamDestroy", fStreamDestroy), E("cuStreamSynchronize", fStreamSynchronize), E("cuEventCreate", fEventCreate),
+    E("cuEventDestroy", fEventDestroy), E("cuEventRecord", fEventRecord), E("cuEventQuery", fEventQuery),
+    E("cuMemcpyAsync", fMemcpyAsync), E("cuModuleLoadData", fModuleLoadData), E("cuModuleUnload", fModuleUnload),
+    E("cuModuleGetFunction", fModuleGetFunction), E("cuLaunchKernel", fLaunchKernel), E("cuMemHostAlloc", fMemHostAlloc),
+    E("cuMemFreeHost", fMemFreeHost), E("cuMemAlloc", fMemAlloc), E("cuMemFree", fMemFree), E("cuMemsetD8", fMemsetD8),
+    E("cuMemCreate", fNotSupported), E("cuMemRelease", fNotSupported), E("cuMemGetAllocationGranularity", fNotSupported),
+    E("cuMemAddressReserve", fNotSupported), E("cuMemAddressFree", fNotSupported), E("cuMemMap", fNotSupported),
+    E("cuMemUnmap", fNotSupported), E("cuMemSetAccess", fNotSupported), E("cuMemExportToShareableHandle", fNotSupported),
+};
+
+}  // namespace
+
+extern "C" {
+// The one symbol the plugin looks up with dlsym; everything else is resolved through it.
+CUresult cuGetProcAddress_v2(const char* symbol, void** pfn, int, cuuint64_t, CUdriverProcAddressQueryResult* status) {
+  for (const Entry& e : kTable) {
+    if (!strcmp(e.name, symbol)) {
+      *pfn = e.fn;
+      if (status) *status = CU_GET_PROC_ADDRESS_SUCCESS;
+      return CUDA_SUCCESS;
+    }
+  }
+  *pfn = nullptr;
+  if (status) *status = CU_GET_PROC_ADDRESS_SYMBOL_NOT_FOUND;
+  return CUDA_ERROR_NOT_FOUND;
+}
+// For the tests themselves: allocate and free "device" memory without going through the table.
+CUresult fake_cuda_mem_alloc(void** p, size_t bytes) {
+  CUdeviceptr d = 0;
+  const CUresult r = fMemAlloc(&d, bytes);
+  *p = reinterpret_cast<void*>(d);
+  return r;
+}
+CUresult fake_cuda_mem_free(void* p) { return fMemFree(reinterpret_cast<CUdeviceptr>(p)); }
+}

@@ -389,6 +389,139 @@ static int scenario_inflight_close(int sock) {
   return close_pair(&q);
 }
 
+// "Device" buffers for CPU runs: with FUNC_NET_DEVICE=1 and the stand-in driver on the library
+// path (it serves device memory out of POSIX shared memory), buffers come from the driver and are
+// registered as NCCL_PTR_CUDA, so the plugin's IPC mapping, copy-kernel and eager-pack paths run.
+struct TestBuf {
+  uint8_t* p = nullptr;
+  size_t n = 0;
+  bool dev = false;
+  uint8_t* data() { return p; }
+  size_t size() const { return n; }
+};
+using FakeAllocFn = int (*)(void**, size_t);
+using FakeFreeFn = int (*)(void*);
+static FakeAllocFn g_dev_alloc = nullptr;
+static FakeFreeFn g_dev_free = nullptr;
+static bool device_mode() {
+  static int mode = -1;
+  if (mode < 0) {
+    mode = 0;
+    if (getenv("FUNC_NET_DEVICE") && atoi(getenv("FUNC_NET_DEVICE"))) {
+      void* h = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+      if (h) {
+        g_dev_alloc = reinterpret_cast<FakeAllocFn>(dlsym(h, "fake_cuda_mem_alloc"));
+        g_dev_free = reinterpret_cast<FakeFreeFn>(dlsym(h, "fake_cuda_mem_free"));
+      }
+      mode = (g_dev_alloc && g_dev_free) ? 1 : 0;
+      if (!mode) fprintf(stderr, "[rank %d] FUNC_NET_DEVICE set but the stand-in driver is not on the library path\n", g_rank);
+    }
+  }
+  return mode == 1;
+}
+static int buf_alloc(TestBuf* b, size_t n) {
+  b->n = n;
+  b->dev = device_mode();
+  if (b->dev) {
+    void* p = nullptr;
+    if (g_dev_alloc(&p, n) != 0) return 1;
+    b->p = static_cast<uint8_t*>(p);
+  } else {
+    b->p = static_cast<uint8_t*>(malloc(n));
+  }
+  return b->p ? 0 : 1;
+}
+static void buf_free(TestBuf* b) {
+  if (!b->p) return;
+  if (b->dev) g_dev_free(b->p);
+  else free(b->p);
+  b->p = nullptr;
+}
+static int buf_type() { return device_mode() ? NCCL_PTR_CUDA : NCCL_PTR_HOST; }
+
+// Sizes around the eager limit and up to several stripes, every message checked byte for byte,
+// several in flight; in device mode this walks the eager-pack path (small), the copy kernel
+// (large) and the receiver's copy of early eager payloads into device memory.
+static int scenario_device_transfer(int sock) {
+  Pair p;
+  if (connect_pair(0, sock, &p)) return 1;
+  const size_t sizes[] = {1, 8, 100, 4096, 8192, 8193, 65536, 300000, 1u << 20, (4u << 20) + 16};
+  const int nmsg = sizeof(sizes) / sizeof(sizes[0]);
+  size_t eager_limit = 8192;   // the plugin's default; the suite also runs with eager switched off
+  for (const char* name : {"B200NET_EAGER_MAX_SIZE", "OFI_NCCL_EAGER_MAX_SIZE"})
+    if (const char* v = getenv(name)) eager_limit = strtoull(v, nullptr, 0);
+  for (int pass = 0; pass < 2; ++pass) {   // pass 0: receives first; pass 1: sends first (early eager)
+    std::vector<TestBuf> sb(nmsg), rb(nmsg);
+    std::vector<void*> smh(nmsg), rmh(nmsg), sreq(nmsg, nullptr), rreq(nmsg, nullptr);
+    for (int i = 0; i < nmsg; ++i) {
+      if (buf_alloc(&sb[i], sizes[i] + 64) || buf_alloc(&rb[i], sizes[i] + 64)) FAIL("buffer allocation failed");
+      std::vector<uint8_t> pat(sizes[i]);
+      fill(pat, 500 + 10 * pass + i + 1000 * g_rank);
+      memcpy(sb[i].data(), pat.data(), sizes[i]);
+      memset(rb[i].data(), 0xCD, rb[i].size());
+      OK(net->regMr(p.s, sb[i].data(), sb[i].size(), buf_type(), &smh[i]));
+      OK(net->regMr(p.r, rb[i].data(), rb[i].size(), buf_type(), &rmh[i]));
+    }
+    if (barrier(sock)) FAIL("barrier");
+    auto post_recvs = [&]() -> int {
+      for (int i = 0; i < nmsg; ++i) {
+        void* d = rb[i].data();
+        size_t cap = sizes[i];
+        int tag = 7;
+        if (post_recv(p.r, 1, &d, &cap, &tag, &rmh[i], &rreq[i])) return 1;
+      }
+      return 0;
+    };
+    auto post_sends = [&]() -> int {
+      for (int i = 0; i < nmsg; ++i) {
+        auto t0 = Clock::now();
+        while (!sreq[i]) {
+          OK(net->isend(p.s, sb[i].data(), sizes[i], 7, smh[i], nullptr, &sreq[i]));
+          if (!sreq[i] && pass == 1 && (sizes[i] > eager_limit || sizes[i] > 8192 || eager_limit == 0)) break;   // no receive yet and not eager: later
+          if (expired(t0)) FAIL("isend of %zu bytes kept returning no request", sizes[i]);
+        }
+      }
+      return 0;
+    };
+    if (pass == 0) {
+      if (post_recvs()) return 1;
+      if (barrier(sock)) FAIL("barrier");
+      if (post_sends()) return 1;
+    } else {
+      if (post_sends()) return 1;   // eager-sized ones go out with no receive posted
+      if (barrier(sock)) FAIL("barrier");
+      if (post_recvs()) return 1;
+      for (int i = 0; i < nmsg; ++i) {
+        auto t0 = Clock::now();
+        while (!sreq[i]) {
+          OK(net->isend(p.s, sb[i].data(), sizes[i], 7, smh[i], nullptr, &sreq[i]));
+          if (expired(t0)) FAIL("late isend of %zu bytes kept returning no request", sizes[i]);
+        }
+      }
+    }
+    std::vector<void*> all;
+    for (void* r : sreq) all.push_back(r);
+    for (void* r : rreq) all.push_back(r);
+    std::vector<int> got;
+    if (wait_all(all, &got)) return 1;
+    for (int i = 0; i < nmsg; ++i) {
+      std::vector<uint8_t> want(sizes[i]);
+      fill(want, 500 + 10 * pass + i + 1000 * (1 - g_rank));
+      if (got[nmsg + i] != static_cast<int>(sizes[i])) FAIL("pass %d message %d: size %d, expected %zu", pass, i, got[nmsg + i], sizes[i]);
+      if (memcmp(want.data(), rb[i].data(), sizes[i])) FAIL("pass %d message %d (%zu bytes): payload differs", pass, i, sizes[i]);
+      if (rb[i].data()[sizes[i]] != 0xCD) FAIL("pass %d message %d: wrote past the end", pass, i);
+    }
+    if (barrier(sock)) FAIL("barrier");
+    for (int i = 0; i < nmsg; ++i) {
+      OK(net->deregMr(p.s, smh[i]));
+      OK(net->deregMr(p.r, rmh[i]));
+      buf_free(&sb[i]);
+      buf_free(&rb[i]);
+    }
+  }
+  return close_pair(&p);
+}
+
 // The access pattern of NCCL's proxy thread: several channels, each a connection in both
 // directions, every channel keeps up to eight receives posted and eight chunk-sized sends in
 // flight, and ONE thread per process drives all of them round-robin with isend / irecv / test,
@@ -400,7 +533,7 @@ static int scenario_proxy_pattern(int sock) {
   const size_t chunk = getenv("FUNC_NET_PROXY_CHUNK") ? strtoul(getenv("FUNC_NET_PROXY_CHUNK"), nullptr, 0) : (1u << 20);
   struct Chan {
     Pair p;
-    std::vector<std::vector<uint8_t>> sbuf, rbuf;
+    std::vector<TestBuf> sbuf, rbuf;
     std::vector<void*> smh, rmh, sreq, rreq;
     std::vector<int> rreq_chunk, sreq_chunk;
     int sent = 0, send_done = 0, posted = 0, recv_done = 0;
@@ -408,8 +541,10 @@ static int scenario_proxy_pattern(int sock) {
   std::vector<Chan> ch(channels);
   for (int c = 0; c < channels; ++c) {
     if (connect_pair(0, sock, &ch[c].p)) return 1;
-    ch[c].sbuf.assign(steps, std::vector<uint8_t>(chunk));
-    ch[c].rbuf.assign(steps, std::vector<uint8_t>(chunk));
+    ch[c].sbuf.assign(steps, TestBuf());
+    ch[c].rbuf.assign(steps, TestBuf());
+    for (int s = 0; s < steps; ++s)
+      if (buf_alloc(&ch[c].sbuf[s], chunk) || buf_alloc(&ch[c].rbuf[s], chunk)) FAIL("buffer allocation failed");
     ch[c].smh.assign(steps, nullptr);
     ch[c].rmh.assign(steps, nullptr);
     ch[c].sreq.assign(steps, nullptr);
@@ -417,15 +552,15 @@ static int scenario_proxy_pattern(int sock) {
     ch[c].rreq_chunk.assign(steps, -1);
     ch[c].sreq_chunk.assign(steps, -1);
     for (int s = 0; s < steps; ++s) {
-      OK(net->regMr(ch[c].p.s, ch[c].sbuf[s].data(), chunk, NCCL_PTR_HOST, &ch[c].smh[s]));
-      OK(net->regMr(ch[c].p.r, ch[c].rbuf[s].data(), chunk, NCCL_PTR_HOST, &ch[c].rmh[s]));
+      OK(net->regMr(ch[c].p.s, ch[c].sbuf[s].data(), chunk, buf_type(), &ch[c].smh[s]));
+      OK(net->regMr(ch[c].p.r, ch[c].rbuf[s].data(), chunk, buf_type(), &ch[c].rmh[s]));
     }
   }
   if (barrier(sock)) FAIL("barrier");
-  auto stamp = [&](std::vector<uint8_t>& b, int c, int k) {
+  auto stamp = [&](TestBuf& b, int c, int k) {
     uint32_t hdr[4] = {0xC0FFEEu, static_cast<uint32_t>(g_rank), static_cast<uint32_t>(c), static_cast<uint32_t>(k)};
     memcpy(b.data(), hdr, sizeof(hdr));
-    b[chunk - 1] = static_cast<uint8_t>(c * 31 + k);
+    b.data()[chunk - 1] = static_cast<uint8_t>(c * 31 + k);
   };
   auto t0 = Clock::now();
   long done_total = 0;
@@ -475,7 +610,7 @@ static int scenario_proxy_pattern(int sock) {
           const int k = x.rreq_chunk[slot];
           if (sz != static_cast<int>(chunk) || hdr[0] != 0xC0FFEEu || hdr[1] != static_cast<uint32_t>(1 - g_rank) ||
               hdr[2] != static_cast<uint32_t>(c) || hdr[3] != static_cast<uint32_t>(k) ||
-              x.rbuf[slot][chunk - 1] != static_cast<uint8_t>(c * 31 + k))
+              x.rbuf[slot].data()[chunk - 1] != static_cast<uint8_t>(c * 31 + k))
             FAIL("channel %d chunk %d arrived wrong (size %d, hdr %x %u %u %u)", c, k, sz, hdr[0], hdr[1], hdr[2], hdr[3]);
           ++x.recv_done;
           ++done_total;
@@ -499,6 +634,8 @@ static int scenario_proxy_pattern(int sock) {
     for (int s = 0; s < steps; ++s) {
       OK(net->deregMr(ch[c].p.s, ch[c].smh[s]));
       OK(net->deregMr(ch[c].p.r, ch[c].rmh[s]));
+      buf_free(&ch[c].sbuf[s]);
+      buf_free(&ch[c].rbuf[s]);
     }
     if (close_pair(&ch[c].p)) return 1;
   }
@@ -599,6 +736,7 @@ static const Scenario kScenarios[] = {
     {"eager", scenario_eager},               {"reuse_listen", scenario_reuse_listen},
     {"inflight_close", scenario_inflight_close}, {"threads", scenario_threads},
     {"bandwidth", scenario_bandwidth},       {"proxy_pattern", scenario_proxy_pattern},
+    {"device_transfer", scenario_device_transfer},
 };
 
 static int run_rank(const char* so, const char* only, int sock) {

@@ -9,6 +9,7 @@
 #include <sched.h>
 #include <unistd.h>
 
+#include <array>
 #include <atomic>
 #include <cerrno>
 #include <chrono>
@@ -76,6 +77,7 @@ class RdmaSendReq : public Request {
   CtrlEntry target{};       // copy of the control entry this send writes into
   std::vector<Stripe> stripes;
   std::vector<uint8_t> bounce;  // host copy of a device source that must travel through host memory
+  bool via_frags = false;       // the target registration has an IPC handle that could not be opened here
   uint64_t serial = 0;          // unique per endpoint; queued retries name the request by it
 };
 
@@ -156,7 +158,11 @@ class RdmaEndpoint : public Endpoint {
   std::map<uint32_t, RdmaRecvComm*> recv_comms;
   std::deque<std::function<int()>> pending;  // posts that met a full ring (-EAGAIN); retried in order
   std::vector<cuda::Stream> streams;
-  std::map<std::pair<uint32_t, uint64_t>, void*> ipc_maps;  // (peer pid, mr key) -> mapped base
+  // (peer pid, IPC handle bytes) -> mapped base. Keyed by the handle, not by the MR key: keys are
+  // recycled when a buffer is deregistered, and a new registration under an old key is a
+  // different allocation.
+  std::map<std::pair<uint32_t, std::array<uint8_t, 64>>, void*> ipc_maps;
+  bool warned_ipc = false;
   std::set<std::pair<MrHandle*, int>> published;
   // Requests a queued retry may still touch, by serial number: a request's address can be handed
   // out again (to another communicator's request) while an old retry for it is still queued.
@@ -234,7 +240,7 @@ RdmaEndpoint::~RdmaEndpoint() {
              static_cast<unsigned long long>(bytes_staged), static_cast<unsigned long long>(bytes_host),
              static_cast<unsigned long long>(bytes_eager));
   for (auto& [k, p] : ipc_maps)
-    if (k.first != static_cast<uint32_t>(getpid())) cuda::ipc_close(p);
+    if (p) cuda::ipc_close(p);
   for (auto s : streams)
     if (s) cuda::stream_destroy(s);
 }
@@ -250,20 +256,18 @@ cuda::Stream RdmaEndpoint::rail_stream(int rail) {
 }
 
 void* RdmaEndpoint::map_peer_cuda(PeerMapping* peer, const MrTableEntry* e) {
-  const auto key = std::make_pair(peer->pid, e->key);
+  if (peer->pid == static_cast<uint32_t>(getpid())) return reinterpret_cast<void*>(e->base);  // same process: directly usable
+  std::array<uint8_t, 64> handle;
+  memcpy(handle.data(), e->ipc_handle, handle.size());
+  const auto key = std::make_pair(peer->pid, handle);
   auto it = ipc_maps.find(key);
   if (it != ipc_maps.end()) return it->second;
   void* mapped = nullptr;
-  if (peer->pid == static_cast<uint32_t>(getpid())) {
-    mapped = reinterpret_cast<void*>(e->base);  // same process: the pointer is directly usable
-  } else {
-    if (domain->device->gpu_ordinal >= 0) cuda::ensure_primary_ctx(domain->device->gpu_ordinal);
-    if (cuda::ipc_open(e->ipc_handle, &mapped) != 0) return nullptr;
-  }
+  if (domain->device->gpu_ordinal >= 0) cuda::ensure_primary_ctx(domain->device->gpu_ordinal);
+  if (cuda::ipc_open(e->ipc_handle, &mapped) != 0) mapped = nullptr;   // remembered: asked once per allocation
   ipc_maps[key] = mapped;
   return mapped;
 }
-
 int RdmaEndpoint::ensure_published(MrHandle* mh) {
   if (!mh) return 0;
   if (published.count({mh, 0})) return 0;
@@ -579,7 +583,8 @@ void RdmaSendComm::bind_eager_queue() {
 int RdmaSendComm::post_stripes(RdmaSendReq* r) {
   RdmaEndpoint* e = rep();
   const MrTableEntry* mr = FabricEndpoint::mr_lookup(peer, r->target.mr_key);
-  const uint32_t kind = mr ? mr->kind : static_cast<uint32_t>(MrKind::HOST);
+  const uint32_t kind = r->via_frags ? static_cast<uint32_t>(MrKind::CUDA_STAGED)
+                                     : (mr ? mr->kind : static_cast<uint32_t>(MrKind::HOST));
   const bool src_dev = !r->bounce.empty() ? false : !cuda::is_host_pointer(r->data);
   const char* src = r->bounce.empty() ? static_cast<const char*>(r->data) : reinterpret_cast<const char*>(r->bounce.data());
   bool all_done = true;
@@ -711,7 +716,16 @@ int RdmaSendComm::start_rendezvous(RdmaSendReq* r, const CtrlEntry& e) {
   if (r->size > e.buff_len) r->size = e.buff_len;  // a send larger than the posted receive is truncated
   const MrTableEntry* mr = FabricEndpoint::mr_lookup(peer, e.mr_key);
   const bool dst_host = !mr || mr->kind == static_cast<uint32_t>(MrKind::HOST);
-  if ((dst_host || (mr && mr->kind == static_cast<uint32_t>(MrKind::CUDA_STAGED))) && r->size &&
+  if (mr && mr->kind == static_cast<uint32_t>(MrKind::CUDA_IPC) && !rep()->map_peer_cuda(peer, mr)) {
+    // the peer's device memory cannot be mapped into this process (another container, a driver
+    // without IPC): the payload travels as fragments that the receiver copies to its device
+    if (!rep()->warned_ipc) {
+      rep()->warned_ipc = true;
+      NET_WARN("device memory of process %u cannot be mapped here; payloads to it are staged through host memory", peer->pid);
+    }
+    r->via_frags = true;
+  }
+  if ((dst_host || r->via_frags || (mr && mr->kind == static_cast<uint32_t>(MrKind::CUDA_STAGED))) && r->size &&
       !cuda::is_host_pointer(r->data)) {
     // device source, destination only reachable through host memory: bounce once
     r->bounce.resize(r->size);
@@ -784,23 +798,31 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
   const void* eager_src = data;
   int eager_slot = -1;
   NetKernels* nk = nullptr;
+  std::vector<uint8_t> eager_bounce;
   if (eager_size_ok && size > 0 && !cuda::is_host_pointer(data)) {
     // device payload: the pack kernel writes header + payload + flag into a pinned slot and the
-    // datagram is sent from there; without the kernels a device payload waits for the rendezvous
+    // datagram is sent from there; without the kernels the copy engine fetches the payload
     nk = size <= NetKernels::EAGER_PAYLOAD_MAX ? e->kernels : nullptr;
-    cuda::Stream st = nk ? e->rail_stream(0) : nullptr;
-    if (!nk || !st || nk->eager_pack(data, size, next_eager_seq, size, st, &eager_slot) != 0) return 0;
-    const auto t0 = std::chrono::steady_clock::now();
-    while (!nk->eager_done(eager_slot)) {
-      if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(2)) {
-        // the slot stays reserved: the kernel may still write it
-        NET_WARN("eager pack kernel did not complete within 2 s");
-        return -EIO;
+    cuda::Stream st = e->rail_stream(0);
+    if (!st) return -EIO;
+    if (nk && nk->eager_pack(data, size, next_eager_seq, size, st, &eager_slot) == 0) {
+      const auto t0 = std::chrono::steady_clock::now();
+      while (!nk->eager_done(eager_slot)) {
+        if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(2)) {
+          // the slot stays reserved: the kernel may still write it
+          NET_WARN("eager pack kernel did not complete within 2 s");
+          return -EIO;
+        }
       }
+      eager_src = nk->eager_slot(eager_slot) + 16;
+    } else {
+      eager_slot = -1;
+      eager_bounce.resize(size);
+      if (cuda::memcpy_async(eager_bounce.data(), data, size, st) != 0 || cuda::stream_synchronize(st) != 0) return -EIO;
+      eager_src = eager_bounce.data();
     }
-    eager_src = nk->eager_slot(eager_slot) + 16;
   }
-  if (eager_size_ok && (eager_slot >= 0 || cuda::is_host_pointer(data))) {
+  if (eager_size_ok) {
     EagerHdr h;
     memset(&h, 0, sizeof(h));
     h.remote_comm_id = remote_comm_id;

@@ -1,0 +1,78 @@
+"""The plugin's device-buffer paths (IPC mapping of a peer's registration, the copy-and-flag and
+eager-pack kernels, copy-engine fallback, staging when a peer cannot be mapped) run here without a
+GPU: the test binary and the plugin load a stand-in ``libcuda.so.1`` whose "device memory" is
+shared host memory and whose "kernels" are host functions that finish after a chosen delay.  The
+stand-in is test code only; the plugin itself is the unmodified shipped library."""
+import os
+import re
+import subprocess
+
+import pytest
+
+
+def _run(built, env_extra, scenario=None, timeout=400):
+    fake = built / "tests" / "fake_cuda"
+    assert (fake / "libcuda.so.1").exists(), "the stand-in driver was not built"
+    env = dict(os.environ, FUNC_NET_DEVICE="1", FUNC_NET_VERBOSE="1")
+    env["LD_LIBRARY_PATH"] = f"{fake}:" + env.get("LD_LIBRARY_PATH", "")
+    env.update(env_extra)
+    cmd = [str(built / "tests" / "func_net"), str(built / "libnccl-net-ofi-b200.so")]
+    if scenario:
+        cmd.append(scenario)
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=built)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    return res.stderr
+
+
+_COUNTERS = re.compile(r"copy kernel (\d+), copy engine (\d+), staged through host (\d+), host writes (\d+), eager (\d+)")
+
+
+def _payload_counters(log):
+    """Sums the per-endpoint byte counters the plugin logs when an endpoint closes (lines of the
+    two ranks can interleave on the shared stderr; a torn line is skipped)."""
+    names = ("copy kernel", "copy engine", "staged through host", "host writes", "eager")
+    total = dict.fromkeys(names, 0)
+    for m in _COUNTERS.finditer(log):
+        for n, v in zip(names, m.groups()):
+            total[n] += int(v)
+    return total
+
+
+@pytest.mark.parametrize("delay_us", ["0", "300"], ids=["sync-kernels", "async-kernels"])
+@pytest.mark.parametrize("proto", ["RDMA", "SENDRECV"])
+def test_every_scenario_with_device_buffers(built, proto, delay_us):
+    _run(built, {"B200NET_PROTOCOL": proto, "B200NET_FORCE_NUM_RAILS": "4", "FAKE_CUDA_LAUNCH_DELAY_US": delay_us})
+
+
+def test_device_payloads_take_the_kernel_and_eager_pack_paths(built):
+    log = _run(built, {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4", "FAKE_CUDA_LAUNCH_DELAY_US": "100"},
+               "device_transfer")
+    c = _payload_counters(log)
+    assert c["copy kernel"] > 0 and c["eager"] > 0, c
+    assert c["staged through host"] == 0 and c["host writes"] == 0, c
+
+
+def test_copy_engine_path_when_the_kernels_are_switched_off(built):
+    log = _run(built, {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "2", "B200NET_COPY_KERNEL": "0",
+                       "FAKE_CUDA_LAUNCH_DELAY_US": "100"}, "device_transfer")
+    c = _payload_counters(log)
+    assert c["copy engine"] > 0 and c["copy kernel"] == 0, c
+
+
+def test_unmappable_peer_memory_falls_back_to_staged_fragments(built):
+    """cuIpcOpenMemHandle fails (as between containers): payloads must still arrive, through host
+    fragments that the receiver copies to its device, and the plugin says so once."""
+    log = _run(built, {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4", "FAKE_CUDA_FAIL_IPC_OPEN": "1"},
+               "device_transfer")
+    c = _payload_counters(log)
+    assert c["staged through host"] > 0 and c["copy kernel"] == 0 and c["copy engine"] == 0, c
+    assert "cannot be mapped here" in log
+
+
+@pytest.mark.parametrize("delay_us", ["0", "200"])
+def test_proxy_pattern_on_device_buffers(built, delay_us):
+    """NCCL's proxy pattern with device chunks and kernels that complete asynchronously: many
+    requests per channel wait on their own completion words while new ones are posted."""
+    env = {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4", "FAKE_CUDA_LAUNCH_DELAY_US": delay_us}
+    for _ in range(3):
+        _run(built, env, "proxy_pattern")
