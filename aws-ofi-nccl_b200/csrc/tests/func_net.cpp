@@ -747,6 +747,11 @@ static int run_rank(const char* so, const char* only, int sock) {
   if (!net) FAIL("ncclNetPlugin_v11 not exported");
   OK(net->init(&g_ctx, 0x1234, nullptr, logger, nullptr));
   int rc = 0;
+  if (only) {
+    bool known = false;
+    for (const auto& s : kScenarios) known = known || !strcmp(only, s.name);
+    if (!known) FAIL("no scenario called %s", only);
+  }
   for (const auto& s : kScenarios) {
     if (only && strcmp(only, s.name)) continue;
     const int r = s.fn(sock);

@@ -48,6 +48,16 @@ def test_address_and_undefined_behaviour():
              {"B200NET_PROTOCOL": proto, "ASAN_OPTIONS": "detect_leaks=0"})
     for sc in ("drop_conn", "peer_exit"):
         _run([tests / "func_fault", so, sc], {"ASAN_OPTIONS": "detect_leaks=0"})
+    # device payloads against the stand-in driver: IPC mappings, copy / pack "kernels" that finish
+    # later, and the staged fallback when the peer's memory cannot be mapped
+    from aws_ofi_nccl_b200 import build
+    build.build_fake_cuda()
+    fake = f"{build.LIB / 'tests' / 'fake_cuda'}:" + os.environ.get("LD_LIBRARY_PATH", "")
+    for extra in ({"FAKE_CUDA_LAUNCH_DELAY_US": "200"}, {"FAKE_CUDA_FAIL_IPC_OPEN": "1"}):
+        for sc in ("device_transfer", "grouped_recv", "eager", "proxy_pattern"):
+            _run([tests / "func_net", so, sc],
+                 {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "2", "ASAN_OPTIONS": "detect_leaks=0",
+                  "FUNC_NET_DEVICE": "1", "LD_LIBRARY_PATH": fake, **extra})
 
 
 def test_thread_sanitizer():
