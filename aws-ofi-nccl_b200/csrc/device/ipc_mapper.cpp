@@ -1,0 +1,83 @@
+#include "b200net/ipc_mapper.h"
+
+#include <cerrno>
+#include <chrono>
+#include <condition_variable>
+#include <cstring>
+#include <deque>
+#include <mutex>
+#include <thread>
+
+namespace b200net {
+namespace {
+
+// Queue state lives for the whole process: the helper may be inside the driver when the plugin's
+// static destructors run, and a condition variable with a waiter must not be destroyed.
+struct Shared {
+  std::mutex mu;
+  std::condition_variable cv;
+  std::deque<std::shared_ptr<IpcMapJob>> jobs;
+  bool started = false;
+};
+Shared& shared() {
+  static Shared* s = new Shared;
+  return *s;
+}
+
+void helper_main() {
+  Shared& s = shared();
+  for (;;) {
+    std::shared_ptr<IpcMapJob> job;
+    {
+      std::unique_lock<std::mutex> lk(s.mu);
+      s.cv.wait(lk, [&] { return !s.jobs.empty(); });
+      job = std::move(s.jobs.front());
+      s.jobs.pop_front();
+    }
+    if (job->ctx) cuda::ctx_set_current(job->ctx);
+    void* p = nullptr;
+    const int rc = cuda::ipc_open(job->handle, &p);
+    job->mapped = p;
+    int expected = 0;
+    if (!job->state.compare_exchange_strong(expected, rc == 0 ? 1 : (rc < 0 ? rc : -EIO), std::memory_order_acq_rel) &&
+        rc == 0)
+      cuda::ipc_close(p);   // abandoned meanwhile: nobody is left to use or close it
+  }
+}
+
+}  // namespace
+
+IpcMapper& IpcMapper::instance() {
+  static IpcMapper* m = new IpcMapper;
+  return *m;
+}
+
+std::shared_ptr<IpcMapJob> IpcMapper::submit(const uint8_t handle[64], cuda::Context ctx) {
+  Shared& s = shared();
+  auto job = std::make_shared<IpcMapJob>();
+  memcpy(job->handle, handle, 64);
+  job->ctx = ctx;
+  std::lock_guard<std::mutex> g(s.mu);
+  if (!s.started) {
+    try {
+      std::thread(helper_main).detach();
+    } catch (...) {
+      return nullptr;
+    }
+    s.started = true;
+  }
+  s.jobs.push_back(job);
+  s.cv.notify_one();
+  return job;
+}
+
+int IpcMapper::wait(const IpcMapJob& job, uint64_t wait_us) {
+  int st = job.state.load(std::memory_order_acquire);
+  if (st != 0 || wait_us == 0) return st;
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::microseconds(wait_us);
+  while ((st = job.state.load(std::memory_order_acquire)) == 0 && std::chrono::steady_clock::now() < deadline)
+    std::this_thread::yield();
+  return st;
+}
+
+}  // namespace b200net

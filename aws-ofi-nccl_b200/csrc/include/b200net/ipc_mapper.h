@@ -1,0 +1,42 @@
+// Opening a peer's device allocation (cuIpcOpenMemHandle) can wait for the device to go idle. The
+// thread that drives the plugin is NCCL's proxy: if it waits for the device while a collective
+// kernel on that device waits for the proxy's data, neither moves. So the open runs on a helper
+// thread; the caller waits a short grace period (the common case finishes well within it) and
+// otherwise sends through host fragments until the mapping has arrived.
+//
+// The reference never needs this: its peers are reached through the NIC, not through a mapping of
+// their memory (registration there is fi_mr_reg, src/nccl_ofi_rdma.cpp:2655-2760, which does not
+// depend on the device being idle).
+#pragma once
+#include <atomic>
+#include <cstdint>
+#include <memory>
+
+#include "b200net/cuda_shim.h"
+
+namespace b200net {
+
+struct IpcMapJob {
+  uint8_t handle[64];
+  cuda::Context ctx = nullptr;       // made current on the helper thread before the open
+  std::atomic<int> state{0};         // 0 in progress, 1 mapped, 2 abandoned by its owner, negative errno
+  void* mapped = nullptr;            // valid once state == 1 (acquire)
+  // The owner is going away. True: the mapping exists and the caller must close it. False: it does
+  // not exist (failed, or still in progress: the helper closes it when it arrives).
+  bool abandon() {
+    int expected = 0;
+    if (state.compare_exchange_strong(expected, 2, std::memory_order_acq_rel)) return false;
+    return expected == 1;
+  }
+};
+
+class IpcMapper {
+ public:
+  static IpcMapper& instance();
+  // Queues the open. Never blocks on the device. nullptr if the helper thread could not start.
+  std::shared_ptr<IpcMapJob> submit(const uint8_t handle[64], cuda::Context ctx);
+  // Polls job->state for at most wait_us microseconds; returns the state seen last.
+  static int wait(const IpcMapJob& job, uint64_t wait_us);
+};
+
+}  // namespace b200net

@@ -124,6 +124,10 @@ struct Params {
   Param<uint64_t> host_copy_threads{"HOST_COPY_THREADS", 0,
                                     "worker threads for large host-to-host stripes (0, the default: the calling thread copies)"};
   Param<uint64_t> host_copy_min_size{"HOST_COPY_MIN_SIZE", 65536, "smallest stripe handed to a copy worker (bytes)"};
+  Param<uint64_t> ipc_map_wait_us{"IPC_MAP_WAIT_US", 20000,
+                                  "how long a send waits for the first mapping of a peer's device allocation (the open "
+                                  "runs on a helper thread because it can wait for the device to go idle); after that "
+                                  "payloads travel through host fragments until the mapping has arrived"};
   Param<bool> nccl_device_buffers{"NCCL_DEVICE_BUFFERS", false,
                                   "make NCCL hand its device buffers to the plugin (sets NCCL_NET_GDR_LEVEL=SYS and "
                                   "NCCL_NET_GDR_READ=1, stops advertising dma-buf): payloads then move with the copy "

@@ -6,6 +6,7 @@
 //
 // Fault injection through the environment (read at cuInit):
 //   FAKE_CUDA_FAIL_IPC_OPEN=1   cuIpcOpenMemHandle fails (the plugin must fall back to staging)
+//   FAKE_CUDA_IPC_OPEN_DELAY_MS=n cuIpcOpenMemHandle takes n milliseconds (a device that is busy)
 //   FAKE_CUDA_LAUNCH_DELAY_US=n kernels "finish" n microseconds after the launch call returns
 //                               (a helper thread performs them), so completions are asynchronous
 #include <cuda.h>
@@ -208,6 +209,7 @@ CUresult fIpcGetMemHandle(CUipcMemHandle* h, CUdeviceptr p) {
 }
 CUresult fIpcOpenMemHandle(CUdeviceptr* out, CUipcMemHandle h, unsigned) {
   if (g_fail_ipc_open) return CUDA_ERROR_INVALID_DEVICE;
+  if (const char* d = getenv("FAKE_CUDA_IPC_OPEN_DELAY_MS")) usleep(1000 * static_cast<useconds_t>(atoi(d)));
   IpcHandlePayload pl;
   memcpy(&pl, &h, sizeof(pl));
   pl.name[sizeof(pl.name) - 1] = 0;

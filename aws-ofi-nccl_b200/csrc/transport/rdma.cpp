@@ -25,6 +25,7 @@
 #include "b200net/cuda_shim.h"
 #include "b200net/freelist.h"
 #include "b200net/histogram.h"
+#include "b200net/ipc_mapper.h"
 #include "b200net/log.h"
 #include "b200net/msgbuff.h"
 #include "b200net/net.h"
@@ -142,6 +143,8 @@ class RdmaEndpoint : public Endpoint {
       if (cuda::ctx_get_current(&ctx) == 0 && ctx) {
         kernels = NetKernels::get();
         kernels_tried = true;
+        // streams too are created here, on a set-up path, not by the first send of a collective
+        for (int rail = 0; rail < num_rails; ++rail) rail_stream(rail);
       }
     }
   }
@@ -161,8 +164,9 @@ class RdmaEndpoint : public Endpoint {
   // (peer pid, IPC handle bytes) -> mapped base. Keyed by the handle, not by the MR key: keys are
   // recycled when a buffer is deregistered, and a new registration under an old key is a
   // different allocation.
-  std::map<std::pair<uint32_t, std::array<uint8_t, 64>>, void*> ipc_maps;
-  bool warned_ipc = false;
+  std::map<std::pair<uint32_t, std::array<uint8_t, 64>>, std::shared_ptr<IpcMapJob>> ipc_maps;
+  bool warned_ipc = false, noted_ipc_wait = false;
+  void note_unmapped(PeerMapping* peer, const MrTableEntry* e);
   std::set<std::pair<MrHandle*, int>> published;
   // Requests a queued retry may still touch, by serial number: a request's address can be handed
   // out again (to another communicator's request) while an old retry for it is still queued.
@@ -239,8 +243,8 @@ RdmaEndpoint::~RdmaEndpoint() {
              static_cast<unsigned long long>(bytes_kernel), static_cast<unsigned long long>(bytes_copy_engine),
              static_cast<unsigned long long>(bytes_staged), static_cast<unsigned long long>(bytes_host),
              static_cast<unsigned long long>(bytes_eager));
-  for (auto& [k, p] : ipc_maps)
-    if (p) cuda::ipc_close(p);
+  for (auto& [k, job] : ipc_maps)
+    if (job && job->abandon()) cuda::ipc_close(job->mapped);
   for (auto s : streams)
     if (s) cuda::stream_destroy(s);
 }
@@ -261,12 +265,32 @@ void* RdmaEndpoint::map_peer_cuda(PeerMapping* peer, const MrTableEntry* e) {
   memcpy(handle.data(), e->ipc_handle, handle.size());
   const auto key = std::make_pair(peer->pid, handle);
   auto it = ipc_maps.find(key);
-  if (it != ipc_maps.end()) return it->second;
-  void* mapped = nullptr;
-  if (domain->device->gpu_ordinal >= 0) cuda::ensure_primary_ctx(domain->device->gpu_ordinal);
-  if (cuda::ipc_open(e->ipc_handle, &mapped) != 0) mapped = nullptr;   // remembered: asked once per allocation
-  ipc_maps[key] = mapped;
-  return mapped;
+  if (it == ipc_maps.end()) {
+    // first use of this allocation: the open runs on the helper thread (it may wait for the device)
+    if (domain->device->gpu_ordinal >= 0) cuda::ensure_primary_ctx(domain->device->gpu_ordinal);
+    cuda::Context ctx = nullptr;
+    cuda::ctx_get_current(&ctx);
+    it = ipc_maps.emplace(key, IpcMapper::instance().submit(e->ipc_handle, ctx)).first;
+    // once an open has outlasted the grace period the device is evidently busy: later first uses
+    // do not stall the caller again
+    if (it->second && !noted_ipc_wait) IpcMapper::wait(*it->second, params().ipc_map_wait_us.get());
+  }
+  if (!it->second) return nullptr;
+  return it->second->state.load(std::memory_order_acquire) == 1 ? it->second->mapped : nullptr;
+}
+// Says once per endpoint why payloads for a peer's device memory go through host fragments.
+void RdmaEndpoint::note_unmapped(PeerMapping* peer, const MrTableEntry* e) {
+  std::array<uint8_t, 64> handle;
+  memcpy(handle.data(), e->ipc_handle, handle.size());
+  auto it = ipc_maps.find(std::make_pair(peer->pid, handle));
+  const bool in_progress = it != ipc_maps.end() && it->second && it->second->state.load(std::memory_order_acquire) == 0;
+  if (in_progress) {
+    if (!noted_ipc_wait) NET_INFO(NCCL_NET, "mapping device memory of process %u is still in progress; payloads are staged through host memory until it arrives", peer->pid);
+    noted_ipc_wait = true;
+  } else {
+    if (!warned_ipc) NET_WARN("device memory of process %u cannot be mapped here; payloads to it are staged through host memory", peer->pid);
+    warned_ipc = true;
+  }
 }
 int RdmaEndpoint::ensure_published(MrHandle* mh) {
   if (!mh) return 0;
@@ -719,10 +743,7 @@ int RdmaSendComm::start_rendezvous(RdmaSendReq* r, const CtrlEntry& e) {
   if (mr && mr->kind == static_cast<uint32_t>(MrKind::CUDA_IPC) && !rep()->map_peer_cuda(peer, mr)) {
     // the peer's device memory cannot be mapped into this process (another container, a driver
     // without IPC): the payload travels as fragments that the receiver copies to its device
-    if (!rep()->warned_ipc) {
-      rep()->warned_ipc = true;
-      NET_WARN("device memory of process %u cannot be mapped here; payloads to it are staged through host memory", peer->pid);
-    }
+    rep()->note_unmapped(peer, mr);
     r->via_frags = true;
   }
   if ((dst_host || r->via_frags || (mr && mr->kind == static_cast<uint32_t>(MrKind::CUDA_STAGED))) && r->size &&

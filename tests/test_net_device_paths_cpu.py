@@ -69,6 +69,22 @@ def test_unmappable_peer_memory_falls_back_to_staged_fragments(built):
     assert "cannot be mapped here" in log
 
 
+def test_slow_peer_mapping_does_not_stall_the_sender(built):
+    """cuIpcOpenMemHandle can wait for the device to go idle, and the device may be running a
+    collective kernel that waits for this very data.  The open therefore runs on a helper thread:
+    with an open that takes 300 ms the payloads leave as host fragments after the grace period."""
+    log = _run(built, {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4", "FAKE_CUDA_IPC_OPEN_DELAY_MS": "300",
+                       "B200NET_IPC_MAP_WAIT_US": "2000", "FAKE_CUDA_LAUNCH_DELAY_US": "100"}, "device_transfer")
+    c = _payload_counters(log)
+    assert c["staged through host"] > 0, c
+    assert "still in progress" in log
+    # the same buffers used again and again: later chunks find the mapping and go direct
+    log = _run(built, {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4", "FAKE_CUDA_IPC_OPEN_DELAY_MS": "20",
+                       "B200NET_IPC_MAP_WAIT_US": "100"}, "proxy_pattern")
+    c = _payload_counters(log)
+    assert c["staged through host"] > 0 and c["copy kernel"] > 0, c
+
+
 @pytest.mark.parametrize("delay_us", ["0", "200"])
 def test_proxy_pattern_on_device_buffers(built, delay_us):
     """NCCL's proxy pattern with device chunks and kernels that complete asynchronously: many
