@@ -5,6 +5,10 @@
 // eager early/late receives, many connections on one listen communicator, close with requests in
 // flight. Every poll loop has a 20 s deadline; ranks report through exit codes.
 // usage: func_net [plugin.so] [scenario]      env: B200NET_* / OFI_NCCL_* parameters apply
+#include <deque>
+#include <map>
+#include <set>
+
 #include "func_common.h"
 
 // ------------------------------------------------------------------------------------------ scenarios
@@ -726,6 +730,187 @@ static int scenario_threads(int) {
   return 0;
 }
 
+// Eager and rendezvous sends against single and grouped receives in every order that the tag
+// rules allow (the cases of the reference's tests/functional/eager_multirecv.cpp:105-1652, as a
+// table): per tag, the k-th send must land in the k-th posted entry of that tag, whatever the
+// interleaving, whether it travelled eagerly or as a write, and whether the receives were posted
+// before or after the sends. The sender posts the way NCCL does: a refused send (null request)
+// holds back later sends of the same tag in that round, other tags go on.
+struct EmrSend {
+  int tag;
+  bool large;
+};
+struct EmrCase {
+  const char* name;
+  std::vector<EmrSend> sends;
+  std::vector<std::vector<int>> groups;   // tags of each posted receive, in posting order
+};
+
+static int run_emr_case(const EmrCase& c, Pair& p, int sock, bool late, int max_recvs) {
+  for (const auto& g : c.groups)
+    if ((int)g.size() > max_recvs) return 0;   // this protocol has no receive groups that large
+  constexpr size_t SMALL = 1024, LARGE = 96 << 10;
+  const int ns = (int)c.sends.size();
+  if (g_rank == 0) {
+    std::vector<std::vector<uint8_t>> buf(ns);
+    std::vector<void*> mh(ns), req(ns, nullptr);
+    for (int i = 0; i < ns; ++i) {
+      buf[i].resize(c.sends[i].large ? LARGE : SMALL);
+      fill(buf[i], 4000 + i);
+      OK(net->regMr(p.s, buf[i].data(), buf[i].size(), NCCL_PTR_HOST, &mh[i]));
+    }
+    if (!late && barrier(sock)) FAIL("barrier");   // early: the receives are already posted
+    std::deque<int> todo;
+    for (int i = 0; i < ns; ++i) todo.push_back(i);
+    std::vector<bool> done(ns, false);
+    const auto t0 = Clock::now();
+    while (!todo.empty()) {
+      std::set<int> held;
+      for (size_t round = todo.size(); round > 0; --round) {
+        const int i = todo.front();
+        todo.pop_front();
+        if (!held.count(c.sends[i].tag)) {
+          OK(net->isend(p.s, buf[i].data(), buf[i].size(), c.sends[i].tag, mh[i], nullptr, &req[i]));
+          if (req[i]) continue;
+          held.insert(c.sends[i].tag);
+        }
+        todo.push_back(i);
+      }
+      for (int i = 0; i < ns; ++i) {   // keep accepted sends moving
+        if (!req[i] || done[i]) continue;
+        int d = 0;
+        OK(net->test(req[i], &d, nullptr));
+        done[i] = d != 0;
+      }
+      if (expired(t0)) FAIL("%s (%s): %zu sends were never accepted", c.name, late ? "late" : "early", todo.size());
+    }
+    for (bool pending = true; pending;) {
+      pending = false;
+      for (int i = 0; i < ns; ++i) {
+        if (done[i]) continue;
+        int d = 0;
+        OK(net->test(req[i], &d, nullptr));
+        done[i] = d != 0;
+        pending = pending || !done[i];
+      }
+      if (expired(t0)) FAIL("%s (%s): sends did not complete", c.name, late ? "late" : "early");
+    }
+    for (int i = 0; i < ns; ++i) OK(net->deregMr(p.s, mh[i]));
+  } else {
+    if (late) usleep(30000);   // let the small sends leave eagerly first
+    const int ng = (int)c.groups.size();
+    std::vector<std::vector<std::vector<uint8_t>>> buf(ng);
+    std::vector<std::vector<void*>> mh(ng);
+    std::vector<void*> req(ng, nullptr);
+    std::map<int, int> seen;   // tag -> how many entries of it were posted so far
+    std::vector<std::vector<int>> source(ng);   // which send each entry must receive
+    for (int g = 0; g < ng; ++g) {
+      const int n = (int)c.groups[g].size();
+      buf[g].resize(n);
+      mh[g].resize(n);
+      void* data[8];
+      size_t sizes[8];
+      int tags[8];
+      for (int k = 0; k < n; ++k) {
+        const int tag = c.groups[g][k];
+        int nth = seen[tag]++, src = -1;
+        for (int i = 0; i < ns && src < 0; ++i)
+          if (c.sends[i].tag == tag && nth-- == 0) src = i;
+        if (src < 0) FAIL("%s: the table posts more receives of tag %d than sends", c.name, tag);
+        source[g].push_back(src);
+        buf[g][k].assign(LARGE + 64, 0);
+        data[k] = buf[g][k].data();
+        sizes[k] = buf[g][k].size();
+        tags[k] = tag;
+        OK(net->regMr(p.r, data[k], sizes[k], NCCL_PTR_HOST, &mh[g][k]));
+      }
+      if (post_recv(p.r, n, data, sizes, tags, mh[g].data(), &req[g])) return 1;
+    }
+    if (!late && barrier(sock)) FAIL("barrier");
+    for (int g = 0; g < ng; ++g) {
+      const int n = (int)c.groups[g].size();
+      std::vector<void*> one{req[g]};
+      std::vector<int> got;
+      if (wait_all(one, &got, n)) FAIL("%s (%s): receive %d did not complete", c.name, late ? "late" : "early", g);
+      for (int k = 0; k < n; ++k) {
+        const int src = source[g][k];
+        std::vector<uint8_t> want(c.sends[src].large ? LARGE : SMALL);
+        fill(want, 4000 + src);
+        if ((size_t)got[k] != want.size())
+          FAIL("%s (%s): receive %d entry %d (tag %d) reports %d bytes, send %d has %zu", c.name, late ? "late" : "early", g, k,
+               c.groups[g][k], got[k], src, want.size());
+        if (memcmp(want.data(), buf[g][k].data(), want.size()))
+          FAIL("%s (%s): receive %d entry %d (tag %d) does not hold send %d", c.name, late ? "late" : "early", g, k,
+               c.groups[g][k], src);
+        OK(net->deregMr(p.r, mh[g][k]));
+      }
+    }
+  }
+  if (barrier(sock)) FAIL("barrier");
+  return 0;
+}
+
+static int scenario_eager_multirecv(int sock) {
+  ncclNetProperties_v11_t props;
+  memset(&props, 0, sizeof(props));
+  OK(net->getProperties(0, &props));
+  Pair p;
+  if (connect_pair(0, sock, &p)) return 1;
+  const bool S = false, L = true;
+  auto two_groups_of_8 = [](const char* name, const std::vector<int>& tag_order, bool large) {
+    EmrCase c;
+    c.name = name;
+    for (int tag : tag_order) c.sends.push_back({tag, large});
+    c.groups = {{0, 1, 2, 3, 4, 5, 6, 7}, {0, 1, 2, 3, 4, 5, 6, 7}};
+    return c;
+  };
+  // tag 1 of the second group is sent before tag 7 of the first
+  const std::vector<int> cuts_in = {0, 1, 2, 3, 4, 5, 6, 1, 7, 0, 2, 3, 4, 5, 6, 7};
+  const std::vector<int> alternating = {0, 0, 1, 1, 2, 2, 3, 3, 4, 4, 5, 5, 6, 6, 7, 7};
+  std::vector<EmrCase> cases = {
+      {"one small send, one receive", {{1, S}}, {{1}}},
+      {"four small sends, four receives", {{1, S}, {1, S}, {1, S}, {1, S}}, {{1}, {1}, {1}, {1}}},
+      {"group of two, both eager", {{20, S}, {21, S}}, {{20, 21}}},
+      {"group of three, eager and write mixed", {{10, S}, {11, L}, {12, S}}, {{10, 11, 12}}},
+      {"group of two, both large", {{30, L}, {31, L}}, {{30, 31}}},
+      {"eager across a single receive and a group", {{1, S}, {40, S}, {41, S}}, {{1}, {40, 41}}},
+      {"eager sends in the order of two groups' tags", {{51, S}, {53, S}, {50, S}, {52, S}}, {{51, 53}, {50, 52}}},
+      {"eager sends across the order of two groups' tags", {{50, S}, {51, S}, {52, S}, {53, S}}, {{51, 53}, {50, 52}}},
+      {"two groups of four, every eager/write pairing per tag",
+       {{60, S}, {61, S}, {62, L}, {63, L}, {60, S}, {61, L}, {62, S}, {63, L}},
+       {{60, 61, 62, 63}, {60, 61, 62, 63}}},
+      {"four groups with the same two tags",
+       {{70, S}, {71, S}, {70, S}, {71, S}, {70, S}, {71, S}, {70, S}, {71, S}},
+       {{70, 71}, {70, 71}, {70, 71}, {70, 71}}},
+      two_groups_of_8("second group cuts in before the first is complete, all writes", cuts_in, L),
+      two_groups_of_8("second group cuts in before the first is complete, all eager", cuts_in, S),
+      {"second group cuts in, eager and write mixed",
+       {{0, S}, {1, S}, {2, L}, {1, S}, {3, L}, {0, S}, {2, L}, {3, L}},
+       {{0, 1, 2, 3}, {0, 1, 2, 3}}},
+      {"three groups interleaved, eager / large / eager",
+       {{0, S}, {1, S}, {0, L}, {0, S}, {1, L}, {1, S}},
+       {{0, 1}, {0, 1}, {0, 1}}},
+      two_groups_of_8("two groups of eight alternating send by send, all writes", alternating, L),
+      two_groups_of_8("two groups of eight alternating send by send, all eager", alternating, S),
+      {"eager batch spanning three groups of four",
+       {{1, S}, {2, S}, {3, S}, {4, S}, {10, S}, {11, S}, {12, S}, {13, S}, {20, S}, {21, S}, {22, S}, {23, S}},
+       {{1, 2, 3, 4}, {10, 11, 12, 13}, {20, 21, 22, 23}}},
+      {"eager batch across single, group, single, group",
+       {{1, S}, {50, S}, {51, S}, {1, S}, {60, S}, {61, S}},
+       {{1}, {50, 51}, {1}, {60, 61}}},
+      {"an eager send that belongs to a later receive than the large sends behind it",
+       {{30, S}, {40, S}, {31, L}, {20, L}},
+       {{30, 31}, {20}, {40}}},
+      {"eager sends for the third group while the first two take writes",
+       {{5, S}, {6, S}, {1, L}, {2, L}, {3, L}, {4, L}},
+       {{1, 2}, {3, 4}, {5, 6}}},
+  };
+  for (const EmrCase& c : cases)
+    for (int late = 0; late < 2; ++late)
+      if (run_emr_case(c, p, sock, late != 0, props.maxRecvs)) return 1;
+  return close_pair(&p);
+}
+
 struct Scenario {
   const char* name;
   int (*fn)(int);
@@ -736,7 +921,7 @@ static const Scenario kScenarios[] = {
     {"eager", scenario_eager},               {"reuse_listen", scenario_reuse_listen},
     {"inflight_close", scenario_inflight_close}, {"threads", scenario_threads},
     {"bandwidth", scenario_bandwidth},       {"proxy_pattern", scenario_proxy_pattern},
-    {"device_transfer", scenario_device_transfer},
+    {"device_transfer", scenario_device_transfer}, {"eager_multirecv", scenario_eager_multirecv},
 };
 
 static int run_rank(const char* so, const char* only, int sock) {

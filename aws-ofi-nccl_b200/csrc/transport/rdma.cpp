@@ -191,6 +191,7 @@ class RdmaSendComm : public SendComm {
   int send(void* data, size_t size, int tag, MrHandle* mh, Request** req) override;
   int close() override;
   void bind_eager_queue();
+  bool tag_is_queued(int tag) const;
   int start_rendezvous(RdmaSendReq* r, const CtrlEntry& e);
   int post_stripes(RdmaSendReq* r);
   void consume_entry(int idx, int num_recvs);
@@ -227,7 +228,7 @@ class RdmaRecvComm : public RecvComm {
   std::unique_ptr<MsgBuff> msgbuff;
   std::list<RdmaRecvReq*> posted;      // incomplete receive groups, oldest first
   std::list<EagerRx> eager_rx;         // arrived eager messages in eager_seq order
-  uint16_t next_eager_seq = 0;
+  uint16_t eager_arrived = 0;          // eager messages with a sequence number before this have all arrived
   uint8_t eager_taken[MAILBOX_SLOTS] = {};  // per group: entries matched to eager messages / completed
   int inflight = 0;
   uint32_t nonce = 0;
@@ -587,21 +588,39 @@ void RdmaSendComm::consume_entry(int idx, int num_recvs) {
 }
 
 
-// Bind queued eager sends (head first, never skipping) to control entries that have arrived.
+// Bind queued eager sends to control entries that have arrived. The queue is walked in send order
+// against the current receive group: a send whose tag has no free entry in that group stays
+// queued for a later group while sends behind it (necessarily of other tags) may still fill this
+// one; when the group is complete the walk starts over on the next. Sends of one tag therefore
+// never overtake each other, and every send lands in the first group, at or after the one that was
+// current when it left, that has a free entry of its tag: the rule the receiver applies too.
 void RdmaSendComm::bind_eager_queue() {
   auto* box = static_cast<CtrlMsg*>(mailbox->data());
-  while (!eager_queue.empty()) {
-    RdmaSendReq* r = eager_queue.front();
+  auto it = eager_queue.begin();
+  while (it != eager_queue.end()) {
+    RdmaSendReq* r = *it;
     int n = 0;
     const int idx = match_entry(box[next_seq % MAILBOX_SLOTS], next_seq, consumed_mask, r->tag, &n);
-    if (idx < 0) return;
+    if (idx == -1) return;   // the group has not arrived yet
+    if (idx < 0) {           // no free entry of this tag here
+      ++it;
+      continue;
+    }
     r->seq = next_seq;
     r->recv_idx = static_cast<uint8_t>(idx);
     r->state = ReqState::COMPLETED;
     B200NET_TRACE_EVENT(SendEagerComplete, dev_id, local_comm_id, r->seq, r->size, r);
-    eager_queue.pop_front();
+    const uint16_t before = next_seq;
+    it = eager_queue.erase(it);
     consume_entry(idx, n);
+    if (next_seq != before) it = eager_queue.begin();
   }
+}
+
+bool RdmaSendComm::tag_is_queued(int tag) const {
+  for (const RdmaSendReq* r : eager_queue)
+    if (r->tag == tag) return true;
+  return false;
 }
 
 int RdmaSendComm::post_stripes(RdmaSendReq* r) {
@@ -775,7 +794,9 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
   bind_eager_queue();
   auto* box = static_cast<CtrlMsg*>(mailbox->data());
   int n = 0;
-  const int idx = eager_queue.empty() ? match_entry(box[next_seq % MAILBOX_SLOTS], next_seq, consumed_mask, tag, &n) : -1;
+  // a send may take an entry directly unless an eager send of the same tag is still waiting for
+  // one (it has to go first); then it queues behind that one (-3: eager if small, else refused)
+  const int idx = tag_is_queued(tag) ? -3 : match_entry(box[next_seq % MAILBOX_SLOTS], next_seq, consumed_mask, tag, &n);
   NET_TRACE(NCCL_NET, "send: seq %u idx %d eagerq %zu ready0 %x size %zu", next_seq, idx, eager_queue.size(),
             box[next_seq % MAILBOX_SLOTS].entries[0].ready.load(), size);
   if (idx >= 0) {
@@ -793,6 +814,7 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
     }
     B200NET_TRACE_EVENT(Send, dev_id, local_comm_id, r->seq, r->size, r);
     consume_entry(idx, n);
+    bind_eager_queue();   // if that completed the group, queued sends may fit the next one
     ++inflight;
     r->serial = e->next_req_serial++;
     e->live_send_reqs[r->serial] = r;
@@ -814,7 +836,7 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
   }
   // no control message yet: eager if allowed
   const size_t eager_max = params().eager_max_size.get();
-  const bool eager_size_ok = idx == -1 && eager_max > 0 && size <= eager_max && size + sizeof(EagerHdr) <= FAB_LARGE_CELL &&
+  const bool eager_size_ok = eager_max > 0 && size <= eager_max && size + sizeof(EagerHdr) <= FAB_LARGE_CELL &&
                              static_cast<int>(eager_queue.size()) < MAX_EAGER_PENDING;
   const void* eager_src = data;
   int eager_slot = -1;
@@ -968,36 +990,55 @@ void RdmaRecvComm::on_eager(const EagerHdr& h, const void* data) {
     it = prev;
   }
   eager_rx.insert(it, std::move(rx));
+  // eager_arrived: every message sent before it is here (they arrive in order; a gap would hold
+  // later ones back until it is filled)
+  for (bool advanced = true; advanced;) {
+    advanced = false;
+    for (const EagerRx& m : eager_rx)
+      if (m.hdr.eager_seq == eager_arrived) {
+        ++eager_arrived;
+        advanced = true;
+      }
+  }
   B200NET_TRACE_EVENT(EagerRecv, dev_id, local_comm_id, h.eager_seq, h.size, nullptr);
   match_eager();
 }
 
-// Repeat the sender's binding rule: the head eager message goes to the first entry, in the oldest
-// group at or after its base_seq that still has one, whose tag matches and which neither an
-// earlier send (base_mask, for the base group) nor anything seen here has taken.
+// Repeat the sender's binding rule. Eager messages are taken in the order they were sent; each goes
+// to the first posted group, at or after the group that was current when it left (base_seq), that
+// has a free entry of its tag: free means taken neither by a send before it (base_mask, for the
+// base group) nor by an eager message matched here. A message that finds no such entry yet waits,
+// and so does every later message of the same tag; messages of other tags go on.
 void RdmaRecvComm::match_eager() {
-  while (!eager_rx.empty()) {
-    EagerRx& rx = eager_rx.front();
-    if (rx.hdr.eager_seq != next_eager_seq) return;  // an earlier eager message is still missing
+  int blocked_tags[MAX_EAGER_PENDING + 1];
+  int nblocked = 0;
+  auto it = eager_rx.begin();
+  while (it != eager_rx.end()) {
+    EagerRx& rx = *it;
+    if (static_cast<int16_t>(rx.hdr.eager_seq - eager_arrived) >= 0) return;  // an earlier one is still missing
+    bool blocked = false;
+    for (int k = 0; k < nblocked; ++k) blocked = blocked || blocked_tags[k] == rx.hdr.tag;
     RdmaRecvReq* target = nullptr;
     int target_idx = -1;
-    for (RdmaRecvReq* r : posted) {
-      if (seq_before(r->seq, rx.hdr.base_seq)) continue;  // the sender had moved past this group
-      uint8_t taken = eager_taken[r->seq % MAILBOX_SLOTS];
-      if (r->seq == rx.hdr.base_seq) taken |= rx.hdr.base_mask;
-      bool group_full = true;
-      for (int i = 0; i < r->n; ++i) {
-        if (taken & (1u << i)) continue;
-        group_full = false;
-        if (r->subs[i].tag == rx.hdr.tag) {
-          target = r;
-          target_idx = i;
-          break;
+    if (!blocked) {
+      for (RdmaRecvReq* r : posted) {
+        if (seq_before(r->seq, rx.hdr.base_seq)) continue;  // the sender had moved past this group
+        uint8_t taken = eager_taken[r->seq % MAILBOX_SLOTS];
+        if (r->seq == rx.hdr.base_seq) taken |= rx.hdr.base_mask;
+        for (int i = 0; i < r->n && !target; ++i) {
+          if (!(taken & (1u << i)) && r->subs[i].tag == rx.hdr.tag) {
+            target = r;
+            target_idx = i;
+          }
         }
+        if (target) break;
       }
-      if (target || !group_full) break;  // the sender never skips a group that still has free entries
     }
-    if (!target) return;
+    if (!target) {
+      if (!blocked && nblocked < MAX_EAGER_PENDING + 1) blocked_tags[nblocked++] = rx.hdr.tag;
+      ++it;
+      continue;
+    }
     SubRecv& s = target->subs[target_idx];
     const size_t nbytes = std::min<size_t>(rx.hdr.size, s.cap);
     if (nbytes) {
@@ -1012,8 +1053,7 @@ void RdmaRecvComm::match_eager() {
       }
     }
     s.received = nbytes;
-    ++next_eager_seq;
-    eager_rx.pop_front();
+    it = eager_rx.erase(it);
     finish_sub(target, target_idx);
   }
 }

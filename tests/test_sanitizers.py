@@ -36,7 +36,7 @@ def test_address_and_undefined_behaviour():
     tests, so = _build("address,undefined")
     for exe in sorted(tests.glob("unit_*")):
         _run([exe])
-    scenarios = ["connection", "message_transfer", "pingpong", "grouped_recv", "eager", "reuse_listen", "threads", "bandwidth", "proxy_pattern"]
+    scenarios = ["connection", "message_transfer", "pingpong", "grouped_recv", "eager", "reuse_listen", "threads", "bandwidth", "proxy_pattern", "eager_multirecv"]
     for proto in ("SENDRECV", "RDMA"):
         for sc in scenarios:
             # leak checking stays on for the single-process unit tests only: LeakSanitizer's report
