@@ -305,7 +305,19 @@ void CollComm::handle_dgram(const DgramHdr& h, const void* payload) {
     const auto* r = static_cast<const ReadRespMsg*>(payload);
     auto it = reads_in_flight_.find(r->req_id);
     if (it != reads_in_flight_.end()) {
-      it->second->store(r->status == 0 ? 1 : r->status);
+      int status = r->status == 0 ? 1 : r->status;
+      auto landing = read_landings_.find(r->req_id);
+      if (landing != read_landings_.end()) {
+        if (status == 1 && !landing->second.host.empty()) {
+          static thread_local cuda::Stream st = nullptr;
+          if ((!st && cuda::stream_create(&st) != 0) ||
+              cuda::memcpy_async(landing->second.device_dst, landing->second.host.data(), landing->second.host.size(), st) != 0 ||
+              cuda::stream_synchronize(st) != 0)
+            status = -EIO;
+        }
+        read_landings_.erase(landing);
+      }
+      it->second->store(status);
       reads_in_flight_.erase(it);
     }
   }
@@ -438,7 +450,16 @@ int CollComm::iput(uint64_t src_off, SymmMr* src, size_t size, uint64_t dst_off,
     const char* lsrc = static_cast<const char*>(src->base) + src_off;
     const RemoteMr& rm = dst->remote[peer_rank];
     if (rm.kind == static_cast<uint32_t>(MrKind::HOST)) {
-      op.local = lsrc;
+      if (src->type == NCCL_PTR_CUDA) {
+        // the host write path reads its source with the CPU: fetch the device bytes first
+        static thread_local cuda::Stream st = nullptr;
+        if (!st && cuda::stream_create(&st) != 0) return -EIO;
+        op.bounce.resize(size);
+        if (cuda::memcpy_async(op.bounce.data(), lsrc, size, st) != 0 || cuda::stream_synchronize(st) != 0) return -EIO;
+        op.local = op.bounce.data();
+      } else {
+        op.local = lsrc;
+      }
       op.remote_addr = rm.addr + dst_off;
     } else if (dst->mapped[peer_rank]) {
       // device window mapped here: copy-engine transfer on a stream, completion through an event
@@ -472,18 +493,36 @@ int CollComm::iget(uint64_t remote_off, SymmMr* remote, size_t size, uint64_t lo
   const RemoteMr& rm = remote->remote[peer_rank];
   int rc = 0;
   if (rm.kind == static_cast<uint32_t>(MrKind::HOST)) {
-    rc = fab_.read_host(peers_[peer_rank].map, rm.addr + remote_off, ldst, size);
+    // host bytes are read by the CPU; a device destination gets them through a host landing buffer
+    const bool to_device = local->type == NCCL_PTR_CUDA;
+    std::vector<uint8_t> landing(to_device ? size : 0);
+    char* host_dst = to_device ? reinterpret_cast<char*>(landing.data()) : ldst;
+    rc = fab_.read_host(peers_[peer_rank].map, rm.addr + remote_off, host_dst, size);
     if (rc == -ENOTSUP) {
       // no direct access to the peer's memory: ask it to write the bytes here
       PeerState& p = peers_[peer_rank];
       ReadReqMsg rq{p.comm_id, static_cast<uint32_t>(rank), next_read_id_++, rm.addr + remote_off, size,
-                    reinterpret_cast<uint64_t>(ldst)};
+                    reinterpret_cast<uint64_t>(host_dst)};
+      if (to_device) {
+        // the landing buffer must keep its address until the response: park it first
+        ReadLanding& l = read_landings_[rq.req_id];
+        l.host = std::move(landing);
+        l.device_dst = ldst;
+        rq.reply_addr = reinterpret_cast<uint64_t>(l.host.data());
+      }
       rc = fab_.send(p.map, DgramType::READ_REQ, 0, &rq, sizeof(rq));
+      if (rc != 0) read_landings_.erase(rq.req_id);
       if (rc == -EAGAIN) return 0;  // no request: call again
       if (rc != 0) return rc;
       reads_in_flight_[rq.req_id] = status;
       *req = new StatusRequest(this, status);
       return 0;
+    }
+    if (rc == 0 && to_device && size) {
+      static thread_local cuda::Stream st = nullptr;
+      if (!st && cuda::stream_create(&st) != 0) return -EIO;
+      rc = cuda::memcpy_async(ldst, landing.data(), size, st);
+      if (rc == 0) rc = cuda::stream_synchronize(st);
     }
   } else if (remote->mapped[peer_rank]) {
     static thread_local cuda::Stream st = nullptr;

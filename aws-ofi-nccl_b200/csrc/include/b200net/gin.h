@@ -94,6 +94,7 @@ struct PendingOp {            // a put whose data copy may still be running
   size_t len = 0, done = 0;
   uint64_t remote_addr = 0;
   const void* local = nullptr;
+  std::vector<uint8_t> bounce;   // host copy of a device source bound for host memory
   bool has_signal = false, data_done = false, signal_sent = false, staged = false;
   MetadataMsg meta{};
   std::shared_ptr<std::atomic<int>> status;  // 0 pending, 1 done, <0 error (shared with the request)
@@ -200,6 +201,12 @@ class CollComm {
   struct ReadService { ReadReqMsg req; size_t done; bool data_done; };
   std::deque<ReadService> read_services_;     // reads this rank is serving for peers without direct access
   std::map<uint64_t, std::shared_ptr<std::atomic<int>>> reads_in_flight_;
+  // a read served by the peer for a device destination lands in host memory first
+  struct ReadLanding {
+    std::vector<uint8_t> host;
+    void* device_dst;
+  };
+  std::map<uint64_t, ReadLanding> read_landings_;
   uint64_t next_read_id_ = 1;
   int serve_reads();
   bool error_ = false, closing_ = false;

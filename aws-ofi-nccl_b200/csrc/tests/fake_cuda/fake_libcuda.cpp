@@ -6,6 +6,8 @@
 //
 // Fault injection through the environment (read at cuInit):
 //   FAKE_CUDA_FAIL_IPC_OPEN=1   cuIpcOpenMemHandle fails (the plugin must fall back to staging)
+//   FAKE_CUDA_PROTECT=0         device addresses stay readable and writable by host code (default:
+//                               they are mapped without access, so a host dereference faults)
 //   FAKE_CUDA_IPC_OPEN_DELAY_MS=n cuIpcOpenMemHandle takes n milliseconds (a device that is busy)
 //   FAKE_CUDA_LAUNCH_DELAY_US=n kernels "finish" n microseconds after the launch call returns
 //                               (a helper thread performs them), so completions are asynchronous
@@ -34,6 +36,7 @@ struct Alloc {
   size_t size;
   std::string shm_name;   // empty: mapping of a peer's allocation
   bool opened_from_peer;
+  unsigned char* shadow;   // readable and writable view of the same pages (the device's own view)
 };
 std::mutex g_mu;
 std::map<uintptr_t, Alloc> g_allocs;   // base -> allocation ("device" address ranges of this process)
@@ -50,6 +53,35 @@ const Alloc* find_alloc(uintptr_t p, uintptr_t* base) {
     return &it->second;
   }
   return nullptr;
+}
+
+// "Device" addresses handed to the program are mapped without access rights, so host code that
+// dereferences one faults at once, as it would on a real device without unified addressing. The
+// stand-in itself (copies, "kernels") works on a second, accessible mapping of the same pages.
+// Host addresses pass through unchanged. FAKE_CUDA_PROTECT=0 switches the protection off.
+bool protect_on() {
+  static const bool on = !(getenv("FAKE_CUDA_PROTECT") && !atoi(getenv("FAKE_CUDA_PROTECT")));
+  return on;
+}
+void* dev_view(const void* p) {
+  std::lock_guard<std::mutex> g(g_mu);
+  uintptr_t base = 0;
+  const Alloc* al = find_alloc(reinterpret_cast<uintptr_t>(p), &base);
+  if (!al) return const_cast<void*>(p);
+  return al->shadow + (reinterpret_cast<uintptr_t>(p) - base);
+}
+// Maps the pages of fd twice: the program's (protected) address and the stand-in's own view.
+bool map_pair(int fd, size_t bytes, void** user, unsigned char** shadow) {
+  void* u = mmap(nullptr, bytes, protect_on() ? PROT_NONE : (PROT_READ | PROT_WRITE), MAP_SHARED, fd, 0);
+  if (u == MAP_FAILED) return false;
+  void* sh = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  if (sh == MAP_FAILED) {
+    munmap(u, bytes);
+    return false;
+  }
+  *user = u;
+  *shadow = static_cast<unsigned char*>(sh);
+  return true;
 }
 
 struct IpcHandlePayload {   // fits the 64 opaque bytes
@@ -172,14 +204,16 @@ CUresult fMemAlloc(CUdeviceptr* out, size_t bytes) {
     shm_unlink(name);
     return CUDA_ERROR_OUT_OF_MEMORY;
   }
-  void* p = mmap(nullptr, rounded, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  void* p = nullptr;
+  unsigned char* shadow = nullptr;
+  const bool mapped = map_pair(fd, rounded, &p, &shadow);
   close(fd);
-  if (p == MAP_FAILED) {
+  if (!mapped) {
     shm_unlink(name);
     return CUDA_ERROR_OUT_OF_MEMORY;
   }
   std::lock_guard<std::mutex> g(g_mu);
-  g_allocs[reinterpret_cast<uintptr_t>(p)] = Alloc{rounded, name, false};
+  g_allocs[reinterpret_cast<uintptr_t>(p)] = Alloc{rounded, name, false, shadow};
   *out = reinterpret_cast<CUdeviceptr>(p);
   return CUDA_SUCCESS;
 }
@@ -188,12 +222,13 @@ CUresult fMemFree(CUdeviceptr p) {
   auto it = g_allocs.find(static_cast<uintptr_t>(p));
   if (it == g_allocs.end()) return CUDA_ERROR_INVALID_VALUE;
   munmap(reinterpret_cast<void*>(it->first), it->second.size);
+  munmap(it->second.shadow, it->second.size);
   if (!it->second.shm_name.empty()) shm_unlink(it->second.shm_name.c_str());
   g_allocs.erase(it);
   return CUDA_SUCCESS;
 }
 CUresult fMemsetD8(CUdeviceptr p, unsigned char v, size_t n) {
-  memset(reinterpret_cast<void*>(p), v, n);
+  memset(dev_view(reinterpret_cast<void*>(p)), v, n);
   return CUDA_SUCCESS;
 }
 CUresult fIpcGetMemHandle(CUipcMemHandle* h, CUdeviceptr p) {
@@ -215,11 +250,13 @@ CUresult fIpcOpenMemHandle(CUdeviceptr* out, CUipcMemHandle h, unsigned) {
   pl.name[sizeof(pl.name) - 1] = 0;
   const int fd = shm_open(pl.name, O_RDWR, 0600);
   if (fd < 0) return CUDA_ERROR_INVALID_VALUE;
-  void* p = mmap(nullptr, pl.size, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  void* p = nullptr;
+  unsigned char* shadow = nullptr;
+  const bool mapped = map_pair(fd, pl.size, &p, &shadow);
   close(fd);
-  if (p == MAP_FAILED) return CUDA_ERROR_OUT_OF_MEMORY;
+  if (!mapped) return CUDA_ERROR_OUT_OF_MEMORY;
   std::lock_guard<std::mutex> g(g_mu);
-  g_allocs[reinterpret_cast<uintptr_t>(p)] = Alloc{pl.size, "", true};
+  g_allocs[reinterpret_cast<uintptr_t>(p)] = Alloc{pl.size, "", true, shadow};
   *out = reinterpret_cast<CUdeviceptr>(p);
   return CUDA_SUCCESS;
 }
@@ -228,6 +265,7 @@ CUresult fIpcCloseMemHandle(CUdeviceptr p) {
   auto it = g_allocs.find(static_cast<uintptr_t>(p));
   if (it == g_allocs.end()) return CUDA_ERROR_INVALID_VALUE;
   munmap(reinterpret_cast<void*>(it->first), it->second.size);
+  munmap(it->second.shadow, it->second.size);
   g_allocs.erase(it);
   return CUDA_SUCCESS;
 }
@@ -262,7 +300,7 @@ CUresult fEventDestroy(CUevent e) {
 CUresult fEventRecord(CUevent, CUstream) { return CUDA_SUCCESS; }
 CUresult fEventQuery(CUevent) { return CUDA_SUCCESS; }
 CUresult fMemcpyAsync(CUdeviceptr d, CUdeviceptr s, size_t n, CUstream) {
-  memcpy(reinterpret_cast<void*>(d), reinterpret_cast<const void*>(s), n);
+  memcpy(dev_view(reinterpret_cast<void*>(d)), dev_view(reinterpret_cast<const void*>(s)), n);
   return CUDA_SUCCESS;
 }
 CUresult fModuleLoadData(CUmodule* m, const void* image) {
@@ -287,8 +325,8 @@ CUresult fLaunchKernel(CUfunction f, unsigned, unsigned, unsigned, unsigned, uns
     auto* flag = *static_cast<unsigned long long**>(args[4]);
     const unsigned long long value = *static_cast<unsigned long long*>(args[5]);
     run_later([=] {
-      memcpy(dst, src, bytes);
-      __atomic_store_n(flag, value, __ATOMIC_RELEASE);
+      memcpy(dev_view(dst), dev_view(src), bytes);
+      __atomic_store_n(static_cast<unsigned long long*>(dev_view(flag)), value, __ATOMIC_RELEASE);
     });
     return CUDA_SUCCESS;
   }
@@ -301,10 +339,11 @@ CUresult fLaunchKernel(CUfunction f, unsigned, unsigned, unsigned, unsigned, uns
     const unsigned flag_off = *static_cast<unsigned*>(args[5]);
     const unsigned long long value = *static_cast<unsigned long long*>(args[6]);
     run_later([=] {
-      memcpy(slot + 16, payload, bytes);
-      memcpy(slot, &h0, 8);
-      memcpy(slot + 8, &h1, 8);
-      __atomic_store_n(reinterpret_cast<unsigned long long*>(slot + flag_off), value, __ATOMIC_RELEASE);
+      auto* out = static_cast<unsigned char*>(dev_view(slot));
+      memcpy(out + 16, dev_view(payload), bytes);
+      memcpy(out, &h0, 8);
+      memcpy(out + 8, &h1, 8);
+      __atomic_store_n(reinterpret_cast<unsigned long long*>(out + flag_off), value, __ATOMIC_RELEASE);
     });
     return CUDA_SUCCESS;
   }
@@ -367,4 +406,6 @@ CUresult fake_cuda_mem_alloc(void** p, size_t bytes) {
   return r;
 }
 CUresult fake_cuda_mem_free(void* p) { return fMemFree(reinterpret_cast<CUdeviceptr>(p)); }
+// The accessible view of a "device" address (what a test uses to fill and check device buffers).
+void* fake_cuda_host_view(void* p) { return dev_view(p); }
 }

@@ -10,6 +10,7 @@
 #include <set>
 
 #include "func_common.h"
+#include "test_buf.h"
 
 // ------------------------------------------------------------------------------------------ scenarios
 static int scenario_connection(int sock) {
@@ -393,55 +394,6 @@ static int scenario_inflight_close(int sock) {
   return close_pair(&q);
 }
 
-// "Device" buffers for CPU runs: with FUNC_NET_DEVICE=1 and the stand-in driver on the library
-// path (it serves device memory out of POSIX shared memory), buffers come from the driver and are
-// registered as NCCL_PTR_CUDA, so the plugin's IPC mapping, copy-kernel and eager-pack paths run.
-struct TestBuf {
-  uint8_t* p = nullptr;
-  size_t n = 0;
-  bool dev = false;
-  uint8_t* data() { return p; }
-  size_t size() const { return n; }
-};
-using FakeAllocFn = int (*)(void**, size_t);
-using FakeFreeFn = int (*)(void*);
-static FakeAllocFn g_dev_alloc = nullptr;
-static FakeFreeFn g_dev_free = nullptr;
-static bool device_mode() {
-  static int mode = -1;
-  if (mode < 0) {
-    mode = 0;
-    if (getenv("FUNC_NET_DEVICE") && atoi(getenv("FUNC_NET_DEVICE"))) {
-      void* h = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
-      if (h) {
-        g_dev_alloc = reinterpret_cast<FakeAllocFn>(dlsym(h, "fake_cuda_mem_alloc"));
-        g_dev_free = reinterpret_cast<FakeFreeFn>(dlsym(h, "fake_cuda_mem_free"));
-      }
-      mode = (g_dev_alloc && g_dev_free) ? 1 : 0;
-      if (!mode) fprintf(stderr, "[rank %d] FUNC_NET_DEVICE set but the stand-in driver is not on the library path\n", g_rank);
-    }
-  }
-  return mode == 1;
-}
-static int buf_alloc(TestBuf* b, size_t n) {
-  b->n = n;
-  b->dev = device_mode();
-  if (b->dev) {
-    void* p = nullptr;
-    if (g_dev_alloc(&p, n) != 0) return 1;
-    b->p = static_cast<uint8_t*>(p);
-  } else {
-    b->p = static_cast<uint8_t*>(malloc(n));
-  }
-  return b->p ? 0 : 1;
-}
-static void buf_free(TestBuf* b) {
-  if (!b->p) return;
-  if (b->dev) g_dev_free(b->p);
-  else free(b->p);
-  b->p = nullptr;
-}
-static int buf_type() { return device_mode() ? NCCL_PTR_CUDA : NCCL_PTR_HOST; }
 
 // Sizes around the eager limit and up to several stripes, every message checked byte for byte,
 // several in flight; in device mode this walks the eager-pack path (small), the copy kernel
@@ -461,8 +413,8 @@ static int scenario_device_transfer(int sock) {
       if (buf_alloc(&sb[i], sizes[i] + 64) || buf_alloc(&rb[i], sizes[i] + 64)) FAIL("buffer allocation failed");
       std::vector<uint8_t> pat(sizes[i]);
       fill(pat, 500 + 10 * pass + i + 1000 * g_rank);
-      memcpy(sb[i].data(), pat.data(), sizes[i]);
-      memset(rb[i].data(), 0xCD, rb[i].size());
+      memcpy(sb[i].host(), pat.data(), sizes[i]);
+      memset(rb[i].host(), 0xCD, rb[i].size());
       OK(net->regMr(p.s, sb[i].data(), sb[i].size(), buf_type(), &smh[i]));
       OK(net->regMr(p.r, rb[i].data(), rb[i].size(), buf_type(), &rmh[i]));
     }
@@ -512,8 +464,8 @@ static int scenario_device_transfer(int sock) {
       std::vector<uint8_t> want(sizes[i]);
       fill(want, 500 + 10 * pass + i + 1000 * (1 - g_rank));
       if (got[nmsg + i] != static_cast<int>(sizes[i])) FAIL("pass %d message %d: size %d, expected %zu", pass, i, got[nmsg + i], sizes[i]);
-      if (memcmp(want.data(), rb[i].data(), sizes[i])) FAIL("pass %d message %d (%zu bytes): payload differs", pass, i, sizes[i]);
-      if (rb[i].data()[sizes[i]] != 0xCD) FAIL("pass %d message %d: wrote past the end", pass, i);
+      if (memcmp(want.data(), rb[i].host(), sizes[i])) FAIL("pass %d message %d (%zu bytes): payload differs", pass, i, sizes[i]);
+      if (rb[i].host()[sizes[i]] != 0xCD) FAIL("pass %d message %d: wrote past the end", pass, i);
     }
     if (barrier(sock)) FAIL("barrier");
     for (int i = 0; i < nmsg; ++i) {
@@ -563,8 +515,8 @@ static int scenario_proxy_pattern(int sock) {
   if (barrier(sock)) FAIL("barrier");
   auto stamp = [&](TestBuf& b, int c, int k) {
     uint32_t hdr[4] = {0xC0FFEEu, static_cast<uint32_t>(g_rank), static_cast<uint32_t>(c), static_cast<uint32_t>(k)};
-    memcpy(b.data(), hdr, sizeof(hdr));
-    b.data()[chunk - 1] = static_cast<uint8_t>(c * 31 + k);
+    memcpy(b.host(), hdr, sizeof(hdr));
+    b.host()[chunk - 1] = static_cast<uint8_t>(c * 31 + k);
   };
   auto t0 = Clock::now();
   long done_total = 0;
@@ -610,11 +562,11 @@ static int scenario_proxy_pattern(int sock) {
         OK(net->test(x.rreq[slot], &d, &sz));
         if (d) {
           uint32_t hdr[4];
-          memcpy(hdr, x.rbuf[slot].data(), sizeof(hdr));
+          memcpy(hdr, x.rbuf[slot].host(), sizeof(hdr));
           const int k = x.rreq_chunk[slot];
           if (sz != static_cast<int>(chunk) || hdr[0] != 0xC0FFEEu || hdr[1] != static_cast<uint32_t>(1 - g_rank) ||
               hdr[2] != static_cast<uint32_t>(c) || hdr[3] != static_cast<uint32_t>(k) ||
-              x.rbuf[slot].data()[chunk - 1] != static_cast<uint8_t>(c * 31 + k))
+              x.rbuf[slot].host()[chunk - 1] != static_cast<uint8_t>(c * 31 + k))
             FAIL("channel %d chunk %d arrived wrong (size %d, hdr %x %u %u %u)", c, k, sz, hdr[0], hdr[1], hdr[2], hdr[3]);
           ++x.recv_done;
           ++done_total;

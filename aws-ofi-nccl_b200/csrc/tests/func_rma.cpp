@@ -1,5 +1,6 @@
 // Functional test of the RMA / GIN tables through the public ABI (dlopen + ncclRmaPlugin_v15,
-// ncclGinPlugin_v13, ncclGinPlugin_v14), N processes on one host, host buffers:
+// ncclGinPlugin_v13, ncclGinPlugin_v14), N processes on one host; host buffers, or with
+// FUNC_NET_DEVICE=1 and the stand-in driver on the library path, device buffers:
 //   * collective connect over the plugin's own ring bootstrap
 //   * 64 iput + 64 iputSignal(INC) + iputSignal(ADD) to every peer; the target polls the signal
 //     word while calling rmaProgress; payload verified
@@ -36,6 +37,8 @@ static int g_rank = 0, g_n = 3;
     ncclResult_t _r = (call);                                      \
     if (_r != ncclSuccess) FAIL("%s returned %d", #call, (int)_r); \
   } while (0)
+
+#include "test_buf.h"
 
 using Clock = std::chrono::steady_clock;
 static bool expired(Clock::time_point t0, int s = 30) { return Clock::now() - t0 > std::chrono::seconds(s); }
@@ -130,18 +133,32 @@ static int run_rank(const char* so) {
 
   // ---- buffers: data window (slot per source rank), signal words, source payload
   const size_t SLOT = 4096;
-  std::vector<uint8_t> window(SLOT * g_n, 0), src(SLOT), got(SLOT, 0);
-  std::vector<uint64_t> signals(16, 0);
+  TestBuf window_b, src_b, got_b, signals_b;
+  // FUNC_RMA_HOST_TARGETS=1 keeps the put targets (window, signals) in host memory while the
+  // sources stay on the device; FUNC_RMA_HOST_SOURCES=1 the other way round (=2: the buffer that
+  // iget fills stays on the device, so a read of host memory lands in device memory)
+  const bool host_targets = getenv("FUNC_RMA_HOST_TARGETS") && atoi(getenv("FUNC_RMA_HOST_TARGETS"));
+  const bool host_sources = getenv("FUNC_RMA_HOST_SOURCES") && atoi(getenv("FUNC_RMA_HOST_SOURCES"));
+  if (buf_alloc(&window_b, SLOT * g_n, !host_targets) || buf_alloc(&src_b, SLOT, !host_sources) ||
+      buf_alloc(&got_b, SLOT, !host_sources || atoi(getenv("FUNC_RMA_HOST_SOURCES")) == 2) || buf_alloc(&signals_b, 16 * 8, !host_targets))
+    FAIL("buffer allocation failed");
+  // window / src / got / signals: where this test reads and writes; the *_b.data() addresses are
+  // what the plugin gets (the same in host mode, inaccessible to host code in device mode)
+  uint8_t *window = window_b.host(), *src = src_b.host(), *got = got_b.host();
+  uint64_t* signals = reinterpret_cast<uint64_t*>(signals_b.host());
+  memset(window, 0, SLOT * g_n);
+  memset(got, 0, SLOT);
+  memset(signals, 0, 16 * 8);
   for (size_t i = 0; i < SLOT; ++i) src[i] = static_cast<uint8_t>(i * 7 + g_rank);
   void *win_mh, *src_mh, *sig_mh, *got_mh;
-  OK(rma->regMrSym(coll, window.data(), window.size(), NCCL_PTR_HOST, 0, &win_mh));
-  OK(rma->regMrSym(coll, src.data(), src.size(), NCCL_PTR_HOST, 0, &src_mh));
-  OK(rma->regMrSym(coll, signals.data(), signals.size() * 8, NCCL_PTR_HOST, NCCL_NET_MR_FLAG_SIGNAL_NEVER_RESET, &sig_mh));
-  OK(rma->regMrSym(coll, got.data(), got.size(), NCCL_PTR_HOST, 0, &got_mh));
+  OK(rma->regMrSym(coll, window_b.data(), SLOT * g_n, buf_type(window_b), 0, &win_mh));
+  OK(rma->regMrSym(coll, src_b.data(), SLOT, buf_type(src_b), 0, &src_mh));
+  OK(rma->regMrSym(coll, signals_b.data(), 16 * 8, buf_type(signals_b), NCCL_NET_MR_FLAG_SIGNAL_NEVER_RESET, &sig_mh));
+  OK(rma->regMrSym(coll, got_b.data(), SLOT, buf_type(got_b), 0, &got_mh));
 
   // duplicate registration: same handle, and it survives one dereg
   void* dup = nullptr;
-  OK(rma->regMrSym(coll, window.data(), window.size(), NCCL_PTR_HOST, 0, &dup));
+  OK(rma->regMrSym(coll, window_b.data(), SLOT * g_n, buf_type(window_b), 0, &dup));
   if (dup != win_mh) FAIL("a second registration of the same buffer got a different handle");
   OK(rma->deregMrSym(coll, dup));
 
@@ -208,6 +225,10 @@ static int run_rank(const char* so) {
   OK(rma->deregMrSym(coll, sig_mh));
   OK(rma->deregMrSym(coll, src_mh));
   OK(rma->deregMrSym(coll, win_mh));
+  buf_free(&window_b);
+  buf_free(&src_b);
+  buf_free(&got_b);
+  buf_free(&signals_b);
   OK(rma->destroyContext(ctx));
   OK(rma->closeColl(coll));
   OK(rma->closeListen(lcomm));

@@ -2,7 +2,10 @@
 eager-pack kernels, copy-engine fallback, staging when a peer cannot be mapped) run here without a
 GPU: the test binary and the plugin load a stand-in ``libcuda.so.1`` whose "device memory" is
 shared host memory and whose "kernels" are host functions that finish after a chosen delay.  The
-stand-in is test code only; the plugin itself is the unmodified shipped library."""
+addresses it hands out as device memory are mapped without access rights, so any place where the
+plugin touches a device buffer with the CPU (instead of going through a copy or a kernel) faults
+here, as it would on a GPU.  The stand-in is test code only; the plugin itself is the unmodified
+shipped library."""
 import os
 import re
 import subprocess
@@ -92,3 +95,26 @@ def test_proxy_pattern_on_device_buffers(built, delay_us):
     env = {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4", "FAKE_CUDA_LAUNCH_DELAY_US": delay_us}
     for _ in range(3):
         _run(built, env, "proxy_pattern")
+
+
+@pytest.mark.parametrize("nranks,env", [
+    (2, {}),
+    (3, {"FAKE_CUDA_LAUNCH_DELAY_US": "100"}),
+    (4, {"B200NET_DISABLE_CMA": "1"}),
+    (3, {"FUNC_RMA_HOST_TARGETS": "1"}),
+    (3, {"FUNC_RMA_HOST_TARGETS": "1", "B200NET_DISABLE_CMA": "1"}),
+    (3, {"FUNC_RMA_HOST_SOURCES": "1"}),
+    (3, {"FUNC_RMA_HOST_SOURCES": "2"}),
+    (3, {"FUNC_RMA_HOST_SOURCES": "2", "B200NET_DISABLE_CMA": "1"}),
+], ids=["2", "3-async", "4-staged", "dev-to-host", "dev-to-host-staged", "host-to-dev", "host-read-into-dev",
+        "host-read-into-dev-served"])
+def test_rma_and_gin_tables_on_device_buffers(built, nranks, env):
+    """Puts, signalled puts, gets and flushes with windows, sources and signal words in device
+    memory, and every host / device pairing of source and target."""
+    fake = built / "tests" / "fake_cuda"
+    e = dict(os.environ, FUNC_NET_DEVICE="1")
+    e["LD_LIBRARY_PATH"] = f"{fake}:" + e.get("LD_LIBRARY_PATH", "")
+    e.update(env)
+    res = subprocess.run([str(built / "tests" / "func_rma"), str(built / "libnccl-net-ofi-b200.so"), str(nranks)],
+                         capture_output=True, text=True, timeout=300, env=e, cwd=built)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
