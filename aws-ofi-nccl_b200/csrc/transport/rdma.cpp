@@ -680,7 +680,8 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
         while (s.done < s.len) {
           const size_t nbytes = std::min(chunk, s.len - s.done);
           DeviceFragHdr fh{r->target.buff_addr + s.offset + s.done, static_cast<uint32_t>(nbytes), 0};
-          const int rc = e->fab.send(peer, static_cast<DgramType>(DGRAM_DEVICE_FRAG), 0, &fh, sizeof(fh),
+          // the large ring even for a short tail: the completion is ordered behind it there
+          const int rc = e->fab.send(peer, static_cast<DgramType>(DGRAM_DEVICE_FRAG), DGRAM_FLAG_ORDER_AFTER_FRAGS, &fh, sizeof(fh),
                                      src + s.offset + s.done, nbytes);
           if (rc == -EAGAIN) {
             back_pressure = true;

@@ -247,7 +247,10 @@ int FabricEndpoint::write_host(PeerMapping* dst, uint64_t remote_addr, const voi
   while (*done < len) {
     const size_t n = std::min(chunk, len - *done);
     FragHdr fh{remote_addr + *done, static_cast<uint32_t>(n), 0};
-    const int rc = send(dst, DgramType::WRITE_FRAG, 0, &fh, sizeof(fh), static_cast<const char*>(local) + *done, n);
+    // always through the large ring, however short: the completion that follows travels there too,
+    // and only datagrams of one ring are seen in the order they were posted
+    const int rc = send(dst, DgramType::WRITE_FRAG, DGRAM_FLAG_ORDER_AFTER_FRAGS, &fh, sizeof(fh),
+                        static_cast<const char*>(local) + *done, n);
     if (rc != 0) return rc;  // -EAGAIN: caller retries later from *done
     *done += n;
   }
