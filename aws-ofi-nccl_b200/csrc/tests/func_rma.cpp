@@ -216,6 +216,33 @@ static int run_rank(const char* so) {
     for (size_t i = 0; i < SLOT; ++i)
       if (got[i] != static_cast<uint8_t>(i * 7 + peer)) FAIL("iget payload differs at byte %zu", i);
   }
+  // ---- kernel-initiated context (device buffers only): every rank allocates a pad of signal and
+  // counter words on its device, the pads are mapped into every peer, and the device-visible
+  // handle block lists {rank, nranks, signals, counters, pad address per rank}
+  if (device_mode()) {
+    ncclGinConfig_v14_t kcfg = {3 + g_rank, 2, 1, 0, -1, 0, 0};   // ranks ask for different counts
+    void* kctx = nullptr;
+    ncclNetDeviceHandle_t* dh = nullptr;
+    OK(gin14->createContext(coll, &kcfg, &kctx, &dh));
+    if (!dh || dh->netDeviceType != NCCL_NET_DEVICE_GIN_GDAKI || dh->needsProxyProgress) FAIL("unexpected device handle");
+    if (dh->size != (4 + (size_t)g_n) * 8) FAIL("handle block of %zu bytes", (size_t)dh->size);
+    const uint64_t* block = static_cast<const uint64_t*>(g_dev_view(dh->handle));
+    if (block[0] != (uint64_t)g_rank || block[1] != (uint64_t)g_n || block[2] != (uint64_t)(3 + g_n - 1) || block[3] != 2)
+      FAIL("handle block says rank %llu of %llu, %llu signals, %llu counters", (unsigned long long)block[0],
+           (unsigned long long)block[1], (unsigned long long)block[2], (unsigned long long)block[3]);
+    // each rank leaves its mark in word [rank] of every pad through the mapping it was given
+    for (int r = 0; r < g_n; ++r) {
+      if (!block[4 + r]) FAIL("pad of rank %d is not mapped", r);
+      auto* pad = static_cast<uint64_t*>(g_dev_view(reinterpret_cast<void*>(block[4 + r])));
+      __atomic_store_n(&pad[g_rank], 0xAB00u + g_rank, __ATOMIC_RELEASE);
+    }
+    if (oob_barrier()) FAIL("barrier");
+    const auto* mine = static_cast<const uint64_t*>(g_dev_view(reinterpret_cast<void*>(block[4 + g_rank])));
+    for (int r = 0; r < g_n; ++r)
+      if (__atomic_load_n(&mine[r], __ATOMIC_ACQUIRE) != 0xAB00u + r) FAIL("pad word %d holds %llx", r, (unsigned long long)mine[r]);
+    if (oob_barrier()) FAIL("barrier");
+    OK(gin14->destroyContext(kctx));
+  }
   bool err = true;
   OK(rma->queryLastError(ctx, &err));
   if (err) FAIL("queryLastError reports an error");

@@ -53,6 +53,9 @@ def test_address_and_undefined_behaviour():
     from aws_ofi_nccl_b200 import build
     build.build_fake_cuda()
     fake = f"{build.LIB / 'tests' / 'fake_cuda'}:" + os.environ.get("LD_LIBRARY_PATH", "")
+    for extra in ({}, {"FUNC_RMA_HOST_TARGETS": "1"}, {"FUNC_RMA_HOST_SOURCES": "2", "B200NET_DISABLE_CMA": "1"}):
+        _run([tests / "func_rma", so, 3],
+             {"ASAN_OPTIONS": "detect_leaks=0", "FUNC_NET_DEVICE": "1", "LD_LIBRARY_PATH": fake, **extra})
     for extra in ({"FAKE_CUDA_LAUNCH_DELAY_US": "200"}, {"FAKE_CUDA_FAIL_IPC_OPEN": "1"}):
         for sc in ("device_transfer", "grouped_recv", "eager", "proxy_pattern"):
             _run([tests / "func_net", so, sc],
@@ -70,3 +73,10 @@ def test_thread_sanitizer():
                                                   "B200NET_HOST_COPY_THREADS": "4"})
     _run([tests / "func_net", so, "proxy_pattern"], {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4",
                                                       "B200NET_HOST_COPY_THREADS": "4"})
+    # the helper thread that maps peers' device memory hands its result to the proxy thread
+    from aws_ofi_nccl_b200 import build
+    build.build_fake_cuda()
+    fake = f"{build.LIB / 'tests' / 'fake_cuda'}:" + os.environ.get("LD_LIBRARY_PATH", "")
+    _run([tests / "func_net", so, "proxy_pattern"],
+         {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "2", "FUNC_NET_DEVICE": "1", "LD_LIBRARY_PATH": fake,
+          "FAKE_CUDA_IPC_OPEN_DELAY_MS": "20", "B200NET_IPC_MAP_WAIT_US": "100", "FAKE_CUDA_LAUNCH_DELAY_US": "100"})
