@@ -103,7 +103,8 @@ CollComm::~CollComm() {
 }
 
 // Blocking helpers over the net transport's own API (used only during collective set-up).
-static int net_send_recv(void* scomm, void* rcomm, const void* sbuf, void* rbuf, size_t n) {
+template <typename Idle>
+static int net_send_recv(void* scomm, void* rcomm, const void* sbuf, void* rbuf, size_t n, Idle&& idle) {
   void *smh = nullptr, *rmh = nullptr;
   if (api::reg_mr(scomm, const_cast<void*>(sbuf), n, NCCL_PTR_HOST, &smh) != ncclSuccess) return -EIO;
   if (api::reg_mr(rcomm, rbuf, n, NCCL_PTR_HOST, &rmh) != ncclSuccess) return -EIO;
@@ -118,6 +119,7 @@ static int net_send_recv(void* scomm, void* rcomm, const void* sbuf, void* rbuf,
     if (sreq && !sdone && api::test(sreq, &sdone, nullptr) != ncclSuccess) return -EIO;
     if (rreq && !rdone && api::test(rreq, &rdone, nullptr) != ncclSuccess) return -EIO;
     if (expired(t0)) return -ETIMEDOUT;
+    idle();
   }
   api::dereg_mr(scomm, smh);
   api::dereg_mr(rcomm, rmh);
@@ -131,7 +133,12 @@ int CollComm::all_gather(void* buf, size_t bytes) {
   for (int s = 0; s < nranks - 1; ++s) {
     const int send_idx = (rank - s + nranks) % nranks;
     const int recv_idx = (rank - s - 1 + nranks) % nranks;
-    const int rc = net_send_recv(ring_send_, ring_recv_, b + send_idx * bytes, b + recv_idx * bytes, bytes);
+    // While this rank waits inside a collective call, peers may still have operations in flight
+    // that need it (a read it has to serve, signals to apply, acknowledgements): keep the engine
+    // turning, as a caller without a progress thread of its own cannot.
+    const int rc = net_send_recv(ring_send_, ring_recv_, b + send_idx * bytes, b + recv_idx * bytes, bytes, [this] {
+      if (!peers_.empty() && peers_[0].map) progress();
+    });
     if (rc) return rc;
   }
   return 0;

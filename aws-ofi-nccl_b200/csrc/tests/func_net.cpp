@@ -460,6 +460,20 @@ static int scenario_device_transfer(int sock) {
     for (void* r : rreq) all.push_back(r);
     std::vector<int> got;
     if (wait_all(all, &got)) return 1;
+    {   // what NCCL does before its kernel reads received device data: a flush over the receive buffers
+      std::vector<void*> fd(nmsg);
+      std::vector<int> fs(nmsg);
+      for (int i = 0; i < nmsg; ++i) {
+        fd[i] = rb[i].data();
+        fs[i] = static_cast<int>(sizes[i]);
+      }
+      void* freq = nullptr;
+      OK(net->iflush(p.r, std::min(nmsg, 8), fd.data(), fs.data(), rmh.data(), &freq));
+      if (freq) {
+        std::vector<void*> fr{freq};
+        if (wait_all(fr)) return 1;
+      }
+    }
     for (int i = 0; i < nmsg; ++i) {
       std::vector<uint8_t> want(sizes[i]);
       fill(want, 500 + 10 * pass + i + 1000 * (1 - g_rank));
