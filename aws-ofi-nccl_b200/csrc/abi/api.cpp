@@ -6,6 +6,7 @@
 #include <set>
 
 #include "b200net/histogram.h"
+#include "b200net/plugin_stats.h"
 #include "b200net/log.h"
 #include "b200net/param.h"
 
@@ -59,8 +60,9 @@ ncclResult_t init(ncclDebugLogger_t log_fn) {
 
 ncclResult_t fini() {
   API_GUARD_BEGIN
+  net_destroy_plugin();   // endpoints add their byte counts to the totals as they go
   stats::print_all_histograms();
-  net_destroy_plugin();
+  PluginStats::get().report();
   return ncclSuccess;
   API_GUARD_END
 }
@@ -126,6 +128,7 @@ ncclResult_t connect(int dev, void* handle, void** scomm, int traffic_class) {
   if (s) {
     hold(s, ep);
     *scomm = s;
+    PluginStats::bump(PluginStats::get().connects);
   }
   return ncclSuccess;
   API_GUARD_END
@@ -148,6 +151,7 @@ ncclResult_t accept(void* lcomm, void** rcomm) {
     }
     hold(r, ep);
     *rcomm = r;
+    PluginStats::bump(PluginStats::get().accepts);
   }
   return ncclSuccess;
   API_GUARD_END
@@ -198,6 +202,14 @@ ncclResult_t isend(void* scomm, void* data, size_t size, int tag, void* mhandle,
   Request* r = nullptr;
   const int rc = s->send(data, size, tag, static_cast<MrHandle*>(mhandle), &r);
   if (rc != 0) return check_return(to_nccl(rc));
+  PluginStats& st = PluginStats::get();
+  if (r) {
+    PluginStats::bump(st.sends);
+    PluginStats::bump(st.send_bytes, size);
+    if (st.histograms_on()) r->t_post_ns = PluginStats::now_ns();
+  } else {
+    PluginStats::bump(st.send_backoffs);
+  }
   *request = r;
   return ncclSuccess;
   API_GUARD_END
@@ -216,6 +228,8 @@ ncclResult_t irecv(void* rcomm, int n, void** data, size_t* sizes, int* tags, vo
   Request* r = nullptr;
   const int rc = rc_->recv(n, data, sizes, tags, reinterpret_cast<MrHandle**>(mhandles), &r, optional_completion);
   if (rc != 0) return check_return(to_nccl(rc));
+  PluginStats::bump(r ? PluginStats::get().recvs : PluginStats::get().recv_backoffs);
+  if (r && PluginStats::get().histograms_on()) r->t_post_ns = PluginStats::now_ns();
   *request = r;
   return ncclSuccess;
   API_GUARD_END
@@ -230,6 +244,7 @@ ncclResult_t iflush(void* rcomm, int n, void** data, int* sizes, void** mhandles
   Request* r = nullptr;
   const int rc = rc_->flush(n, data, sizes, reinterpret_cast<MrHandle**>(mhandles), &r);
   if (rc != 0) return check_return(to_nccl(rc));
+  PluginStats::bump(PluginStats::get().flushes);
   *request = r;
   return ncclSuccess;
   API_GUARD_END
@@ -238,7 +253,9 @@ ncclResult_t iflush(void* rcomm, int n, void** data, int* sizes, void** mhandles
 ncclResult_t test(void* request, int* done, int* sizes) {
   API_GUARD_BEGIN
   if (!request || !done) return check_return(ncclInvalidArgument);
-  return check_return(to_nccl(static_cast<Request*>(request)->test(done, sizes)));
+  const int rc = static_cast<Request*>(request)->test(done, sizes);
+  if (rc != 0) PluginStats::bump(PluginStats::get().requests_failed);
+  return check_return(to_nccl(rc));
   API_GUARD_END
 }
 

@@ -87,6 +87,7 @@ class Request {
   virtual ~Request() = default;
   // Makes progress on the whole endpoint, then reports this request. sizes may be null.
   virtual int test(int* done, int* sizes) = 0;
+  uint64_t t_post_ns = 0;   // when the post was accepted (steady clock); 0 unless latency histograms are on
 };
 
 class Comm {
@@ -128,7 +129,7 @@ class Endpoint : public std::enable_shared_from_this<Endpoint> {
   virtual int dereg_mr(MrHandle* mh) = 0;
   // After invalidate() every call on the endpoint fails fast (a communicator was torn down with
   // requests in flight, so the endpoint's queues can no longer be trusted).
-  void invalidate() { active.store(false); }
+  void invalidate();   // every later call on this endpoint fails fast (counted in the statistics)
   bool is_active() const { return active.load(); }
   Domain* domain;
   std::shared_ptr<Domain> domain_ref;  // keeps the domain (MR cache, key pool, thread table) alive

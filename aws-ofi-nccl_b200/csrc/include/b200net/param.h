@@ -124,6 +124,11 @@ struct Params {
   Param<uint64_t> host_copy_threads{"HOST_COPY_THREADS", 0,
                                     "worker threads for large host-to-host stripes (0, the default: the calling thread copies)"};
   Param<uint64_t> host_copy_min_size{"HOST_COPY_MIN_SIZE", 65536, "smallest stripe handed to a copy worker (bytes)"};
+  Param<std::string> stats_file{"STATS_FILE", "",
+                                "write the plugin's counters and histograms to this file as JSON at finalize (%p = process id)"};
+  Param<bool> stats_histograms{"STATS_HISTOGRAMS", false,
+                               "keep histograms of message sizes, stripes per send and request latencies (printed at "
+                               "finalize; implied by STATS_FILE)"};
   Param<uint64_t> ipc_map_wait_us{"IPC_MAP_WAIT_US", 20000,
                                   "how long a send waits for the first mapping of a peer's device allocation (the open "
                                   "runs on a helper thread because it can wait for the device to go idle); after that "

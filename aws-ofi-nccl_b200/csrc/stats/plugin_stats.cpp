@@ -1,0 +1,145 @@
+#include "b200net/plugin_stats.h"
+
+#include <unistd.h>
+
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <memory>
+
+#include "b200net/histogram.h"
+#include "b200net/log.h"
+#include "b200net/param.h"
+
+namespace b200net {
+namespace {
+
+using SizeHist = stats::Histogram<uint64_t, stats::Log2Binner<uint64_t>>;
+using StripeHist = stats::Histogram<uint64_t, stats::LinearBinner<uint64_t>>;
+using NsHist = stats::Histogram<uint64_t, stats::Log2Binner<uint64_t>>;
+
+struct Hists {
+  SizeHist send_size{"send_message_size", stats::Log2Binner<uint64_t>(36), "bytes"};
+  SizeHist recv_size{"recv_message_size", stats::Log2Binner<uint64_t>(36), "bytes"};
+  StripeHist stripes{"stripes_per_send", stats::LinearBinner<uint64_t>(0, 1, 18), "stripes"};
+  NsHist send_ns{"send_request_latency", stats::Log2Binner<uint64_t>(40), "ns"};
+  NsHist recv_ns{"recv_request_latency", stats::Log2Binner<uint64_t>(40), "ns"};
+};
+Hists* g_hists = nullptr;   // created once, never destroyed (requests may complete during teardown)
+
+struct Named {
+  const char* name;
+  const PluginStats::Counter PluginStats::*field;
+};
+const Named kCounters[] = {
+    {"sends", &PluginStats::sends},
+    {"recvs", &PluginStats::recvs},
+    {"send_bytes", &PluginStats::send_bytes},
+    {"recv_bytes", &PluginStats::recv_bytes},
+    {"eager_sends", &PluginStats::eager_sends},
+    {"rendezvous_sends", &PluginStats::rendezvous_sends},
+    {"send_backoffs", &PluginStats::send_backoffs},
+    {"recv_backoffs", &PluginStats::recv_backoffs},
+    {"bytes_copy_kernel", &PluginStats::bytes_kernel},
+    {"bytes_copy_engine", &PluginStats::bytes_copy_engine},
+    {"bytes_staged_through_host", &PluginStats::bytes_staged},
+    {"bytes_host_writes", &PluginStats::bytes_host},
+    {"bytes_eager", &PluginStats::bytes_eager},
+    {"flushes", &PluginStats::flushes},
+    {"requests_failed", &PluginStats::requests_failed},
+    {"ipc_maps", &PluginStats::ipc_maps},
+    {"ipc_map_failures", &PluginStats::ipc_map_failures},
+    {"ipc_map_deferred", &PluginStats::ipc_map_deferred},
+    {"connects", &PluginStats::connects},
+    {"accepts", &PluginStats::accepts},
+    {"endpoints_aborted", &PluginStats::endpoints_aborted},
+};
+
+}  // namespace
+
+PluginStats::PluginStats() {
+  histograms_ = params().stats_histograms.get() || !params().stats_file.get().empty();
+  if (histograms_) g_hists = new Hists;
+}
+
+PluginStats& PluginStats::get() {
+  static PluginStats* s = new PluginStats;
+  return *s;
+}
+
+uint64_t PluginStats::now_ns() {
+  return static_cast<uint64_t>(
+      std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count());
+}
+
+void PluginStats::sample_send(size_t bytes, size_t stripes, uint64_t ns) {
+  if (!g_hists) return;
+  g_hists->send_size.insert(bytes);
+  g_hists->stripes.insert(stripes);
+  g_hists->send_ns.insert(ns);
+}
+
+void PluginStats::sample_recv(size_t bytes, uint64_t ns) {
+  if (!g_hists) return;
+  g_hists->recv_size.insert(bytes);
+  g_hists->recv_ns.insert(ns);
+}
+
+void PluginStats::reset() {
+  for (const Named& n : kCounters) const_cast<Counter&>(this->*(n.field)).store(0, std::memory_order_relaxed);
+}
+
+std::string PluginStats::to_json() const {
+  std::string o = "{\"pid\":" + std::to_string(getpid()) + ",\"counters\":{";
+  bool first = true;
+  for (const Named& n : kCounters) {
+    if (!first) o += ",";
+    first = false;
+    o += std::string("\"") + n.name + "\":" + std::to_string((this->*(n.field)).load(std::memory_order_relaxed));
+  }
+  o += "},\"histograms\":[";
+  if (g_hists) {
+    const stats::HistogramBase* all[] = {&g_hists->send_size, &g_hists->recv_size, &g_hists->stripes, &g_hists->send_ns,
+                                         &g_hists->recv_ns};
+    first = true;
+    for (const stats::HistogramBase* h : all) {
+      const stats::HistogramSnapshot s = h->snapshot();
+      if (!s.samples) continue;
+      if (!first) o += ",";
+      first = false;
+      std::string body = stats::format_histogram(s, stats::PrintFormat::JSON, true);
+      while (!body.empty() && (body.back() == '\n' || body.back() == ',')) body.pop_back();
+      o += body;
+    }
+  }
+  o += "]}";
+  return o;
+}
+
+void PluginStats::report() const {
+  const uint64_t s = sends.load(), r = recvs.load();
+  if (s | r)
+    NET_INFO(NCCL_NET,
+             "totals: %llu sends (%llu eager, %llu back-offs) %llu bytes; %llu receives (%llu back-offs) %llu bytes; payload by "
+             "path: copy kernel %llu, copy engine %llu, staged through host %llu, host writes %llu, eager %llu",
+             static_cast<unsigned long long>(s), static_cast<unsigned long long>(eager_sends.load()),
+             static_cast<unsigned long long>(send_backoffs.load()), static_cast<unsigned long long>(send_bytes.load()),
+             static_cast<unsigned long long>(r), static_cast<unsigned long long>(recv_backoffs.load()),
+             static_cast<unsigned long long>(recv_bytes.load()), static_cast<unsigned long long>(bytes_kernel.load()),
+             static_cast<unsigned long long>(bytes_copy_engine.load()), static_cast<unsigned long long>(bytes_staged.load()),
+             static_cast<unsigned long long>(bytes_host.load()), static_cast<unsigned long long>(bytes_eager.load()));
+  std::string path = params().stats_file.get();
+  if (path.empty()) return;
+  const size_t at = path.find("%p");
+  if (at != std::string::npos) path.replace(at, 2, std::to_string(getpid()));
+  if (FILE* f = fopen(path.c_str(), "w")) {
+    const std::string js = to_json();
+    fwrite(js.data(), 1, js.size(), f);
+    fputc('\n', f);
+    fclose(f);
+  } else {
+    NET_WARN("cannot write the statistics file %s", path.c_str());
+  }
+}
+
+}  // namespace b200net

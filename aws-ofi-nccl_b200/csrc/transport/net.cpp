@@ -13,6 +13,7 @@
 #include "b200net/log.h"
 #include "b200net/net.h"
 #include "b200net/param.h"
+#include "b200net/plugin_stats.h"
 #include "b200net/scheduler.h"
 #include "b200net/shm_fabric.h"
 #include "b200net/platform.h"
@@ -192,6 +193,10 @@ void net_destroy_plugin() {
   g_plugin = nullptr;
   delete g_topo;
   g_topo = nullptr;
+}
+
+void Endpoint::invalidate() {
+  if (active.exchange(false)) PluginStats::bump(PluginStats::get().endpoints_aborted);
 }
 
 }  // namespace b200net

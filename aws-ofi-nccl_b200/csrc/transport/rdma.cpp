@@ -30,6 +30,7 @@
 #include "b200net/msgbuff.h"
 #include "b200net/net.h"
 #include "b200net/param.h"
+#include "b200net/plugin_stats.h"
 #include "b200net/net_kernels.h"
 #include "b200net/rdma_proto.h"
 #include "b200net/scheduler.h"
@@ -239,6 +240,18 @@ class RdmaRecvComm : public RecvComm {
 RdmaEndpoint::RdmaEndpoint(Domain* d, int rails) : Endpoint(d), cm(&fab), num_rails(rails) {}
 
 RdmaEndpoint::~RdmaEndpoint() {
+  {
+    PluginStats& st = PluginStats::get();
+    PluginStats::bump(st.bytes_kernel, bytes_kernel);
+    PluginStats::bump(st.bytes_copy_engine, bytes_copy_engine);
+    PluginStats::bump(st.bytes_staged, bytes_staged);
+    PluginStats::bump(st.bytes_host, bytes_host);
+    PluginStats::bump(st.bytes_eager, bytes_eager);
+    for (auto& [k, job] : ipc_maps) {
+      const int state = job ? job->state.load(std::memory_order_acquire) : -1;
+      PluginStats::bump(state == 1 ? st.ipc_maps : (state == 0 ? st.ipc_map_deferred : st.ipc_map_failures));
+    }
+  }
   if (bytes_kernel | bytes_copy_engine | bytes_staged | bytes_host | bytes_eager)
     NET_INFO(NCCL_NET, "endpoint payload bytes: copy kernel %llu, copy engine %llu, staged through host %llu, host writes %llu, eager %llu",
              static_cast<unsigned long long>(bytes_kernel), static_cast<unsigned long long>(bytes_copy_engine),
@@ -814,6 +827,7 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
       return rc;
     }
     B200NET_TRACE_EVENT(Send, dev_id, local_comm_id, r->seq, r->size, r);
+    PluginStats::bump(PluginStats::get().rendezvous_sends);
     consume_entry(idx, n);
     bind_eager_queue();   // if that completed the group, queued sends may fit the next one
     ++inflight;
@@ -877,7 +891,10 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
     h.size = size;
     const int rc = e->fab.send(peer, DgramType::EAGER, 0, &h, sizeof(h), eager_src, size);
     if (eager_slot >= 0) nk->eager_release(eager_slot);  // the datagram holds a copy
-    if (rc == 0) e->bytes_eager += size;
+    if (rc == 0) {
+      e->bytes_eager += size;
+      PluginStats::bump(PluginStats::get().eager_sends);
+    }
     if (rc == -EAGAIN) return 0;  // ring full: NCCL calls again
     if (rc != 0) return rc;
     auto* r = new RdmaSendReq();
@@ -918,6 +935,7 @@ int RdmaSendReq::test(int* done, int* sizes) {
     *done = 1;
     if (sizes) sizes[0] = static_cast<int>(size);
     B200NET_TRACE_EVENT(SendEnd, comm->dev_id, comm->local_comm_id, seq, size, this);
+    if (PluginStats::get().histograms_on()) PluginStats::get().sample_send(size, stripes.size(), PluginStats::since(t_post_ns));
     --comm->inflight;
     e->live_send_reqs.erase(serial);
     delete this;
@@ -1126,6 +1144,12 @@ int RdmaRecvReq::test(int* done, int* sizes) {
     if (sizes)
       for (int i = 0; i < n; ++i) sizes[i] = static_cast<int>(subs[i].received);
     B200NET_TRACE_EVENT(RecvEnd, comm->dev_id, comm->local_comm_id, seq, n, this);
+    {
+      size_t total = 0;
+      for (int i = 0; i < n; ++i) total += subs[i].received;
+      PluginStats::bump(PluginStats::get().recv_bytes, total);
+      if (PluginStats::get().histograms_on()) PluginStats::get().sample_recv(total, PluginStats::since(t_post_ns));
+    }
     --comm->inflight;
     delete this;
   } else if (no_completion) {

@@ -16,6 +16,7 @@
 #include "b200net/log.h"
 #include "b200net/net.h"
 #include "b200net/param.h"
+#include "b200net/plugin_stats.h"
 #include "b200net/shm_fabric.h"
 #include "b200net/tracepoint.h"
 
@@ -297,6 +298,7 @@ int SrSendReq::test(int* done, int* sizes) {
     *done = 1;
     if (sizes) sizes[0] = static_cast<int>(size);
     B200NET_TRACE_EVENT(SendEnd, comm->dev_id, comm->local_comm_id, msg_seq, size, this);
+    if (PluginStats::get().histograms_on()) PluginStats::get().sample_send(size, 1, PluginStats::since(t_post_ns));
     --comm->inflight;
     delete this;
   }
@@ -392,6 +394,8 @@ int SrRecvReq::test(int* done, int* sizes) {
         break;
       }
     B200NET_TRACE_EVENT(RecvEnd, comm->dev_id, comm->local_comm_id, msg_seq, 1, this);
+    PluginStats::bump(PluginStats::get().recv_bytes, std::min(received, cap));
+    if (PluginStats::get().histograms_on()) PluginStats::get().sample_recv(std::min(received, cap), PluginStats::since(t_post_ns));
     --comm->inflight;
     delete this;
   }

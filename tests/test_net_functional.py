@@ -101,3 +101,26 @@ def test_gin_rma_tuner_symbols_exported(built):
                 "ncclTunerPlugin_v6"):
         assert hasattr(lib, sym), sym
     assert (built / "libnccl-tuner-ofi-b200.so").exists()
+
+
+def test_statistics_file_at_finalize(built, tmp_path):
+    """B200NET_STATS_FILE: one JSON object per process with the counters (posts, back-offs, bytes by
+    path) and the histograms (sizes, stripes per send, request latencies)."""
+    import json
+
+    _run(built, {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4",
+                 "B200NET_STATS_FILE": str(tmp_path / "stats.%p.json")}, "message_transfer")
+    files = sorted(tmp_path.glob("stats.*.json"))
+    assert len(files) == 2, files
+    for f in files:
+        d = json.loads(f.read_text())
+        c = d["counters"]
+        assert c["sends"] == c["recvs"] > 0 and c["connects"] == c["accepts"] == 1
+        assert c["eager_sends"] + c["rendezvous_sends"] == c["sends"]
+        assert c["send_bytes"] >= c["recv_bytes"] > 0          # sends larger than the posted receive are cut
+        assert c["bytes_host_writes"] + c["bytes_eager"] == c["recv_bytes"]
+        assert c["flushes"] > 0 and c["requests_failed"] == 0 and c["endpoints_aborted"] == 0
+        h = {x["name"]: x for x in d["histograms"]}
+        assert h["send_message_size"]["samples"] == c["sends"]
+        assert h["stripes_per_send"]["max"] <= 4
+        assert h["send_request_latency"]["unit"] == "ns"
