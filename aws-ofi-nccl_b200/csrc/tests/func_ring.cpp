@@ -65,6 +65,8 @@ static void logger(ncclDebugLogLevel level, unsigned long, const char* file, int
   fprintf(stderr, "[rank %d] %s (%s:%d)\n", g_rank, buf, file, line);
 }
 
+#include "test_buf.h"
+
 static void fill(std::vector<uint8_t>& b, uint32_t seed) {
   std::mt19937 g(seed);
   for (auto& x : b) x = static_cast<uint8_t>(g());
@@ -91,13 +93,13 @@ static int run_rank(const char* so) {
 
   const int inflight = 32, rounds = 4;
   const size_t sizes[] = {8, 64, 1000, 4096, 8192, 8200, 65536, 262144 + 3, 1u << 20};
-  std::vector<std::vector<uint8_t>> sbuf(inflight), rbuf(inflight);
+  // host buffers, or device buffers with FUNC_NET_DEVICE=1 and the stand-in driver on the library path
+  std::vector<TestBuf> sbuf(inflight), rbuf(inflight);
   std::vector<void*> smh(inflight), rmh(inflight);
   for (int i = 0; i < inflight; ++i) {
-    sbuf[i].resize(1u << 20);
-    rbuf[i].resize(1u << 20);
-    OK(net->regMr(s, sbuf[i].data(), sbuf[i].size(), NCCL_PTR_HOST, &smh[i]));
-    OK(net->regMr(r, rbuf[i].data(), rbuf[i].size(), NCCL_PTR_HOST, &rmh[i]));
+    if (buf_alloc(&sbuf[i], 1u << 20) || buf_alloc(&rbuf[i], 1u << 20)) FAIL("buffer allocation failed");
+    OK(net->regMr(s, sbuf[i].data(), sbuf[i].size(), buf_type(), &smh[i]));
+    OK(net->regMr(r, rbuf[i].data(), rbuf[i].size(), buf_type(), &rmh[i]));
   }
   for (int round = 0; round < rounds; ++round) {
     std::vector<void*> sreq(inflight, nullptr), rreq(inflight, nullptr);
@@ -106,8 +108,8 @@ static int run_rank(const char* so) {
       len[i] = sizes[(i + round) % (sizeof(sizes) / sizeof(sizes[0]))];
       std::vector<uint8_t> pattern(len[i]);
       fill(pattern, 1000 * g_rank + 100 * round + i);
-      memcpy(sbuf[i].data(), pattern.data(), len[i]);
-      memset(rbuf[i].data(), 0xEE, rbuf[i].size());
+      memcpy(sbuf[i].host(), pattern.data(), len[i]);
+      memset(rbuf[i].host(), 0xEE, rbuf[i].size());
     }
     // post everything, interleaved, retrying refused posts while the others make progress
     int sp = 0, rp = 0;
@@ -167,14 +169,16 @@ static int run_rank(const char* so) {
       if (got[i] != static_cast<int>(len[i])) FAIL("round %d message %d: received %d bytes, expected %zu", round, i, got[i], len[i]);
       std::vector<uint8_t> want(len[i]);
       fill(want, 1000 * prev + 100 * round + i);
-      if (memcmp(want.data(), rbuf[i].data(), len[i])) FAIL("round %d message %d: payload differs", round, i);
-      if (len[i] < rbuf[i].size() && rbuf[i][len[i]] != 0xEE) FAIL("round %d message %d: wrote past the message", round, i);
+      if (memcmp(want.data(), rbuf[i].host(), len[i])) FAIL("round %d message %d: payload differs", round, i);
+      if (len[i] < rbuf[i].size() && rbuf[i].host()[len[i]] != 0xEE) FAIL("round %d message %d: wrote past the message", round, i);
     }
     if (oob_barrier()) FAIL("barrier");
   }
   for (int i = 0; i < inflight; ++i) {
     OK(net->deregMr(s, smh[i]));
     OK(net->deregMr(r, rmh[i]));
+    buf_free(&sbuf[i]);
+    buf_free(&rbuf[i]);
   }
   OK(net->closeSend(s));
   OK(net->closeRecv(r));
