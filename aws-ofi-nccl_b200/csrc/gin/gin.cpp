@@ -102,6 +102,15 @@ CollComm::~CollComm() {
   for (GinContext* c : contexts_) delete c;
 }
 
+// A fragment of a put whose target is device memory that the sender cannot map (no IPC handle for
+// it, or the mapping failed): the owner copies it to its device when it polls.
+constexpr uint16_t GIN_DEVICE_FRAG = static_cast<uint16_t>(DgramType::USER) + 2;
+struct GinDeviceFragHdr {
+  uint32_t comm_id;
+  uint32_t len;
+  uint64_t addr;
+};
+
 // Blocking helpers over the net transport's own API (used only during collective set-up).
 template <typename Idle>
 static int net_send_recv(void* scomm, void* rcomm, const void* sbuf, void* rbuf, size_t n, Idle&& idle) {
@@ -298,6 +307,23 @@ void CollComm::handle_dgram(const DgramHdr& h, const void* payload) {
     if (m->seq > p.rx_applied) p.rx_applied = m->seq;
     const uint32_t interval = static_cast<uint32_t>(params().gin_ack_interval.get());
     if (p.rx_applied - p.rx_acked >= interval) send_ack(m->src_rank);
+  } else if (h.type == GIN_DEVICE_FRAG) {
+    const auto* fh = static_cast<const GinDeviceFragHdr*>(payload);
+    if (fh->comm_id != comm_id || h.len < sizeof(*fh) + fh->len) return;
+    // only into device memory registered with this communicator
+    bool inside = false;
+    for (SymmMr* mr : mrs_) {
+      const uint64_t b = reinterpret_cast<uint64_t>(mr->base);
+      if (mr->type == NCCL_PTR_CUDA && fh->addr >= b && fh->addr + fh->len <= b + mr->size) inside = true;
+    }
+    static thread_local cuda::Stream st = nullptr;
+    if (!inside || (!st && cuda::stream_create(&st) != 0) ||
+        cuda::memcpy_async(reinterpret_cast<void*>(fh->addr), static_cast<const char*>(payload) + sizeof(*fh), fh->len, st) != 0 ||
+        cuda::stream_synchronize(st) != 0) {   // the ring cell is recycled on return
+      NET_WARN("GIN: a fragment for device address %llx (%u bytes) could not be applied", static_cast<unsigned long long>(fh->addr),
+               fh->len);
+      error_ = true;
+    }
   } else if (h.type == static_cast<uint16_t>(DgramType::GIN_ACK)) {
     const auto* a = static_cast<const AckMsg*>(payload);
     if (a->comm_id != comm_id || a->src_rank >= static_cast<uint32_t>(nranks)) return;
@@ -307,7 +333,7 @@ void CollComm::handle_dgram(const DgramHdr& h, const void* payload) {
   } else if (h.type == static_cast<uint16_t>(DgramType::READ_REQ)) {
     const auto* r = static_cast<const ReadReqMsg*>(payload);
     if (r->comm_id != comm_id || r->src_rank >= static_cast<uint32_t>(nranks)) return;
-    read_services_.push_back(ReadService{*r, 0, false});
+    read_services_.push_back(ReadService{*r, 0, false, {}});
   } else if (h.type == static_cast<uint16_t>(DgramType::READ_RESP)) {
     const auto* r = static_cast<const ReadRespMsg*>(payload);
     auto it = reads_in_flight_.find(r->req_id);
@@ -337,14 +363,27 @@ int CollComm::serve_reads() {
     ReadService& sv = read_services_.front();
     PeerState& p = peers_[sv.req.src_rank];
     int status = 0;
-    bool inside = false;
+    bool inside = false, on_device = false;
     for (SymmMr* mr : mrs_) {
       const uint64_t b = reinterpret_cast<uint64_t>(mr->base);
-      if (sv.req.addr >= b && sv.req.addr + sv.req.len <= b + mr->size && mr->type == NCCL_PTR_HOST) inside = true;
+      if (sv.req.addr >= b && sv.req.addr + sv.req.len <= b + mr->size) {
+        inside = true;
+        on_device = mr->type == NCCL_PTR_CUDA;
+      }
     }
     if (!inside) status = -EFAULT;
+    if (!status && on_device && sv.bounce.empty() && sv.req.len) {
+      // the requester cannot map this device memory: fetch it once, then write it back like host memory
+      static thread_local cuda::Stream st = nullptr;
+      sv.bounce.resize(sv.req.len);
+      if ((!st && cuda::stream_create(&st) != 0) ||
+          cuda::memcpy_async(sv.bounce.data(), reinterpret_cast<const void*>(sv.req.addr), sv.req.len, st) != 0 ||
+          cuda::stream_synchronize(st) != 0)
+        status = -EIO;
+    }
     if (!status && !sv.data_done) {
-      const int rc = fab_.write_host(p.map, sv.req.reply_addr, reinterpret_cast<const void*>(sv.req.addr), sv.req.len, &sv.done);
+      const void* from = on_device ? static_cast<const void*>(sv.bounce.data()) : reinterpret_cast<const void*>(sv.req.addr);
+      const int rc = fab_.write_host(p.map, sv.req.reply_addr, from, sv.req.len, &sv.done);
       if (rc == -EAGAIN) return 0;
       if (rc != 0) status = rc;
       sv.data_done = true;
@@ -376,6 +415,26 @@ int CollComm::retire(PeerState& p, uint32_t peer_rank) {
         if (q == 1) return 0;
         cuda::event_destroy(op.event);
         op.event = nullptr;
+        op.data_done = true;
+      } else if (op.len && op.dev_frags) {
+        const size_t chunk = FAB_LARGE_CELL - sizeof(GinDeviceFragHdr) - 64;
+        int rc = 0;
+        while (op.done < op.len) {
+          const size_t nbytes = std::min(chunk, op.len - op.done);
+          GinDeviceFragHdr fh{p.comm_id, static_cast<uint32_t>(nbytes), op.remote_addr + op.done};
+          rc = fab_.send(p.map, static_cast<DgramType>(GIN_DEVICE_FRAG), DGRAM_FLAG_ORDER_AFTER_FRAGS, &fh, sizeof(fh),
+                         static_cast<const char*>(op.local) + op.done, nbytes);
+          if (rc != 0) break;
+          op.done += nbytes;
+        }
+        if (rc == -EAGAIN) return 0;
+        if (rc != 0) {
+          op.status->store(rc);
+          error_ = true;
+          p.ops.pop_front();
+          continue;
+        }
+        op.staged = true;   // the metadata must queue behind the fragments
         op.data_done = true;
       } else if (op.len) {
         const int rc = fab_.write_host(p.map, op.remote_addr, op.local, op.len, &op.done);
@@ -477,7 +536,18 @@ int CollComm::iput(uint64_t src_off, SymmMr* src, size_t size, uint64_t dst_off,
           cuda::event_record(op.event, st) != 0)
         return -EIO;
     } else {
-      return -ENOTSUP;  // a device window that cannot be mapped into this process
+      // a device window that cannot be mapped into this process: fragments through host memory
+      if (src->type == NCCL_PTR_CUDA) {
+        static thread_local cuda::Stream st = nullptr;
+        if (!st && cuda::stream_create(&st) != 0) return -EIO;
+        op.bounce.resize(size);
+        if (cuda::memcpy_async(op.bounce.data(), lsrc, size, st) != 0 || cuda::stream_synchronize(st) != 0) return -EIO;
+        op.local = op.bounce.data();
+      } else {
+        op.local = lsrc;
+      }
+      op.remote_addr = rm.addr + dst_off;
+      op.dev_frags = true;
     }
   }
   auto status = op.status;
@@ -537,7 +607,24 @@ int CollComm::iget(uint64_t remote_off, SymmMr* remote, size_t size, uint64_t lo
     rc = cuda::memcpy_async(ldst, static_cast<char*>(remote->mapped[peer_rank]) + remote_off, size, st);
     if (rc == 0) rc = cuda::stream_synchronize(st);
   } else {
-    rc = -ENOTSUP;
+    // device memory of the peer that cannot be mapped here: the owner reads it and writes it back
+    const bool to_device = local->type == NCCL_PTR_CUDA;
+    PeerState& p = peers_[peer_rank];
+    ReadReqMsg rq{p.comm_id, static_cast<uint32_t>(rank), next_read_id_++, rm.addr + remote_off, size,
+                  reinterpret_cast<uint64_t>(ldst)};
+    if (to_device) {
+      ReadLanding& l = read_landings_[rq.req_id];
+      l.host.resize(size);
+      l.device_dst = ldst;
+      rq.reply_addr = reinterpret_cast<uint64_t>(l.host.data());
+    }
+    rc = fab_.send(p.map, DgramType::READ_REQ, 0, &rq, sizeof(rq));
+    if (rc != 0) read_landings_.erase(rq.req_id);
+    if (rc == -EAGAIN) return 0;  // no request: call again
+    if (rc != 0) return rc;
+    reads_in_flight_[rq.req_id] = status;
+    *req = new StatusRequest(this, status);
+    return 0;
   }
   if (rc != 0) return rc;
   status->store(1);
@@ -611,6 +698,15 @@ int CollComm::create_context(int n_signals, int n_counters, int n_contexts, bool
     for (int r = 0; r < nranks; ++r) {
       if (r == rank) c->peer_pads[r] = c->dev_pad;
       else if (cuda::ipc_open(pads[r].ipc, &c->peer_pads[r]) != 0) c->has_error = true;
+    }
+    if (c->has_error) {
+      // kernels would store through a null pad address: no context rather than a broken one
+      NET_WARN("GIN: a peer's signal pad cannot be mapped into this process; kernel-initiated mode is not available");
+      for (int r = 0; r < nranks; ++r)
+        if (r != rank && c->peer_pads[r]) cuda::ipc_close(c->peer_pads[r]);
+      cuda::mem_free(c->dev_pad);
+      delete c;
+      return -EIO;
     }
     // the device-visible block: {rank, nranks, signals per context, counters per context, pad[nranks]}
     std::vector<uint64_t> block(static_cast<size_t>(4 + nranks));

@@ -94,7 +94,9 @@ struct PendingOp {            // a put whose data copy may still be running
   size_t len = 0, done = 0;
   uint64_t remote_addr = 0;
   const void* local = nullptr;
-  std::vector<uint8_t> bounce;   // host copy of a device source bound for host memory
+  std::vector<uint8_t> bounce;   // host copy of a device source that travels through host memory
+  bool dev_frags = false;        // the target is device memory that cannot be mapped here: the owner
+                                 // copies fragments to its device as they arrive
   bool has_signal = false, data_done = false, signal_sent = false, staged = false;
   MetadataMsg meta{};
   std::shared_ptr<std::atomic<int>> status;  // 0 pending, 1 done, <0 error (shared with the request)
@@ -198,7 +200,7 @@ class CollComm {
   std::vector<SymmMr*> mrs_;
   std::vector<GinContext*> contexts_;
   std::deque<MetadataMsg> deferred_signals_;  // device signals the worker ring had no room for
-  struct ReadService { ReadReqMsg req; size_t done; bool data_done; };
+  struct ReadService { ReadReqMsg req; size_t done; bool data_done; std::vector<uint8_t> bounce; };
   std::deque<ReadService> read_services_;     // reads this rank is serving for peers without direct access
   std::map<uint64_t, std::shared_ptr<std::atomic<int>>> reads_in_flight_;
   // a read served by the peer for a device destination lands in host memory first

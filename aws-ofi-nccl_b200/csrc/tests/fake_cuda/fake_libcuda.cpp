@@ -6,6 +6,7 @@
 //
 // Fault injection through the environment (read at cuInit):
 //   FAKE_CUDA_FAIL_IPC_OPEN=1   cuIpcOpenMemHandle fails (the plugin must fall back to staging)
+//   FAKE_CUDA_FAIL_IPC_GET=1    cuIpcGetMemHandle fails, as for allocations of the virtual-memory API
 //   FAKE_CUDA_PROTECT=0         device addresses stay readable and writable by host code (default:
 //                               they are mapped without access, so a host dereference faults)
 //   FAKE_CUDA_IPC_OPEN_DELAY_MS=n cuIpcOpenMemHandle takes n milliseconds (a device that is busy)
@@ -232,6 +233,8 @@ CUresult fMemsetD8(CUdeviceptr p, unsigned char v, size_t n) {
   return CUDA_SUCCESS;
 }
 CUresult fIpcGetMemHandle(CUipcMemHandle* h, CUdeviceptr p) {
+  // what the driver answers for memory that came from the virtual-memory API (cuMemCreate)
+  if (getenv("FAKE_CUDA_FAIL_IPC_GET") && atoi(getenv("FAKE_CUDA_FAIL_IPC_GET"))) return CUDA_ERROR_INVALID_VALUE;
   std::lock_guard<std::mutex> g(g_mu);
   auto it = g_allocs.find(static_cast<uintptr_t>(p));
   if (it == g_allocs.end() || it->second.shm_name.empty()) return CUDA_ERROR_INVALID_VALUE;

@@ -223,6 +223,14 @@ static int run_rank(const char* so) {
     ncclGinConfig_v14_t kcfg = {3 + g_rank, 2, 1, 0, -1, 0, 0};   // ranks ask for different counts
     void* kctx = nullptr;
     ncclNetDeviceHandle_t* dh = nullptr;
+    // without legacy IPC (handles cannot be made, or cannot be opened) the pads cannot be shared:
+    // the call must fail on every rank and leave nothing behind
+    const bool no_ipc = (getenv("FAKE_CUDA_FAIL_IPC_GET") && atoi(getenv("FAKE_CUDA_FAIL_IPC_GET"))) ||
+                        (getenv("FAKE_CUDA_FAIL_IPC_OPEN") && atoi(getenv("FAKE_CUDA_FAIL_IPC_OPEN")));
+    if (no_ipc) {
+      if (gin14->createContext(coll, &kcfg, &kctx, &dh) == ncclSuccess) FAIL("a context without shared pads was handed out");
+      if (oob_barrier()) FAIL("barrier");
+    } else {
     OK(gin14->createContext(coll, &kcfg, &kctx, &dh));
     if (!dh || dh->netDeviceType != NCCL_NET_DEVICE_GIN_GDAKI || dh->needsProxyProgress) FAIL("unexpected device handle");
     if (dh->size != (4 + (size_t)g_n) * 8) FAIL("handle block of %zu bytes", (size_t)dh->size);
@@ -242,6 +250,7 @@ static int run_rank(const char* so) {
       if (__atomic_load_n(&mine[r], __ATOMIC_ACQUIRE) != 0xAB00u + r) FAIL("pad word %d holds %llx", r, (unsigned long long)mine[r]);
     if (oob_barrier()) FAIL("barrier");
     OK(gin14->destroyContext(kctx));
+    }
   }
   bool err = true;
   OK(rma->queryLastError(ctx, &err));

@@ -88,6 +88,14 @@ def test_slow_peer_mapping_does_not_stall_the_sender(built):
     assert c["staged through host"] > 0 and c["copy kernel"] > 0, c
 
 
+def test_allocations_without_ipc_handles_are_staged(built):
+    """Memory of the virtual-memory API has no legacy IPC handle: such registrations are published
+    as reachable through host fragments only, and every scenario still passes."""
+    log = _run(built, {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4", "FAKE_CUDA_FAIL_IPC_GET": "1"})
+    c = _payload_counters(log)
+    assert c["staged through host"] > 0 and c["copy kernel"] == 0 and c["copy engine"] == 0, c
+
+
 @pytest.mark.parametrize("delay_us", ["0", "200"])
 def test_proxy_pattern_on_device_buffers(built, delay_us):
     """NCCL's proxy pattern with device chunks and kernels that complete asynchronously: many
@@ -106,11 +114,17 @@ def test_proxy_pattern_on_device_buffers(built, delay_us):
     (3, {"FUNC_RMA_HOST_SOURCES": "1"}),
     (3, {"FUNC_RMA_HOST_SOURCES": "2"}),
     (3, {"FUNC_RMA_HOST_SOURCES": "2", "B200NET_DISABLE_CMA": "1"}),
+    (3, {"FAKE_CUDA_FAIL_IPC_GET": "1"}),
+    (3, {"FAKE_CUDA_FAIL_IPC_OPEN": "1", "B200NET_DISABLE_CMA": "1"}),
+    (3, {"FAKE_CUDA_FAIL_IPC_GET": "1", "FUNC_RMA_HOST_SOURCES": "2"}),
 ], ids=["2", "3-async", "4-staged", "dev-to-host", "dev-to-host-staged", "host-to-dev", "host-read-into-dev",
-        "host-read-into-dev-served"])
+        "host-read-into-dev-served", "no-ipc-handles", "ipc-open-fails-staged", "no-ipc-handles-host-sources"])
 def test_rma_and_gin_tables_on_device_buffers(built, nranks, env):
     """Puts, signalled puts, gets and flushes with windows, sources and signal words in device
-    memory, and every host / device pairing of source and target."""
+    memory, every host / device pairing of source and target, and device windows that peers cannot
+    map (allocations without IPC handles, as the virtual-memory API makes them; handles that cannot
+    be opened): those travel as fragments that the owner copies to its device, reads are served by
+    the owner, and a kernel-initiated context is refused."""
     fake = built / "tests" / "fake_cuda"
     e = dict(os.environ, FUNC_NET_DEVICE="1")
     e["LD_LIBRARY_PATH"] = f"{fake}:" + e.get("LD_LIBRARY_PATH", "")
