@@ -161,7 +161,7 @@ def build_host(force: bool = False, sanitize: str | None = None) -> Path | None:
 
 
 def build_tests(force: bool = False, sanitize: str | None = None) -> list[Path]:
-    """Each csrc/tests/<name>.cpp (or .c) is a program whose exit status is the verdict."""
+    """Each csrc/tests/<name>.cpp (or .c) is a program that reports its result through its exit status."""
     tdir = CSRC / "tests"
     if not tdir.exists():
         return []

@@ -409,6 +409,13 @@ CUresult fake_cuda_mem_alloc(void** p, size_t bytes) {
   return r;
 }
 CUresult fake_cuda_mem_free(void* p) { return fMemFree(reinterpret_cast<CUdeviceptr>(p)); }
+// How many peer allocations are mapped into this process right now (opened and not yet closed).
+int fake_cuda_live_peer_mappings() {
+  std::lock_guard<std::mutex> g(g_mu);
+  int n = 0;
+  for (const auto& [base, al] : g_allocs) n += al.opened_from_peer ? 1 : 0;
+  return n;
+}
 // The accessible view of a "device" address (what a test uses to fill and check device buffers).
 void* fake_cuda_host_view(void* p) { return dev_view(p); }
 }

@@ -144,3 +144,11 @@ def test_ring_of_processes_on_device_buffers(built, proto, ranks):
     res = subprocess.run([str(built / "tests" / "func_ring"), str(built / "libnccl-net-ofi-b200.so"), str(ranks)],
                          capture_output=True, text=True, timeout=300, env=e, cwd=built)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+
+
+def test_mapping_helper_thread_hands_over_or_cleans_up(built):
+    fake = built / "tests" / "fake_cuda"
+    e = dict(os.environ)
+    e["LD_LIBRARY_PATH"] = f"{fake}:" + e.get("LD_LIBRARY_PATH", "")
+    res = subprocess.run([str(built / "tests" / "drv_ipc_mapper")], capture_output=True, text=True, timeout=120, env=e, cwd=built)
+    assert res.returncode == 0 and res.stdout.strip().endswith("ok"), res.stdout[-2000:] + res.stderr[-3000:]
