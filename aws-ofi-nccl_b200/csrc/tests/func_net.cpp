@@ -415,6 +415,7 @@ static int scenario_device_transfer(int sock) {
       fill(pat, 500 + 10 * pass + i + 1000 * g_rank);
       memcpy(sb[i].host(), pat.data(), sizes[i]);
       memset(rb[i].host(), 0xCD, rb[i].size());
+      if (sb[i].to_device() || rb[i].to_device()) FAIL("copy to the device failed");
       OK(net->regMr(p.s, sb[i].data(), sb[i].size(), buf_type(), &smh[i]));
       OK(net->regMr(p.r, rb[i].data(), rb[i].size(), buf_type(), &rmh[i]));
     }
@@ -478,6 +479,7 @@ static int scenario_device_transfer(int sock) {
       std::vector<uint8_t> want(sizes[i]);
       fill(want, 500 + 10 * pass + i + 1000 * (1 - g_rank));
       if (got[nmsg + i] != static_cast<int>(sizes[i])) FAIL("pass %d message %d: size %d, expected %zu", pass, i, got[nmsg + i], sizes[i]);
+      if (rb[i].from_device()) FAIL("copy from the device failed");
       if (memcmp(want.data(), rb[i].host(), sizes[i])) FAIL("pass %d message %d (%zu bytes): payload differs", pass, i, sizes[i]);
       if (rb[i].host()[sizes[i]] != 0xCD) FAIL("pass %d message %d: wrote past the end", pass, i);
     }
@@ -531,6 +533,8 @@ static int scenario_proxy_pattern(int sock) {
     uint32_t hdr[4] = {0xC0FFEEu, static_cast<uint32_t>(g_rank), static_cast<uint32_t>(c), static_cast<uint32_t>(k)};
     memcpy(b.host(), hdr, sizeof(hdr));
     b.host()[chunk - 1] = static_cast<uint8_t>(c * 31 + k);
+    b.to_device(0, sizeof(hdr));
+    b.to_device(chunk - 1, 1);
   };
   auto t0 = Clock::now();
   long done_total = 0;
@@ -576,6 +580,8 @@ static int scenario_proxy_pattern(int sock) {
         OK(net->test(x.rreq[slot], &d, &sz));
         if (d) {
           uint32_t hdr[4];
+          x.rbuf[slot].from_device(0, sizeof(hdr));
+          x.rbuf[slot].from_device(chunk - 1, 1);
           memcpy(hdr, x.rbuf[slot].host(), sizeof(hdr));
           const int k = x.rreq_chunk[slot];
           if (sz != static_cast<int>(chunk) || hdr[0] != 0xC0FFEEu || hdr[1] != static_cast<uint32_t>(1 - g_rank) ||

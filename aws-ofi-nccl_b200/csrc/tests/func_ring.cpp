@@ -110,6 +110,7 @@ static int run_rank(const char* so) {
       fill(pattern, 1000 * g_rank + 100 * round + i);
       memcpy(sbuf[i].host(), pattern.data(), len[i]);
       memset(rbuf[i].host(), 0xEE, rbuf[i].size());
+      if (sbuf[i].to_device(0, len[i]) || rbuf[i].to_device()) FAIL("copy to the device failed");
     }
     // post everything, interleaved, retrying refused posts while the others make progress
     int sp = 0, rp = 0;
@@ -167,6 +168,7 @@ static int run_rank(const char* so) {
         if (expired(t0)) FAIL("flush never completed");
       }
       if (got[i] != static_cast<int>(len[i])) FAIL("round %d message %d: received %d bytes, expected %zu", round, i, got[i], len[i]);
+      if (rbuf[i].from_device(0, len[i] + 1)) FAIL("copy from the device failed");
       std::vector<uint8_t> want(len[i]);
       fill(want, 1000 * prev + 100 * round + i);
       if (memcmp(want.data(), rbuf[i].host(), len[i])) FAIL("round %d message %d: payload differs", round, i);

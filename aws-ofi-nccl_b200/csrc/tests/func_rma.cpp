@@ -150,6 +150,7 @@ static int run_rank(const char* so) {
   memset(got, 0, SLOT);
   memset(signals, 0, 16 * 8);
   for (size_t i = 0; i < SLOT; ++i) src[i] = static_cast<uint8_t>(i * 7 + g_rank);
+  if (window_b.to_device() || src_b.to_device() || got_b.to_device() || signals_b.to_device()) FAIL("copy to the device failed");
   void *win_mh, *src_mh, *sig_mh, *got_mh;
   OK(rma->regMrSym(coll, window_b.data(), SLOT * g_n, buf_type(window_b), 0, &win_mh));
   OK(rma->regMrSym(coll, src_b.data(), SLOT, buf_type(src_b), 0, &src_mh));
@@ -190,6 +191,7 @@ static int run_rank(const char* so) {
     const auto t0 = Clock::now();
     for (;;) {
       OK(rma->rmaProgress(ctx));
+      if (signals_b.from_device()) FAIL("copy from the device failed");
       bool all = true;
       for (int p = 0; p < g_n; ++p)
         if (p != g_rank && __atomic_load_n(&signals[p], __ATOMIC_ACQUIRE) != 1064) all = false;
@@ -197,6 +199,7 @@ static int run_rank(const char* so) {
       if (expired(t0)) FAIL("signals did not reach 1064: %llu %llu %llu", (unsigned long long)signals[0],
                             (unsigned long long)signals[1], (unsigned long long)signals[2]);
     }
+    if (window_b.from_device()) FAIL("copy from the device failed");
     for (int p = 0; p < g_n; ++p) {
       if (p == g_rank) continue;
       for (size_t i = 0; i < SLOT; ++i)
@@ -213,13 +216,14 @@ static int run_rank(const char* so) {
     if (wait_req(rma, coll, ctx, req)) return 1;
     OK(rma->iflush(ctx, 0, got_mh, peer, &req));
     if (req && wait_req(rma, coll, ctx, req)) return 1;
+    if (got_b.from_device()) FAIL("copy from the device failed");
     for (size_t i = 0; i < SLOT; ++i)
       if (got[i] != static_cast<uint8_t>(i * 7 + peer)) FAIL("iget payload differs at byte %zu", i);
   }
   // ---- kernel-initiated context (device buffers only): every rank allocates a pad of signal and
   // counter words on its device, the pads are mapped into every peer, and the device-visible
   // handle block lists {rank, nranks, signals, counters, pad address per rank}
-  if (device_mode()) {
+  if (device_mode_kind() == BUF_VIEW) {   // reads the pads through the stand-in's host view
     ncclGinConfig_v14_t kcfg = {3 + g_rank, 2, 1, 0, -1, 0, 0};   // ranks ask for different counts
     void* kctx = nullptr;
     ncclNetDeviceHandle_t* dh = nullptr;

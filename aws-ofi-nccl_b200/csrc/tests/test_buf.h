@@ -1,5 +1,16 @@
-// Buffers for the functional tests: host memory, or, with FUNC_NET_DEVICE=1, "device" memory.
+// Buffers for the functional tests: host memory, or, with FUNC_NET_DEVICE=1, device memory.
 // Included after the test has defined g_rank.
+//
+// Three modes:
+//   host    plain malloc; data() == host().
+//   view    the stand-in driver is on the library path (CPU runs): buffers come from it and are
+//           registered as NCCL_PTR_CUDA, so the plugin's IPC mapping, copy-kernel and eager-pack
+//           paths run. data() is not accessible to host code (a stray dereference faults); host()
+//           is a second mapping of the same bytes, so to_device() / from_device() have nothing to do.
+//   mirror  a real driver (a GPU box), or the stand-in with FUNC_NET_MIRROR=1: data() is device
+//           memory, host() a separate host copy; to_device() pushes the host copy before the
+//           plugin is given the buffer, from_device() fetches it before the test checks it.
+// A test written against host() + to_device() + from_device() runs unchanged in all three.
 #pragma once
 #include <dlfcn.h>
 
@@ -7,32 +18,21 @@
 #include <cstdio>
 #include <cstdlib>
 
+#include "b200net/cuda_shim.h"
 #include "nccl_abi.h"
 
-// "Device" buffers for CPU runs: with FUNC_NET_DEVICE=1 and the stand-in driver on the library
-// path (it serves device memory out of POSIX shared memory), buffers come from the driver and are
-// registered as NCCL_PTR_CUDA, so the plugin's IPC mapping, copy-kernel and eager-pack paths run.
-// The address handed to the plugin is not accessible to host code (a stray dereference faults);
-// the test fills and checks the bytes through host().
-struct TestBuf {
-  uint8_t* p = nullptr;   // the address given to the plugin
-  uint8_t* h = nullptr;   // where the test itself reads and writes the same bytes
-  size_t n = 0;
-  bool dev = false;
-  uint8_t* data() { return p; }
-  uint8_t* host() { return h; }
-  size_t size() const { return n; }
-};
 using FakeAllocFn = int (*)(void**, size_t);
 using FakeFreeFn = int (*)(void*);
 using FakeViewFn = void* (*)(void*);
 static FakeViewFn g_dev_view = nullptr;
 static FakeAllocFn g_dev_alloc = nullptr;
 static FakeFreeFn g_dev_free = nullptr;
-static bool device_mode() {
+
+enum TestBufMode { BUF_HOST = 0, BUF_VIEW = 1, BUF_MIRROR = 2 };
+static int device_mode_kind() {
   static int mode = -1;
   if (mode < 0) {
-    mode = 0;
+    mode = BUF_HOST;
     if (getenv("FUNC_NET_DEVICE") && atoi(getenv("FUNC_NET_DEVICE"))) {
       void* h = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
       if (h) {
@@ -40,20 +40,65 @@ static bool device_mode() {
         g_dev_free = reinterpret_cast<FakeFreeFn>(dlsym(h, "fake_cuda_mem_free"));
         g_dev_view = reinterpret_cast<FakeViewFn>(dlsym(h, "fake_cuda_host_view"));
       }
-      mode = (g_dev_alloc && g_dev_free && g_dev_view) ? 1 : 0;
-      if (!mode) fprintf(stderr, "[rank %d] FUNC_NET_DEVICE set but the stand-in driver is not on the library path\n", g_rank);
+      const bool stand_in = g_dev_alloc && g_dev_free && g_dev_view;
+      const bool want_mirror = getenv("FUNC_NET_MIRROR") && atoi(getenv("FUNC_NET_MIRROR"));
+      if (stand_in && !want_mirror) {
+        mode = BUF_VIEW;
+      } else if (b200net::cuda::available()) {
+        // one GPU per rank where there are several, so that payloads cross NVLink
+        const int count = b200net::cuda::device_count();
+        const char* pick = getenv("FUNC_NET_GPU");
+        const int ordinal = pick ? atoi(pick) : (count > 0 ? g_rank % count : 0);
+        if (b200net::cuda::ensure_primary_ctx(ordinal) == 0) mode = BUF_MIRROR;
+      }
+      if (mode == BUF_HOST) fprintf(stderr, "[rank %d] FUNC_NET_DEVICE set but no usable driver was found: host buffers\n", g_rank);
     }
   }
-  return mode == 1;
+  return mode;
 }
+static bool device_mode() { return device_mode_kind() != BUF_HOST; }
+
+struct TestBuf {
+  uint8_t* p = nullptr;   // the address given to the plugin
+  uint8_t* h = nullptr;   // where the test itself reads and writes the bytes
+  size_t n = 0;
+  bool dev = false;
+  bool mirror = false;
+  uint8_t* data() { return p; }
+  uint8_t* host() { return h; }
+  size_t size() const { return n; }
+  // host() -> data(): call after filling, before the plugin (or a peer) may read or overwrite the buffer
+  int to_device(size_t off = 0, size_t len = ~size_t{0}) { return copy(true, off, len); }
+  // data() -> host(): call before checking what arrived
+  int from_device(size_t off = 0, size_t len = ~size_t{0}) { return copy(false, off, len); }
+
+ private:
+  int copy(bool push, size_t off, size_t len) {
+    if (!mirror || off >= n) return 0;
+    if (len > n - off) len = n - off;
+    static b200net::cuda::Stream st = nullptr;
+    if (!st && b200net::cuda::stream_create(&st) != 0) return 1;
+    const int rc = push ? b200net::cuda::memcpy_async(p + off, h + off, len, st) : b200net::cuda::memcpy_async(h + off, p + off, len, st);
+    return rc != 0 || b200net::cuda::stream_synchronize(st) != 0;
+  }
+};
+
 static int buf_alloc(TestBuf* b, size_t n, bool want_device = true) {
   b->n = n;
-  b->dev = want_device && device_mode();
-  if (b->dev) {
+  const int kind = want_device ? device_mode_kind() : BUF_HOST;
+  b->dev = kind != BUF_HOST;
+  b->mirror = kind == BUF_MIRROR;
+  if (kind == BUF_VIEW) {
     void* p = nullptr;
     if (g_dev_alloc(&p, n) != 0) return 1;
     b->p = static_cast<uint8_t*>(p);
     b->h = static_cast<uint8_t*>(g_dev_view(p));
+  } else if (kind == BUF_MIRROR) {
+    void* p = nullptr;
+    if (b200net::cuda::mem_alloc(&p, n) != 0) return 1;
+    b->p = static_cast<uint8_t*>(p);
+    b->h = static_cast<uint8_t*>(calloc(1, n));
+    if (!b->h) return 1;
   } else {
     b->p = b->h = static_cast<uint8_t*>(malloc(n));
   }
@@ -61,9 +106,15 @@ static int buf_alloc(TestBuf* b, size_t n, bool want_device = true) {
 }
 static void buf_free(TestBuf* b) {
   if (!b->p) return;
-  if (b->dev) g_dev_free(b->p);
-  else free(b->p);
-  b->p = nullptr;
+  if (b->mirror) {
+    b200net::cuda::mem_free(b->p);
+    free(b->h);
+  } else if (b->dev) {
+    g_dev_free(b->p);
+  } else {
+    free(b->p);
+  }
+  b->p = b->h = nullptr;
 }
 static int buf_type() { return device_mode() ? NCCL_PTR_CUDA : NCCL_PTR_HOST; }
 static int buf_type(const TestBuf& b) { return b.dev ? NCCL_PTR_CUDA : NCCL_PTR_HOST; }

@@ -152,3 +152,19 @@ def test_mapping_helper_thread_hands_over_or_cleans_up(built):
     e["LD_LIBRARY_PATH"] = f"{fake}:" + e.get("LD_LIBRARY_PATH", "")
     res = subprocess.run([str(built / "tests" / "drv_ipc_mapper")], capture_output=True, text=True, timeout=120, env=e, cwd=built)
     assert res.returncode == 0 and res.stdout.strip().endswith("ok"), res.stdout[-2000:] + res.stderr[-3000:]
+
+
+@pytest.mark.parametrize("proto", ["RDMA", "SENDRECV"])
+def test_mirror_mode_of_the_test_buffers(built, proto):
+    """The buffer mode a GPU box uses (device memory plus a host mirror with explicit copies), run
+    here against the stand-in driver so that every copy call in the scenarios is exercised."""
+    _run(built, {"B200NET_PROTOCOL": proto, "B200NET_FORCE_NUM_RAILS": "4", "FUNC_NET_MIRROR": "1",
+                 "FAKE_CUDA_LAUNCH_DELAY_US": "100"}, "device_transfer")
+    _run(built, {"B200NET_PROTOCOL": proto, "B200NET_FORCE_NUM_RAILS": "4", "FUNC_NET_MIRROR": "1"}, "proxy_pattern")
+    fake = built / "tests" / "fake_cuda"
+    e = dict(os.environ, FUNC_NET_DEVICE="1", FUNC_NET_MIRROR="1", B200NET_PROTOCOL=proto)
+    e["LD_LIBRARY_PATH"] = f"{fake}:" + e.get("LD_LIBRARY_PATH", "")
+    for exe, arg in (("func_ring", "3"), ("func_rma", "3")):
+        res = subprocess.run([str(built / "tests" / exe), str(built / "libnccl-net-ofi-b200.so"), arg],
+                             capture_output=True, text=True, timeout=300, env=e, cwd=built)
+        assert res.returncode == 0, exe + res.stdout[-2000:] + res.stderr[-4000:]

@@ -1,0 +1,28 @@
+"""The plugin's device-buffer paths on real GPUs, through the public ncclNet table: two processes,
+payloads in device memory (one GPU per rank where there are two), the plugin's own copy and
+eager-pack kernels, IPC mapping of the peer's buffers, byte-exact checks through host mirrors.
+The same binaries run on CPU against a stand-in driver (test_net_device_paths_cpu.py)."""
+import json
+import os
+import subprocess
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("scenario", ["device_transfer", "proxy_pattern"])
+def test_functional_scenarios_on_device_memory(built, tmp_path, scenario):
+    env = dict(os.environ, FUNC_NET_DEVICE="1", B200NET_PROTOCOL="RDMA", B200NET_FORCE_NUM_RAILS="4",
+               B200NET_STATS_FILE=str(tmp_path / "stats.%p.json"))
+    res = subprocess.run([str(built / "tests" / "func_net"), str(built / "libnccl-net-ofi-b200.so"), scenario],
+                         capture_output=True, text=True, timeout=180, env=env, cwd=built)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    assert "host buffers" not in res.stderr, "the test fell back to host memory:\n" + res.stderr[-2000:]
+    files = sorted(tmp_path.glob("stats.*.json"))
+    assert len(files) == 2, files
+    for f in files:
+        c = json.loads(f.read_text())["counters"]
+        # device payloads leave through the copy kernel, the copy engine or host fragments, never as a host write
+        assert c["bytes_copy_kernel"] + c["bytes_copy_engine"] + c["bytes_staged_through_host"] > 0, c
+        assert c["bytes_host_writes"] == 0 and c["requests_failed"] == 0, c
