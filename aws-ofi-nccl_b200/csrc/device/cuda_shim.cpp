@@ -59,6 +59,9 @@ struct Api {
   CUresult (*MemUnmap)(CUdeviceptr, size_t) = nullptr;
   CUresult (*MemSetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
   CUresult (*MemExportToShareableHandle)(void*, CUmemGenericAllocationHandle, CUmemAllocationHandleType, unsigned long long) = nullptr;
+  CUresult (*MemImportFromShareableHandle)(CUmemGenericAllocationHandle*, void*, CUmemAllocationHandleType) = nullptr;
+  CUresult (*MemRetainAllocationHandle)(CUmemGenericAllocationHandle*, void*) = nullptr;
+  CUresult (*CtxGetDevice)(CUdevice*) = nullptr;
   CUresult (*MemGetHandleForAddressRange)(void*, CUdeviceptr, size_t, CUmemRangeHandleType, unsigned long long) = nullptr;
   CUresult (*FlushGPUDirectRDMAWrites)(CUflushGPUDirectRDMAWritesTarget, CUflushGPUDirectRDMAWritesScope) = nullptr;
 };
@@ -128,6 +131,9 @@ void do_init() {
   ok &= sym(g.MemUnmap, "cuMemUnmap");
   ok &= sym(g.MemSetAccess, "cuMemSetAccess");
   ok &= sym(g.MemExportToShareableHandle, "cuMemExportToShareableHandle");
+  sym(g.MemImportFromShareableHandle, "cuMemImportFromShareableHandle", false);
+  sym(g.MemRetainAllocationHandle, "cuMemRetainAllocationHandle", false);
+  sym(g.CtxGetDevice, "cuCtxGetDevice", false);
   sym(g.MemGetHandleForAddressRange, "cuMemGetHandleForAddressRange", false);
   sym(g.FlushGPUDirectRDMAWrites, "cuFlushGPUDirectRDMAWrites", false);
   if (!ok) return;
@@ -332,6 +338,45 @@ int vmm_free(void* ptr, size_t rounded, uint64_t handle) {
 int vmm_export_fd(uint64_t handle, int* fd) {
   if (!available()) return -ENOSYS;
   return rc_of(g.MemExportToShareableHandle(fd, handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
+}
+int vmm_export_range(void* alloc_base, int* fd) {
+  if (!available() || !g.MemRetainAllocationHandle) return -ENOTSUP;
+  CUmemGenericAllocationHandle h;
+  CUresult r = g.MemRetainAllocationHandle(&h, alloc_base);
+  if (r != CUDA_SUCCESS) return rc_of(r);
+  r = g.MemExportToShareableHandle(fd, h, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
+  g.MemRelease(h);   // the retain took a reference of its own
+  return rc_of(r);
+}
+int vmm_import_map(int fd, size_t bytes, void** mapped) {
+  if (!available() || !g.MemImportFromShareableHandle || !g.CtxGetDevice) return -ENOTSUP;
+  CUdevice dev;
+  CUresult r = g.CtxGetDevice(&dev);
+  if (r != CUDA_SUCCESS) return rc_of(r);
+  CUmemGenericAllocationHandle h;
+  r = g.MemImportFromShareableHandle(&h, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)), CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+  if (r != CUDA_SUCCESS) return rc_of(r);
+  CUdeviceptr va = 0;
+  r = g.MemAddressReserve(&va, bytes, 0, 0, 0);
+  if (r != CUDA_SUCCESS) { g.MemRelease(h); return rc_of(r); }
+  r = g.MemMap(va, bytes, 0, h, 0);
+  g.MemRelease(h);   // the mapping keeps the allocation alive
+  if (r != CUDA_SUCCESS) { g.MemAddressFree(va, bytes); return rc_of(r); }
+  CUmemAccessDesc acc;
+  memset(&acc, 0, sizeof(acc));
+  acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  acc.location.id = dev;
+  acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  r = g.MemSetAccess(va, bytes, &acc, 1);
+  if (r != CUDA_SUCCESS) { g.MemUnmap(va, bytes); g.MemAddressFree(va, bytes); return rc_of(r); }
+  *mapped = reinterpret_cast<void*>(va);
+  return 0;
+}
+int vmm_unmap(void* mapped, size_t bytes) {
+  if (!available()) return -ENOSYS;
+  const CUresult r = g.MemUnmap(reinterpret_cast<CUdeviceptr>(mapped), bytes);
+  g.MemAddressFree(reinterpret_cast<CUdeviceptr>(mapped), bytes);
+  return rc_of(r);
 }
 int get_dmabuf_fd(void* ptr, size_t size, int* fd, uint64_t* offset) {
   if (!available() || !g.MemGetHandleForAddressRange) return -ENOTSUP;

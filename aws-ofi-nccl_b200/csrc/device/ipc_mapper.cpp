@@ -1,5 +1,8 @@
 #include "b200net/ipc_mapper.h"
 
+#include <sys/syscall.h>
+#include <unistd.h>
+
 #include <cerrno>
 #include <chrono>
 #include <condition_variable>
@@ -24,6 +27,35 @@ Shared& shared() {
   return *s;
 }
 
+// Duplicates descriptor `fd` of process `pid` into this process (pidfd_open + pidfd_getfd; the same
+// permission as cross-memory attach). Returns the new descriptor or a negative errno.
+int steal_fd(uint32_t pid, int fd) {
+#if defined(SYS_pidfd_open) && defined(SYS_pidfd_getfd)
+  const int pidfd = static_cast<int>(syscall(SYS_pidfd_open, static_cast<pid_t>(pid), 0));
+  if (pidfd < 0) return -errno;
+  const int mine = static_cast<int>(syscall(SYS_pidfd_getfd, pidfd, fd, 0));
+  const int err = errno;
+  close(pidfd);
+  return mine < 0 ? -err : mine;
+#else
+  (void)pid;
+  (void)fd;
+  return -ENOSYS;
+#endif
+}
+
+int open_vmm(IpcMapJob& job, void** mapped) {
+  VmmShare sh;
+  memcpy(&sh, job.handle, sizeof(sh));
+  if (sh.magic != VMM_SHARE_MAGIC || sh.bytes == 0) return -EINVAL;
+  const int fd = steal_fd(sh.pid, sh.fd);
+  if (fd < 0) return fd;
+  job.bytes = sh.bytes;
+  const int rc = cuda::vmm_import_map(fd, sh.bytes, mapped);
+  close(fd);   // the imported handle holds its own reference
+  return rc;
+}
+
 void helper_main() {
   Shared& s = shared();
   for (;;) {
@@ -36,12 +68,12 @@ void helper_main() {
     }
     if (job->ctx) cuda::ctx_set_current(job->ctx);
     void* p = nullptr;
-    const int rc = cuda::ipc_open(job->handle, &p);
+    const int rc = job->vmm ? open_vmm(*job, &p) : cuda::ipc_open(job->handle, &p);
     job->mapped = p;
     int expected = 0;
     if (!job->state.compare_exchange_strong(expected, rc == 0 ? 1 : (rc < 0 ? rc : -EIO), std::memory_order_acq_rel) &&
         rc == 0)
-      cuda::ipc_close(p);   // abandoned meanwhile: nobody is left to use or close it
+      job->close_mapping();   // abandoned meanwhile: nobody is left to use or close it
   }
 }
 
@@ -52,9 +84,10 @@ IpcMapper& IpcMapper::instance() {
   return *m;
 }
 
-std::shared_ptr<IpcMapJob> IpcMapper::submit(const uint8_t handle[64], cuda::Context ctx) {
+std::shared_ptr<IpcMapJob> IpcMapper::submit(const uint8_t handle[64], cuda::Context ctx, bool vmm) {
   Shared& s = shared();
   auto job = std::make_shared<IpcMapJob>();
+  job->vmm = vmm;
   memcpy(job->handle, handle, 64);
   job->ctx = ctx;
   std::lock_guard<std::mutex> g(s.mu);

@@ -58,6 +58,12 @@ int mem_free(void* ptr);
 int vmm_alloc(int device, size_t bytes, void** ptr, size_t* rounded, uint64_t* handle_out);
 int vmm_free(void* ptr, size_t rounded, uint64_t handle);
 int vmm_export_fd(uint64_t handle, int* fd);
+// Peer access to somebody else's allocation of the virtual-memory API (NCCL's own buffers are
+// such): the owner exports the allocation behind a mapped range as a POSIX fd, the peer (once it
+// holds a duplicate of that fd) imports it, maps it and enables access for its current device.
+int vmm_export_range(void* alloc_base, int* fd);
+int vmm_import_map(int fd, size_t bytes, void** mapped);
+int vmm_unmap(void* mapped, size_t bytes);
 // dma-buf descriptor of an address range (for regMrDmaBuf users); -ENOTSUP when unsupported.
 int get_dmabuf_fd(void* ptr, size_t size, int* fd, uint64_t* offset);
 bool dmabuf_supported(int device);

@@ -16,7 +16,22 @@
 
 namespace b200net {
 
+// What the 64 handle bytes of a CUDA_VMM registration hold.
+struct VmmShare {
+  uint32_t magic;    // VMM_SHARE_MAGIC
+  int32_t fd;        // descriptor number in the owner's process
+  uint32_t pid;      // the owner
+  uint32_t pad;
+  uint64_t bytes;    // size of the mapped range the descriptor stands for
+  uint64_t serial;   // unique per export in the owner: descriptor numbers are reused, mappings are cached by these bytes
+};
+constexpr uint32_t VMM_SHARE_MAGIC = 0x564d4d31;   // "VMM1"
+
 struct IpcMapJob {
+  bool vmm = false;                  // handle holds a VmmShare instead of a legacy IPC handle
+  size_t bytes = 0;                  // of the mapping (virtual-memory API only)
+  // Undoes what the helper did (state == 1 only).
+  int close_mapping() const { return vmm ? cuda::vmm_unmap(mapped, bytes) : cuda::ipc_close(mapped); }
   uint8_t handle[64];
   cuda::Context ctx = nullptr;       // made current on the helper thread before the open
   std::atomic<int> state{0};         // 0 in progress, 1 mapped, 2 abandoned by its owner, negative errno
@@ -34,7 +49,7 @@ class IpcMapper {
  public:
   static IpcMapper& instance();
   // Queues the open. Never blocks on the device. nullptr if the helper thread could not start.
-  std::shared_ptr<IpcMapJob> submit(const uint8_t handle[64], cuda::Context ctx);
+  std::shared_ptr<IpcMapJob> submit(const uint8_t handle[64], cuda::Context ctx, bool vmm = false);
   // Polls job->state for at most wait_us microseconds; returns the state seen last.
   static int wait(const IpcMapJob& job, uint64_t wait_us);
 };

@@ -64,7 +64,10 @@ struct Properties {
   int num_rails = 1;
 };
 
-enum class MrKind : uint32_t { HOST = 1, CUDA_IPC = 2, CUDA_STAGED = 3 };
+// How a peer reaches a registration: host memory; device memory with a legacy IPC handle; device
+// memory without any mapping (payloads travel as fragments that the owner copies); device memory
+// of the virtual-memory API, exported as a file descriptor that the peer duplicates and imports.
+enum class MrKind : uint32_t { HOST = 1, CUDA_IPC = 2, CUDA_STAGED = 3, CUDA_VMM = 4 };
 
 class Endpoint;
 class Domain;

@@ -6,6 +6,10 @@
 //
 // Fault injection through the environment (read at cuInit):
 //   FAKE_CUDA_FAIL_IPC_OPEN=1   cuIpcOpenMemHandle fails (the plugin must fall back to staging)
+//   FAKE_CUDA_VMM=1             the tests' device buffers come from the virtual-memory API (create,
+//                               reserve, map), as NCCL's own buffers do: no legacy IPC handle, but
+//                               the allocation can be exported as a file descriptor
+//   FAKE_CUDA_FAIL_VMM_IMPORT=1 importing such a descriptor fails
 //   FAKE_CUDA_FAIL_IPC_GET=1    cuIpcGetMemHandle fails, as for allocations of the virtual-memory API
 //   FAKE_CUDA_PROTECT=0         device addresses stay readable and writable by host code (default:
 //                               they are mapped without access, so a host dereference faults)
@@ -38,6 +42,7 @@ struct Alloc {
   std::string shm_name;   // empty: mapping of a peer's allocation
   bool opened_from_peer;
   unsigned char* shadow;   // readable and writable view of the same pages (the device's own view)
+  unsigned long long vmm_handle = 0;   // non-zero: mapped through the virtual-memory API
 };
 std::mutex g_mu;
 std::map<uintptr_t, Alloc> g_allocs;   // base -> allocation ("device" address ranges of this process)
@@ -179,7 +184,7 @@ CUresult fPointerGetAttribute(void* out, CUpointer_attribute a, CUdeviceptr p) {
   switch (a) {
     case CU_POINTER_ATTRIBUTE_MEMORY_TYPE: *static_cast<unsigned*>(out) = CU_MEMORYTYPE_DEVICE; break;
     case CU_POINTER_ATTRIBUTE_DEVICE_ORDINAL: *static_cast<int*>(out) = 0; break;
-    case CU_POINTER_ATTRIBUTE_IS_LEGACY_CUDA_IPC_CAPABLE: *static_cast<int*>(out) = al->opened_from_peer ? 0 : 1; break;
+    case CU_POINTER_ATTRIBUTE_IS_LEGACY_CUDA_IPC_CAPABLE: *static_cast<int*>(out) = (al->opened_from_peer || al->vmm_handle) ? 0 : 1; break;
     default: return CUDA_ERROR_INVALID_VALUE;
   }
   return CUDA_SUCCESS;
@@ -359,7 +364,129 @@ CUresult fMemFreeHost(void* p) {
   free(p);
   return CUDA_SUCCESS;
 }
-// VMM: not offered by the stand-in
+// ---- the virtual-memory API: an allocation is a memory file, a handle a reference to it
+struct VmmHandle {
+  int fd;
+  size_t size;
+  int refs;
+  bool imported;
+};
+std::map<unsigned long long, VmmHandle> g_handles;   // guarded by g_mu
+unsigned long long g_next_handle = 0x7000;
+
+CUresult fMemGetAllocationGranularity(size_t* gran, const CUmemAllocationProp*, CUmemAllocationGranularity_flags) {
+  *gran = 65536;
+  return CUDA_SUCCESS;
+}
+CUresult fMemCreate(CUmemGenericAllocationHandle* h, size_t size, const CUmemAllocationProp*, unsigned long long) {
+  const int fd = memfd_create("fakecuda-vmm", 0);
+  if (fd < 0 || ftruncate(fd, static_cast<off_t>(size)) != 0) {
+    if (fd >= 0) close(fd);
+    return CUDA_ERROR_OUT_OF_MEMORY;
+  }
+  std::lock_guard<std::mutex> g(g_mu);
+  *h = g_next_handle++;
+  g_handles[*h] = VmmHandle{fd, size, 1, false};
+  return CUDA_SUCCESS;
+}
+CUresult fMemRelease(CUmemGenericAllocationHandle h) {
+  std::lock_guard<std::mutex> g(g_mu);
+  auto it = g_handles.find(h);
+  if (it == g_handles.end()) return CUDA_ERROR_INVALID_VALUE;
+  if (--it->second.refs == 0) {
+    close(it->second.fd);
+    g_handles.erase(it);
+  }
+  return CUDA_SUCCESS;
+}
+CUresult fMemAddressReserve(CUdeviceptr* va, size_t size, size_t, CUdeviceptr, unsigned long long) {
+  void* p = mmap(nullptr, size, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE, -1, 0);
+  if (p == MAP_FAILED) return CUDA_ERROR_OUT_OF_MEMORY;
+  *va = reinterpret_cast<CUdeviceptr>(p);
+  return CUDA_SUCCESS;
+}
+CUresult fMemAddressFree(CUdeviceptr va, size_t size) {
+  munmap(reinterpret_cast<void*>(va), size);
+  return CUDA_SUCCESS;
+}
+CUresult fMemMap(CUdeviceptr va, size_t size, size_t offset, CUmemGenericAllocationHandle h, unsigned long long) {
+  std::lock_guard<std::mutex> g(g_mu);
+  auto it = g_handles.find(h);
+  if (it == g_handles.end() || offset + size > it->second.size) return CUDA_ERROR_INVALID_VALUE;
+  void* user = mmap(reinterpret_cast<void*>(va), size, protect_on() ? PROT_NONE : (PROT_READ | PROT_WRITE), MAP_SHARED | MAP_FIXED,
+                    it->second.fd, static_cast<off_t>(offset));
+  if (user == MAP_FAILED) return CUDA_ERROR_OUT_OF_MEMORY;
+  void* sh = mmap(nullptr, size, PROT_READ | PROT_WRITE, MAP_SHARED, it->second.fd, static_cast<off_t>(offset));
+  if (sh == MAP_FAILED) return CUDA_ERROR_OUT_OF_MEMORY;
+  ++it->second.refs;   // a mapping keeps the allocation alive
+  Alloc al{size, "", it->second.imported, static_cast<unsigned char*>(sh)};
+  al.vmm_handle = h;
+  g_allocs[static_cast<uintptr_t>(va)] = al;
+  return CUDA_SUCCESS;
+}
+CUresult fMemUnmap(CUdeviceptr va, size_t size) {
+  unsigned long long h = 0;
+  {
+    std::lock_guard<std::mutex> g(g_mu);
+    auto it = g_allocs.find(static_cast<uintptr_t>(va));
+    if (it == g_allocs.end() || !it->second.vmm_handle || it->second.size != size) return CUDA_ERROR_INVALID_VALUE;
+    munmap(it->second.shadow, size);
+    h = it->second.vmm_handle;
+    g_allocs.erase(it);
+  }
+  // the address range stays reserved, without backing
+  mmap(reinterpret_cast<void*>(va), size, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE | MAP_FIXED, -1, 0);
+  return fMemRelease(h);
+}
+CUresult fMemSetAccess(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) { return CUDA_SUCCESS; }
+CUresult fMemRetainAllocationHandle(CUmemGenericAllocationHandle* h, void* addr) {
+  std::lock_guard<std::mutex> g(g_mu);
+  uintptr_t base = 0;
+  const Alloc* al = find_alloc(reinterpret_cast<uintptr_t>(addr), &base);
+  if (!al || !al->vmm_handle) return CUDA_ERROR_INVALID_VALUE;
+  *h = al->vmm_handle;
+  ++g_handles[*h].refs;
+  return CUDA_SUCCESS;
+}
+CUresult fMemExportToShareableHandle(void* out, CUmemGenericAllocationHandle h, CUmemAllocationHandleType type, unsigned long long) {
+  if (type != CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) return CUDA_ERROR_NOT_SUPPORTED;
+  std::lock_guard<std::mutex> g(g_mu);
+  auto it = g_handles.find(h);
+  if (it == g_handles.end()) return CUDA_ERROR_INVALID_VALUE;
+  const int fd = dup(it->second.fd);
+  if (fd < 0) return CUDA_ERROR_OUT_OF_MEMORY;
+  *static_cast<int*>(out) = fd;
+  return CUDA_SUCCESS;
+}
+CUresult fMemImportFromShareableHandle(CUmemGenericAllocationHandle* h, void* os_handle, CUmemAllocationHandleType type) {
+  if (type != CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) return CUDA_ERROR_NOT_SUPPORTED;
+  if (getenv("FAKE_CUDA_FAIL_VMM_IMPORT") && atoi(getenv("FAKE_CUDA_FAIL_VMM_IMPORT"))) return CUDA_ERROR_INVALID_DEVICE;
+  const int fd = dup(static_cast<int>(reinterpret_cast<uintptr_t>(os_handle)));
+  struct stat st;
+  if (fd < 0 || fstat(fd, &st) != 0) {
+    if (fd >= 0) close(fd);
+    return CUDA_ERROR_INVALID_VALUE;
+  }
+  std::lock_guard<std::mutex> g(g_mu);
+  *h = g_next_handle++;
+  g_handles[*h] = VmmHandle{fd, static_cast<size_t>(st.st_size), 1, true};
+  return CUDA_SUCCESS;
+}
+CUresult fCtxGetDevice(CUdevice* d) {
+  *d = 0;
+  return CUDA_SUCCESS;
+}
+// a "device" allocation made the way NCCL makes its buffers: create, reserve, map
+CUresult vmm_style_alloc(CUdeviceptr* out, size_t bytes) {
+  const size_t size = (bytes + 65535) & ~static_cast<size_t>(65535);
+  CUmemGenericAllocationHandle h;
+  if (fMemCreate(&h, size, nullptr, 0) != CUDA_SUCCESS) return CUDA_ERROR_OUT_OF_MEMORY;
+  CUdeviceptr va = 0;
+  if (fMemAddressReserve(&va, size, 0, 0, 0) != CUDA_SUCCESS || fMemMap(va, size, 0, h, 0) != CUDA_SUCCESS) return CUDA_ERROR_OUT_OF_MEMORY;
+  fMemRelease(h);   // the mapping holds the allocation from here on
+  *out = va;
+  return CUDA_SUCCESS;
+}
 CUresult fNotSupported() { return CUDA_ERROR_NOT_SUPPORTED; }
 
 struct Entry {
@@ -380,9 +507,11 @@ const Entry kTable[] = {
     E("cuMemcpyAsync", fMemcpyAsync), E("cuModuleLoadData", fModuleLoadData), E("cuModuleUnload", fModuleUnload),
     E("cuModuleGetFunction", fModuleGetFunction), E("cuLaunchKernel", fLaunchKernel), E("cuMemHostAlloc", fMemHostAlloc),
     E("cuMemFreeHost", fMemFreeHost), E("cuMemAlloc", fMemAlloc), E("cuMemFree", fMemFree), E("cuMemsetD8", fMemsetD8),
-    E("cuMemCreate", fNotSupported), E("cuMemRelease", fNotSupported), E("cuMemGetAllocationGranularity", fNotSupported),
-    E("cuMemAddressReserve", fNotSupported), E("cuMemAddressFree", fNotSupported), E("cuMemMap", fNotSupported),
-    E("cuMemUnmap", fNotSupported), E("cuMemSetAccess", fNotSupported), E("cuMemExportToShareableHandle", fNotSupported),
+    E("cuMemCreate", fMemCreate), E("cuMemRelease", fMemRelease), E("cuMemGetAllocationGranularity", fMemGetAllocationGranularity),
+    E("cuMemAddressReserve", fMemAddressReserve), E("cuMemAddressFree", fMemAddressFree), E("cuMemMap", fMemMap),
+    E("cuMemUnmap", fMemUnmap), E("cuMemSetAccess", fMemSetAccess), E("cuMemExportToShareableHandle", fMemExportToShareableHandle),
+    E("cuMemImportFromShareableHandle", fMemImportFromShareableHandle), E("cuMemRetainAllocationHandle", fMemRetainAllocationHandle),
+    E("cuCtxGetDevice", fCtxGetDevice),
 };
 
 }  // namespace
@@ -404,11 +533,23 @@ CUresult cuGetProcAddress_v2(const char* symbol, void** pfn, int, cuuint64_t, CU
 // For the tests themselves: allocate and free "device" memory without going through the table.
 CUresult fake_cuda_mem_alloc(void** p, size_t bytes) {
   CUdeviceptr d = 0;
-  const CUresult r = fMemAlloc(&d, bytes);
+  const bool vmm = getenv("FAKE_CUDA_VMM") && atoi(getenv("FAKE_CUDA_VMM"));
+  const CUresult r = vmm ? vmm_style_alloc(&d, bytes) : fMemAlloc(&d, bytes);
   *p = reinterpret_cast<void*>(d);
   return r;
 }
-CUresult fake_cuda_mem_free(void* p) { return fMemFree(reinterpret_cast<CUdeviceptr>(p)); }
+CUresult fake_cuda_mem_free(void* p) {
+  size_t vmm_size = 0;
+  {
+    std::lock_guard<std::mutex> g(g_mu);
+    auto it = g_allocs.find(reinterpret_cast<uintptr_t>(p));
+    if (it != g_allocs.end() && it->second.vmm_handle) vmm_size = it->second.size;
+  }
+  if (!vmm_size) return fMemFree(reinterpret_cast<CUdeviceptr>(p));
+  const CUresult r = fMemUnmap(reinterpret_cast<CUdeviceptr>(p), vmm_size);
+  fMemAddressFree(reinterpret_cast<CUdeviceptr>(p), vmm_size);
+  return r;
+}
 // How many peer allocations are mapped into this process right now (opened and not yet closed).
 int fake_cuda_live_peer_mappings() {
   std::lock_guard<std::mutex> g(g_mu);

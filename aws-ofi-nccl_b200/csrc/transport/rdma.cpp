@@ -17,6 +17,7 @@
 #include <deque>
 #include <functional>
 #include <list>
+#include <map>
 #include <memory>
 #include <set>
 
@@ -169,6 +170,7 @@ class RdmaEndpoint : public Endpoint {
   bool warned_ipc = false, noted_ipc_wait = false;
   void note_unmapped(PeerMapping* peer, const MrTableEntry* e);
   std::set<std::pair<MrHandle*, int>> published;
+  std::map<MrHandle*, int> export_fds;   // descriptors kept open for peers that import a CUDA_VMM registration
   // Requests a queued retry may still touch, by serial number: a request's address can be handed
   // out again (to another communicator's request) while an old retry for it is still queued.
   std::map<uint64_t, RdmaSendReq*> live_send_reqs;
@@ -258,7 +260,8 @@ RdmaEndpoint::~RdmaEndpoint() {
              static_cast<unsigned long long>(bytes_staged), static_cast<unsigned long long>(bytes_host),
              static_cast<unsigned long long>(bytes_eager));
   for (auto& [k, job] : ipc_maps)
-    if (job && job->abandon()) cuda::ipc_close(job->mapped);
+    if (job && job->abandon()) job->close_mapping();
+  for (auto& [mh, fd] : export_fds) ::close(fd);
   for (auto s : streams)
     if (s) cuda::stream_destroy(s);
 }
@@ -284,10 +287,13 @@ void* RdmaEndpoint::map_peer_cuda(PeerMapping* peer, const MrTableEntry* e) {
     if (domain->device->gpu_ordinal >= 0) cuda::ensure_primary_ctx(domain->device->gpu_ordinal);
     cuda::Context ctx = nullptr;
     cuda::ctx_get_current(&ctx);
-    it = ipc_maps.emplace(key, IpcMapper::instance().submit(e->ipc_handle, ctx)).first;
+    it = ipc_maps.emplace(key, IpcMapper::instance().submit(e->ipc_handle, ctx, e->kind == static_cast<uint32_t>(MrKind::CUDA_VMM))).first;
     // once an open has outlasted the grace period the device is evidently busy: later first uses
-    // do not stall the caller again
-    if (it->second && !noted_ipc_wait) IpcMapper::wait(*it->second, params().ipc_map_wait_us.get());
+    // stall the caller only briefly (an open that does not have to wait for the device takes microseconds)
+    if (it->second) {
+      const uint64_t grace = params().ipc_map_wait_us.get();
+      IpcMapper::wait(*it->second, noted_ipc_wait ? std::min<uint64_t>(grace, 500) : grace);
+    }
   }
   if (!it->second) return nullptr;
   return it->second->state.load(std::memory_order_acquire) == 1 ? it->second->mapped : nullptr;
@@ -327,6 +333,28 @@ int RdmaEndpoint::ensure_published(MrHandle* mh) {
       mh->kind = MrKind::CUDA_STAGED;
       e.kind = static_cast<uint32_t>(MrKind::CUDA_STAGED);
     }
+  } else if (mh->kind == MrKind::CUDA_VMM) {
+    // memory of the virtual-memory API (NCCL's own buffers are such): peers import the allocation
+    // behind the mapped range through a descriptor that this process keeps open for them
+    void* base = nullptr;
+    size_t sz = 0;
+    int dev = 0, fd = -1;
+    const bool ok = cuda::pointer_info(mh->base, &dev, &base, &sz, nullptr) == 0 &&
+                    static_cast<char*>(base) + sz >= static_cast<char*>(mh->base) + mh->size &&   // one allocation covers it
+                    cuda::vmm_export_range(base, &fd) == 0;
+    if (ok) {
+      static std::atomic<uint64_t> next_export{1};
+      VmmShare sh{VMM_SHARE_MAGIC, fd, static_cast<uint32_t>(getpid()), 0, sz, next_export.fetch_add(1)};
+      static_assert(sizeof(sh) <= sizeof(e.ipc_handle), "share record fits the handle bytes");
+      memcpy(e.ipc_handle, &sh, sizeof(sh));
+      e.base = reinterpret_cast<uint64_t>(base);
+      e.size = sz;
+      e.device = static_cast<uint32_t>(dev);
+      export_fds[mh] = fd;
+    } else {
+      mh->kind = MrKind::CUDA_STAGED;
+      e.kind = static_cast<uint32_t>(MrKind::CUDA_STAGED);
+    }
   }
   const int rc = fab.mr_publish(e);
   if (rc == 0) published.insert({mh, 0});
@@ -360,7 +388,7 @@ int RdmaEndpoint::reg_mr(void* data, size_t size, int type, MrHandle** out) {
       delete mh;
       return -EINVAL;
     }
-    mh->kind = vmm ? MrKind::CUDA_STAGED : MrKind::CUDA_IPC;
+    mh->kind = vmm ? MrKind::CUDA_VMM : MrKind::CUDA_IPC;
   }
   if (cache) {
     const int rc = cache->insert(key, mh);
@@ -389,6 +417,10 @@ int RdmaEndpoint::dereg_mr(MrHandle* mh) {
   }
   fab.mr_unpublish(mh->key);
   published.erase({mh, 0});
+  if (auto fd = export_fds.find(mh); fd != export_fds.end()) {
+    ::close(fd->second);
+    export_fds.erase(fd);
+  }
   domain->mr_keys.free_id(mh->key - 1);
   delete mh;
   return 0;
@@ -647,7 +679,7 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
   bool back_pressure = false;   // some ring was full: the post must be retried in order
   for (Stripe& s : r->stripes) {
     if (!s.complete) {
-      if (kind == static_cast<uint32_t>(MrKind::CUDA_IPC)) {
+      if (kind == static_cast<uint32_t>(MrKind::CUDA_IPC) || kind == static_cast<uint32_t>(MrKind::CUDA_VMM)) {
         if (!s.posted) {
           void* mapped = e->map_peer_cuda(peer, mr);
           cuda::Stream st = e->rail_stream(s.rail);
@@ -773,7 +805,8 @@ int RdmaSendComm::start_rendezvous(RdmaSendReq* r, const CtrlEntry& e) {
   if (r->size > e.buff_len) r->size = e.buff_len;  // a send larger than the posted receive is truncated
   const MrTableEntry* mr = FabricEndpoint::mr_lookup(peer, e.mr_key);
   const bool dst_host = !mr || mr->kind == static_cast<uint32_t>(MrKind::HOST);
-  if (mr && mr->kind == static_cast<uint32_t>(MrKind::CUDA_IPC) && !rep()->map_peer_cuda(peer, mr)) {
+  const bool mappable = mr && (mr->kind == static_cast<uint32_t>(MrKind::CUDA_IPC) || mr->kind == static_cast<uint32_t>(MrKind::CUDA_VMM));
+  if (mappable && !rep()->map_peer_cuda(peer, mr)) {
     // the peer's device memory cannot be mapped into this process (another container, a driver
     // without IPC): the payload travels as fragments that the receiver copies to its device
     rep()->note_unmapped(peer, mr);

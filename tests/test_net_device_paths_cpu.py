@@ -168,3 +168,23 @@ def test_mirror_mode_of_the_test_buffers(built, proto):
         res = subprocess.run([str(built / "tests" / exe), str(built / "libnccl-net-ofi-b200.so"), arg],
                              capture_output=True, text=True, timeout=300, env=e, cwd=built)
         assert res.returncode == 0, exe + res.stdout[-2000:] + res.stderr[-4000:]
+
+
+def test_buffers_of_the_virtual_memory_api_are_imported_through_a_descriptor(built):
+    """NCCL allocates its own buffers with cuMemCreate: no legacy IPC handle exists for them.  The
+    owner exports the allocation as a file descriptor, the peer duplicates it (pidfd_getfd), imports
+    and maps it, and payloads then take the same copy-kernel path as legacy allocations."""
+    log = _run(built, {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4", "FAKE_CUDA_VMM": "1",
+                       "FAKE_CUDA_LAUNCH_DELAY_US": "100"})
+    c = _payload_counters(log)
+    # (on a loaded machine a mapping can miss its grace period; those few payloads go through host fragments)
+    assert c["copy kernel"] > 0 and c["staged through host"] < c["copy kernel"] // 20, c
+    # an import that fails degrades to host fragments
+    log = _run(built, {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4", "FAKE_CUDA_VMM": "1",
+                       "FAKE_CUDA_FAIL_VMM_IMPORT": "1"}, "device_transfer")
+    c = _payload_counters(log)
+    assert c["staged through host"] > 0 and c["copy kernel"] == 0, c
+    assert "cannot be mapped here" in log
+    # buffers registered, released and replaced: descriptor numbers recur, mappings must not
+    for _ in range(2):
+        _run(built, {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "2", "FAKE_CUDA_VMM": "1"}, "proxy_pattern")

@@ -56,7 +56,7 @@ def test_address_and_undefined_behaviour():
     for extra in ({}, {"FUNC_RMA_HOST_TARGETS": "1"}, {"FUNC_RMA_HOST_SOURCES": "2", "B200NET_DISABLE_CMA": "1"}):
         _run([tests / "func_rma", so, 3],
              {"ASAN_OPTIONS": "detect_leaks=0", "FUNC_NET_DEVICE": "1", "LD_LIBRARY_PATH": fake, **extra})
-    for extra in ({"FAKE_CUDA_LAUNCH_DELAY_US": "200"}, {"FAKE_CUDA_FAIL_IPC_OPEN": "1"}):
+    for extra in ({"FAKE_CUDA_LAUNCH_DELAY_US": "200"}, {"FAKE_CUDA_FAIL_IPC_OPEN": "1"}, {"FAKE_CUDA_VMM": "1"}):
         for sc in ("device_transfer", "grouped_recv", "eager", "proxy_pattern"):
             _run([tests / "func_net", so, sc],
                  {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "2", "ASAN_OPTIONS": "detect_leaks=0",
