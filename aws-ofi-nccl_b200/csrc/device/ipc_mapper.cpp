@@ -104,6 +104,19 @@ std::shared_ptr<IpcMapJob> IpcMapper::submit(const uint8_t handle[64], cuda::Con
   return job;
 }
 
+int IpcMapper::open_now(const uint8_t handle[64], bool vmm, void** mapped, size_t* bytes) {
+  if (!vmm) {
+    *bytes = 0;
+    return cuda::ipc_open(handle, mapped);
+  }
+  IpcMapJob job;
+  memcpy(job.handle, handle, 64);
+  job.vmm = true;
+  const int rc = open_vmm(job, mapped);
+  *bytes = job.bytes;
+  return rc;
+}
+
 int IpcMapper::wait(const IpcMapJob& job, uint64_t wait_us) {
   int st = job.state.load(std::memory_order_acquire);
   if (st != 0 || wait_us == 0) return st;

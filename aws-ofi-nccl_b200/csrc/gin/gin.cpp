@@ -1,4 +1,5 @@
 #include "b200net/gin.h"
+#include "b200net/ipc_mapper.h"
 
 #include <unistd.h>
 
@@ -216,25 +217,43 @@ int CollComm::reg_mr_sym(void* data, size_t size, int type, uint64_t flags, Symm
     if (!vmm && cuda::ipc_get_handle(base, mine.ipc_handle) == 0) {
       mine.kind = static_cast<uint32_t>(MrKind::CUDA_IPC);
       mine.key = reinterpret_cast<uint64_t>(base);  // allocation base: offsets are taken from it
+    } else if (vmm && static_cast<char*>(base) + sz >= static_cast<char*>(data) + size &&
+               cuda::vmm_export_range(base, &m->export_fd) == 0) {
+      // memory of the virtual-memory API backed by one allocation: peers import it through a descriptor
+      static std::atomic<uint64_t> next_export{1};
+      VmmShare sh{VMM_SHARE_MAGIC, m->export_fd, static_cast<uint32_t>(getpid()), 0, sz, next_export.fetch_add(1)};
+      memcpy(mine.ipc_handle, &sh, sizeof(sh));
+      mine.kind = static_cast<uint32_t>(MrKind::CUDA_VMM);
+      mine.key = reinterpret_cast<uint64_t>(base);
     }
   }
   m->remote[rank] = mine;
   const int rc = all_gather(m->remote.data(), sizeof(RemoteMr));
   if (rc) {
+    if (m->export_fd >= 0) ::close(m->export_fd);
     delete m;
     return rc;
   }
   m->mapped.assign(static_cast<size_t>(nranks), nullptr);
+  m->mapped_bytes.assign(static_cast<size_t>(nranks), 0);
   if (type == NCCL_PTR_CUDA) {
     for (int r = 0; r < nranks; ++r) {
+      const uint32_t kind = m->remote[r].kind;
       if (r == rank) {
         m->mapped[r] = data;
-      } else if (m->remote[r].kind == static_cast<uint32_t>(MrKind::CUDA_IPC)) {
+      } else if (kind == static_cast<uint32_t>(MrKind::CUDA_IPC) || kind == static_cast<uint32_t>(MrKind::CUDA_VMM)) {
         void* p = nullptr;
-        if (cuda::ipc_open(m->remote[r].ipc_handle, &p) == 0)
+        if (IpcMapper::open_now(m->remote[r].ipc_handle, kind == static_cast<uint32_t>(MrKind::CUDA_VMM), &p, &m->mapped_bytes[r]) == 0)
           m->mapped[r] = static_cast<char*>(p) + (m->remote[r].addr - m->remote[r].key);
       }
     }
+  }
+  if (type == NCCL_PTR_CUDA) {
+    int direct = 0;
+    for (int r = 0; r < nranks; ++r) direct += (r != rank && m->mapped[r]) ? 1 : 0;
+    NET_INFO(NCCL_NET, "GIN registration of %zu bytes of device memory: %d of %d peers mapped directly (%s)", size, direct,
+             nranks - 1, mine.kind == static_cast<uint32_t>(MrKind::CUDA_VMM) ? "exported as a descriptor"
+                         : mine.kind == static_cast<uint32_t>(MrKind::CUDA_IPC) ? "legacy IPC handle" : "no handle: peers send fragments");
   }
   mrs_.push_back(m);
   B200NET_TRACE_EVENT(GinRegMr, dev, comm_id, 0, size, m);
@@ -254,7 +273,9 @@ int CollComm::dereg_mr_sym(SymmMr* mr) {
   if (mr->type == NCCL_PTR_CUDA)
     for (int r = 0; r < nranks; ++r)
       if (r != rank && mr->mapped[r])
-        cuda::ipc_close(static_cast<char*>(mr->mapped[r]) - (mr->remote[r].addr - mr->remote[r].key));
+        IpcMapper::close_now(static_cast<char*>(mr->mapped[r]) - (mr->remote[r].addr - mr->remote[r].key),
+                             mr->remote[r].kind == static_cast<uint32_t>(MrKind::CUDA_VMM), mr->mapped_bytes[r]);
+  if (mr->export_fd >= 0) ::close(mr->export_fd);
   if (mr->gpu_handle_block) cuda::mem_free(mr->gpu_handle_block);
   B200NET_TRACE_EVENT(GinDeregMr, dev, comm_id, 0, mr->size, mr);
   delete mr;

@@ -78,6 +78,8 @@ struct SymmMr {
   MrHandle* local = nullptr;
   std::vector<RemoteMr> remote;     // indexed by rank
   std::vector<void*> mapped;        // device registrations: peer bases mapped into this process
+  std::vector<size_t> mapped_bytes; // per peer: size of a virtual-memory-API mapping (0: legacy IPC)
+  int export_fd = -1;               // descriptor kept open for peers that import this registration
   void* gpu_handle_block = nullptr; // kernel-initiated mode: peer base pointers in GPU memory
   int refcnt = 1;
 };

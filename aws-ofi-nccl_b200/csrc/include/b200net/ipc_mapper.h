@@ -50,6 +50,10 @@ class IpcMapper {
   static IpcMapper& instance();
   // Queues the open. Never blocks on the device. nullptr if the helper thread could not start.
   std::shared_ptr<IpcMapJob> submit(const uint8_t handle[64], cuda::Context ctx, bool vmm = false);
+  // The same open on the calling thread, for set-up paths where waiting for the device is harmless
+  // (collective registration). 0 or a negative errno; *bytes is the mapping's size for close_now().
+  static int open_now(const uint8_t handle[64], bool vmm, void** mapped, size_t* bytes);
+  static int close_now(void* mapped, bool vmm, size_t bytes) { return vmm ? cuda::vmm_unmap(mapped, bytes) : cuda::ipc_close(mapped); }
   // Polls job->state for at most wait_us microseconds; returns the state seen last.
   static int wait(const IpcMapJob& job, uint64_t wait_us);
 };

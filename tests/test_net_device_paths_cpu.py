@@ -188,3 +188,21 @@ def test_buffers_of_the_virtual_memory_api_are_imported_through_a_descriptor(bui
     # buffers registered, released and replaced: descriptor numbers recur, mappings must not
     for _ in range(2):
         _run(built, {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "2", "FAKE_CUDA_VMM": "1"}, "proxy_pattern")
+
+
+@pytest.mark.parametrize("env,direct", [({}, True), ({"FAKE_CUDA_FAIL_VMM_IMPORT": "1"}, False),
+                                        ({"FUNC_RMA_HOST_SOURCES": "2", "B200NET_DISABLE_CMA": "1"}, True)],
+                         ids=["imported", "import-fails", "imported-mixed-staged"])
+def test_rma_windows_of_the_virtual_memory_api(built, env, direct):
+    """Symmetric registrations of cuMemCreate memory (what NCCL's windows are): every peer imports
+    the allocation through the exported descriptor at registration; when that fails, puts travel
+    as fragments and reads are served by the owner."""
+    fake = built / "tests" / "fake_cuda"
+    e = dict(os.environ, FUNC_NET_DEVICE="1", FUNC_NET_VERBOSE="1", FAKE_CUDA_VMM="1")
+    e["LD_LIBRARY_PATH"] = f"{fake}:" + e.get("LD_LIBRARY_PATH", "")
+    e.update(env)
+    res = subprocess.run([str(built / "tests" / "func_rma"), str(built / "libnccl-net-ofi-b200.so"), "3"],
+                         capture_output=True, text=True, timeout=300, env=e, cwd=built)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    assert "exported as a descriptor" in res.stderr
+    assert ("2 of 2 peers mapped directly" in res.stderr) == direct
