@@ -550,6 +550,24 @@ CUresult fake_cuda_mem_free(void* p) {
   fMemAddressFree(reinterpret_cast<CUdeviceptr>(p), vmm_size);
   return r;
 }
+// One address range backed by several allocations of the virtual-memory API (seg_bytes each, a
+// multiple of 64 KiB), the way an application may build a large window.
+CUresult fake_cuda_mem_alloc_segments(void** p, size_t seg_bytes, int nseg) {
+  CUdeviceptr va = 0;
+  if (seg_bytes % 65536 || nseg < 1 || fMemAddressReserve(&va, seg_bytes * nseg, 0, 0, 0) != CUDA_SUCCESS) return CUDA_ERROR_INVALID_VALUE;
+  for (int i = 0; i < nseg; ++i) {
+    CUmemGenericAllocationHandle h;
+    if (fMemCreate(&h, seg_bytes, nullptr, 0) != CUDA_SUCCESS || fMemMap(va + i * seg_bytes, seg_bytes, 0, h, 0) != CUDA_SUCCESS)
+      return CUDA_ERROR_OUT_OF_MEMORY;
+    fMemRelease(h);
+  }
+  *p = reinterpret_cast<void*>(va);
+  return CUDA_SUCCESS;
+}
+CUresult fake_cuda_mem_free_segments(void* p, size_t seg_bytes, int nseg) {
+  for (int i = 0; i < nseg; ++i) fMemUnmap(reinterpret_cast<CUdeviceptr>(p) + i * seg_bytes, seg_bytes);
+  return fMemAddressFree(reinterpret_cast<CUdeviceptr>(p), seg_bytes * nseg);
+}
 // How many peer allocations are mapped into this process right now (opened and not yet closed).
 int fake_cuda_live_peer_mappings() {
   std::lock_guard<std::mutex> g(g_mu);

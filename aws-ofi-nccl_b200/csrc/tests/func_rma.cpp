@@ -139,22 +139,51 @@ static int run_rank(const char* so) {
   // iget fills stays on the device, so a read of host memory lands in device memory)
   const bool host_targets = getenv("FUNC_RMA_HOST_TARGETS") && atoi(getenv("FUNC_RMA_HOST_TARGETS"));
   const bool host_sources = getenv("FUNC_RMA_HOST_SOURCES") && atoi(getenv("FUNC_RMA_HOST_SOURCES"));
+  // FUNC_RMA_MULTISEG=1 (stand-in driver only): the signal words live in one address range backed by
+  // two separate allocations, and ranks signal into different ones
+  const size_t SEG = 65536;
+  const bool multiseg = device_mode_kind() == BUF_VIEW && getenv("FUNC_RMA_MULTISEG") && atoi(getenv("FUNC_RMA_MULTISEG"));
+  using SegAlloc = int (*)(void**, size_t, int);
+  using SegFree = int (*)(void*, size_t, int);
+  SegAlloc seg_alloc = nullptr;
+  SegFree seg_free = nullptr;
+  if (multiseg) {
+    void* drv = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+    seg_alloc = drv ? reinterpret_cast<SegAlloc>(dlsym(drv, "fake_cuda_mem_alloc_segments")) : nullptr;
+    seg_free = drv ? reinterpret_cast<SegFree>(dlsym(drv, "fake_cuda_mem_free_segments")) : nullptr;
+    if (!seg_alloc || !seg_free) FAIL("the stand-in driver offers no segmented allocation");
+  }
+  auto sig_off = [&](int r) -> uint64_t { return multiseg ? (r % 2) * SEG + static_cast<uint64_t>(r) * 8 : static_cast<uint64_t>(r) * 8; };
+  const size_t sig_bytes = multiseg ? 2 * SEG : 16 * 8;
   if (buf_alloc(&window_b, SLOT * g_n, !host_targets) || buf_alloc(&src_b, SLOT, !host_sources) ||
-      buf_alloc(&got_b, SLOT, !host_sources || atoi(getenv("FUNC_RMA_HOST_SOURCES")) == 2) || buf_alloc(&signals_b, 16 * 8, !host_targets))
+      buf_alloc(&got_b, SLOT, !host_sources || atoi(getenv("FUNC_RMA_HOST_SOURCES")) == 2))
     FAIL("buffer allocation failed");
+  if (multiseg) {
+    void* p = nullptr;
+    if (seg_alloc(&p, SEG, 2) != 0) FAIL("segmented allocation failed");
+    signals_b.p = static_cast<uint8_t*>(p);
+    signals_b.h = nullptr;   // two separate views: looked up per word below
+    signals_b.n = sig_bytes;
+    signals_b.dev = true;
+  } else if (buf_alloc(&signals_b, sig_bytes, !host_targets)) {
+    FAIL("buffer allocation failed");
+  }
+  auto sig_word = [&](int r) -> uint64_t* {
+    return multiseg ? static_cast<uint64_t*>(g_dev_view(signals_b.data() + sig_off(r)))
+                    : reinterpret_cast<uint64_t*>(signals_b.host() + sig_off(r));
+  };
   // window / src / got / signals: where this test reads and writes; the *_b.data() addresses are
   // what the plugin gets (the same in host mode, inaccessible to host code in device mode)
   uint8_t *window = window_b.host(), *src = src_b.host(), *got = got_b.host();
-  uint64_t* signals = reinterpret_cast<uint64_t*>(signals_b.host());
   memset(window, 0, SLOT * g_n);
   memset(got, 0, SLOT);
-  memset(signals, 0, 16 * 8);
+  for (int r = 0; r < 16; ++r) *sig_word(r) = 0;
   for (size_t i = 0; i < SLOT; ++i) src[i] = static_cast<uint8_t>(i * 7 + g_rank);
-  if (window_b.to_device() || src_b.to_device() || got_b.to_device() || signals_b.to_device()) FAIL("copy to the device failed");
+  if (window_b.to_device() || src_b.to_device() || got_b.to_device() || (!multiseg && signals_b.to_device())) FAIL("copy to the device failed");
   void *win_mh, *src_mh, *sig_mh, *got_mh;
   OK(rma->regMrSym(coll, window_b.data(), SLOT * g_n, buf_type(window_b), 0, &win_mh));
   OK(rma->regMrSym(coll, src_b.data(), SLOT, buf_type(src_b), 0, &src_mh));
-  OK(rma->regMrSym(coll, signals_b.data(), 16 * 8, buf_type(signals_b), NCCL_NET_MR_FLAG_SIGNAL_NEVER_RESET, &sig_mh));
+  OK(rma->regMrSym(coll, signals_b.data(), sig_bytes, buf_type(signals_b), NCCL_NET_MR_FLAG_SIGNAL_NEVER_RESET, &sig_mh));
   OK(rma->regMrSym(coll, got_b.data(), SLOT, buf_type(got_b), 0, &got_mh));
 
   // duplicate registration: same handle, and it survives one dereg
@@ -173,7 +202,7 @@ static int run_rank(const char* so) {
         if (i % 2 == 0)
           OK(rma->iput(ctx, 0, (i % 16) * 256, src_mh, 256, g_rank * SLOT + (i % 16) * 256, win_mh, p, 0, &req));
         else
-          OK(rma->iputSignal(ctx, 0, (i % 16) * 256, src_mh, 256, g_rank * SLOT + (i % 16) * 256, win_mh, p, g_rank * 8,
+          OK(rma->iputSignal(ctx, 0, (i % 16) * 256, src_mh, 256, g_rank * SLOT + (i % 16) * 256, win_mh, p, sig_off(g_rank),
                              sig_mh, 1, NCCL_NET_SIGNAL_OP_INC, false, 0, &req));
         OK(rma->rmaProgress(ctx));
         if (expired(t0)) FAIL("iput kept returning no request");
@@ -181,7 +210,7 @@ static int run_rank(const char* so) {
       if (wait_req(rma, coll, ctx, req)) return 1;
     }
     void* req = nullptr;
-    OK(rma->iputSignal(ctx, 0, 0, src_mh, 0, 0, win_mh, p, g_rank * 8, sig_mh, 1000, NCCL_NET_SIGNAL_OP_ADD, true,
+    OK(rma->iputSignal(ctx, 0, 0, src_mh, 0, 0, win_mh, p, sig_off(g_rank), sig_mh, 1000, NCCL_NET_SIGNAL_OP_ADD, true,
                        ncclRmaOptFlagsAggregateRequests, &req));
     if (!req) FAIL("signal-only put returned no request");
     if (wait_req(rma, coll, ctx, req)) return 1;
@@ -191,13 +220,13 @@ static int run_rank(const char* so) {
     const auto t0 = Clock::now();
     for (;;) {
       OK(rma->rmaProgress(ctx));
-      if (signals_b.from_device()) FAIL("copy from the device failed");
+      if (!multiseg && signals_b.from_device()) FAIL("copy from the device failed");
       bool all = true;
       for (int p = 0; p < g_n; ++p)
-        if (p != g_rank && __atomic_load_n(&signals[p], __ATOMIC_ACQUIRE) != 1064) all = false;
+        if (p != g_rank && __atomic_load_n(sig_word(p), __ATOMIC_ACQUIRE) != 1064) all = false;
       if (all) break;
-      if (expired(t0)) FAIL("signals did not reach 1064: %llu %llu %llu", (unsigned long long)signals[0],
-                            (unsigned long long)signals[1], (unsigned long long)signals[2]);
+      if (expired(t0)) FAIL("signals did not reach 1064: %llu %llu %llu", (unsigned long long)*sig_word(0),
+                            (unsigned long long)*sig_word(1), (unsigned long long)*sig_word(2));
     }
     if (window_b.from_device()) FAIL("copy from the device failed");
     for (int p = 0; p < g_n; ++p) {
@@ -268,7 +297,8 @@ static int run_rank(const char* so) {
   buf_free(&window_b);
   buf_free(&src_b);
   buf_free(&got_b);
-  buf_free(&signals_b);
+  if (multiseg) seg_free(signals_b.data(), SEG, 2);
+  else buf_free(&signals_b);
   OK(rma->destroyContext(ctx));
   OK(rma->closeColl(coll));
   OK(rma->closeListen(lcomm));

@@ -206,3 +206,17 @@ def test_rma_windows_of_the_virtual_memory_api(built, env, direct):
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     assert "exported as a descriptor" in res.stderr
     assert ("2 of 2 peers mapped directly" in res.stderr) == direct
+
+
+@pytest.mark.parametrize("vmm", ["0", "1"])
+def test_signal_words_in_a_range_backed_by_several_allocations(built, vmm):
+    """One address range, two cuMemCreate allocations behind it, ranks signalling into different
+    ones (the reference's rma_multiseg_signal): no single handle covers the registration, so it is
+    published without one and signals still land, applied by their owner."""
+    fake = built / "tests" / "fake_cuda"
+    e = dict(os.environ, FUNC_NET_DEVICE="1", FUNC_NET_VERBOSE="1", FUNC_RMA_MULTISEG="1", FAKE_CUDA_VMM=vmm)
+    e["LD_LIBRARY_PATH"] = f"{fake}:" + e.get("LD_LIBRARY_PATH", "")
+    res = subprocess.run([str(built / "tests" / "func_rma"), str(built / "libnccl-net-ofi-b200.so"), "4"],
+                         capture_output=True, text=True, timeout=300, env=e, cwd=built)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    assert "131072 bytes of device memory: 0 of 3 peers mapped directly" in res.stderr
