@@ -53,7 +53,8 @@ def test_address_and_undefined_behaviour():
     from aws_ofi_nccl_b200 import build
     build.build_fake_cuda()
     fake = f"{build.LIB / 'tests' / 'fake_cuda'}:" + os.environ.get("LD_LIBRARY_PATH", "")
-    for extra in ({}, {"FUNC_RMA_HOST_TARGETS": "1"}, {"FUNC_RMA_HOST_SOURCES": "2", "B200NET_DISABLE_CMA": "1"}):
+    for extra in ({}, {"FUNC_RMA_HOST_TARGETS": "1"}, {"FUNC_RMA_HOST_SOURCES": "2", "B200NET_DISABLE_CMA": "1"},
+                  {"FAKE_CUDA_VMM": "1"}, {"FAKE_CUDA_FAIL_IPC_GET": "1"}, {"FUNC_RMA_MULTISEG": "1"}):
         _run([tests / "func_rma", so, 3],
              {"ASAN_OPTIONS": "detect_leaks=0", "FUNC_NET_DEVICE": "1", "LD_LIBRARY_PATH": fake, **extra})
     for extra in ({"FAKE_CUDA_LAUNCH_DELAY_US": "200"}, {"FAKE_CUDA_FAIL_IPC_OPEN": "1"}, {"FAKE_CUDA_VMM": "1"}):
