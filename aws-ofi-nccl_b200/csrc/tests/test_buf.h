@@ -10,6 +10,7 @@
 //   mirror  a real driver (a GPU box), or the stand-in with FUNC_NET_MIRROR=1: data() is device
 //           memory, host() a separate host copy; to_device() pushes the host copy before the
 //           plugin is given the buffer, from_device() fetches it before the test checks it.
+//           FUNC_NET_VMM=1 makes the device memory a cuMemCreate allocation (as NCCL's buffers are).
 // A test written against host() + to_device() + from_device() runs unchanged in all three.
 #pragma once
 #include <dlfcn.h>
@@ -64,6 +65,8 @@ struct TestBuf {
   size_t n = 0;
   bool dev = false;
   bool mirror = false;
+  size_t vmm_rounded = 0;     // mirror mode with FUNC_NET_VMM=1: the buffer is a cuMemCreate allocation
+  uint64_t vmm_handle = 0;
   uint8_t* data() { return p; }
   uint8_t* host() { return h; }
   size_t size() const { return n; }
@@ -95,7 +98,15 @@ static int buf_alloc(TestBuf* b, size_t n, bool want_device = true) {
     b->h = static_cast<uint8_t*>(g_dev_view(p));
   } else if (kind == BUF_MIRROR) {
     void* p = nullptr;
-    if (b200net::cuda::mem_alloc(&p, n) != 0) return 1;
+    if (getenv("FUNC_NET_VMM") && atoi(getenv("FUNC_NET_VMM"))) {
+      // the way NCCL allocates its own buffers: create, reserve, map (exportable as a descriptor)
+      const int count = b200net::cuda::device_count();
+      const char* pick = getenv("FUNC_NET_GPU");
+      const int ordinal = pick ? atoi(pick) : (count > 0 ? g_rank % count : 0);
+      if (b200net::cuda::vmm_alloc(ordinal, n, &p, &b->vmm_rounded, &b->vmm_handle) != 0) return 1;
+    } else if (b200net::cuda::mem_alloc(&p, n) != 0) {
+      return 1;
+    }
     b->p = static_cast<uint8_t*>(p);
     b->h = static_cast<uint8_t*>(calloc(1, n));
     if (!b->h) return 1;
@@ -107,7 +118,9 @@ static int buf_alloc(TestBuf* b, size_t n, bool want_device = true) {
 static void buf_free(TestBuf* b) {
   if (!b->p) return;
   if (b->mirror) {
-    b200net::cuda::mem_free(b->p);
+    if (b->vmm_rounded) b200net::cuda::vmm_free(b->p, b->vmm_rounded, b->vmm_handle);
+    else b200net::cuda::mem_free(b->p);
+    b->vmm_rounded = 0;
     free(b->h);
   } else if (b->dev) {
     g_dev_free(b->p);

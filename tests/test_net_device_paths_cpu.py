@@ -161,6 +161,9 @@ def test_mirror_mode_of_the_test_buffers(built, proto):
     _run(built, {"B200NET_PROTOCOL": proto, "B200NET_FORCE_NUM_RAILS": "4", "FUNC_NET_MIRROR": "1",
                  "FAKE_CUDA_LAUNCH_DELAY_US": "100"}, "device_transfer")
     _run(built, {"B200NET_PROTOCOL": proto, "B200NET_FORCE_NUM_RAILS": "4", "FUNC_NET_MIRROR": "1"}, "proxy_pattern")
+    # the same with buffers made through the plugin's own cuMemCreate wrapper (FUNC_NET_VMM=1 on a GPU box)
+    _run(built, {"B200NET_PROTOCOL": proto, "B200NET_FORCE_NUM_RAILS": "4", "FUNC_NET_MIRROR": "1", "FUNC_NET_VMM": "1"},
+         "device_transfer")
     fake = built / "tests" / "fake_cuda"
     e = dict(os.environ, FUNC_NET_DEVICE="1", FUNC_NET_MIRROR="1", B200NET_PROTOCOL=proto)
     e["LD_LIBRARY_PATH"] = f"{fake}:" + e.get("LD_LIBRARY_PATH", "")
