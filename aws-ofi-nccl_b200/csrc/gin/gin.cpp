@@ -10,6 +10,7 @@
 #include "b200net/api.h"
 #include "b200net/log.h"
 #include "b200net/param.h"
+#include "b200net/plugin_stats.h"
 #include "b200net/tracepoint.h"
 
 namespace b200net::gin {
@@ -313,6 +314,7 @@ int CollComm::apply_signal(const MetadataMsg& m) {
     __atomic_fetch_add(reinterpret_cast<uint64_t*>(m.signal_addr), add, __ATOMIC_RELEASE);
   }
   B200NET_TRACE_EVENT(GinSignalDeliver, dev, comm_id, static_cast<uint32_t>(m.seq), add, this);
+  PluginStats::bump(PluginStats::get().gin_signals_applied);
   return 0;
 }
 
@@ -355,6 +357,7 @@ void CollComm::handle_dgram(const DgramHdr& h, const void* payload) {
     const auto* r = static_cast<const ReadReqMsg*>(payload);
     if (r->comm_id != comm_id || r->src_rank >= static_cast<uint32_t>(nranks)) return;
     read_services_.push_back(ReadService{*r, 0, false, {}});
+    PluginStats::bump(PluginStats::get().gin_reads_served);
   } else if (h.type == static_cast<uint16_t>(DgramType::READ_RESP)) {
     const auto* r = static_cast<const ReadRespMsg*>(payload);
     auto it = reads_in_flight_.find(r->req_id);
@@ -536,6 +539,11 @@ int CollComm::iput(uint64_t src_off, SymmMr* src, size_t size, uint64_t dst_off,
   if (size) {
     const char* lsrc = static_cast<const char*>(src->base) + src_off;
     const RemoteMr& rm = dst->remote[peer_rank];
+    PluginStats& st_ = PluginStats::get();
+    PluginStats::bump(rm.kind == static_cast<uint32_t>(MrKind::HOST) ? st_.gin_bytes_host
+                      : dst->mapped[peer_rank]                        ? st_.gin_bytes_direct
+                                                                      : st_.gin_bytes_fragments,
+                      size);
     if (rm.kind == static_cast<uint32_t>(MrKind::HOST)) {
       if (src->type == NCCL_PTR_CUDA) {
         // the host write path reads its source with the CPU: fetch the device bytes first
@@ -571,6 +579,7 @@ int CollComm::iput(uint64_t src_off, SymmMr* src, size_t size, uint64_t dst_off,
       op.dev_frags = true;
     }
   }
+  PluginStats::bump(PluginStats::get().gin_puts);
   auto status = op.status;
   p.ops.push_back(std::move(op));
   retire(p, peer_rank);
@@ -586,6 +595,7 @@ int CollComm::iget(uint64_t remote_off, SymmMr* remote, size_t size, uint64_t lo
   if (remote_off + size > remote->remote[peer_rank].size || local_off + size > local->size) return -EINVAL;
   progress();
   B200NET_TRACE_EVENT(GinGetBegin, dev, comm_id, 0, size, nullptr);
+  PluginStats::bump(PluginStats::get().gin_gets);
   auto status = std::make_shared<std::atomic<int>>(0);
   char* ldst = static_cast<char*>(local->base) + local_off;
   const RemoteMr& rm = remote->remote[peer_rank];

@@ -24,6 +24,9 @@ struct PluginStats {
   Counter flushes{0}, requests_failed{0};
   Counter ipc_maps{0}, ipc_map_failures{0}, ipc_map_deferred{0};
   Counter connects{0}, accepts{0}, endpoints_aborted{0};
+  // GIN / RMA: operations and where their payload went
+  Counter gin_puts{0}, gin_gets{0}, gin_signals_applied{0};
+  Counter gin_bytes_direct{0}, gin_bytes_host{0}, gin_bytes_fragments{0}, gin_reads_served{0};
 
   static PluginStats& get();
   static void bump(Counter& c, uint64_t n = 1) { c.fetch_add(n, std::memory_order_relaxed); }

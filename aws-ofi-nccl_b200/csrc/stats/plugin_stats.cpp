@@ -53,6 +53,13 @@ const Named kCounters[] = {
     {"connects", &PluginStats::connects},
     {"accepts", &PluginStats::accepts},
     {"endpoints_aborted", &PluginStats::endpoints_aborted},
+    {"gin_puts", &PluginStats::gin_puts},
+    {"gin_gets", &PluginStats::gin_gets},
+    {"gin_signals_applied", &PluginStats::gin_signals_applied},
+    {"gin_bytes_direct", &PluginStats::gin_bytes_direct},
+    {"gin_bytes_host_writes", &PluginStats::gin_bytes_host},
+    {"gin_bytes_fragments", &PluginStats::gin_bytes_fragments},
+    {"gin_reads_served", &PluginStats::gin_reads_served},
 };
 
 }  // namespace
@@ -128,6 +135,14 @@ void PluginStats::report() const {
              static_cast<unsigned long long>(recv_bytes.load()), static_cast<unsigned long long>(bytes_kernel.load()),
              static_cast<unsigned long long>(bytes_copy_engine.load()), static_cast<unsigned long long>(bytes_staged.load()),
              static_cast<unsigned long long>(bytes_host.load()), static_cast<unsigned long long>(bytes_eager.load()));
+  if (gin_puts.load() | gin_gets.load())
+    NET_INFO(NCCL_NET,
+             "GIN totals: %llu puts, %llu gets, %llu signals applied; put payload: %llu bytes direct to device windows, %llu "
+             "host writes, %llu as fragments; %llu reads served for peers",
+             static_cast<unsigned long long>(gin_puts.load()), static_cast<unsigned long long>(gin_gets.load()),
+             static_cast<unsigned long long>(gin_signals_applied.load()), static_cast<unsigned long long>(gin_bytes_direct.load()),
+             static_cast<unsigned long long>(gin_bytes_host.load()), static_cast<unsigned long long>(gin_bytes_fragments.load()),
+             static_cast<unsigned long long>(gin_reads_served.load()));
   std::string path = params().stats_file.get();
   if (path.empty()) return;
   const size_t at = path.find("%p");

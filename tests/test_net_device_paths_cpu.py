@@ -196,12 +196,13 @@ def test_buffers_of_the_virtual_memory_api_are_imported_through_a_descriptor(bui
 @pytest.mark.parametrize("env,direct", [({}, True), ({"FAKE_CUDA_FAIL_VMM_IMPORT": "1"}, False),
                                         ({"FUNC_RMA_HOST_SOURCES": "2", "B200NET_DISABLE_CMA": "1"}, True)],
                          ids=["imported", "import-fails", "imported-mixed-staged"])
-def test_rma_windows_of_the_virtual_memory_api(built, env, direct):
+def test_rma_windows_of_the_virtual_memory_api(built, tmp_path, env, direct):
     """Symmetric registrations of cuMemCreate memory (what NCCL's windows are): every peer imports
     the allocation through the exported descriptor at registration; when that fails, puts travel
     as fragments and reads are served by the owner."""
     fake = built / "tests" / "fake_cuda"
-    e = dict(os.environ, FUNC_NET_DEVICE="1", FUNC_NET_VERBOSE="1", FAKE_CUDA_VMM="1")
+    e = dict(os.environ, FUNC_NET_DEVICE="1", FUNC_NET_VERBOSE="1", FAKE_CUDA_VMM="1",
+             B200NET_STATS_FILE=str(tmp_path / "stats.%p.json"))
     e["LD_LIBRARY_PATH"] = f"{fake}:" + e.get("LD_LIBRARY_PATH", "")
     e.update(env)
     res = subprocess.run([str(built / "tests" / "func_rma"), str(built / "libnccl-net-ofi-b200.so"), "3"],
@@ -209,6 +210,13 @@ def test_rma_windows_of_the_virtual_memory_api(built, env, direct):
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     assert "exported as a descriptor" in res.stderr
     assert ("2 of 2 peers mapped directly" in res.stderr) == direct
+    # the counters say the same: payload for device windows went direct, or as fragments
+    import json
+    stats = [json.loads(f.read_text())["counters"] for f in sorted(tmp_path.glob("stats.*.json"))]
+    assert len(stats) == 3
+    for c in stats:
+        assert c["gin_puts"] == 2 * 129 and c["gin_gets"] == 1 and c["gin_signals_applied"] == 2 * 65, c
+        assert (c["gin_bytes_direct"] > 0) == direct and (c["gin_bytes_fragments"] > 0) == (not direct), c
 
 
 @pytest.mark.parametrize("vmm", ["0", "1"])
