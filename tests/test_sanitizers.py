@@ -81,3 +81,7 @@ def test_thread_sanitizer():
     _run([tests / "func_net", so, "proxy_pattern"],
          {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "2", "FUNC_NET_DEVICE": "1", "LD_LIBRARY_PATH": fake,
           "FAKE_CUDA_IPC_OPEN_DELAY_MS": "20", "B200NET_IPC_MAP_WAIT_US": "100", "FAKE_CUDA_LAUNCH_DELAY_US": "100"})
+    # GIN / RMA: the proxy thread, the device-signal worker and (for served reads) the peers' requests
+    _run([tests / "func_rma", so, 3])
+    for extra in ({}, {"FAKE_CUDA_VMM": "1"}, {"FUNC_RMA_HOST_SOURCES": "2", "B200NET_DISABLE_CMA": "1"}):
+        _run([tests / "func_rma", so, 3], {"FUNC_NET_DEVICE": "1", "LD_LIBRARY_PATH": fake, **extra})
