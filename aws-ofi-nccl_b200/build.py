@@ -187,15 +187,18 @@ def build_tests(force: bool = False, sanitize: str | None = None) -> list[Path]:
     return outs
 
 
-def build_fake_cuda(force: bool = False) -> Path:
-    """The stand-in driver for CPU tests of the device-buffer paths: lib/tests/fake_cuda/libcuda.so.1."""
+def build_fake_cuda(force: bool = False, sanitize: str | None = None) -> Path:
+    """The stand-in driver for CPU tests of the device-buffer paths: lib/tests/fake_cuda/libcuda.so.1
+    (with `sanitize`, an instrumented copy under build/san, so that a race detector sees the
+    release / acquire pairs between its "kernels" and the plugin)."""
     src = CSRC / "tests" / "fake_cuda" / "fake_libcuda.cpp"
-    outdir = LIB / "tests" / "fake_cuda"
+    outdir = LIB / "tests" / "fake_cuda" if not sanitize else OBJ / "san" / f"fake_cuda-{sanitize}"
     outdir.mkdir(parents=True, exist_ok=True)
     out = outdir / "libcuda.so.1"
     if force or _stale(out, [src]):
-        _run([CXX, "-std=c++20", "-O1", "-g", "-fPIC", "-shared", "-I", f"{CUDA_HOME}/include", str(src), "-o", str(out),
-              "-pthread", "-lrt"])
+        extra = [f"-fsanitize={sanitize}", "-fno-omit-frame-pointer"] if sanitize else []
+        _run([SAN_CXX if sanitize else CXX, "-std=c++20", "-O1", "-g", "-fPIC", "-shared", *extra, "-I", f"{CUDA_HOME}/include",
+              str(src), "-o", str(out), "-pthread", "-lrt"])
     return out
 
 

@@ -75,12 +75,18 @@ def test_thread_sanitizer():
     _run([tests / "func_net", so, "proxy_pattern"], {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "4",
                                                       "B200NET_HOST_COPY_THREADS": "4"})
     # the helper thread that maps peers' device memory hands its result to the proxy thread
+    # (against a copy of the stand-in driver built with the same instrumentation, so that the
+    # release / acquire pairs between its "kernels" and the plugin are visible to the detector)
     from aws_ofi_nccl_b200 import build
-    build.build_fake_cuda()
-    fake = f"{build.LIB / 'tests' / 'fake_cuda'}:" + os.environ.get("LD_LIBRARY_PATH", "")
+    fake = f"{build.build_fake_cuda(sanitize='thread').parent}:" + os.environ.get("LD_LIBRARY_PATH", "")
     _run([tests / "func_net", so, "proxy_pattern"],
          {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "2", "FUNC_NET_DEVICE": "1", "LD_LIBRARY_PATH": fake,
           "FAKE_CUDA_IPC_OPEN_DELAY_MS": "20", "B200NET_IPC_MAP_WAIT_US": "100", "FAKE_CUDA_LAUNCH_DELAY_US": "100"})
+    # device payloads with "kernels" that finish on another thread: completion words, eager slots
+    for sc in ("device_transfer", "eager_multirecv"):
+        _run([tests / "func_net", so, sc],
+             {"B200NET_PROTOCOL": "RDMA", "B200NET_FORCE_NUM_RAILS": "2", "FUNC_NET_DEVICE": "1", "LD_LIBRARY_PATH": fake,
+              "FAKE_CUDA_LAUNCH_DELAY_US": "100"})
     # GIN / RMA: the proxy thread, the device-signal worker and (for served reads) the peers' requests
     _run([tests / "func_rma", so, 3])
     for extra in ({}, {"FAKE_CUDA_VMM": "1"}, {"FUNC_RMA_HOST_SOURCES": "2", "B200NET_DISABLE_CMA": "1"}):
