@@ -30,6 +30,10 @@ DeviceSignalWorker::~DeviceSignalWorker() {
   if (thread_.joinable()) thread_.join();
 }
 bool DeviceSignalWorker::submit(const SignalWork& w) {
+  if (!ctx_.load(std::memory_order_acquire)) {
+    cuda::Context cur = nullptr;
+    if (cuda::ctx_get_current(&cur) == 0 && cur) ctx_.store(cur, std::memory_order_release);
+  }
   if (!ring_.push(w)) return false;
   submitted_.fetch_add(1);
   return true;
@@ -55,7 +59,8 @@ void DeviceSignalWorker::run() {
     }
     idle = 0;
     if (!stream_) {
-      cuda::ensure_primary_ctx(0);
+      if (void* ctx = ctx_.load(std::memory_order_acquire)) cuda::ctx_set_current(ctx);
+      else cuda::ensure_primary_ctx(0);
       cuda::stream_create(&stream_);
     }
     for (auto& [addr, add] : batch) {

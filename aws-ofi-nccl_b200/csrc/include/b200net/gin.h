@@ -143,6 +143,10 @@ class DeviceSignalWorker {
   std::atomic<uint64_t> submitted_{0}, completed_{0};
   std::map<uint64_t, uint64_t> shadow_;
   cuda::Stream stream_ = nullptr;
+  // the context of the first caller that submitted work: the worker issues its copies in it (the
+  // reference's worker likewise runs in the context captured when the communicator was made,
+  // src/rdma/gin/nccl_ofi_gin.cpp:39-104)
+  std::atomic<void*> ctx_{nullptr};
 };
 
 struct GinContext {
