@@ -1,10 +1,17 @@
 // Functional test of the net plugin through its public ABI only (dlopen + ncclNetPlugin_v11), two
-// processes on one host, host buffers. Scenarios: connection set-up on every device (1 and 4
+// processes on one host, host or device buffers. Scenarios: connection set-up on every device (1 and 4
 // threads), message transfer over a table of (send, recv) sizes incl. truncation with 32 requests
 // in flight, the 8 B - 4 MiB ping-pong with tags 0-7 and 8 concurrent requests, grouped receives,
 // eager early/late receives, many connections on one listen communicator, close with requests in
-// flight. Every poll loop has a 20 s deadline; ranks report through exit codes.
+// flight, a bandwidth sweep, NCCL's proxy pattern (many channels, one driving thread), transfers
+// of device payloads, and the table of eager / grouped-receive orderings. Every poll loop has a
+// 20 s deadline; ranks report through exit codes.
 // usage: func_net [plugin.so] [scenario]      env: B200NET_* / OFI_NCCL_* parameters apply
+//   FUNC_NET_DEVICE=1  payload buffers of the device scenarios (and of proxy_pattern) live in device
+//                      memory: on a GPU box through the driver (FUNC_NET_VMM=1 for cuMemCreate
+//                      allocations, FUNC_NET_GPU=n to pin the GPU), on a CPU box through the
+//                      stand-in driver when it is on the library path (see test_buf.h)
+//   FUNC_NET_VERBOSE=1 pass the plugin's INFO lines through
 #include <deque>
 #include <map>
 #include <set>
