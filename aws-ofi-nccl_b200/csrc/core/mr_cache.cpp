@@ -32,7 +32,8 @@ void* MrCache::lookup(const MrCacheKey& key) {
                              [](uintptr_t v, const Entry& e) { return v < e.addr; });
   while (it != entries_.begin()) {
     --it;
-    const bool contains = it->addr <= base && base + pages * page_size_ <= it->addr + it->pages * page_size_;
+    const bool contains = key.exact ? (it->exact && it->raw_addr == key.addr && it->raw_len == key.len)
+                                    : (!it->exact && it->addr <= base && base + pages * page_size_ <= it->addr + it->pages * page_size_);
     const bool same_owner = it->ep == key.ep && it->kind == key.kind && (key.kind == MrKeyKind::IOVEC || it->fd == key.fd);
     if (contains && same_owner) {
       ++it->refcnt;
@@ -52,9 +53,10 @@ int MrCache::insert(const MrCacheKey& key, void* handle) {
   auto it = std::lower_bound(entries_.begin(), entries_.end(), base,
                              [](const Entry& e, uintptr_t v) { return e.addr < v; });
   for (auto j = it; j != entries_.end() && j->addr == base; ++j) {
-    if (j->pages == pages && j->ep == key.ep && j->kind == key.kind && j->fd == key.fd) return -EEXIST;
+    const bool same_range = key.exact ? (j->exact && j->raw_addr == key.addr && j->raw_len == key.len) : (!j->exact && j->pages == pages);
+    if (same_range && j->ep == key.ep && j->kind == key.kind && j->fd == key.fd) return -EEXIST;
   }
-  entries_.insert(it, Entry{base, pages, 1, handle, key.ep, key.kind, key.fd});
+  entries_.insert(it, Entry{base, pages, 1, handle, key.ep, key.kind, key.fd, key.exact, key.addr, key.len});
   return 0;
 }
 

@@ -47,6 +47,9 @@ struct Api {
                            void**, void**) = nullptr;
   CUresult (*MemHostAlloc)(void**, size_t, unsigned) = nullptr;
   CUresult (*MemFreeHost)(void*) = nullptr;
+  CUresult (*MemHostRegister)(void*, size_t, unsigned) = nullptr;
+  CUresult (*MemHostUnregister)(void*) = nullptr;
+  CUresult (*CtxSynchronize)() = nullptr;
   CUresult (*MemAlloc)(CUdeviceptr*, size_t) = nullptr;
   CUresult (*MemFree)(CUdeviceptr) = nullptr;
   CUresult (*MemsetD8)(CUdeviceptr, unsigned char, size_t) = nullptr;
@@ -119,6 +122,9 @@ void do_init() {
   sym(g.LaunchKernel, "cuLaunchKernel", false);
   sym(g.MemHostAlloc, "cuMemHostAlloc", false);
   sym(g.MemFreeHost, "cuMemFreeHost", false);
+  sym(g.MemHostRegister, "cuMemHostRegister", false);
+  sym(g.MemHostUnregister, "cuMemHostUnregister", false);
+  sym(g.CtxSynchronize, "cuCtxSynchronize", false);
   ok &= sym(g.MemAlloc, "cuMemAlloc");
   ok &= sym(g.MemFree, "cuMemFree");
   ok &= sym(g.MemsetD8, "cuMemsetD8");
@@ -277,6 +283,11 @@ int host_alloc(void** ptr, size_t bytes) {
   return rc_of(g.MemHostAlloc(ptr, bytes, CU_MEMHOSTALLOC_PORTABLE | CU_MEMHOSTALLOC_DEVICEMAP));
 }
 int host_free(void* ptr) { return (available() && g.MemFreeHost) ? rc_of(g.MemFreeHost(ptr)) : -ENOSYS; }
+int host_register(void* ptr, size_t bytes) {
+  if (!available() || !g.MemHostRegister) return -ENOSYS;
+  return rc_of(g.MemHostRegister(ptr, bytes, CU_MEMHOSTREGISTER_PORTABLE));
+}
+int host_unregister(void* ptr) { return (available() && g.MemHostUnregister) ? rc_of(g.MemHostUnregister(ptr)) : -ENOSYS; }
 
 int memcpy_async(void* dst, const void* src, size_t n, Stream s) {
   if (!available()) return -ENOSYS;
@@ -289,6 +300,9 @@ int mem_alloc(void** ptr, size_t bytes) {
   CUresult r = g.MemAlloc(&p, bytes);
   if (r != CUDA_SUCCESS) return rc_of(r);
   r = g.MemsetD8(p, 0, bytes);
+  // The fill runs on the legacy default stream and may still be in flight when the call returns;
+  // the callers go on to use the memory on non-blocking streams, which do not wait for that stream.
+  if (r == CUDA_SUCCESS && g.CtxSynchronize) r = g.CtxSynchronize();
   if (r != CUDA_SUCCESS) {
     g.MemFree(p);
     return rc_of(r);

@@ -7,7 +7,9 @@
 #include <chrono>
 #include <condition_variable>
 #include <cstring>
+#include <array>
 #include <deque>
+#include <map>
 #include <mutex>
 #include <thread>
 
@@ -104,10 +106,35 @@ std::shared_ptr<IpcMapJob> IpcMapper::submit(const uint8_t handle[64], cuda::Con
   return job;
 }
 
+// Legacy handles opened on the calling thread, shared by everything in this process that names the
+// same allocation: the driver does not promise that one handle can be opened twice.
+namespace {
+struct NowOpen {
+  void* mapped;
+  int refs;
+};
+std::mutex g_now_mu;
+std::map<std::array<uint8_t, 64>, NowOpen>& now_open() {
+  static auto* m = new std::map<std::array<uint8_t, 64>, NowOpen>;
+  return *m;
+}
+}  // namespace
+
 int IpcMapper::open_now(const uint8_t handle[64], bool vmm, void** mapped, size_t* bytes) {
   if (!vmm) {
     *bytes = 0;
-    return cuda::ipc_open(handle, mapped);
+    std::array<uint8_t, 64> key;
+    memcpy(key.data(), handle, 64);
+    std::lock_guard<std::mutex> g(g_now_mu);
+    auto it = now_open().find(key);
+    if (it != now_open().end()) {
+      ++it->second.refs;
+      *mapped = it->second.mapped;
+      return 0;
+    }
+    const int rc = cuda::ipc_open(handle, mapped);
+    if (rc == 0) now_open()[key] = NowOpen{*mapped, 1};
+    return rc;
   }
   IpcMapJob job;
   memcpy(job.handle, handle, 64);
@@ -115,6 +142,20 @@ int IpcMapper::open_now(const uint8_t handle[64], bool vmm, void** mapped, size_
   const int rc = open_vmm(job, mapped);
   *bytes = job.bytes;
   return rc;
+}
+
+int IpcMapper::close_now(void* mapped, bool vmm, size_t bytes) {
+  if (vmm) return cuda::vmm_unmap(mapped, bytes);
+  {
+    std::lock_guard<std::mutex> g(g_now_mu);
+    for (auto it = now_open().begin(); it != now_open().end(); ++it) {
+      if (it->second.mapped != mapped) continue;
+      if (--it->second.refs > 0) return 0;
+      now_open().erase(it);
+      break;
+    }
+  }
+  return cuda::ipc_close(mapped);
 }
 
 int IpcMapper::wait(const IpcMapJob& job, uint64_t wait_us) {

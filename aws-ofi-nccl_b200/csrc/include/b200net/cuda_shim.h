@@ -49,6 +49,10 @@ int launch_kernel(void* fn, unsigned grid, unsigned block, unsigned smem_bytes, 
 // Page-locked host memory that the GPU can write (portable, mapped).
 int host_alloc(void** ptr, size_t bytes);
 int host_free(void* ptr);
+// Page-locks memory the caller already owns (whole pages), so asynchronous copies from and to it
+// do not pass through the driver's staging buffer; -ENOSYS when the driver does not offer it.
+int host_register(void* ptr, size_t bytes);
+int host_unregister(void* ptr);
 
 // Plain device allocation (IPC-exportable with ipc_get_handle), zero-filled.
 int mem_alloc(void** ptr, size_t bytes);

@@ -36,6 +36,7 @@ struct IpcMapJob {
   cuda::Context ctx = nullptr;       // made current on the helper thread before the open
   std::atomic<int> state{0};         // 0 in progress, 1 mapped, 2 abandoned by its owner, negative errno
   void* mapped = nullptr;            // valid once state == 1 (acquire)
+  bool waited = false;               // owner's note: the grace period has been spent on this open already
   // The owner is going away. True: the mapping exists and the caller must close it. False: it does
   // not exist (failed, or still in progress: the helper closes it when it arrives).
   bool abandon() {
@@ -53,7 +54,7 @@ class IpcMapper {
   // The same open on the calling thread, for set-up paths where waiting for the device is harmless
   // (collective registration). 0 or a negative errno; *bytes is the mapping's size for close_now().
   static int open_now(const uint8_t handle[64], bool vmm, void** mapped, size_t* bytes);
-  static int close_now(void* mapped, bool vmm, size_t bytes) { return vmm ? cuda::vmm_unmap(mapped, bytes) : cuda::ipc_close(mapped); }
+  static int close_now(void* mapped, bool vmm, size_t bytes);
   // Polls job->state for at most wait_us microseconds; returns the state seen last.
   static int wait(const IpcMapJob& job, uint64_t wait_us);
 };

@@ -2,6 +2,11 @@
 // A lookup hits when the cached entry CONTAINS the requested range; inserting an existing range
 // reports EEXIST; delete returns 1 when the last reference went away and the caller must really
 // deregister (reference: src/nccl_ofi_mr.cpp, include/nccl_ofi_mr.h).
+//
+// Keys marked `exact` stand for one device allocation (its base and size): they hit only an entry
+// with the very same base and size, never by page containment. The driver packs small device
+// allocations a few hundred bytes apart, so several share a page, and a handle that describes one
+// of them (its IPC handle, its bounds) must not be handed out for a neighbour.
 #pragma once
 #include <cstddef>
 #include <cstdint>
@@ -21,6 +26,12 @@ struct MrCacheKey {
   int fd = -1;          // dmabuf only
   uint64_t offset = 0;  // dmabuf only
   const void* ep = nullptr;  // registrations tied to an endpoint only hit for the same endpoint
+  bool exact = false;        // match base and length exactly (one device allocation)
+  static MrCacheKey from_allocation(const void* base, size_t len, const void* ep = nullptr) {
+    MrCacheKey k{MrKeyKind::IOVEC, reinterpret_cast<uintptr_t>(base), len, -1, 0, ep};
+    k.exact = true;
+    return k;
+  }
   static MrCacheKey from_iovec(const void* p, size_t len, const void* ep = nullptr) {
     return {MrKeyKind::IOVEC, reinterpret_cast<uintptr_t>(p), len, -1, 0, ep};
   }
@@ -45,7 +56,8 @@ class MrCache {
   void page_range(const MrCacheKey& key, uintptr_t* base, size_t* pages) const;
 
  private:
-  struct Entry { uintptr_t addr; size_t pages; int refcnt; void* handle; const void* ep; MrKeyKind kind; int fd; };
+  struct Entry { uintptr_t addr; size_t pages; int refcnt; void* handle; const void* ep; MrKeyKind kind; int fd;
+                 bool exact; uintptr_t raw_addr; size_t raw_len; };
   size_t page_size_;
   mutable std::mutex mu_;
   std::vector<Entry> entries_;  // sorted by addr

@@ -60,7 +60,8 @@ struct MrTableEntry {
   uint32_t kind;         // 1 host, 2 cuda (ipc handle valid), 3 cuda staged (no direct mapping)
   uint32_t device;
   uint8_t ipc_handle[64];
-  uint8_t pad[32];
+  uint64_t serial;       // unique per publication in the owner's process (keys are recycled)
+  uint8_t pad[24];
 };
 static_assert(sizeof(MrTableEntry) == 128, "MR table entries are 128 bytes");
 

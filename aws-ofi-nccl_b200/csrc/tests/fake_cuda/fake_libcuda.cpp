@@ -14,8 +14,16 @@
 //   FAKE_CUDA_PROTECT=0         device addresses stay readable and writable by host code (default:
 //                               they are mapped without access, so a host dereference faults)
 //   FAKE_CUDA_IPC_OPEN_DELAY_MS=n cuIpcOpenMemHandle takes n milliseconds (a device that is busy)
-//   FAKE_CUDA_LAUNCH_DELAY_US=n kernels "finish" n microseconds after the launch call returns
-//                               (a helper thread performs them), so completions are asynchronous
+//   FAKE_CUDA_LAUNCH_DELAY_US=n kernels and asynchronous copies "finish" n microseconds after the call
+//                               that queued them returns (a helper thread performs them in order),
+//                               and an event is complete once everything queued before its record
+//                               has been performed: completions are asynchronous, as on a device
+//   FAKE_CUDA_FAIL_MEMCPY_AFTER=n the n-th cuMemcpyAsync from now on and every later one fails
+//   FAKE_CUDA_SUBALLOC_MAX=n    cuMemAlloc requests below n bytes (default 65536) are carved at
+//                               256-byte granularity out of shared 2 MiB blocks, as the driver does
+//                               with small allocations: several allocations share a page, an IPC
+//                               handle names the block plus the offset, and a peer that opens it may
+//                               touch only the bytes of that one allocation (anything else aborts)
 #include <cuda.h>
 #include <fcntl.h>
 #include <sys/mman.h>
@@ -43,10 +51,28 @@ struct Alloc {
   bool opened_from_peer;
   unsigned char* shadow;   // readable and writable view of the same pages (the device's own view)
   unsigned long long vmm_handle = 0;   // non-zero: mapped through the virtual-memory API
+  // carved out of a shared block (own small allocations), or a window into a peer's block:
+  int block = -1;              // own: index into g_blocks
+  size_t block_off = 0;        // offset of this allocation inside the block
+  void* map_base = nullptr;    // peer window: what to unmap on close (the whole block was mapped)
+  unsigned char* map_shadow = nullptr;
+  size_t map_size = 0;
 };
+// A 2 MiB shared segment that small allocations are carved from.
+struct Block {
+  std::string shm_name;
+  unsigned char* user = nullptr;     // PROT_NONE view (addresses handed to the program)
+  unsigned char* shadow = nullptr;
+  std::map<size_t, size_t> used;     // offset -> bytes
+};
+constexpr size_t kBlockBytes = 2u << 20;
+constexpr size_t kSubGranule = 256;
 std::mutex g_mu;
 std::map<uintptr_t, Alloc> g_allocs;   // base -> allocation ("device" address ranges of this process)
+std::map<int, Block> g_blocks;          // guarded by g_mu
+int g_next_block = 0;
 std::atomic<int> g_next_alloc{0};
+std::atomic<long> g_memcpy_budget{-1};  // < 0: copies never fail
 bool g_fail_ipc_open = false;
 int g_launch_delay_us = 0;
 
@@ -69,12 +95,18 @@ bool protect_on() {
   static const bool on = !(getenv("FAKE_CUDA_PROTECT") && !atoi(getenv("FAKE_CUDA_PROTECT")));
   return on;
 }
-void* dev_view(const void* p) {
+void* dev_view(const void* p, size_t n = 0) {
   std::lock_guard<std::mutex> g(g_mu);
   uintptr_t base = 0;
   const Alloc* al = find_alloc(reinterpret_cast<uintptr_t>(p), &base);
   if (!al) return const_cast<void*>(p);
-  return al->shadow + (reinterpret_cast<uintptr_t>(p) - base);
+  const size_t off = reinterpret_cast<uintptr_t>(p) - base;
+  if (off + n > al->size) {
+    // a real device would write into a neighbour's bytes (or fault): never let that pass
+    fprintf(stderr, "fake libcuda: access of %zu bytes at offset %zu runs past an allocation of %zu bytes\n", n, off, al->size);
+    abort();
+  }
+  return al->shadow + off;
 }
 // Maps the pages of fd twice: the program's (protected) address and the stand-in's own view.
 bool map_pair(int fd, size_t bytes, void** user, unsigned char** shadow) {
@@ -91,8 +123,10 @@ bool map_pair(int fd, size_t bytes, void** user, unsigned char** shadow) {
 }
 
 struct IpcHandlePayload {   // fits the 64 opaque bytes
-  char name[48];
-  uint64_t size;
+  char name[40];
+  uint64_t size;      // of the segment to map
+  uint64_t offset;    // of the allocation inside it (small allocations share a block)
+  uint64_t bytes;     // of the allocation
 };
 static_assert(sizeof(IpcHandlePayload) <= sizeof(CUipcMemHandle), "handle payload too large");
 
@@ -105,6 +139,9 @@ std::condition_variable& g_wcv = *new std::condition_variable;
 WorkQueue& g_work = *new WorkQueue;
 std::thread* g_worker = nullptr;
 std::atomic<int> g_outstanding{0};   // queued or running
+// Work handed to the delayed worker is numbered; an event remembers the number current when it was
+// recorded and is complete once the worker has passed it.
+std::atomic<unsigned long long> g_submitted{0}, g_performed{0};
 void worker_main() {
   for (;;) {
     std::function<void()> fn;
@@ -121,17 +158,21 @@ void worker_main() {
       g_work.pop_front();
     }
     fn();
+    g_performed.fetch_add(1);
     g_outstanding.fetch_sub(1);
   }
 }
 void run_later(std::function<void()> fn) {
   if (g_launch_delay_us <= 0) {
     fn();
+    g_submitted.fetch_add(1);
+    g_performed.fetch_add(1);
     return;
   }
   std::lock_guard<std::mutex> g(g_wmu);
   if (!g_worker) g_worker = new std::thread(worker_main);   // lives until the process exits
   g_outstanding.fetch_add(1);
+  g_submitted.fetch_add(1);
   g_work.emplace_back(std::chrono::steady_clock::now() + std::chrono::microseconds(g_launch_delay_us), std::move(fn));
   g_wcv.notify_one();
 }
@@ -142,6 +183,7 @@ enum FakeFn : uintptr_t { FN_COPY_FLAG = 0x101, FN_EAGER_PACK = 0x102 };
 CUresult fInit(unsigned) {
   g_fail_ipc_open = getenv("FAKE_CUDA_FAIL_IPC_OPEN") && atoi(getenv("FAKE_CUDA_FAIL_IPC_OPEN"));
   g_launch_delay_us = getenv("FAKE_CUDA_LAUNCH_DELAY_US") ? atoi(getenv("FAKE_CUDA_LAUNCH_DELAY_US")) : 0;
+  if (const char* v = getenv("FAKE_CUDA_FAIL_MEMCPY_AFTER")) g_memcpy_budget.store(atol(v));
   return CUDA_SUCCESS;
 }
 CUresult fDeviceGetCount(int* n) {
@@ -198,8 +240,59 @@ CUresult fMemGetAddressRange(CUdeviceptr* base_out, size_t* size_out, CUdevicept
   if (size_out) *size_out = al->size;
   return CUDA_SUCCESS;
 }
+size_t suballoc_max() {
+  static const size_t v = getenv("FAKE_CUDA_SUBALLOC_MAX") ? strtoull(getenv("FAKE_CUDA_SUBALLOC_MAX"), nullptr, 0) : 65536;
+  return v;
+}
+// A small allocation: first fit at 256-byte granularity inside a shared block. g_mu is held.
+bool carve_locked(size_t bytes, CUdeviceptr* out) {
+  const size_t need = (bytes + kSubGranule - 1) & ~(kSubGranule - 1);
+  for (int pass = 0; pass < 2; ++pass) {
+    for (auto& [id, b] : g_blocks) {
+      size_t at = 0;
+      for (const auto& [off, len] : b.used) {
+        if (off - at >= need) break;
+        at = off + ((len + kSubGranule - 1) & ~(kSubGranule - 1));
+      }
+      if (at + need > kBlockBytes) continue;
+      b.used[at] = bytes;
+      Alloc al{bytes, b.shm_name, false, b.shadow + at};
+      al.block = id;
+      al.block_off = at;
+      g_allocs[reinterpret_cast<uintptr_t>(b.user + at)] = al;
+      *out = reinterpret_cast<CUdeviceptr>(b.user + at);
+      return true;
+    }
+    if (pass == 1) break;
+    // no block has room: make one
+    char name[40];
+    snprintf(name, sizeof(name), "/fakecuda.%d.b%d", static_cast<int>(getpid()), g_next_block);
+    shm_unlink(name);
+    const int fd = shm_open(name, O_CREAT | O_EXCL | O_RDWR, 0600);
+    if (fd < 0) return false;
+    void* user = nullptr;
+    unsigned char* shadow = nullptr;
+    const bool ok = ftruncate(fd, static_cast<off_t>(kBlockBytes)) == 0 && map_pair(fd, kBlockBytes, &user, &shadow);
+    close(fd);
+    if (!ok) {
+      shm_unlink(name);
+      return false;
+    }
+    Block b;
+    b.shm_name = name;
+    b.user = static_cast<unsigned char*>(user);
+    b.shadow = shadow;
+    g_blocks[g_next_block++] = std::move(b);
+  }
+  return false;
+}
 CUresult fMemAlloc(CUdeviceptr* out, size_t bytes) {
-  char name[48];
+  if (bytes == 0) return CUDA_ERROR_INVALID_VALUE;
+  if (bytes < suballoc_max()) {
+    std::lock_guard<std::mutex> g(g_mu);
+    return carve_locked(bytes, out) ? CUDA_SUCCESS : CUDA_ERROR_OUT_OF_MEMORY;
+  }
+  char name[40];
   snprintf(name, sizeof(name), "/fakecuda.%d.%d", static_cast<int>(getpid()), g_next_alloc.fetch_add(1));
   shm_unlink(name);
   const int fd = shm_open(name, O_CREAT | O_EXCL | O_RDWR, 0600);
@@ -219,22 +312,38 @@ CUresult fMemAlloc(CUdeviceptr* out, size_t bytes) {
     return CUDA_ERROR_OUT_OF_MEMORY;
   }
   std::lock_guard<std::mutex> g(g_mu);
-  g_allocs[reinterpret_cast<uintptr_t>(p)] = Alloc{rounded, name, false, shadow};
+  Alloc al{bytes, name, false, shadow};
+  al.map_size = rounded;
+  g_allocs[reinterpret_cast<uintptr_t>(p)] = al;
   *out = reinterpret_cast<CUdeviceptr>(p);
   return CUDA_SUCCESS;
 }
 CUresult fMemFree(CUdeviceptr p) {
   std::lock_guard<std::mutex> g(g_mu);
   auto it = g_allocs.find(static_cast<uintptr_t>(p));
-  if (it == g_allocs.end()) return CUDA_ERROR_INVALID_VALUE;
-  munmap(reinterpret_cast<void*>(it->first), it->second.size);
-  munmap(it->second.shadow, it->second.size);
+  if (it == g_allocs.end() || it->second.opened_from_peer) return CUDA_ERROR_INVALID_VALUE;
+  if (it->second.block >= 0) {
+    auto b = g_blocks.find(it->second.block);
+    if (b != g_blocks.end()) {
+      b->second.used.erase(it->second.block_off);
+      if (b->second.used.empty()) {   // the last allocation of the block: the block goes too
+        munmap(b->second.user, kBlockBytes);
+        munmap(b->second.shadow, kBlockBytes);
+        shm_unlink(b->second.shm_name.c_str());
+        g_blocks.erase(b);
+      }
+    }
+    g_allocs.erase(it);
+    return CUDA_SUCCESS;
+  }
+  munmap(reinterpret_cast<void*>(it->first), it->second.map_size);
+  munmap(it->second.shadow, it->second.map_size);
   if (!it->second.shm_name.empty()) shm_unlink(it->second.shm_name.c_str());
   g_allocs.erase(it);
   return CUDA_SUCCESS;
 }
 CUresult fMemsetD8(CUdeviceptr p, unsigned char v, size_t n) {
-  memset(dev_view(reinterpret_cast<void*>(p)), v, n);
+  memset(dev_view(reinterpret_cast<void*>(p), n), v, n);
   return CUDA_SUCCESS;
 }
 CUresult fIpcGetMemHandle(CUipcMemHandle* h, CUdeviceptr p) {
@@ -245,7 +354,9 @@ CUresult fIpcGetMemHandle(CUipcMemHandle* h, CUdeviceptr p) {
   if (it == g_allocs.end() || it->second.shm_name.empty()) return CUDA_ERROR_INVALID_VALUE;
   IpcHandlePayload pl{};
   snprintf(pl.name, sizeof(pl.name), "%s", it->second.shm_name.c_str());
-  pl.size = it->second.size;
+  pl.size = it->second.block >= 0 ? kBlockBytes : it->second.map_size;
+  pl.offset = it->second.block >= 0 ? it->second.block_off : 0;
+  pl.bytes = it->second.size;
   memset(h, 0, sizeof(*h));
   memcpy(h, &pl, sizeof(pl));
   return CUDA_SUCCESS;
@@ -264,16 +375,22 @@ CUresult fIpcOpenMemHandle(CUdeviceptr* out, CUipcMemHandle h, unsigned) {
   close(fd);
   if (!mapped) return CUDA_ERROR_OUT_OF_MEMORY;
   std::lock_guard<std::mutex> g(g_mu);
-  g_allocs[reinterpret_cast<uintptr_t>(p)] = Alloc{pl.size, "", true, shadow};
-  *out = reinterpret_cast<CUdeviceptr>(p);
+  // the pointer handed back stands for the allocation the handle was taken from, and only its
+  // bytes are reachable through it, although the whole segment is mapped behind it
+  Alloc al{pl.bytes, "", true, shadow + pl.offset};
+  al.map_base = p;
+  al.map_shadow = shadow;
+  al.map_size = pl.size;
+  g_allocs[reinterpret_cast<uintptr_t>(p) + pl.offset] = al;
+  *out = reinterpret_cast<CUdeviceptr>(p) + pl.offset;
   return CUDA_SUCCESS;
 }
 CUresult fIpcCloseMemHandle(CUdeviceptr p) {
   std::lock_guard<std::mutex> g(g_mu);
   auto it = g_allocs.find(static_cast<uintptr_t>(p));
-  if (it == g_allocs.end()) return CUDA_ERROR_INVALID_VALUE;
-  munmap(reinterpret_cast<void*>(it->first), it->second.size);
-  munmap(it->second.shadow, it->second.size);
+  if (it == g_allocs.end() || !it->second.opened_from_peer) return CUDA_ERROR_INVALID_VALUE;
+  munmap(it->second.map_base, it->second.map_size);
+  munmap(it->second.map_shadow, it->second.map_size);
   g_allocs.erase(it);
   return CUDA_SUCCESS;
 }
@@ -293,31 +410,42 @@ CUresult fStreamCreate(CUstream* s, unsigned) {
 }
 CUresult fStreamDestroy(CUstream) { return CUDA_SUCCESS; }
 CUresult fStreamSynchronize(CUstream) {
-  // delayed "kernels" are not tied to streams: wait until none is queued or running
+  // delayed work is not tied to streams: wait until none is queued or running
   while (g_outstanding.load() > 0) usleep(50);
   return CUDA_SUCCESS;
 }
 CUresult fEventCreate(CUevent* e, unsigned) {
-  *e = reinterpret_cast<CUevent>(new int(0));
+  *e = reinterpret_cast<CUevent>(new std::atomic<unsigned long long>(0));
   return CUDA_SUCCESS;
 }
 CUresult fEventDestroy(CUevent e) {
-  delete reinterpret_cast<int*>(e);
+  delete reinterpret_cast<std::atomic<unsigned long long>*>(e);
   return CUDA_SUCCESS;
 }
-CUresult fEventRecord(CUevent, CUstream) { return CUDA_SUCCESS; }
-CUresult fEventQuery(CUevent) { return CUDA_SUCCESS; }
+CUresult fEventRecord(CUevent e, CUstream) {
+  reinterpret_cast<std::atomic<unsigned long long>*>(e)->store(g_submitted.load());
+  return CUDA_SUCCESS;
+}
+CUresult fEventQuery(CUevent e) {
+  return g_performed.load() >= reinterpret_cast<std::atomic<unsigned long long>*>(e)->load() ? CUDA_SUCCESS : CUDA_ERROR_NOT_READY;
+}
 CUresult fMemcpyAsync(CUdeviceptr d, CUdeviceptr s, size_t n, CUstream) {
-  void* to = dev_view(reinterpret_cast<void*>(d));
-  const void* from = dev_view(reinterpret_cast<const void*>(s));
-  if (n == 8 && reinterpret_cast<uintptr_t>(to) % 8 == 0 && reinterpret_cast<uintptr_t>(from) % 8 == 0) {
-    // an aligned word (a signal): one indivisible store, as the copy engine does it, so that a
-    // reader polling the word with an atomic load is not a data race in the eyes of a race detector
-    __atomic_store_n(static_cast<unsigned long long*>(to), __atomic_load_n(static_cast<const unsigned long long*>(from), __ATOMIC_ACQUIRE),
-                     __ATOMIC_RELEASE);
-    return CUDA_SUCCESS;
+  if (g_memcpy_budget.load() >= 0 && g_memcpy_budget.fetch_sub(1) <= 0) {
+    g_memcpy_budget.store(0);
+    return CUDA_ERROR_INVALID_VALUE;
   }
-  memcpy(to, from, n);
+  void* to = dev_view(reinterpret_cast<void*>(d), n);
+  const void* from = dev_view(reinterpret_cast<const void*>(s), n);
+  run_later([=] {
+    if (n == 8 && reinterpret_cast<uintptr_t>(to) % 8 == 0 && reinterpret_cast<uintptr_t>(from) % 8 == 0) {
+      // an aligned word (a signal): one indivisible store, as the copy engine does it, so that a
+      // reader polling the word with an atomic load is not a data race in the eyes of a race detector
+      __atomic_store_n(static_cast<unsigned long long*>(to), __atomic_load_n(static_cast<const unsigned long long*>(from), __ATOMIC_ACQUIRE),
+                       __ATOMIC_RELEASE);
+      return;
+    }
+    memcpy(to, from, n);
+  });
   return CUDA_SUCCESS;
 }
 CUresult fModuleLoadData(CUmodule* m, const void* image) {
@@ -342,7 +470,7 @@ CUresult fLaunchKernel(CUfunction f, unsigned, unsigned, unsigned, unsigned, uns
     auto* flag = *static_cast<unsigned long long**>(args[4]);
     const unsigned long long value = *static_cast<unsigned long long*>(args[5]);
     run_later([=] {
-      memcpy(dev_view(dst), dev_view(src), bytes);
+      memcpy(dev_view(dst, bytes), dev_view(src, bytes), bytes);
       __atomic_store_n(static_cast<unsigned long long*>(dev_view(flag)), value, __ATOMIC_RELEASE);
     });
     return CUDA_SUCCESS;
@@ -357,7 +485,7 @@ CUresult fLaunchKernel(CUfunction f, unsigned, unsigned, unsigned, unsigned, uns
     const unsigned long long value = *static_cast<unsigned long long*>(args[6]);
     run_later([=] {
       auto* out = static_cast<unsigned char*>(dev_view(slot));
-      memcpy(out + 16, dev_view(payload), bytes);
+      memcpy(out + 16, dev_view(payload, bytes), bytes);
       memcpy(out, &h0, 8);
       memcpy(out + 8, &h1, 8);
       __atomic_store_n(reinterpret_cast<unsigned long long*>(out + flag_off), value, __ATOMIC_RELEASE);
@@ -371,6 +499,12 @@ CUresult fMemHostAlloc(void** p, size_t bytes, unsigned) {
 }
 CUresult fMemFreeHost(void* p) {
   free(p);
+  return CUDA_SUCCESS;
+}
+CUresult fMemHostRegister(void*, size_t, unsigned) { return CUDA_SUCCESS; }
+CUresult fMemHostUnregister(void*) { return CUDA_SUCCESS; }
+CUresult fCtxSynchronize() {
+  while (g_outstanding.load() > 0) usleep(50);
   return CUDA_SUCCESS;
 }
 // ---- the virtual-memory API: an allocation is a memory file, a handle a reference to it
@@ -520,7 +654,8 @@ const Entry kTable[] = {
     E("cuMemAddressReserve", fMemAddressReserve), E("cuMemAddressFree", fMemAddressFree), E("cuMemMap", fMemMap),
     E("cuMemUnmap", fMemUnmap), E("cuMemSetAccess", fMemSetAccess), E("cuMemExportToShareableHandle", fMemExportToShareableHandle),
     E("cuMemImportFromShareableHandle", fMemImportFromShareableHandle), E("cuMemRetainAllocationHandle", fMemRetainAllocationHandle),
-    E("cuCtxGetDevice", fCtxGetDevice),
+    E("cuCtxGetDevice", fCtxGetDevice), E("cuMemHostRegister", fMemHostRegister), E("cuMemHostUnregister", fMemHostUnregister),
+    E("cuCtxSynchronize", fCtxSynchronize),
 };
 
 }  // namespace
@@ -584,6 +719,8 @@ int fake_cuda_live_peer_mappings() {
   for (const auto& [base, al] : g_allocs) n += al.opened_from_peer ? 1 : 0;
   return n;
 }
+// From now on the n-th asynchronous copy and every later one fails (n < 0: copies work again).
+void fake_cuda_fail_memcpy_after(long n) { g_memcpy_budget.store(n); }
 // The accessible view of a "device" address (what a test uses to fill and check device buffers).
 void* fake_cuda_host_view(void* p) { return dev_view(p); }
 }

@@ -161,6 +161,59 @@ static int scenario_peer_exit(int sock) {
   return 0;
 }
 
+// The receiver's copy of an eager payload into device memory fails (error code from the stand-in
+// driver's cuMemcpyAsync; it runs only against that stand-in): test() of that receive must report
+// an error instead of a size, not "done" with nothing delivered.
+static int scenario_device_copy_failure(int sock) {
+  void* drv = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+  auto dev_alloc = drv ? reinterpret_cast<int (*)(void**, size_t)>(dlsym(drv, "fake_cuda_mem_alloc")) : nullptr;
+  auto dev_free = drv ? reinterpret_cast<int (*)(void*)>(dlsym(drv, "fake_cuda_mem_free")) : nullptr;
+  auto fail_after = drv ? reinterpret_cast<void (*)(long)>(dlsym(drv, "fake_cuda_fail_memcpy_after")) : nullptr;
+  if (!dev_alloc || !dev_free || !fail_after) FAIL("this scenario needs the stand-in driver on the library path");
+  Pair p;
+  if (connect_pair(0, sock, &p)) return 1;
+  const size_t n = 1024;   // eager-sized
+  std::vector<uint8_t> buf(n);
+  fill(buf, 9);
+  void* dev = nullptr;
+  if (dev_alloc(&dev, n) != 0) FAIL("device allocation failed");
+  void *mhs = nullptr, *mhr = nullptr;
+  OK(net->regMr(p.s, buf.data(), n, NCCL_PTR_HOST, &mhs));
+  OK(net->regMr(p.r, dev, n, NCCL_PTR_CUDA, &mhr));
+  if (g_rank == 1) {
+    // the host payload leaves eagerly, before any receive is posted
+    void* rs = nullptr;
+    if (post_send(p.s, buf.data(), n, 11, mhs, &rs)) return 1;
+    if (barrier(sock)) FAIL("barrier");
+    std::vector<void*> reqs{rs};
+    if (wait_all(reqs)) return 1;
+    if (barrier(sock)) FAIL("barrier");
+  } else {
+    if (barrier(sock)) FAIL("barrier");
+    fail_after(0);   // every copy from here on answers with an error code
+    void* data = dev;
+    size_t sz = n;
+    int tag = 11;
+    void* rr = nullptr;
+    if (post_recv(p.r, 1, &data, &sz, &tag, &mhr, &rr)) return 1;
+    const auto t0 = Clock::now();
+    int done = 0, rc = 0;
+    while (!done && rc == 0 && !expired(t0, kGiveUpSeconds)) {
+      int szs[8];
+      rc = timed([&] { return (int)net->test(rr, &done, szs); }, "test(recv)");
+    }
+    fail_after(-1);
+    if (done) FAIL("the receive reported success although the copy to the device failed");
+    if (rc == 0) FAIL("the receive neither failed nor completed");
+    if (rc >= 1000) FAIL("test blocked");
+    if (barrier(sock)) FAIL("barrier");
+  }
+  OK(net->deregMr(p.s, mhs));
+  OK(net->deregMr(p.r, mhr));
+  dev_free(dev);
+  return close_pair(&p);
+}
+
 static const struct {
   const char* name;
   int (*fn)(int);
@@ -171,6 +224,7 @@ static const struct {
     {"drop_conn", scenario_drop_conn, "", "1:1", false},               // CM_CONN
     {"drop_completion", scenario_drop_completion, "", "4:1", false},   // WRITE_COMPLETION
     {"peer_exit", scenario_peer_exit, "", "", true},
+    {"device_copy_failure", scenario_device_copy_failure, "", "", false},
 };
 
 static int run_rank(const char* so, const char* only, int sock) {

@@ -487,7 +487,14 @@ static int scenario_device_transfer(int sock) {
       fill(want, 500 + 10 * pass + i + 1000 * (1 - g_rank));
       if (got[nmsg + i] != static_cast<int>(sizes[i])) FAIL("pass %d message %d: size %d, expected %zu", pass, i, got[nmsg + i], sizes[i]);
       if (rb[i].from_device()) FAIL("copy from the device failed");
-      if (memcmp(want.data(), rb[i].host(), sizes[i])) FAIL("pass %d message %d (%zu bytes): payload differs", pass, i, sizes[i]);
+      if (memcmp(want.data(), rb[i].host(), sizes[i])) {
+        size_t at = 0;
+        while (at < sizes[i] && want[at] == rb[i].host()[at]) ++at;
+        FAIL("pass %d message %d (%zu bytes): payload differs from byte %zu on: got %02x %02x %02x %02x, expected %02x %02x %02x %02x "
+             "(cd = never written, 00 = zero-filled)", pass, i, sizes[i], at, rb[i].host()[at], rb[i].host()[std::min(at + 1, sizes[i] - 1)],
+             rb[i].host()[std::min(at + 2, sizes[i] - 1)], rb[i].host()[std::min(at + 3, sizes[i] - 1)], want[at],
+             want[std::min(at + 1, sizes[i] - 1)], want[std::min(at + 2, sizes[i] - 1)], want[std::min(at + 3, sizes[i] - 1)]);
+      }
       if (rb[i].host()[sizes[i]] != 0xCD) FAIL("pass %d message %d: wrote past the end", pass, i);
     }
     if (barrier(sock)) FAIL("barrier");

@@ -39,5 +39,17 @@ int main() {
   CHECK_EQ(c.insert(MrCacheKey::from_iovec(base + 0x80000, 4096, &ep1), &h5), 0);
   CHECK(c.lookup(MrCacheKey::from_iovec(base + 0x80000, 8, &ep2)) == nullptr);
   CHECK(c.lookup(MrCacheKey::from_iovec(base + 0x80000, 8, &ep1)) == &h5);
+  // exact keys (one device allocation each): two small allocations in one page never share a handle
+  int a1, a2;
+  CHECK_EQ(c.insert(MrCacheKey::from_allocation(base + 0x200000, 65), &a1), 0);
+  CHECK(c.lookup(MrCacheKey::from_allocation(base + 0x200000 + 512, 72)) == nullptr);   // a neighbour in the same page
+  CHECK_EQ(c.insert(MrCacheKey::from_allocation(base + 0x200000 + 512, 72), &a2), 0);
+  CHECK(c.lookup(MrCacheKey::from_allocation(base + 0x200000, 65)) == &a1);
+  CHECK(c.lookup(MrCacheKey::from_allocation(base + 0x200000 + 512, 72)) == &a2);
+  CHECK(c.lookup(MrCacheKey::from_allocation(base + 0x200000, 64)) == nullptr);         // same base, other size
+  CHECK(c.lookup(MrCacheKey::from_iovec(base + 0x200000, 16)) == nullptr);              // a containment key never hits an exact entry
+  CHECK_EQ(c.insert(MrCacheKey::from_allocation(base + 0x200000, 65), &a2), -EEXIST);
+  CHECK_EQ(c.del(&a1), 0);
+  CHECK_EQ(c.del(&a1), 1);
   TEST_MAIN_END();
 }

@@ -4,8 +4,17 @@
 // (reference: src/nccl_ofi_rdma.cpp — send() :5646-5877, recv() :3545-3746, test() :2234-2307,
 //  the completion loop :1485-1568, pending-request retries :1376-1453, close :3895-4304).
 //
-// The "wire" is the shared-memory fabric for host buffers and CUDA IPC mappings + copy-engine
-// copies on per-rail streams for device buffers; the protocol state machine is independent of it.
+// The "wire" is the shared-memory fabric for host buffers and CUDA IPC / VMM mappings of the peer's
+// device buffers, written by the plugin's own copy kernel (or the copy engine) on per-rail streams;
+// the protocol state machine is independent of it.
+//
+// Nothing on the send / receive / test path waits for the device: a copy is posted, the request
+// stays pending, and its completion word or event is polled from test(). The thread that drives
+// this code is NCCL's proxy, and NCCL's kernel on the same device waits for the proxy, so a driver
+// call that waits for the device could wait for ever. Requests, eager staging slots and events
+// come from pools that belong to the endpoint and are sized when it is created
+// (reference: the request, control, eager and flush freelists, src/nccl_ofi_rdma.cpp:4762-4978, and
+// the receive-buffer pools :1795-1919).
 #include <sched.h>
 #include <unistd.h>
 
@@ -19,7 +28,9 @@
 #include <list>
 #include <map>
 #include <memory>
+#include <new>
 #include <set>
+#include <vector>
 
 #include "b200net/assert.h"
 #include "b200net/cm.h"
@@ -53,12 +64,18 @@ struct DeviceFragHdr {
 
 // ------------------------------------------------------------------------------------------ requests
 struct Stripe {
-  int rail;
-  size_t offset, len, done;
-  cuda::Event event;   // non-null while a copy-engine transfer is in flight
-  bool posted, complete, notified;
+  int rail = 0;
+  size_t offset = 0, len = 0, done = 0;
+  cuda::Event event = nullptr;   // non-null while a copy-engine transfer is in flight (from the endpoint's pool)
+  bool posted = false, complete = false, notified = false;
   int kslot = -1;      // completion slot of a copy-kernel transfer in flight
   std::shared_ptr<std::atomic<int>> job;  // status of a stripe handed to a host copy worker
+};
+
+// Where a send writes: the fields of the control entry it was matched to.
+struct SendTarget {
+  uint64_t buff_addr = 0, mr_key = 0, buff_len = 0;
+  uint16_t flags = 0;
 };
 
 class RdmaSendReq : public Request {
@@ -66,9 +83,10 @@ class RdmaSendReq : public Request {
   int test(int* done, int* sizes) override;
   // A stripe still held by a copy worker reads this request's source buffer: wait for it.
   ~RdmaSendReq() override {
-    for (Stripe& s : stripes)
-      while (s.job && s.job->load(std::memory_order_acquire) == 0) sched_yield();
+    for (int i = 0; i < nstripes; ++i)
+      while (stripes[i].job && stripes[i].job->load(std::memory_order_acquire) == 0) sched_yield();
   }
+  FreelistEntry* fl = nullptr;   // the pool entry this object lives in
   RdmaSendComm* comm = nullptr;
   void* data = nullptr;
   size_t size = 0;
@@ -77,11 +95,23 @@ class RdmaSendReq : public Request {
   bool eager = false;       // sent eagerly, waiting to be bound to a control entry
   uint16_t seq = 0;
   uint8_t recv_idx = 0;
-  CtrlEntry target{};       // copy of the control entry this send writes into
-  std::vector<Stripe> stripes;
-  std::vector<uint8_t> bounce;  // host copy of a device source that must travel through host memory
+  SendTarget target;
+  Stripe stripes[MAX_NUM_RAILS];
+  int nstripes = 0;
+  // A device source whose destination is only reachable through host memory is fetched once into
+  // `bounce`; the stripes start when the event behind that copy has completed.
+  std::vector<uint8_t> bounce;
+  cuda::Event bounce_ev = nullptr;
   bool via_frags = false;       // the target registration has an IPC handle that could not be opened here
   uint64_t serial = 0;          // unique per endpoint; queued retries name the request by it
+  // eager sends: the datagram leaves from the communicator's outbox, in eager_seq order, once the
+  // payload is in host memory (pack kernel: completion word of `pack_slot`; copy engine: `stage_ev`)
+  EagerHdr ehdr{};
+  bool dgram_sent = false;
+  int pack_slot = -1;
+  FreelistEntry* stage = nullptr;
+  cuda::Event stage_ev = nullptr;
+  uint64_t t_outbox_ns = 0;
 };
 
 struct SubRecv {
@@ -98,6 +128,7 @@ struct SubRecv {
 class RdmaRecvReq : public Request {
  public:
   int test(int* done, int* sizes) override;
+  FreelistEntry* fl = nullptr;
   RdmaRecvComm* comm = nullptr;
   uint16_t seq = 0;
   int n = 0;
@@ -112,13 +143,53 @@ class RdmaFlushReq : public Request {
  public:
   explicit RdmaFlushReq(RdmaEndpoint* e) : ep(e) {}
   int test(int* done, int* sizes) override;
+  FreelistEntry* fl = nullptr;
   RdmaEndpoint* ep;
 };
 
 struct EagerRx {  // an eager message that arrived before (or without) a matching posted receive
   EagerHdr hdr;
-  std::vector<uint8_t> data;
+  FreelistEntry* slot;   // staging slot holding the payload (null for an empty message)
 };
+
+// Receiver-side work that has to wait for a copy on the endpoint's receive stream, kept in issue
+// order: the stream runs its copies in order, so the queue is retired from the front.
+struct Deferred {
+  enum Kind : uint8_t { FRAG_COPY, EAGER_COPY, WRITE_COMPLETION } kind;
+  cuda::Event ev = nullptr;        // null: ready as soon as everything before it has retired
+  FreelistEntry* slot = nullptr;   // staging slot to give back
+  uint32_t comm_id = 0;            // EAGER_COPY: the receive it completes
+  uint16_t seq = 0;
+  uint8_t idx = 0;
+  WriteCompletion wc{};            // WRITE_COMPLETION: applied once the fragments before it have landed
+};
+
+// A typed view of a Freelist: objects are constructed when taken and destroyed when given back.
+template <typename T>
+class ObjPool {
+ public:
+  ObjPool(const char* name, size_t initial, size_t grow, size_t max = 0)
+      : fl_(Freelist::Options{sizeof(T), initial, grow, max, alignof(T) < 8 ? 8 : alignof(T), 4096, nullptr, nullptr, nullptr, nullptr, name}) {}
+  template <typename... A>
+  T* take(A&&... a) {
+    FreelistEntry* e = fl_.entry_alloc();
+    if (!e) return nullptr;
+    T* t = new (e->ptr) T(std::forward<A>(a)...);
+    t->fl = e;
+    return t;
+  }
+  void give(T* t) {
+    FreelistEntry* e = t->fl;
+    t->~T();
+    fl_.entry_free(e);
+  }
+  size_t in_use() const { return fl_.in_use(); }
+
+ private:
+  Freelist fl_;
+};
+
+constexpr size_t STAGE_BYTES = FAB_LARGE_CELL;   // one eager payload or one fragment
 
 // ------------------------------------------------------------------------------------------ endpoint
 class RdmaEndpoint : public Endpoint {
@@ -133,23 +204,26 @@ class RdmaEndpoint : public Endpoint {
 
   int progress();
   void handle_dgram(const DgramHdr& h, const void* payload);
+  void retire_deferred();
+  void flush_outboxes();
+  void fail_endpoint(const char* why, int rc);
   int ensure_published(MrHandle* mh);
   cuda::Stream rail_stream(int rail);
-  void* map_peer_cuda(PeerMapping* peer, const MrTableEntry* e);
-  // Loads the plugin's device kernels into the current context. Only called from set-up paths
-  // (registration, connect, listen): loading a module or a function while a collective kernel
-  // that waits for this very transport is running can block forever.
-  void prepare_kernels() {
-    if (!kernels_tried && cuda::available()) {
-      cuda::Context ctx = nullptr;
-      if (cuda::ctx_get_current(&ctx) == 0 && ctx) {
-        kernels = NetKernels::get();
-        kernels_tried = true;
-        // streams too are created here, on a set-up path, not by the first send of a collective
-        for (int rail = 0; rail < num_rails; ++rail) rail_stream(rail);
-      }
-    }
-  }
+  // The mapping of a peer's device registration in this process, or nullptr while it does not
+  // exist (in progress on the helper thread, or failed). wait: give a first open the grace period.
+  void* map_peer_cuda(PeerMapping* peer, const MrTableEntry* e, bool wait = true);
+  // Queues the open of every device registration the peer has published so far. Called on set-up
+  // paths (a connection completes, a buffer is registered), so that the first send rarely has to.
+  void premap_peer(PeerMapping* peer);
+  // Loads the plugin's device kernels into the current context, creates the streams, the event
+  // pool and the page-locked staging slots. Only called from set-up paths (registration, connect,
+  // listen): loading a module, creating a stream or page-locking memory while a collective kernel
+  // that waits for this very transport is running can block for ever.
+  void prepare_kernels();
+  cuda::Event take_event();
+  void give_event(cuda::Event ev) { if (ev) free_events.push_back(ev); }
+  Freelist& staging() { return *staging_; }
+
   NetKernels* kernels = nullptr;   // null: copy engine only
   bool kernels_tried = false;
   // payload bytes by the path they took (reported when the endpoint goes away)
@@ -161,7 +235,12 @@ class RdmaEndpoint : public Endpoint {
   IdPool comm_ids{NET_MAX_COMMS};
   std::map<uint32_t, RdmaSendComm*> send_comms;
   std::map<uint32_t, RdmaRecvComm*> recv_comms;
-  std::deque<std::function<int()>> pending;  // posts that met a full ring (-EAGAIN); retried in order
+  // Sends whose post met a full ring (-EAGAIN), by serial number, retried strictly in order. A
+  // request's address can be handed out again (to another communicator's request) while an old
+  // retry for it is still queued; its serial number cannot.
+  std::deque<uint64_t> pending;
+  std::map<uint64_t, RdmaSendReq*> live_send_reqs;
+  uint64_t next_req_serial = 1;
   std::vector<cuda::Stream> streams;
   // (peer pid, IPC handle bytes) -> mapped base. Keyed by the handle, not by the MR key: keys are
   // recycled when a buffer is deregistered, and a new registration under an old key is a
@@ -171,10 +250,14 @@ class RdmaEndpoint : public Endpoint {
   void note_unmapped(PeerMapping* peer, const MrTableEntry* e);
   std::set<std::pair<MrHandle*, int>> published;
   std::map<MrHandle*, int> export_fds;   // descriptors kept open for peers that import a CUDA_VMM registration
-  // Requests a queued retry may still touch, by serial number: a request's address can be handed
-  // out again (to another communicator's request) while an old retry for it is still queued.
-  std::map<uint64_t, RdmaSendReq*> live_send_reqs;
-  uint64_t next_req_serial = 1;
+  // pools
+  ObjPool<RdmaSendReq> send_reqs{"send requests", 256, 256};
+  ObjPool<RdmaRecvReq> recv_reqs{"receive requests", NET_MAX_REQUESTS, NET_MAX_REQUESTS};
+  ObjPool<RdmaFlushReq> flush_reqs{"flush requests", 32, 32};
+  std::unique_ptr<Freelist> staging_;
+  std::vector<cuda::Event> free_events;
+  std::deque<Deferred> deferred;
+  int outbox_total = 0;        // eager sends of all communicators whose datagram has not left yet
   bool in_progress = false;
 };
 
@@ -207,6 +290,9 @@ class RdmaSendComm : public SendComm {
   uint8_t consumed_mask = 0;   // entries of that group already taken
   uint16_t next_eager_seq = 0;
   std::deque<RdmaSendReq*> eager_queue;
+  std::deque<RdmaSendReq*> outbox;   // eager sends whose datagram has not left yet, in eager_seq order
+  void flush_outbox();
+  void release(RdmaSendReq* r);
   std::unique_ptr<ThresholdScheduler> sched;
   int inflight = 0;
   uint32_t nonce = 0;
@@ -223,6 +309,8 @@ class RdmaRecvComm : public RecvComm {
   void on_eager(const EagerHdr& h, const void* data);
   void match_eager();
   void finish_sub(RdmaRecvReq* r, int idx);
+  void fail_sub(RdmaRecvReq* r, int idx);
+  void release(RdmaRecvReq* r);
   RdmaEndpoint* rep() { return static_cast<RdmaEndpoint*>(ep); }
 
   std::unique_ptr<ShmWindow> mailbox;  // sender's mailbox, mapped
@@ -230,7 +318,7 @@ class RdmaRecvComm : public RecvComm {
   uint16_t next_seq = 0;
   std::unique_ptr<MsgBuff> msgbuff;
   std::list<RdmaRecvReq*> posted;      // incomplete receive groups, oldest first
-  std::list<EagerRx> eager_rx;         // arrived eager messages in eager_seq order
+  std::vector<EagerRx> eager_rx;       // arrived eager messages in eager_seq order (at most a few dozen)
   uint16_t eager_arrived = 0;          // eager messages with a sequence number before this have all arrived
   uint8_t eager_taken[MAILBOX_SLOTS] = {};  // per group: entries matched to eager messages / completed
   int inflight = 0;
@@ -239,7 +327,26 @@ class RdmaRecvComm : public RecvComm {
 };
 
 // ------------------------------------------------------------------------------------------ endpoint impl
-RdmaEndpoint::RdmaEndpoint(Domain* d, int rails) : Endpoint(d), cm(&fab), num_rails(rails) {}
+RdmaEndpoint::RdmaEndpoint(Domain* d, int rails) : Endpoint(d), cm(&fab), num_rails(rails) {
+  // Staging slots for eager payloads and fragments. Page-locked when a CUDA context is current at
+  // the time a block is added (asynchronous copies from page-locked memory do not pass through the
+  // driver's staging buffer); plain memory otherwise, which is all a host-only run needs.
+  Freelist::Options o;
+  o.entry_size = STAGE_BYTES;
+  o.initial_count = 0;
+  o.grow_count = 64;
+  o.max_count = 2048;
+  o.entry_align = 64;
+  o.name = "staging slots";
+  o.reg = [](void* base, size_t bytes, void** handle) {
+    *handle = nullptr;
+    cuda::Context ctx = nullptr;
+    if (cuda::available() && cuda::ctx_get_current(&ctx) == 0 && ctx && cuda::host_register(base, bytes) == 0) *handle = base;
+    return 0;
+  };
+  o.dereg = [](void* handle) { return handle ? cuda::host_unregister(handle) : 0; };
+  staging_ = std::make_unique<Freelist>(std::move(o));
+}
 
 RdmaEndpoint::~RdmaEndpoint() {
   {
@@ -259,11 +366,46 @@ RdmaEndpoint::~RdmaEndpoint() {
              static_cast<unsigned long long>(bytes_kernel), static_cast<unsigned long long>(bytes_copy_engine),
              static_cast<unsigned long long>(bytes_staged), static_cast<unsigned long long>(bytes_host),
              static_cast<unsigned long long>(bytes_eager));
+  // Tear-down may wait for the device: copies that still read staging slots must be over before
+  // the slots are unpinned and unmapped.
+  for (auto s : streams)
+    if (s) cuda::stream_synchronize(s);
+  for (Deferred& d : deferred) {
+    give_event(d.ev);
+    if (d.slot) staging_->entry_free(d.slot);
+  }
+  deferred.clear();
   for (auto& [k, job] : ipc_maps)
     if (job && job->abandon()) job->close_mapping();
   for (auto& [mh, fd] : export_fds) ::close(fd);
+  for (cuda::Event ev : free_events) cuda::event_destroy(ev);
   for (auto s : streams)
     if (s) cuda::stream_destroy(s);
+}
+
+void RdmaEndpoint::prepare_kernels() {
+  if (kernels_tried || !cuda::available()) return;
+  cuda::Context ctx = nullptr;
+  if (cuda::ctx_get_current(&ctx) != 0 || !ctx) return;
+  kernels = NetKernels::get();
+  kernels_tried = true;
+  for (int rail = 0; rail < num_rails; ++rail) rail_stream(rail);
+  for (int i = 0; i < 128; ++i) {
+    cuda::Event ev = nullptr;
+    if (cuda::event_create(&ev) == 0) free_events.push_back(ev);
+  }
+  // the first block of staging slots is page-locked here, not under a running collective
+  if (FreelistEntry* e = staging_->entry_alloc()) staging_->entry_free(e);
+}
+
+cuda::Event RdmaEndpoint::take_event() {
+  if (!free_events.empty()) {
+    cuda::Event ev = free_events.back();
+    free_events.pop_back();
+    return ev;
+  }
+  cuda::Event ev = nullptr;   // the pool ran dry (more copies in flight than it was sized for)
+  return cuda::event_create(&ev) == 0 ? ev : nullptr;
 }
 
 cuda::Stream RdmaEndpoint::rail_stream(int rail) {
@@ -276,7 +418,7 @@ cuda::Stream RdmaEndpoint::rail_stream(int rail) {
   return streams[rail];
 }
 
-void* RdmaEndpoint::map_peer_cuda(PeerMapping* peer, const MrTableEntry* e) {
+void* RdmaEndpoint::map_peer_cuda(PeerMapping* peer, const MrTableEntry* e, bool wait) {
   if (peer->pid == static_cast<uint32_t>(getpid())) return reinterpret_cast<void*>(e->base);  // same process: directly usable
   std::array<uint8_t, 64> handle;
   memcpy(handle.data(), e->ipc_handle, handle.size());
@@ -288,16 +430,29 @@ void* RdmaEndpoint::map_peer_cuda(PeerMapping* peer, const MrTableEntry* e) {
     cuda::Context ctx = nullptr;
     cuda::ctx_get_current(&ctx);
     it = ipc_maps.emplace(key, IpcMapper::instance().submit(e->ipc_handle, ctx, e->kind == static_cast<uint32_t>(MrKind::CUDA_VMM))).first;
-    // once an open has outlasted the grace period the device is evidently busy: later first uses
-    // stall the caller only briefly (an open that does not have to wait for the device takes microseconds)
-    if (it->second) {
-      const uint64_t grace = params().ipc_map_wait_us.get();
-      IpcMapper::wait(*it->second, noted_ipc_wait ? std::min<uint64_t>(grace, 500) : grace);
-    }
   }
   if (!it->second) return nullptr;
+  if (wait && it->second->state.load(std::memory_order_acquire) == 0 && !it->second->waited) {
+    // once an open has outlasted the grace period the device is evidently busy: later first uses
+    // stall the caller only briefly (an open that does not have to wait for the device takes microseconds)
+    it->second->waited = true;
+    const uint64_t grace = params().ipc_map_wait_us.get();
+    IpcMapper::wait(*it->second, noted_ipc_wait ? std::min<uint64_t>(grace, 500) : grace);
+  }
   return it->second->state.load(std::memory_order_acquire) == 1 ? it->second->mapped : nullptr;
 }
+
+void RdmaEndpoint::premap_peer(PeerMapping* peer) {
+  if (!peer || !peer->mr_table || !cuda::available()) return;
+  cuda::Context ctx = nullptr;
+  if (cuda::ctx_get_current(&ctx) != 0 || !ctx) return;
+  for (size_t i = 0; i < FAB_MR_TABLE_SLOTS; ++i) {
+    const MrTableEntry* e = &peer->mr_table[i];
+    if (reinterpret_cast<const std::atomic<uint64_t>*>(&e->key)->load(std::memory_order_acquire) == 0) continue;
+    if (e->kind == static_cast<uint32_t>(MrKind::CUDA_IPC) || e->kind == static_cast<uint32_t>(MrKind::CUDA_VMM)) map_peer_cuda(peer, e, false);
+  }
+}
+
 // Says once per endpoint why payloads for a peer's device memory go through host fragments.
 void RdmaEndpoint::note_unmapped(PeerMapping* peer, const MrTableEntry* e) {
   std::array<uint8_t, 64> handle;
@@ -312,43 +467,40 @@ void RdmaEndpoint::note_unmapped(PeerMapping* peer, const MrTableEntry* e) {
     warned_ipc = true;
   }
 }
+
+// Publishes what a peer needs to write into the registration. For device memory the entry
+// describes the ALLOCATION the registration lies in: its base and size as the driver reports them
+// and the handle taken from that base. A peer adds (address - base) to what its open of the handle
+// returned, which is the driver's contract for a handle; nothing is assumed about what else lies
+// in the same page or the same backing block.
 int RdmaEndpoint::ensure_published(MrHandle* mh) {
   if (!mh) return 0;
   if (published.count({mh, 0})) return 0;
+  static std::atomic<uint64_t> next_serial{1};
   MrTableEntry e;
   memset(&e, 0, sizeof(e));
   e.key = mh->key;
   e.base = reinterpret_cast<uint64_t>(mh->base);
   e.size = mh->size;
   e.kind = static_cast<uint32_t>(mh->kind);
+  e.serial = next_serial.fetch_add(1);
   if (mh->kind == MrKind::CUDA_IPC) {
-    void* base = nullptr;
-    size_t sz = 0;
     int dev = 0;
-    if (cuda::pointer_info(mh->base, &dev, &base, &sz, nullptr) != 0) return -EINVAL;
-    e.base = reinterpret_cast<uint64_t>(base);
-    e.size = sz;
+    cuda::pointer_info(mh->base, &dev, nullptr, nullptr, nullptr);
     e.device = static_cast<uint32_t>(dev);
-    if (cuda::ipc_get_handle(base, e.ipc_handle) != 0) {
+    if (cuda::ipc_get_handle(mh->base, e.ipc_handle) != 0) {
       mh->kind = MrKind::CUDA_STAGED;
       e.kind = static_cast<uint32_t>(MrKind::CUDA_STAGED);
     }
   } else if (mh->kind == MrKind::CUDA_VMM) {
     // memory of the virtual-memory API (NCCL's own buffers are such): peers import the allocation
     // behind the mapped range through a descriptor that this process keeps open for them
-    void* base = nullptr;
-    size_t sz = 0;
     int dev = 0, fd = -1;
-    const bool ok = cuda::pointer_info(mh->base, &dev, &base, &sz, nullptr) == 0 &&
-                    static_cast<char*>(base) + sz >= static_cast<char*>(mh->base) + mh->size &&   // one allocation covers it
-                    cuda::vmm_export_range(base, &fd) == 0;
-    if (ok) {
-      static std::atomic<uint64_t> next_export{1};
-      VmmShare sh{VMM_SHARE_MAGIC, fd, static_cast<uint32_t>(getpid()), 0, sz, next_export.fetch_add(1)};
+    cuda::pointer_info(mh->base, &dev, nullptr, nullptr, nullptr);
+    if (cuda::vmm_export_range(mh->base, &fd) == 0) {
+      VmmShare sh{VMM_SHARE_MAGIC, fd, static_cast<uint32_t>(getpid()), 0, mh->size, e.serial};
       static_assert(sizeof(sh) <= sizeof(e.ipc_handle), "share record fits the handle bytes");
       memcpy(e.ipc_handle, &sh, sizeof(sh));
-      e.base = reinterpret_cast<uint64_t>(base);
-      e.size = sz;
       e.device = static_cast<uint32_t>(dev);
       export_fds[mh] = fd;
     } else {
@@ -361,50 +513,82 @@ int RdmaEndpoint::ensure_published(MrHandle* mh) {
   return rc;
 }
 
+// Host memory: the handle describes the page-rounded range and is shared by every registration
+// inside it (the reference registers page-rounded ranges the same way, src/nccl_ofi_mr.cpp).
+// Device memory: the handle describes the allocation that contains the range and is shared by
+// registrations of that very allocation only; a range that no single allocation covers (an address
+// range backed by several allocations of the virtual-memory API) gets a handle of its own and its
+// payloads travel as fragments.
 int RdmaEndpoint::reg_mr(void* data, size_t size, int type, MrHandle** out) {
   std::lock_guard<std::recursive_mutex> g(ep_lock);
   if (type != NCCL_PTR_HOST) prepare_kernels();
-  MrCache* cache = domain->mr_cache.get();
-  const MrCacheKey key = MrCacheKey::from_iovec(data, size);
-  if (cache) {
-    if (void* h = cache->lookup(key)) {
-      *out = static_cast<MrHandle*>(h);
-      return 0;
-    }
-  }
-  const uint64_t id = domain->mr_keys.allocate();
-  if (id == IdPool::ID_NONE) return -ENOSPC;
-  auto* mh = new MrHandle();
-  mh->key = id + 1;
-  mh->base = data;
-  mh->size = size;
-  mh->type = type;
-  mh->domain = domain;
-  mh->kind = MrKind::HOST;
+  void* base = data;
+  size_t bytes = size;
+  MrKind kind = MrKind::HOST;
+  MrCacheKey key = MrCacheKey::from_iovec(data, size);
   if (type == NCCL_PTR_CUDA) {
+    void* abase = nullptr;
+    size_t asize = 0;
     bool vmm = false;
-    if (!cuda::available() || cuda::pointer_info(data, nullptr, nullptr, nullptr, &vmm) != 0) {
-      domain->mr_keys.free_id(id);
-      delete mh;
-      return -EINVAL;
+    if (!cuda::available() || cuda::pointer_info(data, nullptr, &abase, &asize, &vmm) != 0) return -EINVAL;
+    const bool covered = static_cast<char*>(abase) <= static_cast<char*>(data) &&
+                         static_cast<char*>(data) + size <= static_cast<char*>(abase) + asize;
+    if (covered) {
+      base = abase;
+      bytes = asize;
+      kind = vmm ? MrKind::CUDA_VMM : MrKind::CUDA_IPC;
+    } else {
+      kind = MrKind::CUDA_STAGED;
     }
-    mh->kind = vmm ? MrKind::CUDA_VMM : MrKind::CUDA_IPC;
+    key = MrCacheKey::from_allocation(base, bytes);
+  } else {
+    const uintptr_t lo = round_down<uintptr_t>(reinterpret_cast<uintptr_t>(data), MR_CACHE_PAGE_SIZE);
+    const uintptr_t hi = round_up<uintptr_t>(reinterpret_cast<uintptr_t>(data) + (size ? size : 1), MR_CACHE_PAGE_SIZE);
+    base = reinterpret_cast<void*>(lo);
+    bytes = hi - lo;
   }
-  if (cache) {
-    const int rc = cache->insert(key, mh);
-    if (rc != 0 && rc != -EEXIST) {
-      domain->mr_keys.free_id(id);
-      delete mh;
+  MrCache* cache = domain->mr_cache.get();
+  MrHandle* mh = cache ? static_cast<MrHandle*>(cache->lookup(key)) : nullptr;
+  if (!mh) {
+    const uint64_t id = domain->mr_keys.allocate();
+    if (id == IdPool::ID_NONE) return -ENOSPC;
+    mh = new MrHandle();
+    mh->key = id + 1;
+    mh->base = base;
+    mh->size = bytes;
+    mh->type = type;
+    mh->domain = domain;
+    mh->kind = kind;
+    if (cache) {
+      const int rc = cache->insert(key, mh);
+      if (rc != 0 && rc != -EEXIST) {
+        domain->mr_keys.free_id(id);
+        delete mh;
+        return rc;
+      }
+    }
+    B200NET_TRACE_EVENT(GinRegMr, domain->device->dev_id, 0, 0, size, mh);
+  }
+  if (type == NCCL_PTR_CUDA) {
+    // The export (IPC handle, descriptor) is a driver call: made here, on a set-up path, so that
+    // the first receive does not have to make it under a running collective. Peers that are
+    // already connected start mapping what the other side has published so far.
+    const int rc = ensure_published(mh);
+    if (rc != 0) {
+      dereg_mr(mh);
       return rc;
     }
+    for (auto& [id, sc] : send_comms) premap_peer(sc->peer);
   }
-  B200NET_TRACE_EVENT(GinRegMr, domain->device->dev_id, 0, 0, size, mh);
   *out = mh;
   return 0;
 }
 
-int RdmaEndpoint::reg_mr_dmabuf(void* data, size_t size, int type, uint64_t, int, MrHandle** mh) {
-  // On NVLink a dma-buf descriptor adds nothing over the virtual address: register the range.
+int RdmaEndpoint::reg_mr_dmabuf(void* data, size_t size, int type, uint64_t offset, int fd, MrHandle** mh) {
+  // On NVLink a peer reaches the memory through a mapping of the allocation, which the virtual
+  // address identifies; the descriptor names the same allocation. It is checked, not exported.
+  if (fd < 0) return -EINVAL;
+  (void)offset;
   return reg_mr(data, size, type, mh);
 }
 
@@ -426,11 +610,25 @@ int RdmaEndpoint::dereg_mr(MrHandle* mh) {
   return 0;
 }
 
+void RdmaEndpoint::fail_endpoint(const char* why, int rc) {
+  NET_WARN("%s (%d): endpoint aborted", why, rc);
+  PluginStats::bump(PluginStats::get().requests_failed);
+  invalidate();
+}
+
 void RdmaEndpoint::handle_dgram(const DgramHdr& h, const void* payload) {
   if (cm.handle_dgram(h, payload)) return;
   switch (h.type) {
     case static_cast<uint16_t>(DgramType::WRITE_COMPLETION): {
       const auto* wc = static_cast<const WriteCompletion*>(payload);
+      if (!deferred.empty()) {
+        // fragments that arrived before this completion are still on their way to the device
+        Deferred d;
+        d.kind = Deferred::WRITE_COMPLETION;
+        d.wc = *wc;
+        deferred.push_back(d);
+        break;
+      }
       auto it = recv_comms.find(wc->remote_comm_id);
       if (it != recv_comms.end()) it->second->on_write_completion(*wc);
       break;
@@ -450,17 +648,79 @@ void RdmaEndpoint::handle_dgram(const DgramHdr& h, const void* payload) {
       break;
     }
     case DGRAM_DEVICE_FRAG: {
+      // A piece of a payload whose sender cannot map this process's device memory. The ring cell is
+      // recycled on return, so the bytes move to a staging slot; the copy to the device is queued
+      // on the receive stream and the write completion that follows waits for it in `deferred`.
       const auto* fh = static_cast<const DeviceFragHdr*>(payload);
-      cuda::Stream s = rail_stream(0);
-      if (s) {
-        cuda::memcpy_async(reinterpret_cast<void*>(fh->remote_addr), static_cast<const char*>(payload) + sizeof(*fh),
-                           fh->len, s);
-        cuda::stream_synchronize(s);  // the ring cell is recycled on return
+      cuda::Stream st = rail_stream(0);
+      FreelistEntry* slot = fh->len <= STAGE_BYTES ? staging_->entry_alloc() : nullptr;
+      cuda::Event ev = slot ? take_event() : nullptr;
+      if (!st) {
+        fail_endpoint("no stream for a fragment copy", -EIO);
+      } else if (slot && ev) {
+        memcpy(slot->ptr, static_cast<const char*>(payload) + sizeof(*fh), fh->len);
+        int rc = cuda::memcpy_async(reinterpret_cast<void*>(fh->remote_addr), slot->ptr, fh->len, st);
+        if (rc == 0) rc = cuda::event_record(ev, st);
+        if (rc != 0) {
+          fail_endpoint("copy of a fragment to the device failed", rc);
+        } else {
+          Deferred d;
+          d.kind = Deferred::FRAG_COPY;
+          d.ev = ev;
+          d.slot = slot;
+          deferred.push_back(d);
+          slot = nullptr;
+          ev = nullptr;
+        }
+      } else {
+        // no staging slot or event left: copy straight from the ring cell and wait for this one
+        // copy (it runs on the copy engine and depends on no kernel)
+        int rc = cuda::memcpy_async(reinterpret_cast<void*>(fh->remote_addr), static_cast<const char*>(payload) + sizeof(*fh), fh->len, st);
+        if (rc == 0) rc = cuda::stream_synchronize(st);
+        if (rc != 0) fail_endpoint("copy of a fragment to the device failed", rc);
       }
+      if (slot) staging_->entry_free(slot);
+      give_event(ev);
       break;
     }
     default:
       NET_INFO(NCCL_NET, "unexpected datagram type %u dropped", h.type);
+  }
+}
+
+void RdmaEndpoint::retire_deferred() {
+  while (!deferred.empty()) {
+    Deferred& d = deferred.front();
+    if (d.ev) {
+      const int q = cuda::event_query(d.ev);
+      if (q == 1) return;
+      if (q < 0) {
+        fail_endpoint("a copy on the receive stream failed", q);
+        // drop what was queued: the endpoint refuses every later call
+        for (Deferred& x : deferred) {
+          give_event(x.ev);
+          if (x.slot) staging_->entry_free(x.slot);
+        }
+        deferred.clear();
+        return;
+      }
+      give_event(d.ev);
+    }
+    if (d.slot) staging_->entry_free(d.slot);
+    const Deferred done = d;
+    deferred.pop_front();
+    if (done.kind == Deferred::WRITE_COMPLETION) {
+      auto it = recv_comms.find(done.wc.remote_comm_id);
+      if (it != recv_comms.end()) it->second->on_write_completion(done.wc);
+    } else if (done.kind == Deferred::EAGER_COPY) {
+      auto it = recv_comms.find(done.comm_id);
+      if (it == recv_comms.end()) continue;
+      void* elem = nullptr;
+      MsgElemType ty;
+      MsgStatus st;
+      if (it->second->msgbuff->retrieve(done.seq, &elem, &ty, &st) == MsgResult::SUCCESS && ty == MsgElemType::REQ)
+        it->second->finish_sub(static_cast<RdmaRecvReq*>(elem), done.idx);
+    }
   }
 }
 
@@ -470,10 +730,17 @@ int RdmaEndpoint::progress() {
   const int budget = params().cq_read_count.get() * 16;
   B200NET_TRACE_EVENT(ProcessCompletionsRdma, domain->device->dev_id, 0, 0, 0, this);
   fab.poll(budget, [this](const DgramHdr& h, const void* p) { handle_dgram(h, p); });
+  if (!deferred.empty()) retire_deferred();
+  if (outbox_total > 0) flush_outboxes();
   // retry queue: strictly in order, stop at the first post that is still back-pressured
   while (!pending.empty()) {
-    const int rc = pending.front()();
-    if (rc == -EAGAIN) break;
+    auto live = live_send_reqs.find(pending.front());
+    if (live != live_send_reqs.end() && live->second->state == ReqState::PENDING) {
+      RdmaSendReq* r = live->second;
+      const int rc = r->comm->post_stripes(r);
+      if (rc == -EAGAIN) break;
+      if (rc != 0 && rc != -EINPROGRESS) r->state = ReqState::ERROR;
+    }
     pending.pop_front();
     B200NET_TRACE_EVENT(PendingQueueRemove, domain->device->dev_id, 0, 0, 0, this);
   }
@@ -551,6 +818,7 @@ int RdmaEndpoint::connect(ConnHandle* handle, SendComm** scomm, int) {
   sc->remote_comm_id = reinterpret_cast<const ConnRespPayload*>(resp.data())->comm_id;
   sc->connector.reset();
   sc->connected = true;
+  premap_peer(sc->peer);   // whatever the receiver has registered by now is mapped ahead of the first send
   handle->state.stage = CommStage::COMM_CONNECTED;
   handle->state.comm = nullptr;
   *scomm = sc;
@@ -624,6 +892,19 @@ int RdmaListenComm::close() {
 // ------------------------------------------------------------------------------------------ send side
 RdmaSendComm::~RdmaSendComm() = default;
 
+void RdmaSendComm::release(RdmaSendReq* r) {
+  RdmaEndpoint* e = rep();
+  --inflight;
+  e->live_send_reqs.erase(r->serial);
+  // whatever the request still holds goes back to its pool; a copy that is still running keeps
+  // its kernel slot (the kernel may yet write the completion word)
+  for (int i = 0; i < r->nstripes; ++i) e->give_event(r->stripes[i].event);
+  e->give_event(r->bounce_ev);
+  e->give_event(r->stage_ev);
+  if (r->stage) e->staging().entry_free(r->stage);
+  e->send_reqs.give(r);
+}
+
 void RdmaSendComm::consume_entry(int idx, int num_recvs) {
   consumed_mask |= static_cast<uint8_t>(1u << idx);
   if (__builtin_popcount(consumed_mask) >= num_recvs) {
@@ -653,7 +934,7 @@ void RdmaSendComm::bind_eager_queue() {
     }
     r->seq = next_seq;
     r->recv_idx = static_cast<uint8_t>(idx);
-    r->state = ReqState::COMPLETED;
+    if (r->state == ReqState::PENDING) r->state = ReqState::COMPLETED;
     B200NET_TRACE_EVENT(SendEagerComplete, dev_id, local_comm_id, r->seq, r->size, r);
     const uint16_t before = next_seq;
     it = eager_queue.erase(it);
@@ -668,8 +949,68 @@ bool RdmaSendComm::tag_is_queued(int tag) const {
   return false;
 }
 
+// Eager datagrams leave in eager_seq order, each as soon as its payload is in host memory: a host
+// source at once, a device source when the pack kernel has set the slot's completion word or the
+// copy engine's event has completed. Nothing here waits; a payload that is not ready (or a full
+// ring) leaves the rest of the outbox for the next call.
+void RdmaSendComm::flush_outbox() {
+  RdmaEndpoint* e = rep();
+  while (!outbox.empty()) {
+    RdmaSendReq* r = outbox.front();
+    const void* src = r->data;
+    bool failed = false;
+    if (r->pack_slot >= 0) {
+      if (!e->kernels->eager_done(r->pack_slot)) {
+        if (PluginStats::now_ns() - r->t_outbox_ns < 10000000000ull) return;
+        NET_WARN("eager pack kernel did not complete within 10 s");   // the slot stays reserved: the kernel may still write it
+        r->pack_slot = -1;
+        failed = true;
+      } else {
+        src = e->kernels->eager_slot(r->pack_slot) + 16;
+      }
+    } else if (r->stage_ev) {
+      const int q = cuda::event_query(r->stage_ev);
+      if (q == 1) return;
+      failed = q < 0;
+      src = r->stage->ptr;
+    }
+    int rc = failed ? -EIO : e->fab.send(peer, DgramType::EAGER, 0, &r->ehdr, sizeof(r->ehdr), src, r->size);
+    if (rc == -EAGAIN) return;
+    if (r->pack_slot >= 0) e->kernels->eager_release(r->pack_slot);  // the datagram holds a copy
+    r->pack_slot = -1;
+    if (r->stage) e->staging().entry_free(r->stage);
+    r->stage = nullptr;
+    e->give_event(r->stage_ev);
+    r->stage_ev = nullptr;
+    outbox.pop_front();
+    --e->outbox_total;
+    if (rc != 0) {
+      // the receiver waits for this sequence number before it takes later eager messages: the
+      // connection cannot continue
+      r->state = ReqState::ERROR;
+      e->fail_endpoint("an eager payload could not be sent", rc);
+      return;
+    }
+    r->dgram_sent = true;
+    e->bytes_eager += r->size;
+    PluginStats::bump(PluginStats::get().eager_sends);
+  }
+}
+
+void RdmaEndpoint::flush_outboxes() {
+  for (auto& [id, sc] : send_comms)
+    if (!sc->outbox.empty()) sc->flush_outbox();
+}
+
 int RdmaSendComm::post_stripes(RdmaSendReq* r) {
   RdmaEndpoint* e = rep();
+  if (r->bounce_ev) {   // the device source is still on its way into the bounce buffer
+    const int q = cuda::event_query(r->bounce_ev);
+    if (q == 1) return -EINPROGRESS;
+    if (q < 0) return -EIO;
+    e->give_event(r->bounce_ev);
+    r->bounce_ev = nullptr;
+  }
   const MrTableEntry* mr = FabricEndpoint::mr_lookup(peer, r->target.mr_key);
   const uint32_t kind = r->via_frags ? static_cast<uint32_t>(MrKind::CUDA_STAGED)
                                      : (mr ? mr->kind : static_cast<uint32_t>(MrKind::HOST));
@@ -677,13 +1018,21 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
   const char* src = r->bounce.empty() ? static_cast<const char*>(r->data) : reinterpret_cast<const char*>(r->bounce.data());
   bool all_done = true;
   bool back_pressure = false;   // some ring was full: the post must be retried in order
-  for (Stripe& s : r->stripes) {
+  for (int si = 0; si < r->nstripes; ++si) {
+    Stripe& s = r->stripes[si];
     if (!s.complete) {
       if (kind == static_cast<uint32_t>(MrKind::CUDA_IPC) || kind == static_cast<uint32_t>(MrKind::CUDA_VMM)) {
         if (!s.posted) {
           void* mapped = e->map_peer_cuda(peer, mr);
           cuda::Stream st = e->rail_stream(s.rail);
           if (!mapped || !st) return -EIO;
+          // the peer's address minus the base of the allocation its handle stands for, applied to
+          // what the open of that handle returned here; never outside that allocation
+          if (r->target.buff_addr < mr->base || r->target.buff_addr + r->size > mr->base + mr->size) {
+            NET_WARN("receive buffer %#llx+%zu lies outside its registration %#llx+%llu", static_cast<unsigned long long>(r->target.buff_addr),
+                     r->size, static_cast<unsigned long long>(mr->base), static_cast<unsigned long long>(mr->size));
+            return -EINVAL;
+          }
           char* dst = static_cast<char*>(mapped) + (r->target.buff_addr - mr->base) + s.offset;
           // device source: the plugin's own copy kernel moves the stripe over NVLink and sets a
           // completion word in pinned memory; anything else goes through the copy engine
@@ -691,11 +1040,10 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
           if (nk && nk->copy_flag(dst, src + s.offset, s.len, st, 0, &s.kslot) == 0) {
             e->bytes_kernel += s.len;
           } else {
-            e->bytes_copy_engine += s.len;
             s.kslot = -1;
-            if (cuda::event_create(&s.event) != 0 || cuda::memcpy_async(dst, src + s.offset, s.len, st) != 0 ||
-                cuda::event_record(s.event, st) != 0)
-              return -EIO;
+            s.event = e->take_event();
+            if (!s.event || cuda::memcpy_async(dst, src + s.offset, s.len, st) != 0 || cuda::event_record(s.event, st) != 0) return -EIO;
+            e->bytes_copy_engine += s.len;
           }
           s.posted = true;
           B200NET_TRACE_EVENT(SendWriteSegmentStart, dev_id, local_comm_id, r->seq, s.len, r);
@@ -713,7 +1061,7 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
           const int q = cuda::event_query(s.event);
           if (q < 0) return -EIO;
           if (q == 0) {
-            cuda::event_destroy(s.event);
+            e->give_event(s.event);
             s.event = nullptr;
             s.done = s.len;
             s.complete = true;
@@ -771,7 +1119,7 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
       }
     }
     if (s.complete && !s.notified) {
-      WriteCompletion wc{remote_comm_id, r->seq, r->recv_idx, static_cast<uint8_t>(r->stripes.size()), s.len};
+      WriteCompletion wc{remote_comm_id, r->seq, r->recv_idx, static_cast<uint8_t>(r->nstripes), s.len};
       // data that travelled as fragments must be applied before its completion is seen
       const bool staged = kind == static_cast<uint32_t>(MrKind::CUDA_STAGED) ||
                           (kind == static_cast<uint32_t>(MrKind::HOST) && e->fab.writes_are_staged(peer));
@@ -808,23 +1156,32 @@ int RdmaSendComm::start_rendezvous(RdmaSendReq* r, const CtrlEntry& e) {
   const bool mappable = mr && (mr->kind == static_cast<uint32_t>(MrKind::CUDA_IPC) || mr->kind == static_cast<uint32_t>(MrKind::CUDA_VMM));
   if (mappable && !rep()->map_peer_cuda(peer, mr)) {
     // the peer's device memory cannot be mapped into this process (another container, a driver
-    // without IPC): the payload travels as fragments that the receiver copies to its device
+    // without IPC) or its mapping has not arrived yet: the payload travels as fragments that the
+    // receiver copies to its device
     rep()->note_unmapped(peer, mr);
     r->via_frags = true;
   }
   if ((dst_host || r->via_frags || (mr && mr->kind == static_cast<uint32_t>(MrKind::CUDA_STAGED))) && r->size &&
       !cuda::is_host_pointer(r->data)) {
-    // device source, destination only reachable through host memory: bounce once
+    // device source, destination only reachable through host memory: fetch it once; the stripes
+    // start when the event behind the copy has completed (post_stripes polls it)
     r->bounce.resize(r->size);
     cuda::Stream st = rep()->rail_stream(0);
-    if (!st || cuda::memcpy_async(r->bounce.data(), r->data, r->size, st) != 0 || cuda::stream_synchronize(st) != 0)
+    r->bounce_ev = rep()->take_event();
+    if (!st || !r->bounce_ev || cuda::memcpy_async(r->bounce.data(), r->data, r->size, st) != 0 ||
+        cuda::event_record(r->bounce_ev, st) != 0)
       return -EIO;
   }
   Schedule* sc = sched->get_schedule(r->size, rep()->num_rails);
   if (!sc) return -ENOMEM;
-  for (size_t i = 0; i < sc->num_xfer_infos; ++i)
-    r->stripes.push_back(Stripe{sc->xfers[i].rail_id, sc->xfers[i].offset, sc->xfers[i].msg_size, 0, nullptr, false,
-                                false, false});
+  r->nstripes = 0;
+  for (size_t i = 0; i < sc->num_xfer_infos && i < static_cast<size_t>(MAX_NUM_RAILS); ++i) {
+    Stripe& s = r->stripes[r->nstripes++];
+    s = Stripe{};
+    s.rail = sc->xfers[i].rail_id;
+    s.offset = sc->xfers[i].offset;
+    s.len = sc->xfers[i].msg_size;
+  }
   sched->release_schedule(sc);
   r->state = ReqState::PENDING;
   return 0;
@@ -837,6 +1194,7 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
   if (!e->is_active()) return -ECONNABORTED;
   if (peer_closed) return -ENOTCONN;
   e->progress();
+  if (!e->is_active()) return -ECONNABORTED;
   if (inflight >= NET_MAX_SEND_REQUESTS) return 0;
   bind_eager_queue();
   auto* box = static_cast<CtrlMsg*>(mailbox->data());
@@ -847,37 +1205,32 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
   NET_TRACE(NCCL_NET, "send: seq %u idx %d eagerq %zu ready0 %x size %zu", next_seq, idx, eager_queue.size(),
             box[next_seq % MAILBOX_SLOTS].entries[0].ready.load(), size);
   if (idx >= 0) {
-    auto* r = new RdmaSendReq();
+    RdmaSendReq* r = e->send_reqs.take();
+    if (!r) return 0;   // pool exhausted: NCCL calls again after completions
     r->comm = this;
     r->data = data;
     r->size = size;
     r->tag = tag;
     r->seq = next_seq;
     r->recv_idx = static_cast<uint8_t>(idx);
+    r->serial = e->next_req_serial++;
+    ++inflight;
+    e->live_send_reqs[r->serial] = r;
     const int rc = start_rendezvous(r, box[next_seq % MAILBOX_SLOTS].entries[idx]);
     if (rc != 0) {
-      delete r;
+      release(r);
       return rc;
     }
     B200NET_TRACE_EVENT(Send, dev_id, local_comm_id, r->seq, r->size, r);
     PluginStats::bump(PluginStats::get().rendezvous_sends);
     consume_entry(idx, n);
     bind_eager_queue();   // if that completed the group, queued sends may fit the next one
-    ++inflight;
-    r->serial = e->next_req_serial++;
-    e->live_send_reqs[r->serial] = r;
     const int prc = post_stripes(r);
     if (prc != 0 && prc != -EAGAIN && prc != -EINPROGRESS) {
       r->state = ReqState::ERROR;
     } else if (prc == -EAGAIN) {
       B200NET_TRACE_EVENT(PendingQueueInsert, dev_id, local_comm_id, r->seq, r->size, r);
-      e->pending.push_back([this, e, r, serial = r->serial]() {
-        auto live = e->live_send_reqs.find(serial);
-        if (live == e->live_send_reqs.end() || live->second != r || r->state != ReqState::PENDING) return 0;
-        const int rc2 = post_stripes(r);
-        if (rc2 != 0 && rc2 != -EAGAIN && rc2 != -EINPROGRESS) r->state = ReqState::ERROR;
-        return rc2 == -EAGAIN ? -EAGAIN : 0;
-      });
+      e->pending.push_back(r->serial);
     }
     *req = r;
     return 0;
@@ -886,65 +1239,66 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
   const size_t eager_max = params().eager_max_size.get();
   const bool eager_size_ok = eager_max > 0 && size <= eager_max && size + sizeof(EagerHdr) <= FAB_LARGE_CELL &&
                              static_cast<int>(eager_queue.size()) < MAX_EAGER_PENDING;
-  const void* eager_src = data;
-  int eager_slot = -1;
-  NetKernels* nk = nullptr;
-  std::vector<uint8_t> eager_bounce;
-  if (eager_size_ok && size > 0 && !cuda::is_host_pointer(data)) {
-    // device payload: the pack kernel writes header + payload + flag into a pinned slot and the
-    // datagram is sent from there; without the kernels the copy engine fetches the payload
-    nk = size <= NetKernels::EAGER_PAYLOAD_MAX ? e->kernels : nullptr;
+  if (!eager_size_ok) return 0;  // neither control message nor eager: *req stays null and NCCL retries
+  RdmaSendReq* r = e->send_reqs.take();
+  if (!r) return 0;
+  r->comm = this;
+  r->data = data;
+  r->size = size;
+  r->tag = tag;
+  r->eager = true;
+  r->state = ReqState::PENDING;
+  memset(&r->ehdr, 0, sizeof(r->ehdr));
+  r->ehdr.remote_comm_id = remote_comm_id;
+  r->ehdr.eager_seq = next_eager_seq;
+  r->ehdr.base_seq = next_seq;
+  r->ehdr.base_mask = consumed_mask;
+  r->ehdr.tag = tag;
+  r->ehdr.size = size;
+  const bool dev_src = size > 0 && !cuda::is_host_pointer(data);
+  if (dev_src) {
+    // device payload: the pack kernel writes header + payload + flag into a pinned slot; without
+    // the kernels the copy engine fetches the payload into a staging slot. Either way the datagram
+    // leaves from the outbox once the payload has arrived; this call does not wait for it.
+    NetKernels* nk = size <= NetKernels::EAGER_PAYLOAD_MAX ? e->kernels : nullptr;
     cuda::Stream st = e->rail_stream(0);
-    if (!st) return -EIO;
-    if (nk && nk->eager_pack(data, size, next_eager_seq, size, st, &eager_slot) == 0) {
-      const auto t0 = std::chrono::steady_clock::now();
-      while (!nk->eager_done(eager_slot)) {
-        if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(2)) {
-          // the slot stays reserved: the kernel may still write it
-          NET_WARN("eager pack kernel did not complete within 2 s");
-          return -EIO;
-        }
-      }
-      eager_src = nk->eager_slot(eager_slot) + 16;
-    } else {
-      eager_slot = -1;
-      eager_bounce.resize(size);
-      if (cuda::memcpy_async(eager_bounce.data(), data, size, st) != 0 || cuda::stream_synchronize(st) != 0) return -EIO;
-      eager_src = eager_bounce.data();
+    bool ok = st != nullptr;
+    if (ok && !(nk && nk->eager_pack(data, size, next_eager_seq, size, st, &r->pack_slot) == 0)) {
+      r->pack_slot = -1;
+      r->stage = e->staging().entry_alloc();
+      r->stage_ev = r->stage ? e->take_event() : nullptr;
+      ok = r->stage && r->stage_ev && cuda::memcpy_async(r->stage->ptr, data, size, st) == 0 && cuda::event_record(r->stage_ev, st) == 0;
     }
-  }
-  if (eager_size_ok) {
-    EagerHdr h;
-    memset(&h, 0, sizeof(h));
-    h.remote_comm_id = remote_comm_id;
-    h.eager_seq = next_eager_seq;
-    h.base_seq = next_seq;
-    h.base_mask = consumed_mask;
-    h.tag = tag;
-    h.size = size;
-    const int rc = e->fab.send(peer, DgramType::EAGER, 0, &h, sizeof(h), eager_src, size);
-    if (eager_slot >= 0) nk->eager_release(eager_slot);  // the datagram holds a copy
-    if (rc == 0) {
-      e->bytes_eager += size;
-      PluginStats::bump(PluginStats::get().eager_sends);
+    if (!ok) {
+      e->give_event(r->stage_ev);
+      if (r->stage) e->staging().entry_free(r->stage);
+      e->send_reqs.give(r);
+      return -EIO;
     }
-    if (rc == -EAGAIN) return 0;  // ring full: NCCL calls again
-    if (rc != 0) return rc;
-    auto* r = new RdmaSendReq();
-    r->comm = this;
-    r->data = data;
-    r->size = size;
-    r->tag = tag;
-    r->eager = true;
-    r->state = ReqState::PENDING;
-    ++next_eager_seq;
-    ++inflight;
-    eager_queue.push_back(r);
-    B200NET_TRACE_EVENT(SendEagerStart, dev_id, local_comm_id, h.eager_seq, size, r);
-    *req = r;
-    return 0;
+  } else if (outbox.empty()) {
+    const int rc = e->fab.send(peer, DgramType::EAGER, 0, &r->ehdr, sizeof(r->ehdr), data, size);
+    if (rc != 0) {
+      e->send_reqs.give(r);
+      return rc == -EAGAIN ? 0 : rc;  // ring full: NCCL calls again
+    }
+    r->dgram_sent = true;
+    e->bytes_eager += size;
+    PluginStats::bump(PluginStats::get().eager_sends);
   }
-  return 0;  // neither control message nor eager: *req stays null and NCCL retries
+  r->serial = e->next_req_serial++;
+  e->live_send_reqs[r->serial] = r;
+  ++next_eager_seq;
+  ++inflight;
+  eager_queue.push_back(r);
+  if (!r->dgram_sent) {
+    r->t_outbox_ns = PluginStats::now_ns();
+    outbox.push_back(r);
+    ++e->outbox_total;
+    flush_outbox();
+  }
+  B200NET_TRACE_EVENT(SendEagerStart, dev_id, local_comm_id, r->ehdr.eager_seq, size, r);
+  *req = r;
+  return 0;
 }
 
 int RdmaSendReq::test(int* done, int* sizes) {
@@ -953,25 +1307,25 @@ int RdmaSendReq::test(int* done, int* sizes) {
   *done = 0;
   if (!e->is_active()) return -ECONNABORTED;
   e->progress();
-  if (state == ReqState::PENDING && eager) comm->bind_eager_queue();
-  if (state == ReqState::PENDING && !eager) {
+  if (!e->is_active()) return -ECONNABORTED;
+  if (eager) {
+    if (!dgram_sent && state != ReqState::ERROR) comm->flush_outbox();
+    if (state == ReqState::PENDING) comm->bind_eager_queue();
+  } else if (state == ReqState::PENDING) {
     const int rc = comm->post_stripes(this);
     if (rc != 0 && rc != -EAGAIN && rc != -EINPROGRESS) state = ReqState::ERROR;
   }
   if (state == ReqState::ERROR) {
-    --comm->inflight;
-    e->live_send_reqs.erase(serial);
-    delete this;
+    PluginStats::bump(PluginStats::get().requests_failed);
+    comm->release(this);
     return -EIO;
   }
-  if (state == ReqState::COMPLETED) {
+  if (state == ReqState::COMPLETED && (!eager || dgram_sent)) {
     *done = 1;
     if (sizes) sizes[0] = static_cast<int>(size);
     B200NET_TRACE_EVENT(SendEnd, comm->dev_id, comm->local_comm_id, seq, size, this);
-    if (PluginStats::get().histograms_on()) PluginStats::get().sample_send(size, stripes.size(), PluginStats::since(t_post_ns));
-    --comm->inflight;
-    e->live_send_reqs.erase(serial);
-    delete this;
+    if (PluginStats::get().histograms_on()) PluginStats::get().sample_send(size, static_cast<size_t>(nstripes), PluginStats::since(t_post_ns));
+    comm->release(this);
   }
   return 0;
 }
@@ -986,6 +1340,8 @@ int RdmaSendComm::close() {
       e->invalidate();
       e->pending.clear();
     }
+    e->outbox_total -= static_cast<int>(outbox.size());
+    outbox.clear();
     if (!params().disable_close_message.get() && peer && connected) {
       CloseMsg m{remote_comm_id, nonce};
       e->fab.send(peer, DgramType::CLOSE, 0, &m, sizeof(m));
@@ -998,19 +1354,32 @@ int RdmaSendComm::close() {
 }
 
 // ------------------------------------------------------------------------------------------ receive side
-RdmaRecvComm::~RdmaRecvComm() = default;
+RdmaRecvComm::~RdmaRecvComm() {
+  for (EagerRx& rx : eager_rx)
+    if (rx.slot) rep()->staging().entry_free(rx.slot);
+}
+
+void RdmaRecvComm::release(RdmaRecvReq* r) { rep()->recv_reqs.give(r); }
 
 void RdmaRecvComm::finish_sub(RdmaRecvReq* r, int idx) {
   if (r->subs[idx].done) return;
   r->subs[idx].done = true;
   eager_taken[r->seq % MAILBOX_SLOTS] |= static_cast<uint8_t>(1u << idx);
   if (++r->ndone == r->n) {
-    r->state = ReqState::COMPLETED;
+    if (r->state != ReqState::ERROR) r->state = ReqState::COMPLETED;
     MsgStatus st;
     msgbuff->complete(r->seq, &st);
     posted.remove(r);
-    if (r->user_released) delete r;
+    if (r->user_released) release(r);
   }
+}
+
+// The payload of one sub-receive could not be delivered: the request reports an error from test()
+// instead of a size (its other sub-receives still retire the bookkeeping).
+void RdmaRecvComm::fail_sub(RdmaRecvReq* r, int idx) {
+  r->state = ReqState::ERROR;
+  PluginStats::bump(PluginStats::get().requests_failed);
+  finish_sub(r, idx);
 }
 
 void RdmaRecvComm::on_write_completion(const WriteCompletion& wc) {
@@ -1033,15 +1402,19 @@ void RdmaRecvComm::on_write_completion(const WriteCompletion& wc) {
 void RdmaRecvComm::on_eager(const EagerHdr& h, const void* data) {
   EagerRx rx;
   rx.hdr = h;
-  rx.data.assign(static_cast<const uint8_t*>(data), static_cast<const uint8_t*>(data) + h.size);
-  // keep the list ordered by eager_seq (datagrams of one sender arrive in order; be safe anyway)
-  auto it = eager_rx.end();
-  while (it != eager_rx.begin()) {
-    auto prev = std::prev(it);
-    if (static_cast<int16_t>(h.eager_seq - prev->hdr.eager_seq) >= 0) break;
-    it = prev;
+  rx.slot = nullptr;
+  if (h.size) {
+    rx.slot = h.size <= STAGE_BYTES ? rep()->staging().entry_alloc() : nullptr;
+    if (!rx.slot) {
+      rep()->fail_endpoint("no staging slot for an eager payload", -ENOMEM);
+      return;
+    }
+    memcpy(rx.slot->ptr, data, h.size);
   }
-  eager_rx.insert(it, std::move(rx));
+  // keep the list ordered by eager_seq (datagrams of one sender arrive in order; be safe anyway)
+  size_t at = eager_rx.size();
+  while (at > 0 && static_cast<int16_t>(h.eager_seq - eager_rx[at - 1].hdr.eager_seq) < 0) --at;
+  eager_rx.insert(eager_rx.begin() + static_cast<std::ptrdiff_t>(at), rx);
   // eager_arrived: every message sent before it is here (they arrive in order; a gap would hold
   // later ones back until it is filled)
   for (bool advanced = true; advanced;) {
@@ -1061,12 +1434,17 @@ void RdmaRecvComm::on_eager(const EagerHdr& h, const void* data) {
 // has a free entry of its tag: free means taken neither by a send before it (base_mask, for the
 // base group) nor by an eager message matched here. A message that finds no such entry yet waits,
 // and so does every later message of the same tag; messages of other tags go on.
+//
+// A payload for host memory is copied at once. A payload for device memory is queued on the
+// receive stream from its (page-locked) staging slot and the sub-receive completes when the event
+// behind the copy has; nothing here waits for the device.
 void RdmaRecvComm::match_eager() {
+  RdmaEndpoint* e = rep();
   int blocked_tags[MAX_EAGER_PENDING + 1];
   int nblocked = 0;
-  auto it = eager_rx.begin();
-  while (it != eager_rx.end()) {
-    EagerRx& rx = *it;
+  size_t at = 0;
+  while (at < eager_rx.size()) {
+    EagerRx& rx = eager_rx[at];
     if (static_cast<int16_t>(rx.hdr.eager_seq - eager_arrived) >= 0) return;  // an earlier one is still missing
     bool blocked = false;
     for (int k = 0; k < nblocked; ++k) blocked = blocked || blocked_tags[k] == rx.hdr.tag;
@@ -1088,24 +1466,39 @@ void RdmaRecvComm::match_eager() {
     }
     if (!target) {
       if (!blocked && nblocked < MAX_EAGER_PENDING + 1) blocked_tags[nblocked++] = rx.hdr.tag;
-      ++it;
+      ++at;
       continue;
     }
     SubRecv& s = target->subs[target_idx];
     const size_t nbytes = std::min<size_t>(rx.hdr.size, s.cap);
-    if (nbytes) {
-      if (s.mem_type == NCCL_PTR_CUDA) {
-        cuda::Stream st = rep()->rail_stream(0);
-        if (st) {
-          cuda::memcpy_async(s.buf, rx.data.data(), nbytes, st);
-          cuda::stream_synchronize(st);
-        }
-      } else {
-        memcpy(s.buf, rx.data.data(), nbytes);
-      }
-    }
+    FreelistEntry* slot = rx.slot;
+    eager_rx.erase(eager_rx.begin() + static_cast<std::ptrdiff_t>(at));   // `rx` is gone from here on
+    eager_taken[target->seq % MAILBOX_SLOTS] |= static_cast<uint8_t>(1u << target_idx);
     s.received = nbytes;
-    it = eager_rx.erase(it);
+    if (nbytes && s.mem_type == NCCL_PTR_CUDA) {
+      cuda::Stream st = e->rail_stream(0);
+      cuda::Event ev = st ? e->take_event() : nullptr;
+      int rc = (st && ev) ? cuda::memcpy_async(s.buf, slot->ptr, nbytes, st) : -EIO;
+      if (rc == 0) rc = cuda::event_record(ev, st);
+      if (rc != 0) {
+        NET_WARN("copy of an eager payload to the device failed (%d)", rc);
+        e->give_event(ev);
+        e->staging().entry_free(slot);
+        fail_sub(target, target_idx);
+        continue;
+      }
+      Deferred d;
+      d.kind = Deferred::EAGER_COPY;
+      d.ev = ev;
+      d.slot = slot;
+      d.comm_id = local_comm_id;
+      d.seq = target->seq;
+      d.idx = static_cast<uint8_t>(target_idx);
+      e->deferred.push_back(d);
+      continue;
+    }
+    if (nbytes) memcpy(s.buf, slot->ptr, nbytes);
+    if (slot) e->staging().entry_free(slot);
     finish_sub(target, target_idx);
   }
 }
@@ -1117,17 +1510,19 @@ int RdmaRecvComm::recv(int n, void** data, size_t* sizes, int* tags, MrHandle** 
   if (!e->is_active()) return -ECONNABORTED;
   if (n < 1 || n > MAX_RECVS) return -EINVAL;
   e->progress();
+  if (!e->is_active()) return -ECONNABORTED;
   if (inflight >= NET_MAX_REQUESTS) return 0;
   // the mailbox slot of this sequence number must not still describe a live group
   const uint16_t seq = next_seq;
-  auto* r = new RdmaRecvReq();
+  RdmaRecvReq* r = e->recv_reqs.take();
+  if (!r) return 0;
   r->comm = this;
   r->seq = seq;
   r->n = n;
   r->no_completion = optional && params().early_completion.get();
   MsgStatus st;
   if (msgbuff->insert(seq, r, MsgElemType::REQ, &st) != MsgResult::SUCCESS) {
-    delete r;
+    release(r);
     return 0;  // window full: try again after completions
   }
   eager_taken[seq % MAILBOX_SLOTS] = 0;
@@ -1137,10 +1532,10 @@ int RdmaRecvComm::recv(int n, void** data, size_t* sizes, int* tags, MrHandle** 
   for (int i = 0; i < n; ++i) {
     r->subs[i] = SubRecv{data[i], sizes[i], tags[i], mh ? mh[i] : nullptr, (mh && mh[i]) ? mh[i]->type : NCCL_PTR_HOST};
     if (mh && mh[i]) {
-      const int rc = e->ensure_published(mh[i]);
+      const int rc = e->ensure_published(mh[i]);   // device registrations were published when they were made
       if (rc != 0) {
         msgbuff->complete(seq, &st);
-        delete r;
+        release(r);
         return rc;
       }
     }
@@ -1172,6 +1567,13 @@ int RdmaRecvReq::test(int* done, int* sizes) {
   *done = 0;
   if (!e->is_active()) return -ECONNABORTED;
   e->progress();
+  if (!e->is_active()) return -ECONNABORTED;
+  if (state == ReqState::ERROR && ndone == n) {
+    // a payload could not be delivered (its copy to the device failed)
+    --comm->inflight;
+    comm->release(this);
+    return -EIO;
+  }
   if (state == ReqState::COMPLETED) {
     *done = 1;
     if (sizes)
@@ -1184,8 +1586,8 @@ int RdmaRecvReq::test(int* done, int* sizes) {
       if (PluginStats::get().histograms_on()) PluginStats::get().sample_recv(total, PluginStats::since(t_post_ns));
     }
     --comm->inflight;
-    delete this;
-  } else if (no_completion) {
+    comm->release(this);
+  } else if (no_completion && state != ReqState::ERROR) {
     // early completion: report the posted sizes now, retire the bookkeeping when the writes land
     *done = 1;
     if (sizes)
@@ -1197,10 +1599,11 @@ int RdmaRecvReq::test(int* done, int* sizes) {
 }
 
 int RdmaFlushReq::test(int* done, int*) {
-  std::lock_guard<std::recursive_mutex> g(ep->ep_lock);
-  ep->progress();
+  RdmaEndpoint* e = ep;
+  std::lock_guard<std::recursive_mutex> g(e->ep_lock);
+  e->progress();
   *done = 1;
-  delete this;
+  e->flush_reqs.give(this);
   return 0;
 }
 
@@ -1218,8 +1621,8 @@ int RdmaRecvComm::flush(int n, void**, int* sizes, MrHandle** mh, Request** req)
   B200NET_TRACE_EVENT(Flush, dev_id, local_comm_id, 0, static_cast<uint64_t>(n), this);
   std::atomic_thread_fence(std::memory_order_acq_rel);
   if (any && params().cuda_flush_enable.get()) cuda::flush_gpudirect_rdma_writes();
-  *req = new RdmaFlushReq(e);
-  return 0;
+  *req = e->flush_reqs.take(e);
+  return *req ? 0 : -ENOMEM;
 }
 
 int RdmaRecvComm::close() {
@@ -1231,6 +1634,9 @@ int RdmaRecvComm::close() {
       e->invalidate();
       e->pending.clear();
     }
+    // copies queued for this communicator's receives complete into nothing: keep only their slots and events
+    for (Deferred& d : e->deferred)
+      if (d.kind == Deferred::EAGER_COPY && d.comm_id == local_comm_id) d.kind = Deferred::FRAG_COPY;
     if (!params().disable_close_message.get() && peer) {
       CloseMsg m{remote_comm_id, nonce};
       e->fab.send(peer, DgramType::CLOSE, 0, &m, sizeof(m));

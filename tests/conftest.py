@@ -10,6 +10,20 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 GPU (run with -m gpu on a GPU box)")
 
 
+# Files whose tests run after everything else, in this order: the plugin's device-buffer scenarios
+# (two processes per test on the GPU) and then the entry point that allocates nothing, so that a
+# run that stops at the first failure has already run every other test.
+RUN_LAST = ("test_net_device_gpu.py", "test_zz_no_alloc.py")
+
+
+def pytest_collection_modifyitems(config, items):
+    def rank(item):
+        name = os.path.basename(str(item.fspath))
+        return RUN_LAST.index(name) + 1 if name in RUN_LAST else 0
+
+    items.sort(key=rank)   # stable: every other test keeps its place
+
+
 @pytest.fixture(scope="session")
 def built():
     """Make sure the native libraries are built (incremental, no-op when fresh)."""

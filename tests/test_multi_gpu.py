@@ -1,5 +1,6 @@
 """Multi-GPU tests: each launches a torchrun job over the visible GPUs (2..8) and checks its exit code."""
 import os
+import signal
 import socket
 import subprocess
 import sys
@@ -23,9 +24,18 @@ def _run(worker: str, nproc: int, env_extra: dict | None = None, timeout: int = 
     env.update(env_extra or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(ROOT / "tests" / "workers" / worker)]
-    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
-    assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-4000:]
-    return res.stdout
+    # The job runs in a process group of its own: when the limit passes, the launcher AND its
+    # workers are ended (a worker left behind would keep its kernels spinning on the GPU).
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env, cwd=ROOT,
+                            start_new_session=True)
+    try:
+        out, err = proc.communicate(timeout=timeout)
+    except subprocess.TimeoutExpired:
+        os.killpg(proc.pid, signal.SIGKILL)
+        out, err = proc.communicate()
+        raise AssertionError(f"{worker} on {nproc} ranks did not finish within {timeout} s\n" + out[-3000:] + err[-3000:])
+    assert proc.returncode == 0, out[-4000:] + err[-4000:]
+    return out
 
 
 def _ngpus() -> int:
@@ -61,12 +71,8 @@ def test_unmodified_nccl_runs_over_the_net_plugin(tmp_path):
         "NCCL_P2P_DISABLE": "1", "NCCL_SHM_DISABLE": "1", "NCCL_DEBUG": "INFO", "NCCL_DEBUG_SUBSYS": "INIT,NET",
         "NCCL_DEBUG_FILE": str(log) + ".%p", "NCCL_NVLS_ENABLE": "0", "NCCL_CUMEM_ENABLE": "0",
     }
-    # One retry: NCCL's first collective over the plugin has stalled on rare runs (twice in about
-    # ten on the development machines, cause not yet found); a stall is cut off after three minutes.
-    try:
-        out = _run("nccl_plugin_worker.py", 2, env, timeout=180)
-    except subprocess.TimeoutExpired:
-        out = _run("nccl_plugin_worker.py", 2, env, timeout=180)
+    # a job that stalls is cut off after three minutes and fails the test; it is never run again
+    out = _run("nccl_plugin_worker.py", 2, env, timeout=180)
     assert "nccl plugin worker OK" in out
     text = "".join(p.read_text() for p in tmp_path.glob("nccl.log.*"))
     assert "B200NVL" in text, text[-3000:]
