@@ -45,6 +45,7 @@ struct Api {
   CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
   CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
                            void**, void**) = nullptr;
+  CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
   CUresult (*MemHostAlloc)(void**, size_t, unsigned) = nullptr;
   CUresult (*MemFreeHost)(void*) = nullptr;
   CUresult (*MemHostRegister)(void*, size_t, unsigned) = nullptr;
@@ -120,6 +121,7 @@ void do_init() {
   sym(g.ModuleUnload, "cuModuleUnload", false);
   sym(g.ModuleGetFunction, "cuModuleGetFunction", false);
   sym(g.LaunchKernel, "cuLaunchKernel", false);
+  sym(g.FuncSetAttribute, "cuFuncSetAttribute", false);
   sym(g.MemHostAlloc, "cuMemHostAlloc", false);
   sym(g.MemFreeHost, "cuMemFreeHost", false);
   sym(g.MemHostRegister, "cuMemHostRegister", false);
@@ -272,6 +274,10 @@ int module_get_function(void* module, const char* name, void** fn) {
   const int rc = rc_of(g.ModuleGetFunction(&f, static_cast<CUmodule>(module), name));
   *fn = f;
   return rc;
+}
+int func_set_max_dynamic_smem(void* fn, int bytes) {
+  if (!available() || !g.FuncSetAttribute) return -ENOSYS;
+  return rc_of(g.FuncSetAttribute(static_cast<CUfunction>(fn), CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, bytes));
 }
 int launch_kernel(void* fn, unsigned grid, unsigned block, unsigned smem_bytes, Stream s, void** args) {
   if (!available() || !g.LaunchKernel) return -ENOSYS;

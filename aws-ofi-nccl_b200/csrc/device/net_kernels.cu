@@ -6,6 +6,11 @@
 //                       over NVLink by however many CTAs the host chose for the stripe, then ONE
 //                       release-ordered store of a completion word in pinned host memory, so the
 //                       proxy thread polls a cache line instead of calling into the driver.
+//  b200net_copy_bulk  : the same transfer for 16-byte aligned stripes, driven by the bulk-copy (TMA)
+//                       unit: one thread per CTA keeps four 32 KiB pieces in flight, global ->
+//                       shared memory -> the peer's memory, so a handful of CTAs with one warp each
+//                       hold megabytes in flight over NVLink and leave the SMs' issue slots to the
+//                       collective kernel that is running beside it. No load is multicast.
 //  b200net_eager_pack : small device payload -> one pinned host slot laid out as
 //                       [header 16 B][payload][flag 8 B]: payload and header first, the flag last
 //                       with release ordering, so a reader that sees the flag sees the whole slot.
@@ -23,18 +28,42 @@ __device__ __forceinline__ void st_release_sys_u64(unsigned long long* p, unsign
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
-// All threads of all CTAs call it; returns true in every thread of the CTA that finished last.
-__device__ __forceinline__ bool last_cta(unsigned int* counter) {
+constexpr unsigned int kCtaFailed = 0x80000000u;   // set in the slot's counter by a CTA whose wait ran out
+
+// All threads of all CTAs call it; returns non-zero in every thread of the CTA that finished last:
+// 1 when every CTA copied its share, 2 when one of them gave up.
+__device__ __forceinline__ int last_cta(unsigned int* counter, bool failed = false) {
   __shared__ int is_last;
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
+    if (failed) atomicOr(counter, kCtaFailed);
     const unsigned int prev = atomicAdd(counter, 1u);
-    is_last = prev == gridDim.x - 1;
+    is_last = (prev & ~kCtaFailed) == gridDim.x - 1 ? (((prev & kCtaFailed) || failed) ? 2 : 1) : 0;
     if (is_last) *counter = 0;  // rearm for the next launch that uses this slot
   }
   __syncthreads();
-  return is_last != 0;
+  return is_last;
+}
+
+__device__ __forceinline__ unsigned int smem_u32(const void* p) { return static_cast<unsigned int>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits for the phase of an mbarrier; gives up (false) once `deadline_ns` of the global timer has passed.
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned int bar, unsigned int parity, unsigned long long deadline_ns) {
+  for (unsigned int spins = 0;; ++spins) {
+    unsigned int ok;
+    asm volatile(
+        "{\n .reg .pred P;\n mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n selp.u32 %0, 1, 0, P;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((spins & 1023u) == 1023u && global_ns() > deadline_ns) return false;
+  }
 }
 
 }  // namespace
@@ -63,6 +92,70 @@ extern "C" __global__ void __launch_bounds__(512)
     for (unsigned long long b = tid; b < bytes; b += nthreads) dst[b] = src[b];
   }
   if (last_cta(counter) && threadIdx.x == 0) st_release_sys_u64(flag, flag_value);
+}
+
+// dst, src and bytes are multiples of 16 (the host checks). One warp per CTA; lane 0 does the work.
+// Dynamic shared memory: kBulkStages pieces of kBulkChunk bytes, then one mbarrier per stage.
+// The completion word receives flag_value, or flag_value | 1 << 63 when a wait ran out (the host
+// then fails the request instead of reporting bytes that may not have landed).
+constexpr unsigned int kBulkChunk = 32768;
+constexpr int kBulkStages = 4;
+extern "C" __global__ void __launch_bounds__(32)
+    b200net_copy_bulk(unsigned char* dst, const unsigned char* src, unsigned long long bytes, unsigned int* counter,
+                      unsigned long long* flag, unsigned long long flag_value, unsigned long long wait_limit_ns) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + kBulkStages * kBulkChunk);
+  bool failed = false;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kBulkStages; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bars[s])));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const unsigned long long nchunks = (bytes + kBulkChunk - 1) / kBulkChunk;
+    // chunks blockIdx.x, blockIdx.x + gridDim.x, ... belong to this CTA
+    const unsigned long long mine = nchunks > blockIdx.x ? (nchunks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const unsigned long long deadline = global_ns() + wait_limit_ns;
+    auto chunk_off = [&](unsigned long long k) { return (blockIdx.x + k * gridDim.x) * static_cast<unsigned long long>(kBulkChunk); };
+    auto chunk_len = [&](unsigned long long k) {
+      const unsigned long long off = chunk_off(k);
+      return static_cast<unsigned int>(bytes - off < kBulkChunk ? bytes - off : kBulkChunk);
+    };
+    auto load = [&](unsigned long long k) {
+      const int s = static_cast<int>(k % kBulkStages);
+      const unsigned int len = chunk_len(k);
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&bars[s])), "r"(len) : "memory");
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                       smem_u32(smem + s * kBulkChunk)),
+                   "l"(src + chunk_off(k)), "r"(len), "r"(smem_u32(&bars[s]))
+                   : "memory");
+    };
+    unsigned long long loaded = 0;
+    for (; loaded < mine && loaded < kBulkStages; ++loaded) load(loaded);
+    unsigned long long k = 0;
+    for (; k < mine; ++k) {
+      const int s = static_cast<int>(k % kBulkStages);
+      if (!mbar_wait_bounded(smem_u32(&bars[s]), static_cast<unsigned int>((k / kBulkStages) & 1), deadline)) {
+        failed = true;
+        break;
+      }
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + chunk_off(k)),
+                   "r"(smem_u32(smem + s * kBulkChunk)), "r"(chunk_len(k))
+                   : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      // the stage of the piece before this one is free once its store has read shared memory
+      if (k >= 1 && loaded < mine) {
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        load(loaded++);
+      }
+    }
+    if (failed) {
+      // loads already issued may still write this CTA's shared memory: give each one more bounded wait
+      const unsigned long long again = global_ns() + wait_limit_ns;
+      for (unsigned long long j = k; j < loaded; ++j)
+        mbar_wait_bounded(smem_u32(&bars[j % kBulkStages]), static_cast<unsigned int>((j / kBulkStages) & 1), again);
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+  const int last = last_cta(counter, failed);
+  if (last && threadIdx.x == 0) st_release_sys_u64(flag, last == 2 ? (flag_value | (1ull << 63)) : flag_value);
 }
 
 // One CTA. slot: [hdr0 u64][hdr1 u64][payload ...][pad to 8][flag u64 at slot + flag_off].

@@ -45,6 +45,8 @@ int stream_synchronize(Stream s);
 int module_load_data(const void* image, void** module);
 int module_unload(void* module);
 int module_get_function(void* module, const char* name, void** fn);
+// Raises the dynamic shared memory a kernel may be launched with (above the 48 KiB default).
+int func_set_max_dynamic_smem(void* fn, int bytes);
 int launch_kernel(void* fn, unsigned grid, unsigned block, unsigned smem_bytes, Stream s, void** args);
 // Page-locked host memory that the GPU can write (portable, mapped).
 int host_alloc(void** ptr, size_t bytes);

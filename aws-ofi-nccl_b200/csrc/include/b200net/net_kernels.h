@@ -20,6 +20,8 @@ class NetKernels {
   static constexpr int NUM_FLAGS = 1024;
   static constexpr int NUM_EAGER_SLOTS = 64;
   static constexpr size_t EAGER_PAYLOAD_MAX = 8192;
+  static constexpr size_t BULK_MIN = 65536;
+  static constexpr unsigned BULK_SMEM = 4 * 32768 + 64;   // four pieces and their mbarriers
   static constexpr size_t EAGER_SLOT_BYTES = 16 + EAGER_PAYLOAD_MAX + 8 + 8;  // header, payload, pad, flag
 
   // The instance of the calling thread's current CUDA context; nullptr when there is no GPU, no
@@ -28,8 +30,12 @@ class NetKernels {
 
   // dst[0,n) = src[0,n) on stream `st` with `ctas` CTAs (0 = size based); *slot receives the
   // completion slot to poll with done() and to give back with release(). -EAGAIN: no slot free.
+  // 16-byte aligned transfers of at least BULK_MIN bytes go to the bulk-copy kernel (one thread per
+  // CTA driving cp.async.bulk through shared memory) unless B200NET_COPY_KERNEL_BULK=0.
   int copy_flag(void* dst, const void* src, size_t n, cuda::Stream st, int ctas, int* slot);
   bool done(int slot) const;
+  // 0 while the copy runs, 1 when it has completed, -EIO when the kernel gave up on a wait.
+  int status(int slot) const;
   void release(int slot);
 
   // Packs a device payload (n <= EAGER_PAYLOAD_MAX) and a 16-byte header into a pinned slot.
@@ -43,9 +49,11 @@ class NetKernels {
  private:
   NetKernels() = default;
   int init();
+  int copy_impl(void* dst, const void* src, size_t n, cuda::Stream st, int ctas, int* slot, bool warm_bulk);
   void* module_ = nullptr;
   void* fn_copy_ = nullptr;
   void* fn_pack_ = nullptr;
+  void* fn_bulk_ = nullptr;      // null: not in the image or shared memory cannot be raised
   volatile uint64_t* flags_ = nullptr;   // pinned host, NUM_FLAGS words
   uint32_t* counters_ = nullptr;         // device, NUM_FLAGS words, zero when idle
   uint8_t* eager_ = nullptr;             // pinned host, NUM_EAGER_SLOTS slots

@@ -133,12 +133,14 @@ struct Params {
                                   "how long a send waits for the first mapping of a peer's device allocation (the open "
                                   "runs on a helper thread because it can wait for the device to go idle); after that "
                                   "payloads travel through host fragments until the mapping has arrived"};
-  Param<bool> nccl_device_buffers{"NCCL_DEVICE_BUFFERS", false,
-                                  "make NCCL hand its device buffers to the plugin (sets NCCL_NET_GDR_LEVEL=SYS and "
-                                  "NCCL_NET_GDR_READ=1, stops advertising dma-buf): payloads then move with the copy "
-                                  "kernels over NVLink instead of through host memory"};
+  Param<bool> nccl_device_buffers{"NCCL_DEVICE_BUFFERS", true,
+                                  "make NCCL hand its device buffers to the plugin (publishes NCCL_NET_GDR_LEVEL=SYS and "
+                                  "NCCL_NET_GDR_READ=1 unless the user has set them): payloads then move with the copy "
+                                  "kernels over NVLink instead of through host memory; 0 keeps NCCL's chunks in host memory"};
   Param<bool> copy_kernel{"COPY_KERNEL", true,
                           "move device payloads with the plugin's own copy / eager-pack kernels (0: copy engine only)"};
+  Param<bool> copy_kernel_bulk{"COPY_KERNEL_BULK", true,
+                               "aligned stripes of 64 KiB and more use the bulk-copy (TMA) kernel; 0: the vector-copy kernel only"};
   Param<uint64_t> copy_kernel_ctas{"COPY_KERNEL_CTAS", 0, "CTAs per copy-kernel launch (0: chosen from the size)"};
   Param<uint64_t> min_stripe_size{"MIN_STRIPE_SIZE", 128 * 1024, "smallest stripe when a message is split over rails"};
   Param<uint64_t> sched_max_small_rr_size{"SCHED_MAX_SMALL_RR_SIZE", 64, "messages below this go to one rail round-robin"};

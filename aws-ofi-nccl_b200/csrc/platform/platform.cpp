@@ -22,16 +22,17 @@ int PlatformB200::init(std::string*) {
 }
 
 std::vector<std::pair<std::string, std::string>> PlatformB200::nccl_env() const {
-  // chunks sized for copy-engine stripes over NVLink (MiB-sized copies) rather than for NIC MTUs
-  // NCCL_NET_GDR_LEVEL is left alone on purpose: with NCCL's default the topology distance to this
-  // transport's virtual NIC keeps NCCL's own chunks in host memory. Forcing device buffers through
-  // (NCCL_NET_GDR_LEVEL=SYS) stalled NCCL's first collective: the peer buffer is mapped on first use,
-  // from the proxy thread, while NCCL's kernel is already waiting for that very transfer.
+  // Chunks sized for MiB-sized copies over NVLink rather than for NIC MTUs. NCCL attaches this
+  // transport's virtual NICs to the CPU (they are no PCI devices), which is farther from the GPUs
+  // than its default limit for handing device buffers to a network, so the limit is raised: the
+  // "NIC" is the GPU's own NVLink port. LL128 stays off: it relies on a network that delivers the
+  // bytes of a 128-byte line in order, which a copy kernel with many threads does not promise.
   std::vector<std::pair<std::string, std::string>> env = {{"NCCL_BUFFSIZE", "33554432"},
                                                           {"NCCL_P2P_NET_CHUNKSIZE", "4194304"},
                                                           {"NCCL_NVLS_CHUNKSIZE", "524288"},
-                                                          {"NCCL_NET_FORCE_FLUSH", "0"}};
-  if (params().nccl_device_buffers.get()) {   // opt-in, see the comment above
+                                                          {"NCCL_NET_FORCE_FLUSH", "0"},
+                                                          {"NCCL_PROTO", "^LL128"}};
+  if (params().nccl_device_buffers.get()) {
     env.emplace_back("NCCL_NET_GDR_LEVEL", "SYS");
     env.emplace_back("NCCL_NET_GDR_READ", "1");
   }

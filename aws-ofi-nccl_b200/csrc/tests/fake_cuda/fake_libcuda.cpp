@@ -177,7 +177,7 @@ void run_later(std::function<void()> fn) {
   g_wcv.notify_one();
 }
 
-enum FakeFn : uintptr_t { FN_COPY_FLAG = 0x101, FN_EAGER_PACK = 0x102 };
+enum FakeFn : uintptr_t { FN_COPY_FLAG = 0x101, FN_EAGER_PACK = 0x102, FN_COPY_BULK = 0x103 };
 
 // ------------------------------------------------------------------------------------------ entry points
 CUresult fInit(unsigned) {
@@ -454,16 +454,18 @@ CUresult fModuleLoadData(CUmodule* m, const void* image) {
   return CUDA_SUCCESS;
 }
 CUresult fModuleUnload(CUmodule) { return CUDA_SUCCESS; }
+CUresult fFuncSetAttribute(CUfunction, CUfunction_attribute, int) { return CUDA_SUCCESS; }
 CUresult fModuleGetFunction(CUfunction* f, CUmodule, const char* name) {
   if (!strcmp(name, "b200net_copy_flag")) *f = reinterpret_cast<CUfunction>(FN_COPY_FLAG);
   else if (!strcmp(name, "b200net_eager_pack")) *f = reinterpret_cast<CUfunction>(FN_EAGER_PACK);
+  else if (!strcmp(name, "b200net_copy_bulk")) *f = reinterpret_cast<CUfunction>(FN_COPY_BULK);
   else return CUDA_ERROR_NOT_FOUND;
   return CUDA_SUCCESS;
 }
 CUresult fLaunchKernel(CUfunction f, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void** args,
                        void**) {
   const uintptr_t id = reinterpret_cast<uintptr_t>(f);
-  if (id == FN_COPY_FLAG) {
+  if (id == FN_COPY_FLAG || id == FN_COPY_BULK) {
     auto* dst = *static_cast<unsigned char**>(args[0]);
     auto* src = *static_cast<const unsigned char**>(args[1]);
     const unsigned long long bytes = *static_cast<unsigned long long*>(args[2]);
@@ -655,7 +657,7 @@ const Entry kTable[] = {
     E("cuMemUnmap", fMemUnmap), E("cuMemSetAccess", fMemSetAccess), E("cuMemExportToShareableHandle", fMemExportToShareableHandle),
     E("cuMemImportFromShareableHandle", fMemImportFromShareableHandle), E("cuMemRetainAllocationHandle", fMemRetainAllocationHandle),
     E("cuCtxGetDevice", fCtxGetDevice), E("cuMemHostRegister", fMemHostRegister), E("cuMemHostUnregister", fMemHostUnregister),
-    E("cuCtxSynchronize", fCtxSynchronize),
+    E("cuCtxSynchronize", fCtxSynchronize), E("cuFuncSetAttribute", fFuncSetAttribute),
 };
 
 }  // namespace

@@ -673,6 +673,65 @@ static int scenario_bandwidth(int sock) {
   return close_pair(&p);
 }
 
+// One-way throughput of isend / irecv / test on buffers of the mode under test (device memory with
+// FUNC_NET_DEVICE=1: the copy kernel over NVLink when the two ranks sit on two GPUs), for several
+// message sizes with eight messages in flight. Prints one line per size on rank 1; the last
+// window of every size is checked byte for byte.
+static int scenario_device_bandwidth(int sock) {
+  Pair p;
+  if (connect_pair(0, sock, &p)) return 1;
+  const int window = 8;
+  const size_t max_n = getenv("FUNC_NET_BW_MAX") ? strtoull(getenv("FUNC_NET_BW_MAX"), nullptr, 0) : (32u << 20);
+  std::vector<TestBuf> bufs(window);
+  std::vector<void*> mhs(window);
+  void* comm = g_rank == 0 ? p.s : p.r;
+  for (int i = 0; i < window; ++i) {
+    if (buf_alloc(&bufs[i], max_n)) FAIL("buffer allocation failed");
+    std::vector<uint8_t> pat(max_n);
+    fill(pat, 300 + i + 50 * g_rank);
+    memcpy(bufs[i].host(), pat.data(), max_n);
+    if (bufs[i].to_device()) FAIL("copy to the device failed");
+    OK(net->regMr(comm, bufs[i].data(), max_n, buf_type(), &mhs[i]));
+  }
+  for (size_t n = 64u << 10; n <= max_n; n *= 4) {
+    const int rounds = n >= (8u << 20) ? 12 : 40;
+    if (barrier(sock)) FAIL("barrier");
+    double secs = 0;
+    for (int r = -2; r < rounds; ++r) {   // two warm-up rounds (first use maps the peer's buffers)
+      const auto t0 = Clock::now();
+      std::vector<void*> reqs(window);
+      for (int i = 0; i < window; ++i) {
+        if (g_rank == 0) {
+          if (post_send(p.s, bufs[i].data(), n, 9, mhs[i], &reqs[i])) return 1;
+        } else {
+          void* d = bufs[i].data();
+          size_t sz = n;
+          int tag = 9;
+          if (post_recv(p.r, 1, &d, &sz, &tag, &mhs[i], &reqs[i])) return 1;
+        }
+      }
+      if (wait_all(reqs)) return 1;
+      if (r >= 0) secs += std::chrono::duration<double>(Clock::now() - t0).count();
+    }
+    if (g_rank == 1) {
+      for (int i = 0; i < window; ++i) {
+        std::vector<uint8_t> want(max_n);
+        fill(want, 300 + i);
+        if (bufs[i].from_device(0, n)) FAIL("copy from the device failed");
+        if (memcmp(bufs[i].host(), want.data(), n)) FAIL("payload %d of %zu bytes differs after the bandwidth run", i, n);
+      }
+      fprintf(stderr, "[rank 1] %s bandwidth %8zu KiB x %d in flight: %8.2f GB/s one way, %7.1f us per message\n",
+              device_mode() ? "device" : "host", n >> 10, window, rounds * window * static_cast<double>(n) / secs / 1e9,
+              secs / (rounds * window) * 1e6);
+    }
+  }
+  for (int i = 0; i < window; ++i) {
+    OK(net->deregMr(comm, mhs[i]));
+    buf_free(&bufs[i]);
+  }
+  return close_pair(&p);
+}
+
 static int scenario_threads(int) {
   // each thread gets its own endpoint: 4 threads connect to themselves (loopback) concurrently
   std::vector<std::thread> th;
@@ -908,6 +967,7 @@ static const Scenario kScenarios[] = {
     {"inflight_close", scenario_inflight_close}, {"threads", scenario_threads},
     {"bandwidth", scenario_bandwidth},       {"proxy_pattern", scenario_proxy_pattern},
     {"device_transfer", scenario_device_transfer}, {"eager_multirecv", scenario_eager_multirecv},
+    {"device_bandwidth", scenario_device_bandwidth},
 };
 
 static int run_rank(const char* so, const char* only, int sock) {

@@ -49,7 +49,11 @@ int main() {
   struct Case { size_t n, src_off, dst_off; int ctas; };
   const Case cases[] = {{8, 0, 0, 0},       {1, 3, 5, 0},          {4096, 0, 0, 1},        {4099, 16, 32, 0},
                         {65536, 1, 0, 0},   {(1u << 20) + 7, 0, 0, 0}, {(16u << 20), 16, 16, 0}, {(64u << 20), 0, 0, 32},
-                        {12345, 7, 7, 3}};
+                        {12345, 7, 7, 3},
+                        // 16-byte aligned stripes of 64 KiB and more: the bulk-copy kernel (one piece, a ragged
+                        // last piece, more CTAs than pieces, many pieces per CTA)
+                        {65536, 0, 0, 0},   {65536 + 16, 16, 48, 0}, {(1u << 20) + 16, 0, 32, 5}, {(3u << 20) + 48, 64, 16, 0},
+                        {32768 * 3, 0, 0, 16}, {(48u << 20), 0, 0, 2}};
   for (const Case& c : cases) {
     // poison the destination so stale bytes cannot pass
     std::vector<uint8_t> poison(c.n + 64, 0xA5);

@@ -102,6 +102,7 @@ class RdmaSendReq : public Request {
   // `bounce`; the stripes start when the event behind that copy has completed.
   std::vector<uint8_t> bounce;
   cuda::Event bounce_ev = nullptr;
+  bool src_dev = false;         // the source is device memory (from its registration, else asked of the driver)
   bool via_frags = false;       // the target registration has an IPC handle that could not be opened here
   uint64_t serial = 0;          // unique per endpoint; queued retries name the request by it
   // eager sends: the datagram leaves from the communicator's outbox, in eager_seq order, once the
@@ -1014,7 +1015,7 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
   const MrTableEntry* mr = FabricEndpoint::mr_lookup(peer, r->target.mr_key);
   const uint32_t kind = r->via_frags ? static_cast<uint32_t>(MrKind::CUDA_STAGED)
                                      : (mr ? mr->kind : static_cast<uint32_t>(MrKind::HOST));
-  const bool src_dev = !r->bounce.empty() ? false : !cuda::is_host_pointer(r->data);
+  const bool src_dev = r->bounce.empty() && r->src_dev;
   const char* src = r->bounce.empty() ? static_cast<const char*>(r->data) : reinterpret_cast<const char*>(r->bounce.data());
   bool all_done = true;
   bool back_pressure = false;   // some ring was full: the post must be retried in order
@@ -1051,7 +1052,14 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
         if (s.kslot >= 0) {
           NetKernels* nk = e->kernels;
           if (!nk) return -EIO;
-          if (nk->done(s.kslot)) {
+          const int ks = nk->status(s.kslot);
+          if (ks < 0) {
+            NET_WARN("the copy kernel gave up on a wait: stripe of %zu bytes not delivered", s.len);
+            nk->release(s.kslot);
+            s.kslot = -1;
+            return ks;
+          }
+          if (ks == 1) {
             nk->release(s.kslot);
             s.kslot = -1;
             s.done = s.len;
@@ -1161,8 +1169,7 @@ int RdmaSendComm::start_rendezvous(RdmaSendReq* r, const CtrlEntry& e) {
     rep()->note_unmapped(peer, mr);
     r->via_frags = true;
   }
-  if ((dst_host || r->via_frags || (mr && mr->kind == static_cast<uint32_t>(MrKind::CUDA_STAGED))) && r->size &&
-      !cuda::is_host_pointer(r->data)) {
+  if ((dst_host || r->via_frags || (mr && mr->kind == static_cast<uint32_t>(MrKind::CUDA_STAGED))) && r->size && r->src_dev) {
     // device source, destination only reachable through host memory: fetch it once; the stripes
     // start when the event behind the copy has completed (post_stripes polls it)
     r->bounce.resize(r->size);
@@ -1187,7 +1194,7 @@ int RdmaSendComm::start_rendezvous(RdmaSendReq* r, const CtrlEntry& e) {
   return 0;
 }
 
-int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** req) {
+int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle* mh, Request** req) {
   RdmaEndpoint* e = rep();
   std::lock_guard<std::recursive_mutex> g(e->ep_lock);
   *req = nullptr;
@@ -1197,6 +1204,7 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
   if (!e->is_active()) return -ECONNABORTED;
   if (inflight >= NET_MAX_SEND_REQUESTS) return 0;
   bind_eager_queue();
+  const bool src_is_device = size > 0 && (mh ? mh->type == NCCL_PTR_CUDA : !cuda::is_host_pointer(data));
   auto* box = static_cast<CtrlMsg*>(mailbox->data());
   int n = 0;
   // a send may take an entry directly unless an eager send of the same tag is still waiting for
@@ -1213,6 +1221,7 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
     r->tag = tag;
     r->seq = next_seq;
     r->recv_idx = static_cast<uint8_t>(idx);
+    r->src_dev = src_is_device;
     r->serial = e->next_req_serial++;
     ++inflight;
     e->live_send_reqs[r->serial] = r;
@@ -1255,7 +1264,7 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle*, Request** re
   r->ehdr.base_mask = consumed_mask;
   r->ehdr.tag = tag;
   r->ehdr.size = size;
-  const bool dev_src = size > 0 && !cuda::is_host_pointer(data);
+  const bool dev_src = src_is_device;
   if (dev_src) {
     // device payload: the pack kernel writes header + payload + flag into a pinned slot; without
     // the kernels the copy engine fetches the payload into a staging slot. Either way the datagram

@@ -15,6 +15,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import signal
 import socket
 import subprocess
 import sys
@@ -98,7 +99,7 @@ def main(argv=None) -> int:
         return 0
     result = {"gpus": args.gpus}
     for arm in args.arms:
-        env = dict(os.environ, NCCL_P2P_DISABLE="1", NCCL_SHM_DISABLE="1", NCCL_NVLS_ENABLE="0", NCCL_CUMEM_ENABLE="0")
+        env = dict(os.environ, NCCL_P2P_DISABLE="1", NCCL_SHM_DISABLE="1", NCCL_NVLS_ENABLE="0")
         if arm == "plugin":
             env.update(NCCL_NET_PLUGIN="ofi-b200", LD_LIBRARY_PATH=f"{LIB}:" + env.get("LD_LIBRARY_PATH", ""))
         else:
@@ -107,14 +108,18 @@ def main(argv=None) -> int:
                "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), "-m",
                "aws_ofi_nccl_b200.utils.bench_plugin", "--worker", "--min-bytes", str(args.min_bytes), "--max-bytes",
                str(args.max_bytes), "--warmup", str(args.warmup), "--iters", str(args.iters)]
+        # a process group of its own, so that a job that runs out of time is ended with all its ranks
+        proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env, start_new_session=True)
         try:
-            res = subprocess.run(cmd, capture_output=True, text=True, timeout=args.timeout, env=env)
+            out, err = proc.communicate(timeout=args.timeout)
         except subprocess.TimeoutExpired:
+            os.killpg(proc.pid, signal.SIGKILL)
+            proc.communicate()
             print(f"{arm}: timed out", flush=True)
             continue
-        got = [ln for ln in res.stdout.splitlines() if ln.startswith("PLUGIN_BENCH_ROWS ")]
-        if res.returncode != 0 or not got:
-            print(f"{arm}: failed\n{res.stderr[-1500:]}", flush=True)
+        got = [ln for ln in out.splitlines() if ln.startswith("PLUGIN_BENCH_ROWS ")]
+        if proc.returncode != 0 or not got:
+            print(f"{arm}: failed\n{err[-1500:]}", flush=True)
             continue
         result[arm] = json.loads(got[-1][len("PLUGIN_BENCH_ROWS "):])
     if "plugin" in result:
