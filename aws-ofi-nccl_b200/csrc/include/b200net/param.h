@@ -139,6 +139,9 @@ struct Params {
                                   "kernels over NVLink instead of through host memory; 0 keeps NCCL's chunks in host memory"};
   Param<bool> copy_kernel{"COPY_KERNEL", true,
                           "move device payloads with the plugin's own copy / eager-pack kernels (0: copy engine only)"};
+  Param<uint64_t> stall_report_ms{"STALL_REPORT_MS", 30000,
+                                  "an endpoint with requests in flight that sees no datagram, completion or accepted post for "
+                                  "this long writes one report of its queues to the log (0: never)"};
   Param<bool> copy_kernel_bulk{"COPY_KERNEL_BULK", true,
                                "aligned stripes of 64 KiB and more use the bulk-copy (TMA) kernel; 0: the vector-copy kernel only"};
   Param<uint64_t> copy_kernel_ctas{"COPY_KERNEL_CTAS", 0, "CTAs per copy-kernel launch (0: chosen from the size)"};
@@ -158,6 +161,8 @@ struct Params {
   EnumParam tuner_type{"TUNER_TYPE", "Measured", {"Internal", "Region", "Model", "Measured"}, "tuner back-end"};
   Param<int> tuner_num_channels{"TUNER_NUM_CHANNELS", 8, ""};
   Param<float> tuner_net_latency{"TUNER_NET_LATENCY", 20.f, "network latency assumed by the model tuner (us)"};
+  Param<bool> tuner_self_register{"TUNER_SELF_REGISTER", true,
+                                  "publish NCCL_TUNER_PLUGIN=<this library> at start-up unless the user has set it"};
   Param<std::string> tuner_table{"TUNER_TABLE", "", "path of a measured-bandwidth JSON table"};
   Param<std::string> platform{"PLATFORM", "", "force a platform implementation by name"};
   EnumParam nvtx_trace_dimension{"NVTX_TRACE_DIMENSION", "PER_COMM", {"PER_COMM", "PER_DEV"}, ""};

@@ -20,9 +20,13 @@ class Platform {
   virtual const char* get_name() const = 0;
   virtual int get_priority() const = 0;         // <0: does not apply to this machine
   virtual int init(std::string* provider_filter) { (void)provider_filter; return 0; }
-  virtual int config_endpoint(void* ep) { (void)ep; return 0; }
   // Order the rails (copy channels) of one GPU; default keeps the order.
   virtual void sort_rails(std::vector<int>& rails) { (void)rails; }
+  // Points NCCL's tuner loader at the shared object this code lives in (unless the user named a
+  // tuner, or B200NET_TUNER_SELF_REGISTER=0): the library carries the tuner tables next to the net
+  // plugin, and NCCL only looks for a tuner where NCCL_TUNER_PLUGIN says
+  // (reference: src/platform-aws.cpp:577-648). Returns the path that was published, "" if none.
+  std::string register_tuner() const;
   virtual uint64_t device_get_guid(int dev_index) const;
   // A human-actionable hint for an error code seen on the completion path ("" if none).
   virtual std::string log_error_hint(int err) const { (void)err; return ""; }

@@ -1,6 +1,10 @@
 #include "b200net/platform.h"
 
+#include <dlfcn.h>
+#include <limits.h>
+
 #include <cerrno>
+#include <cstdlib>
 #include <cstring>
 
 #include "b200net/cuda_shim.h"
@@ -11,6 +15,19 @@
 
 namespace b200net {
 
+std::string Platform::register_tuner() const {
+  if (!params().tuner_self_register.get() || getenv("NCCL_TUNER_PLUGIN")) return "";
+  Dl_info info;
+  static const int anchor = 0;   // any address inside this shared object
+  if (!dladdr(&anchor, &info) || !info.dli_fname || !*info.dli_fname) return "";
+  char resolved[PATH_MAX];
+  const std::string path = realpath(info.dli_fname, resolved) ? resolved : info.dli_fname;
+  // only a shared object can be named; a test program that links the code statically has no tuner to offer
+  if (path.size() < 3 || path.find(".so") == std::string::npos) return "";
+  EnvManager::instance().insert_envvar("NCCL_TUNER_PLUGIN", path, false);
+  return path;
+}
+
 uint64_t Platform::device_get_guid(int dev_index) const {
   return (static_cast<uint64_t>(system_node_id()) << 8) | static_cast<uint64_t>(dev_index & 0xff);
 }
@@ -18,6 +35,8 @@ uint64_t Platform::device_get_guid(int dev_index) const {
 // ---------------------------------------------------------------- B200
 int PlatformB200::init(std::string*) {
   for (auto& [k, v] : nccl_env()) EnvManager::instance().insert_envvar(k, v, false);
+  const std::string tuner = register_tuner();
+  if (!tuner.empty()) NET_INFO(NCCL_INIT | NCCL_TUNING, "NCCL_TUNER_PLUGIN set to %s", tuner.c_str());
   return 0;
 }
 

@@ -260,6 +260,15 @@ class RdmaEndpoint : public Endpoint {
   std::deque<Deferred> deferred;
   int outbox_total = 0;        // eager sends of all communicators whose datagram has not left yet
   bool in_progress = false;
+  // stall report: when requests are in flight and nothing has moved for STALL_REPORT_MS, the state
+  // of every queue goes to the log once (and again after the next sign of life)
+  uint64_t last_activity_ns = 0;
+  bool stall_reported = false;
+  void note_activity() {
+    last_activity_ns = PluginStats::now_ns();
+    stall_reported = false;
+  }
+  void report_stall();
 };
 
 class RdmaListenComm : public ListenComm {
@@ -730,7 +739,7 @@ int RdmaEndpoint::progress() {
   in_progress = true;
   const int budget = params().cq_read_count.get() * 16;
   B200NET_TRACE_EVENT(ProcessCompletionsRdma, domain->device->dev_id, 0, 0, 0, this);
-  fab.poll(budget, [this](const DgramHdr& h, const void* p) { handle_dgram(h, p); });
+  if (fab.poll(budget, [this](const DgramHdr& h, const void* p) { handle_dgram(h, p); }) > 0) note_activity();
   if (!deferred.empty()) retire_deferred();
   if (outbox_total > 0) flush_outboxes();
   // retry queue: strictly in order, stop at the first post that is still back-pressured
@@ -745,8 +754,53 @@ int RdmaEndpoint::progress() {
     pending.pop_front();
     B200NET_TRACE_EVENT(PendingQueueRemove, domain->device->dev_id, 0, 0, 0, this);
   }
+  if (!stall_reported && last_activity_ns) {
+    const uint64_t limit_ms = params().stall_report_ms.get();
+    if (limit_ms && PluginStats::now_ns() - last_activity_ns > limit_ms * 1000000ull) report_stall();
+  }
   in_progress = false;
   return 0;
+}
+
+void RdmaEndpoint::report_stall() {
+  stall_reported = true;
+  size_t posted = 0;
+  for (auto& [id, rc] : recv_comms) posted += rc->posted.size();
+  if (live_send_reqs.empty() && posted == 0) return;   // idle, not stalled
+  NET_WARN("no progress for %llu ms with %zu sends and %zu receive groups in flight; retry queue %zu, deferred %zu, outbox %d, "
+           "ring-full answers %llu",
+           static_cast<unsigned long long>(params().stall_report_ms.get()), live_send_reqs.size(), posted, pending.size(),
+           deferred.size(), outbox_total, static_cast<unsigned long long>(fab.eagain_count()));
+  for (auto& [id, sc] : send_comms) {
+    if (sc->inflight == 0) continue;
+    auto* box = static_cast<CtrlMsg*>(sc->mailbox->data());
+    NET_WARN("  send comm %u -> %u: %d in flight, group %u taken %#x (ready word %#x), %zu eager unbound, %zu in the outbox%s", id,
+             sc->remote_comm_id, sc->inflight, sc->next_seq, sc->consumed_mask,
+             box[sc->next_seq % MAILBOX_SLOTS].entries[0].ready.load(), sc->eager_queue.size(), sc->outbox.size(),
+             sc->peer_closed ? ", peer closed" : "");
+  }
+  int shown = 0;
+  for (auto& [serial, r] : live_send_reqs) {
+    if (++shown > 8) break;
+    int posted_s = 0, complete_s = 0, notified_s = 0, kernel_s = 0;
+    for (int i = 0; i < r->nstripes; ++i) {
+      posted_s += r->stripes[i].posted;
+      complete_s += r->stripes[i].complete;
+      notified_s += r->stripes[i].notified;
+      kernel_s += r->stripes[i].kslot >= 0;
+    }
+    NET_WARN("    send %llu on comm %u: %zu bytes tag %d state %d %s seq %u; stripes %d posted %d complete %d notified %d (kernel %d)%s%s",
+             static_cast<unsigned long long>(serial), r->comm->local_comm_id, r->size, r->tag, static_cast<int>(r->state),
+             r->eager ? (r->dgram_sent ? "eager, sent" : "eager, in the outbox") : "write", r->seq, r->nstripes, posted_s, complete_s,
+             notified_s, kernel_s, r->via_frags ? ", as fragments" : "", r->bounce_ev ? ", source still being fetched" : "");
+  }
+  for (auto& [id, rc] : recv_comms) {
+    if (rc->posted.empty() && rc->eager_rx.empty()) continue;
+    NET_WARN("  recv comm %u <- %u: %d in flight, %zu groups posted (oldest seq %u), next seq %u, %zu eager messages unmatched, "
+             "eager sequence %u%s",
+             id, rc->remote_comm_id, rc->inflight, rc->posted.size(), rc->posted.empty() ? 0 : rc->posted.front()->seq, rc->next_seq,
+             rc->eager_rx.size(), rc->eager_arrived, rc->peer_closed ? ", peer closed" : "");
+  }
 }
 
 // ------------------------------------------------------------------------------------------ listen / connect / accept
@@ -1241,6 +1295,7 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle* mh, Request**
       B200NET_TRACE_EVENT(PendingQueueInsert, dev_id, local_comm_id, r->seq, r->size, r);
       e->pending.push_back(r->serial);
     }
+    e->note_activity();
     *req = r;
     return 0;
   }
@@ -1306,6 +1361,7 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle* mh, Request**
     flush_outbox();
   }
   B200NET_TRACE_EVENT(SendEagerStart, dev_id, local_comm_id, r->ehdr.eager_seq, size, r);
+  e->note_activity();
   *req = r;
   return 0;
 }
@@ -1334,6 +1390,7 @@ int RdmaSendReq::test(int* done, int* sizes) {
     if (sizes) sizes[0] = static_cast<int>(size);
     B200NET_TRACE_EVENT(SendEnd, comm->dev_id, comm->local_comm_id, seq, size, this);
     if (PluginStats::get().histograms_on()) PluginStats::get().sample_send(size, static_cast<size_t>(nstripes), PluginStats::since(t_post_ns));
+    e->note_activity();
     comm->release(this);
   }
   return 0;
@@ -1566,6 +1623,7 @@ int RdmaRecvComm::recv(int n, void** data, size_t* sizes, int* tags, MrHandle** 
   ++inflight;
   posted.push_back(r);
   match_eager();
+  e->note_activity();
   *req = r;
   return 0;
 }
@@ -1595,6 +1653,7 @@ int RdmaRecvReq::test(int* done, int* sizes) {
       if (PluginStats::get().histograms_on()) PluginStats::get().sample_recv(total, PluginStats::since(t_post_ns));
     }
     --comm->inflight;
+    e->note_activity();
     comm->release(this);
   } else if (no_completion && state != ReqState::ERROR) {
     // early completion: report the posted sizes now, retire the bookkeeping when the writes land

@@ -15,11 +15,11 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import signal
 import socket
-import subprocess
 import sys
 from pathlib import Path
+
+from .proc import run_job
 
 LIB = Path(__file__).resolve().parent.parent / "lib"
 
@@ -75,6 +75,8 @@ def _worker(args) -> None:
             ms = float(t.item())
             rows.append({"coll": name, "bytes": numel * 2, "us": ms * 1e3, "busbw_GBs": numel * 2 * factor / ms / 1e6,
                          "correct": ok})
+        if rank == 0:
+            print(f"[bench_plugin] {numel * 2} bytes done", file=sys.stderr, flush=True)
         size *= 2
     if rank == 0:
         print("PLUGIN_BENCH_ROWS " + json.dumps(rows), flush=True)
@@ -108,17 +110,12 @@ def main(argv=None) -> int:
                "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), "-m",
                "aws_ofi_nccl_b200.utils.bench_plugin", "--worker", "--min-bytes", str(args.min_bytes), "--max-bytes",
                str(args.max_bytes), "--warmup", str(args.warmup), "--iters", str(args.iters)]
-        # a process group of its own, so that a job that runs out of time is ended with all its ranks
-        proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env, start_new_session=True)
-        try:
-            out, err = proc.communicate(timeout=args.timeout)
-        except subprocess.TimeoutExpired:
-            os.killpg(proc.pid, signal.SIGKILL)
-            proc.communicate()
-            print(f"{arm}: timed out", flush=True)
+        rc, out, err = run_job(cmd, env=env, timeout=args.timeout)   # ends every rank when the limit passes
+        if rc is None:
+            print(f"{arm}: timed out\n{err[-1500:]}", flush=True)
             continue
         got = [ln for ln in out.splitlines() if ln.startswith("PLUGIN_BENCH_ROWS ")]
-        if proc.returncode != 0 or not got:
+        if rc != 0 or not got:
             print(f"{arm}: failed\n{err[-1500:]}", flush=True)
             continue
         result[arm] = json.loads(got[-1][len("PLUGIN_BENCH_ROWS "):])

@@ -16,8 +16,9 @@ import argparse
 import json
 import os
 import socket
-import subprocess
 import sys
+
+from .proc import run_job
 
 ALGOS = {"Tree": 0, "Ring": 1, "NVLS": 4, "NVLSTree": 5, "PAT": 6}
 PROTOS = {"LL": 0, "LL128": 1, "Simple": 2}
@@ -97,13 +98,12 @@ def main(argv=None) -> int:
                    "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), "-m",
                    "aws_ofi_nccl_b200.utils.tuner_calibrate", "--worker", "--min-bytes", str(args.min_bytes),
                    "--max-bytes", str(args.max_bytes), "--step", str(args.step), "--iters", str(args.iters)]
-            try:
-                res = subprocess.run(cmd, capture_output=True, text=True, timeout=args.timeout, env=env)
-            except subprocess.TimeoutExpired:
+            rc, out, _ = run_job(cmd, env=env, timeout=args.timeout)   # ends every rank when the limit passes
+            if rc is None:
                 print(f"{algo}/{proto}: timed out, skipped", flush=True)
                 continue
-            got = [ln for ln in res.stdout.splitlines() if ln.startswith("CALIBRATION_ROWS ")]
-            if res.returncode != 0 or not got:
+            got = [ln for ln in out.splitlines() if ln.startswith("CALIBRATION_ROWS ")]
+            if rc != 0 or not got:
                 print(f"{algo}/{proto}: not available here", flush=True)
                 continue
             part = json.loads(got[-1][len("CALIBRATION_ROWS "):])

@@ -1,8 +1,6 @@
 """Multi-GPU tests: each launches a torchrun job over the visible GPUs (2..8) and checks its exit code."""
 import os
-import signal
 import socket
-import subprocess
 import sys
 from pathlib import Path
 
@@ -11,6 +9,8 @@ import torch
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+from aws_ofi_nccl_b200.utils.proc import run_job  # noqa: E402
 
 
 def _free_port() -> int:
@@ -24,17 +24,11 @@ def _run(worker: str, nproc: int, env_extra: dict | None = None, timeout: int = 
     env.update(env_extra or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(ROOT / "tests" / "workers" / worker)]
-    # The job runs in a process group of its own: when the limit passes, the launcher AND its
-    # workers are ended (a worker left behind would keep its kernels spinning on the GPU).
-    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env, cwd=ROOT,
-                            start_new_session=True)
-    try:
-        out, err = proc.communicate(timeout=timeout)
-    except subprocess.TimeoutExpired:
-        os.killpg(proc.pid, signal.SIGKILL)
-        out, err = proc.communicate()
-        raise AssertionError(f"{worker} on {nproc} ranks did not finish within {timeout} s\n" + out[-3000:] + err[-3000:])
-    assert proc.returncode == 0, out[-4000:] + err[-4000:]
+    # when the limit passes, the launcher AND every worker it started are ended (a worker left
+    # behind would keep its kernels spinning on the GPU)
+    rc, out, err = run_job(cmd, env=env, cwd=ROOT, timeout=timeout)
+    assert rc is not None, f"{worker} on {nproc} ranks did not finish within {timeout} s\n" + out[-3000:] + err[-3000:]
+    assert rc == 0, out[-4000:] + err[-4000:]
     return out
 
 
