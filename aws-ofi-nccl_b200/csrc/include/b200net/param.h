@@ -154,7 +154,10 @@ struct Params {
   Param<int> max_posted_eager_buffers{"RDMA_MAX_POSTED_EAGER_BUFFERS", 128, ""};
   Param<int> min_posted_control_buffers{"RDMA_MIN_POSTED_CONTROL_BUFFERS", 16, ""};
   Param<int> max_posted_control_buffers{"RDMA_MAX_POSTED_CONTROL_BUFFERS", 32, ""};
-  Param<bool> early_completion{"EARLY_COMPLETION", true, "complete LL/LL128 receives without waiting for write completions"};
+  Param<bool> early_completion{"EARLY_COMPLETION", false,
+                               "report a receive whose completion NCCL calls optional (LL / LL128) as done when it is posted. "
+                               "Only honoured with eager sends off (EAGER_MAX_SIZE=0): once such a receive is done NCCL stops "
+                               "calling into the plugin, and an eager payload needs the receiver's progress loop to land"};
   Param<bool> disable_close_message{"DISABLE_CLOSE_MESSAGE", false, "skip the close handshake"};
   Param<bool> abort_on_error{"ABORT_ON_ERROR", false, "abort() instead of returning an error code"};
   Param<int> force_num_rails{"FORCE_NUM_RAILS", 0, "override the number of copy channels per peer (0 = from topology)"};

@@ -763,10 +763,13 @@ int RdmaEndpoint::progress() {
 }
 
 void RdmaEndpoint::report_stall() {
-  stall_reported = true;
   size_t posted = 0;
   for (auto& [id, rc] : recv_comms) posted += rc->posted.size();
-  if (live_send_reqs.empty() && posted == 0) return;   // idle, not stalled
+  if (live_send_reqs.empty() && posted == 0) {   // idle, not stalled
+    last_activity_ns = PluginStats::now_ns();
+    return;
+  }
+  stall_reported = true;
   NET_WARN("no progress for %llu ms with %zu sends and %zu receive groups in flight; retry queue %zu, deferred %zu, outbox %d, "
            "ring-full answers %llu",
            static_cast<unsigned long long>(params().stall_report_ms.get()), live_send_reqs.size(), posted, pending.size(),
@@ -1585,7 +1588,10 @@ int RdmaRecvComm::recv(int n, void** data, size_t* sizes, int* tags, MrHandle** 
   r->comm = this;
   r->seq = seq;
   r->n = n;
-  r->no_completion = optional && params().early_completion.get();
+  // Early completion is safe only when every byte reaches the buffer without this process's help
+  // (a write into mapped or attached memory): after an early "done" NCCL may never call the plugin
+  // again for this transfer, and eager payloads are delivered by the receiver's progress loop.
+  r->no_completion = optional && params().early_completion.get() && params().eager_max_size.get() == 0;
   MsgStatus st;
   if (msgbuff->insert(seq, r, MsgElemType::REQ, &st) != MsgResult::SUCCESS) {
     release(r);
