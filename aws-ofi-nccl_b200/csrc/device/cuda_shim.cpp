@@ -189,6 +189,15 @@ bool is_host_pointer(const void* ptr) {
   return r != CUDA_SUCCESS || mem_type != CU_MEMORYTYPE_DEVICE;
 }
 
+int host_device_alias(const void* host_ptr, void** device_ptr) {
+  if (!available()) return -ENOSYS;
+  CUdeviceptr d = 0;
+  if (g.PointerGetAttribute(&d, CU_POINTER_ATTRIBUTE_DEVICE_POINTER, reinterpret_cast<CUdeviceptr>(host_ptr)) != CUDA_SUCCESS || !d)
+    return -EINVAL;
+  *device_ptr = reinterpret_cast<void*>(d);
+  return 0;
+}
+
 int ipc_get_handle(void* alloc_base, uint8_t out[64]) {
   if (!available()) return -ENOSYS;
   CUipcMemHandle h;
@@ -291,7 +300,7 @@ int host_alloc(void** ptr, size_t bytes) {
 int host_free(void* ptr) { return (available() && g.MemFreeHost) ? rc_of(g.MemFreeHost(ptr)) : -ENOSYS; }
 int host_register(void* ptr, size_t bytes) {
   if (!available() || !g.MemHostRegister) return -ENOSYS;
-  return rc_of(g.MemHostRegister(ptr, bytes, CU_MEMHOSTREGISTER_PORTABLE));
+  return rc_of(g.MemHostRegister(ptr, bytes, CU_MEMHOSTREGISTER_PORTABLE | CU_MEMHOSTREGISTER_DEVICEMAP));
 }
 int host_unregister(void* ptr) { return (available() && g.MemHostUnregister) ? rc_of(g.MemHostUnregister(ptr)) : -ENOSYS; }
 

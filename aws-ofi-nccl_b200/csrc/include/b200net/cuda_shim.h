@@ -21,6 +21,9 @@ int device_count();
 // Pointer classification. Returns 0 and fills the outputs if `ptr` is device memory.
 int pointer_info(const void* ptr, int* device, void** alloc_base, size_t* alloc_size, bool* is_vmm);
 bool is_host_pointer(const void* ptr);
+// The address at which kernels of the current device can read page-locked host memory (memory
+// from the driver's host allocators or registered with it). -EINVAL for pageable memory.
+int host_device_alias(const void* host_ptr, void** device_ptr);
 
 // Legacy IPC (cudaMalloc-style allocations): 64-byte handles.
 int ipc_get_handle(void* alloc_base, uint8_t out[64]);

@@ -32,7 +32,7 @@ class NetKernels {
   // completion slot to poll with done() and to give back with release(). -EAGAIN: no slot free.
   // 16-byte aligned transfers of at least BULK_MIN bytes go to the bulk-copy kernel (one thread per
   // CTA driving cp.async.bulk through shared memory) unless B200NET_COPY_KERNEL_BULK=0.
-  int copy_flag(void* dst, const void* src, size_t n, cuda::Stream st, int ctas, int* slot);
+  int copy_flag(void* dst, const void* src, size_t n, cuda::Stream st, int ctas, int* slot, bool allow_bulk = true);
   bool done(int slot) const;
   // 0 while the copy runs, 1 when it has completed, -EIO when the kernel gave up on a wait.
   int status(int slot) const;
@@ -49,7 +49,7 @@ class NetKernels {
  private:
   NetKernels() = default;
   int init();
-  int copy_impl(void* dst, const void* src, size_t n, cuda::Stream st, int ctas, int* slot, bool warm_bulk);
+  int copy_impl(void* dst, const void* src, size_t n, cuda::Stream st, int ctas, int* slot, bool warm_bulk, bool allow_bulk);
   void* module_ = nullptr;
   void* fn_copy_ = nullptr;
   void* fn_pack_ = nullptr;

@@ -218,8 +218,26 @@ CUresult fDeviceGetUuid(CUuuid* u, CUdevice d) {
   u->bytes[15] = static_cast<char>(d);
   return CUDA_SUCCESS;
 }
+std::map<uintptr_t, size_t> g_pinned;   // page-locked host ranges (guarded by g_mu)
 CUresult fPointerGetAttribute(void* out, CUpointer_attribute a, CUdeviceptr p) {
   std::lock_guard<std::mutex> g(g_mu);
+  if (a == CU_POINTER_ATTRIBUTE_DEVICE_POINTER) {
+    // page-locked host memory is readable by kernels at its own address; pageable memory is not
+    auto it = g_pinned.upper_bound(static_cast<uintptr_t>(p));
+    if (it != g_pinned.begin()) {
+      --it;
+      if (p >= it->first && p < it->first + it->second) {
+        *static_cast<CUdeviceptr*>(out) = p;
+        return CUDA_SUCCESS;
+      }
+    }
+    uintptr_t b = 0;
+    if (find_alloc(static_cast<uintptr_t>(p), &b)) {
+      *static_cast<CUdeviceptr*>(out) = p;
+      return CUDA_SUCCESS;
+    }
+    return CUDA_ERROR_INVALID_VALUE;
+  }
   uintptr_t base = 0;
   const Alloc* al = find_alloc(static_cast<uintptr_t>(p), &base);
   if (!al) return CUDA_ERROR_INVALID_VALUE;   // what the driver answers for plain host memory
@@ -497,14 +515,30 @@ CUresult fLaunchKernel(CUfunction f, unsigned, unsigned, unsigned, unsigned, uns
   return CUDA_ERROR_INVALID_HANDLE;
 }
 CUresult fMemHostAlloc(void** p, size_t bytes, unsigned) {
-  return posix_memalign(p, 4096, (bytes + 4095) & ~static_cast<size_t>(4095)) == 0 ? CUDA_SUCCESS : CUDA_ERROR_OUT_OF_MEMORY;
+  const size_t rounded = (bytes + 4095) & ~static_cast<size_t>(4095);
+  if (posix_memalign(p, 4096, rounded) != 0) return CUDA_ERROR_OUT_OF_MEMORY;
+  std::lock_guard<std::mutex> g(g_mu);
+  g_pinned[reinterpret_cast<uintptr_t>(*p)] = rounded;
+  return CUDA_SUCCESS;
 }
 CUresult fMemFreeHost(void* p) {
+  {
+    std::lock_guard<std::mutex> g(g_mu);
+    g_pinned.erase(reinterpret_cast<uintptr_t>(p));
+  }
   free(p);
   return CUDA_SUCCESS;
 }
-CUresult fMemHostRegister(void*, size_t, unsigned) { return CUDA_SUCCESS; }
-CUresult fMemHostUnregister(void*) { return CUDA_SUCCESS; }
+CUresult fMemHostRegister(void* p, size_t bytes, unsigned) {
+  std::lock_guard<std::mutex> g(g_mu);
+  g_pinned[reinterpret_cast<uintptr_t>(p)] = bytes;
+  return CUDA_SUCCESS;
+}
+CUresult fMemHostUnregister(void* p) {
+  std::lock_guard<std::mutex> g(g_mu);
+  g_pinned.erase(reinterpret_cast<uintptr_t>(p));
+  return CUDA_SUCCESS;
+}
 CUresult fCtxSynchronize() {
   while (g_outstanding.load() > 0) usleep(50);
   return CUDA_SUCCESS;

@@ -103,6 +103,7 @@ class RdmaSendReq : public Request {
   std::vector<uint8_t> bounce;
   cuda::Event bounce_ev = nullptr;
   bool src_dev = false;         // the source is device memory (from its registration, else asked of the driver)
+  const char* src_alias = nullptr;  // page-locked host source: where the copy kernel reads it
   bool via_frags = false;       // the target registration has an IPC handle that could not be opened here
   uint64_t serial = 0;          // unique per endpoint; queued retries name the request by it
   // eager sends: the datagram leaves from the communicator's outbox, in eager_seq order, once the
@@ -157,7 +158,9 @@ struct EagerRx {  // an eager message that arrived before (or without) a matchin
 // order: the stream runs its copies in order, so the queue is retired from the front.
 struct Deferred {
   enum Kind : uint8_t { FRAG_COPY, EAGER_COPY, WRITE_COMPLETION } kind;
-  cuda::Event ev = nullptr;        // null: ready as soon as everything before it has retired
+  cuda::Event ev = nullptr;        // copy-engine copy: its event. No event and no kernel slot: ready as soon
+                                   // as everything before it has retired
+  int kslot = -1;                  // copy-kernel copy: its completion slot
   FreelistEntry* slot = nullptr;   // staging slot to give back
   uint32_t comm_id = 0;            // EAGER_COPY: the receive it completes
   uint16_t seq = 0;
@@ -222,6 +225,10 @@ class RdmaEndpoint : public Endpoint {
   // that waits for this very transport is running can block for ever.
   void prepare_kernels();
   cuda::Event take_event();
+  // Queues dst[0,n) = the staging slot's bytes on the receive stream: the copy kernel reading the
+  // page-locked slot in place when the kernels are loaded, else the copy engine. Fills d->kslot or
+  // d->ev. 0 or a negative error.
+  int stage_to_device(void* dst, FreelistEntry* slot, size_t n, Deferred* d);
   void give_event(cuda::Event ev) { if (ev) free_events.push_back(ev); }
   Freelist& staging() { return *staging_; }
 
@@ -416,6 +423,25 @@ cuda::Event RdmaEndpoint::take_event() {
   }
   cuda::Event ev = nullptr;   // the pool ran dry (more copies in flight than it was sized for)
   return cuda::event_create(&ev) == 0 ? ev : nullptr;
+}
+
+int RdmaEndpoint::stage_to_device(void* dst, FreelistEntry* slot, size_t n, Deferred* d) {
+  cuda::Stream st = rail_stream(0);
+  if (!st) return -EIO;
+  void* alias = nullptr;
+  if (kernels && slot->mr_handle && cuda::host_device_alias(slot->ptr, &alias) == 0 &&
+      kernels->copy_flag(dst, alias, n, st, 1, &d->kslot, false) == 0)
+    return 0;
+  d->kslot = -1;
+  d->ev = take_event();
+  if (!d->ev) return -ENOMEM;
+  int rc = cuda::memcpy_async(dst, slot->ptr, n, st);
+  if (rc == 0) rc = cuda::event_record(d->ev, st);
+  if (rc != 0) {
+    give_event(d->ev);
+    d->ev = nullptr;
+  }
+  return rc;
 }
 
 cuda::Stream RdmaEndpoint::rail_stream(int rail) {
@@ -662,35 +688,26 @@ void RdmaEndpoint::handle_dgram(const DgramHdr& h, const void* payload) {
       // recycled on return, so the bytes move to a staging slot; the copy to the device is queued
       // on the receive stream and the write completion that follows waits for it in `deferred`.
       const auto* fh = static_cast<const DeviceFragHdr*>(payload);
-      cuda::Stream st = rail_stream(0);
       FreelistEntry* slot = fh->len <= STAGE_BYTES ? staging_->entry_alloc() : nullptr;
-      cuda::Event ev = slot ? take_event() : nullptr;
-      if (!st) {
-        fail_endpoint("no stream for a fragment copy", -EIO);
-      } else if (slot && ev) {
+      if (slot) {
         memcpy(slot->ptr, static_cast<const char*>(payload) + sizeof(*fh), fh->len);
-        int rc = cuda::memcpy_async(reinterpret_cast<void*>(fh->remote_addr), slot->ptr, fh->len, st);
-        if (rc == 0) rc = cuda::event_record(ev, st);
+        Deferred d;
+        d.kind = Deferred::FRAG_COPY;
+        d.slot = slot;
+        const int rc = stage_to_device(reinterpret_cast<void*>(fh->remote_addr), slot, fh->len, &d);
         if (rc != 0) {
+          staging_->entry_free(slot);
           fail_endpoint("copy of a fragment to the device failed", rc);
         } else {
-          Deferred d;
-          d.kind = Deferred::FRAG_COPY;
-          d.ev = ev;
-          d.slot = slot;
           deferred.push_back(d);
-          slot = nullptr;
-          ev = nullptr;
         }
       } else {
-        // no staging slot or event left: copy straight from the ring cell and wait for this one
-        // copy (it runs on the copy engine and depends on no kernel)
-        int rc = cuda::memcpy_async(reinterpret_cast<void*>(fh->remote_addr), static_cast<const char*>(payload) + sizeof(*fh), fh->len, st);
+        // no staging slot left: copy straight from the ring cell and wait for this one copy
+        cuda::Stream st = rail_stream(0);
+        int rc = st ? cuda::memcpy_async(reinterpret_cast<void*>(fh->remote_addr), static_cast<const char*>(payload) + sizeof(*fh), fh->len, st) : -EIO;
         if (rc == 0) rc = cuda::stream_synchronize(st);
         if (rc != 0) fail_endpoint("copy of a fragment to the device failed", rc);
       }
-      if (slot) staging_->entry_free(slot);
-      give_event(ev);
       break;
     }
     default:
@@ -701,6 +718,21 @@ void RdmaEndpoint::handle_dgram(const DgramHdr& h, const void* payload) {
 void RdmaEndpoint::retire_deferred() {
   while (!deferred.empty()) {
     Deferred& d = deferred.front();
+    if (d.kslot >= 0) {
+      const int ks = kernels ? kernels->status(d.kslot) : -EIO;
+      if (ks == 0) return;
+      if (kernels) kernels->release(d.kslot);
+      d.kslot = -1;
+      if (ks < 0) {
+        fail_endpoint("a copy on the receive stream failed", ks);
+        for (Deferred& x : deferred) {
+          give_event(x.ev);
+          if (x.slot) staging_->entry_free(x.slot);
+        }
+        deferred.clear();
+        return;
+      }
+    }
     if (d.ev) {
       const int q = cuda::event_query(d.ev);
       if (q == 1) return;
@@ -1092,10 +1124,14 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
             return -EINVAL;
           }
           char* dst = static_cast<char*>(mapped) + (r->target.buff_addr - mr->base) + s.offset;
-          // device source: the plugin's own copy kernel moves the stripe over NVLink and sets a
-          // completion word in pinned memory; anything else goes through the copy engine
-          NetKernels* nk = src_dev ? e->kernels : nullptr;
-          if (nk && nk->copy_flag(dst, src + s.offset, s.len, st, 0, &s.kslot) == 0) {
+          // The plugin's own copy kernel moves the stripe over NVLink and sets a completion word in
+          // pinned memory: from a device source, or from a page-locked host source through the
+          // address kernels read it at. The copy engine is the path of a run without the kernels
+          // only: a copy-engine transfer into a peer's memory, queued while a collective kernel
+          // runs on this device, was seen never to complete.
+          const char* ksrc = src_dev ? src : (r->bounce.empty() ? r->src_alias : nullptr);
+          NetKernels* nk = ksrc ? e->kernels : nullptr;
+          if (nk && nk->copy_flag(dst, ksrc + s.offset, s.len, st, 0, &s.kslot, src_dev) == 0) {
             e->bytes_kernel += s.len;
           } else {
             s.kslot = -1;
@@ -1219,7 +1255,14 @@ int RdmaSendComm::start_rendezvous(RdmaSendReq* r, const CtrlEntry& e) {
   const MrTableEntry* mr = FabricEndpoint::mr_lookup(peer, e.mr_key);
   const bool dst_host = !mr || mr->kind == static_cast<uint32_t>(MrKind::HOST);
   const bool mappable = mr && (mr->kind == static_cast<uint32_t>(MrKind::CUDA_IPC) || mr->kind == static_cast<uint32_t>(MrKind::CUDA_VMM));
-  if (mappable && !rep()->map_peer_cuda(peer, mr)) {
+  if (mappable && !r->src_dev && r->size && rep()->kernels) {
+    // host source, device destination: the copy kernel reads page-locked host memory in place;
+    // pageable memory travels as fragments that the receiver copies into its own device
+    void* alias = nullptr;
+    if (cuda::host_device_alias(r->data, &alias) == 0) r->src_alias = static_cast<const char*>(alias);
+    else r->via_frags = true;
+  }
+  if (mappable && !r->via_frags && !rep()->map_peer_cuda(peer, mr)) {
     // the peer's device memory cannot be mapped into this process (another container, a driver
     // without IPC) or its mapping has not arrived yet: the payload travels as fragments that the
     // receiver copies to its device
@@ -1545,24 +1588,19 @@ void RdmaRecvComm::match_eager() {
     eager_taken[target->seq % MAILBOX_SLOTS] |= static_cast<uint8_t>(1u << target_idx);
     s.received = nbytes;
     if (nbytes && s.mem_type == NCCL_PTR_CUDA) {
-      cuda::Stream st = e->rail_stream(0);
-      cuda::Event ev = st ? e->take_event() : nullptr;
-      int rc = (st && ev) ? cuda::memcpy_async(s.buf, slot->ptr, nbytes, st) : -EIO;
-      if (rc == 0) rc = cuda::event_record(ev, st);
-      if (rc != 0) {
-        NET_WARN("copy of an eager payload to the device failed (%d)", rc);
-        e->give_event(ev);
-        e->staging().entry_free(slot);
-        fail_sub(target, target_idx);
-        continue;
-      }
       Deferred d;
       d.kind = Deferred::EAGER_COPY;
-      d.ev = ev;
       d.slot = slot;
       d.comm_id = local_comm_id;
       d.seq = target->seq;
       d.idx = static_cast<uint8_t>(target_idx);
+      const int rc = e->stage_to_device(s.buf, slot, nbytes, &d);
+      if (rc != 0) {
+        NET_WARN("copy of an eager payload to the device failed (%d)", rc);
+        e->staging().entry_free(slot);
+        fail_sub(target, target_idx);
+        continue;
+      }
       e->deferred.push_back(d);
       continue;
     }

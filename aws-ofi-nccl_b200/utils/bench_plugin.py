@@ -36,9 +36,19 @@ def _worker(args) -> None:
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
+    verbose = bool(int(os.environ.get("BENCH_PLUGIN_VERBOSE", "0")))
+    if verbose:   # where every rank stands, should the job stop moving
+        import faulthandler
+        faulthandler.dump_traceback_later(int(os.environ.get("BENCH_PLUGIN_DUMP_AFTER", "25")), exit=False)
+
+    def say(msg):
+        if verbose:
+            print(f"[bench_plugin rank {rank}] {msg}", file=sys.stderr, flush=True)
+
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
+    say("process group up")
     rows = []
     size = args.min_bytes
     while size <= args.max_bytes:
@@ -50,10 +60,13 @@ def _worker(args) -> None:
         # correctness once per size: all_reduce against an fp64 sum of the gathered inputs
         xs = [torch.empty_like(x) for _ in range(world)]
         dist.all_gather(xs, x)
+        torch.cuda.synchronize(dev)
+        say(f"{numel * 2} bytes: all_gather for the check done")
         z = x.clone()
         dist.all_reduce(z)
         ref = sum(t.double() for t in xs)
         ok = bool(torch.allclose(z.double(), ref, rtol=5e-2, atol=5e-2 * world))
+        say(f"{numel * 2} bytes: check {ok}")
         calls = {"all_reduce": (lambda: dist.all_reduce(x), 2 * (world - 1) / world),
                  "all_gather": (lambda: dist.all_gather_into_tensor(y, part), (world - 1) / world),
                  "reduce_scatter": (lambda: dist.reduce_scatter_tensor(part, y), (world - 1) / world),
@@ -73,6 +86,7 @@ def _worker(args) -> None:
             t = torch.tensor([a.elapsed_time(b) / iters], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
+            say(f"{numel * 2} bytes: {name} {ms * 1e3:.1f} us")
             rows.append({"coll": name, "bytes": numel * 2, "us": ms * 1e3, "busbw_GBs": numel * 2 * factor / ms / 1e6,
                          "correct": ok})
         if rank == 0:

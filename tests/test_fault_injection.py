@@ -18,7 +18,9 @@ def test_failed_copy_to_the_device_is_reported_by_test(built):
     """The stand-in driver makes the receiver's cuMemcpyAsync fail: the receive must end with an error
     from test(), never with a success status and no data."""
     import os
-    env = dict(os.environ, LD_LIBRARY_PATH=f"{built / 'tests' / 'fake_cuda'}:" + os.environ.get("LD_LIBRARY_PATH", ""))
+    # the copy engine delivers the payload in this run (with the copy kernels there is no cuMemcpyAsync to fail)
+    env = dict(os.environ, B200NET_COPY_KERNEL="0",
+               LD_LIBRARY_PATH=f"{built / 'tests' / 'fake_cuda'}:" + os.environ.get("LD_LIBRARY_PATH", ""))
     cmd = [str(built / "tests" / "func_fault"), str(built / "libnccl-net-ofi-b200.so"), "device_copy_failure"]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=120, cwd=built, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
