@@ -732,6 +732,91 @@ static int scenario_device_bandwidth(int sock) {
   return close_pair(&p);
 }
 
+// Several thousand messages over ONE connection, so that the 10-bit message sequence numbers, the
+// 16-bit eager sequence numbers' low bits and the mailbox slots all wrap several times, with eight
+// messages in flight, sizes that alternate between eager and rendezvous, and every payload checked.
+static int scenario_seq_wrap(int sock) {
+  Pair p;
+  if (connect_pair(0, sock, &p)) return 1;
+  const int total = getenv("FUNC_NET_WRAP_MESSAGES") ? atoi(getenv("FUNC_NET_WRAP_MESSAGES")) : 5000, window = 8;
+  const size_t sizes[] = {64, 40000, 24, 300000, 4096, 9000};
+  const size_t cap = 300000;
+  std::vector<TestBuf> sb(window), rb(window);
+  std::vector<void*> smh(window), rmh(window);
+  for (int i = 0; i < window; ++i) {
+    if (buf_alloc(&sb[i], cap) || buf_alloc(&rb[i], cap)) FAIL("buffer allocation failed");
+    OK(net->regMr(p.s, sb[i].data(), cap, buf_type(), &smh[i]));
+    OK(net->regMr(p.r, rb[i].data(), cap, buf_type(), &rmh[i]));
+  }
+  if (barrier(sock)) FAIL("barrier");
+  for (int base = 0; base < total; base += window) {
+    std::vector<void*> reqs;
+    std::vector<bool> sent(window, false);
+    // odd rounds post the sends first, so that eager-sized ones leave before their receive exists
+    const int mode = getenv("FUNC_NET_WRAP_MODE") ? atoi(getenv("FUNC_NET_WRAP_MODE")) : 0;   // 1: receives always first, 2: sends always first
+    const bool sends_first = mode == 1 ? false : mode == 2 ? true : ((base / window) & 1);
+    for (int phase = 0; phase < 2; ++phase) {
+      const bool do_sends = (phase == 0) == sends_first;
+      for (int i = 0; i < window && base + i < total; ++i) {
+        const int k = base + i;
+        const size_t n = sizes[k % 6];
+        void* req = nullptr;
+        if (do_sends) {
+          uint32_t hdr[2] = {0xABCD0000u + static_cast<uint32_t>(g_rank), static_cast<uint32_t>(k)};
+          memcpy(sb[i].host(), hdr, 8);
+          sb[i].host()[n - 1] = static_cast<uint8_t>(k * 7 + g_rank);
+          sb[i].to_device(0, 8);
+          sb[i].to_device(n - 1, 1);
+          auto t0 = Clock::now();
+          while (!req) {
+            OK(net->isend(p.s, sb[i].data(), n, i, smh[i], nullptr, &req));
+            if (!req && sends_first && n > 8192) break;   // not eager and no receive yet: after the receives
+            if (expired(t0)) FAIL("isend %d kept returning no request", k);
+          }
+          if (req) {
+            reqs.push_back(req);
+            sent[i] = true;
+          }
+        } else {
+          void* d = rb[i].data();
+          size_t sz = n;
+          int tag = i;   // one tag per slot: a round's messages may be sent in another order than its receives are posted
+          if (post_recv(p.r, 1, &d, &sz, &tag, &rmh[i], &req)) return 1;
+          reqs.push_back(req);
+        }
+      }
+    }
+    if (sends_first) {   // the sends that had to wait for their receive
+      for (int i = 0; i < window && base + i < total; ++i) {
+        const size_t n = sizes[(base + i) % 6];
+        if (sent[i]) continue;   // went out before the receives (eager, or its receive was already there)
+        void* req = nullptr;
+        if (post_send(p.s, sb[i].data(), n, i, smh[i], &req)) return 1;
+        reqs.push_back(req);
+      }
+    }
+    if (wait_all(reqs)) return 1;
+    for (int i = 0; i < window && base + i < total; ++i) {
+      const int k = base + i;
+      const size_t n = sizes[k % 6];
+      rb[i].from_device(0, 8);
+      rb[i].from_device(n - 1, 1);
+      uint32_t hdr[2];
+      memcpy(hdr, rb[i].host(), 8);
+      if (hdr[0] != 0xABCD0000u + static_cast<uint32_t>(1 - g_rank) || hdr[1] != static_cast<uint32_t>(k) ||
+          rb[i].host()[n - 1] != static_cast<uint8_t>(k * 7 + (1 - g_rank)))
+        FAIL("message %d (%zu bytes) arrived as %x / %u", k, n, hdr[0], hdr[1]);
+    }
+  }
+  for (int i = 0; i < window; ++i) {
+    OK(net->deregMr(p.s, smh[i]));
+    OK(net->deregMr(p.r, rmh[i]));
+    buf_free(&sb[i]);
+    buf_free(&rb[i]);
+  }
+  return close_pair(&p);
+}
+
 static int scenario_threads(int) {
   // each thread gets its own endpoint: 4 threads connect to themselves (loopback) concurrently
   std::vector<std::thread> th;
@@ -967,7 +1052,7 @@ static const Scenario kScenarios[] = {
     {"inflight_close", scenario_inflight_close}, {"threads", scenario_threads},
     {"bandwidth", scenario_bandwidth},       {"proxy_pattern", scenario_proxy_pattern},
     {"device_transfer", scenario_device_transfer}, {"eager_multirecv", scenario_eager_multirecv},
-    {"device_bandwidth", scenario_device_bandwidth},
+    {"device_bandwidth", scenario_device_bandwidth}, {"seq_wrap", scenario_seq_wrap},
 };
 
 static int run_rank(const char* so, const char* only, int sock) {

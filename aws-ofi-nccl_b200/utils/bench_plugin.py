@@ -126,7 +126,7 @@ def main(argv=None) -> int:
                str(args.max_bytes), "--warmup", str(args.warmup), "--iters", str(args.iters)]
         rc, out, err = run_job(cmd, env=env, timeout=args.timeout)   # ends every rank when the limit passes
         if rc is None:
-            print(f"{arm}: timed out\n{err[-1500:]}", flush=True)
+            print(f"{arm}: timed out\n{out[-3000:]}\n{err[-3000:]}", flush=True)
             continue
         got = [ln for ln in out.splitlines() if ln.startswith("PLUGIN_BENCH_ROWS ")]
         if rc != 0 or not got:
