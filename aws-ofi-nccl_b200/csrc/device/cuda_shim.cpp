@@ -33,6 +33,8 @@ struct Api {
   CUresult (*CtxSetCurrent)(CUcontext) = nullptr;
   CUresult (*DevicePrimaryCtxRetain)(CUcontext*, CUdevice) = nullptr;
   CUresult (*StreamCreate)(CUstream*, unsigned) = nullptr;
+  CUresult (*StreamCreateWithPriority)(CUstream*, unsigned, int) = nullptr;
+  CUresult (*CtxGetStreamPriorityRange)(int*, int*) = nullptr;
   CUresult (*StreamDestroy)(CUstream) = nullptr;
   CUresult (*StreamSynchronize)(CUstream) = nullptr;
   CUresult (*EventCreate)(CUevent*, unsigned) = nullptr;
@@ -110,6 +112,8 @@ void do_init() {
   ok &= sym(g.CtxSetCurrent, "cuCtxSetCurrent");
   ok &= sym(g.DevicePrimaryCtxRetain, "cuDevicePrimaryCtxRetain");
   ok &= sym(g.StreamCreate, "cuStreamCreate");
+  sym(g.StreamCreateWithPriority, "cuStreamCreateWithPriority", false);
+  sym(g.CtxGetStreamPriorityRange, "cuCtxGetStreamPriorityRange", false);
   ok &= sym(g.StreamDestroy, "cuStreamDestroy");
   ok &= sym(g.StreamSynchronize, "cuStreamSynchronize");
   ok &= sym(g.EventCreate, "cuEventCreate");
@@ -246,6 +250,17 @@ int stream_create(Stream* s) {
   const CUresult r = g.StreamCreate(&st, CU_STREAM_NON_BLOCKING);
   *s = st;
   return rc_of(r);
+}
+int stream_create_high_priority(Stream* s) {
+  if (!available()) return -ENOSYS;
+  int least = 0, greatest = 0;
+  if (!g.StreamCreateWithPriority || !g.CtxGetStreamPriorityRange || g.CtxGetStreamPriorityRange(&least, &greatest) != CUDA_SUCCESS)
+    return stream_create(s);
+  CUstream st = nullptr;
+  const CUresult r = g.StreamCreateWithPriority(&st, CU_STREAM_NON_BLOCKING, greatest);
+  if (r != CUDA_SUCCESS) return stream_create(s);
+  *s = st;
+  return 0;
 }
 int stream_destroy(Stream s) { return available() ? rc_of(g.StreamDestroy(static_cast<CUstream>(s))) : -ENOSYS; }
 int stream_synchronize(Stream s) { return available() ? rc_of(g.StreamSynchronize(static_cast<CUstream>(s))) : -ENOSYS; }

@@ -36,6 +36,8 @@ int ctx_set_current(Context ctx);
 int ensure_primary_ctx(int device);
 
 int stream_create(Stream* s);
+// A non-blocking stream of the greatest priority the device offers.
+int stream_create_high_priority(Stream* s);
 int stream_destroy(Stream s);
 int event_create(Event* e);
 int event_destroy(Event e);

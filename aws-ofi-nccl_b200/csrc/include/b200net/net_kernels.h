@@ -44,6 +44,13 @@ class NetKernels {
   const uint8_t* eager_slot(int slot) const { return eager_ + static_cast<size_t>(slot) * EAGER_SLOT_BYTES; }
   void eager_release(int slot);
 
+  // The one stream all of the plugin's device work of this context runs on (created with the
+  // instance, greatest priority). One stream, not one per rail or endpoint: the device has a
+  // handful of hardware work queues that all streams of the process share, and work queued behind
+  // a collective kernel in the queue that this work lands in would wait for that kernel, which in
+  // turn waits for this work. Every further stream is one more chance to share such a queue.
+  cuda::Stream stream() const { return stream_; }
+
   uint64_t launches() const { return launches_.load(); }
 
  private:
@@ -53,6 +60,7 @@ class NetKernels {
   void* module_ = nullptr;
   void* fn_copy_ = nullptr;
   void* fn_pack_ = nullptr;
+  cuda::Stream stream_ = nullptr;
   void* fn_bulk_ = nullptr;      // null: not in the image or shared memory cannot be raised
   volatile uint64_t* flags_ = nullptr;   // pinned host, NUM_FLAGS words
   uint32_t* counters_ = nullptr;         // device, NUM_FLAGS words, zero when idle

@@ -142,6 +142,8 @@ struct Params {
   Param<uint64_t> stall_report_ms{"STALL_REPORT_MS", 30000,
                                   "an endpoint with requests in flight that sees no datagram, completion or accepted post for "
                                   "this long writes one report of its queues to the log (0: never)"};
+  Param<bool> shared_stream{"SHARED_STREAM", true,
+                            "all device work of the plugin runs on one stream per process (0: one stream per rail and endpoint)"};
   Param<bool> copy_kernel_bulk{"COPY_KERNEL_BULK", true,
                                "aligned stripes of 64 KiB and more use the bulk-copy (TMA) kernel; 0: the vector-copy kernel only"};
   Param<uint64_t> copy_kernel_ctas{"COPY_KERNEL_CTAS", 0, "CTAs per copy-kernel launch (0: chosen from the size)"};

@@ -741,6 +741,10 @@ static int scenario_seq_wrap(int sock) {
   const int total = getenv("FUNC_NET_WRAP_MESSAGES") ? atoi(getenv("FUNC_NET_WRAP_MESSAGES")) : 5000, window = 8;
   const size_t sizes[] = {64, 40000, 24, 300000, 4096, 9000};
   const size_t cap = 300000;
+  size_t eager_limit = 8192;   // the plugin's default; the suite also runs with eager switched off
+  for (const char* name : {"B200NET_EAGER_MAX_SIZE", "OFI_NCCL_EAGER_MAX_SIZE"})
+    if (const char* v = getenv(name)) eager_limit = strtoull(v, nullptr, 0);
+  eager_limit = std::min<size_t>(eager_limit, 8192);
   std::vector<TestBuf> sb(window), rb(window);
   std::vector<void*> smh(window), rmh(window);
   for (int i = 0; i < window; ++i) {
@@ -770,7 +774,7 @@ static int scenario_seq_wrap(int sock) {
           auto t0 = Clock::now();
           while (!req) {
             OK(net->isend(p.s, sb[i].data(), n, i, smh[i], nullptr, &req));
-            if (!req && sends_first && n > 8192) break;   // not eager and no receive yet: after the receives
+            if (!req && sends_first && n > eager_limit) break;   // not eager and no receive yet: after the receives
             if (expired(t0)) FAIL("isend %d kept returning no request", k);
           }
           if (req) {

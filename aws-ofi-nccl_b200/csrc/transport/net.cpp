@@ -134,9 +134,10 @@ int net_create_plugin(Plugin** out) {
     return -EINVAL;
   }
 
-  // rails = copy channels per peer: forced, else 4 on an NVSwitch box, else 1
+  // rails = stripes a large message is cut into: forced, else 1. One copy-kernel launch with
+  // enough CTAs moves a whole message; more rails only add launches on the same stream.
   int rails = params().force_num_rails.get();
-  if (rails <= 0) rails = topo->all_nvlink() ? 4 : 1;
+  if (rails <= 0) rails = 1;
   if (rails > MAX_NUM_RAILS) rails = MAX_NUM_RAILS;
 
   // protocol: parameter, then platform default, then by rail count

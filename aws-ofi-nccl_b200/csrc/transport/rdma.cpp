@@ -445,6 +445,8 @@ int RdmaEndpoint::stage_to_device(void* dst, FreelistEntry* slot, size_t n, Defe
 }
 
 cuda::Stream RdmaEndpoint::rail_stream(int rail) {
+  // with the kernels loaded, everything runs on their one stream (see NetKernels::stream)
+  if (kernels && kernels->stream() && params().shared_stream.get()) return kernels->stream();
   if (streams.empty()) streams.assign(static_cast<size_t>(num_rails), nullptr);
   rail %= num_rails;
   if (!streams[rail]) {
@@ -817,17 +819,17 @@ void RdmaEndpoint::report_stall() {
   int shown = 0;
   for (auto& [serial, r] : live_send_reqs) {
     if (++shown > 8) break;
-    int posted_s = 0, complete_s = 0, notified_s = 0, kernel_s = 0;
-    for (int i = 0; i < r->nstripes; ++i) {
-      posted_s += r->stripes[i].posted;
-      complete_s += r->stripes[i].complete;
-      notified_s += r->stripes[i].notified;
-      kernel_s += r->stripes[i].kslot >= 0;
+    char per_stripe[MAX_NUM_RAILS * 24 + 8] = "";
+    size_t at = 0;
+    for (int i = 0; i < r->nstripes && at + 24 < sizeof(per_stripe); ++i) {
+      const Stripe& st = r->stripes[i];
+      at += static_cast<size_t>(snprintf(per_stripe + at, sizeof(per_stripe) - at, " [rail %d %zuK %s]", st.rail, st.len >> 10,
+                                         st.notified ? "done" : st.complete ? "copied" : st.kslot >= 0 ? "kernel" : st.event ? "engine" : st.posted ? "posted" : "new"));
     }
-    NET_WARN("    send %llu on comm %u: %zu bytes tag %d state %d %s seq %u; stripes %d posted %d complete %d notified %d (kernel %d)%s%s",
-             static_cast<unsigned long long>(serial), r->comm->local_comm_id, r->size, r->tag, static_cast<int>(r->state),
-             r->eager ? (r->dgram_sent ? "eager, sent" : "eager, in the outbox") : "write", r->seq, r->nstripes, posted_s, complete_s,
-             notified_s, kernel_s, r->via_frags ? ", as fragments" : "", r->bounce_ev ? ", source still being fetched" : "");
+    NET_WARN("    send %llu on comm %u: %zu bytes tag %d state %d %s seq %u;%s%s%s", static_cast<unsigned long long>(serial),
+             r->comm->local_comm_id, r->size, r->tag, static_cast<int>(r->state),
+             r->eager ? (r->dgram_sent ? "eager, sent" : "eager, in the outbox") : "write", r->seq, per_stripe,
+             r->via_frags ? ", as fragments" : "", r->bounce_ev ? ", source still being fetched" : "");
   }
   for (auto& [id, rc] : recv_comms) {
     if (rc->posted.empty() && rc->eager_rx.empty()) continue;

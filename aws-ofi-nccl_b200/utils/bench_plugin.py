@@ -64,6 +64,8 @@ def _worker(args) -> None:
         say(f"{numel * 2} bytes: all_gather for the check done")
         z = x.clone()
         dist.all_reduce(z)
+        if os.environ.get("BENCH_PLUGIN_SYNC_AFTER_CHECK") == "1":
+            torch.cuda.synchronize(dev)
         ref = sum(t.double() for t in xs)
         ok = bool(torch.allclose(z.double(), ref, rtol=5e-2, atol=5e-2 * world))
         say(f"{numel * 2} bytes: check {ok}")
@@ -116,6 +118,12 @@ def main(argv=None) -> int:
     result = {"gpus": args.gpus}
     for arm in args.arms:
         env = dict(os.environ, NCCL_P2P_DISABLE="1", NCCL_SHM_DISABLE="1", NCCL_NVLS_ENABLE="0")
+        # The plugin's proxy thread launches copy kernels while NCCL's kernel waits for them, so
+        # nothing in the process may make the device wait for that kernel first: kernels are loaded
+        # when the process starts (a lazy load synchronises the context) and the device gets its
+        # full set of hardware work queues (fewer queues shared by more streams).
+        env.setdefault("CUDA_MODULE_LOADING", "EAGER")
+        env.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
         if arm == "plugin":
             env.update(NCCL_NET_PLUGIN="ofi-b200", LD_LIBRARY_PATH=f"{LIB}:" + env.get("LD_LIBRARY_PATH", ""))
         else:
