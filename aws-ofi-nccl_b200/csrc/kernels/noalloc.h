@@ -25,7 +25,10 @@ extern "C" {
 //  * The first call on a device looks up the array's device address (one cudaGetSymbolAddress with
 //    that device current). Make that first call before starting any stream capture.
 //  * The device must be current on the calling thread; the function does not switch devices.
-//  * H above B200_NOALLOC_MAX_H (or not a multiple of 8) is refused with error 10004 / 10001.
+//  * H above B200_NOALLOC_MAX_H (or not a multiple of 8) is refused with error 10004 / 10001; so is
+//    any of dy, x, w, dres, dx, dw that is not 16-byte aligned (10001): rows move as 16-byte vectors.
+//  * The looked-up address belongs to the device's context and is cached for the life of the
+//    process; it does not survive a cudaDeviceReset.
 //  * All calls share the one staging array, which keeps the previous call's contents. Every row a
 //    call reads is fully rewritten by that call first, so nothing needs clearing — but two calls
 //    that overlap in time on the same GPU (different streams) race on it. Serialise them.

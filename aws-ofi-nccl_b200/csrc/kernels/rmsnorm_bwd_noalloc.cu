@@ -4,6 +4,9 @@
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
 #include <stdint.h>
 #include <stdio.h>
 
@@ -127,8 +130,12 @@ __global__ void colsum_kernel(const float* __restrict__ partial, bf16* __restric
   dw[h] = __float2bfloat16(s);
 }
 
-// Device address of the staging array, looked up once per device (index = device ordinal).
-float* g_partial_addr[64] = {nullptr};
+// Device address of the staging array and SM count, looked up once per device (index = device
+// ordinal). The address is published last, with release ordering, and read with acquire ordering:
+// a thread that sees it also sees the SM count. Two threads making the first call at once both do
+// the look-up and store the same values. The address belongs to the device's current context: it
+// does not survive a cudaDeviceReset (the next call after one would use a stale address).
+std::atomic<float*> g_partial_addr[64];
 int g_sm_count[64] = {0};
 
 }  // namespace
@@ -137,6 +144,10 @@ extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const voi
                                         const void* dres, void* dx, void* dw, int accumulate_dw, int T, int H,
                                         void* stream) {
   if (!dy || !x || !w || !rstd || !dx || !dw || T <= 0 || H <= 0 || H % 8) return 10001;
+  // the kernels move rows as 16-byte vectors: a misaligned pointer would fault on the device
+  const uintptr_t all = reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) |
+                        reinterpret_cast<uintptr_t>(dres) | reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(dw);
+  if ((all & 15) || (reinterpret_cast<uintptr_t>(rstd) & 3)) return 10001;
   if (H > B200_NOALLOC_MAX_H) {
     fprintf(stderr, "[b200ops] rmsnorm_bwd_noalloc: H=%d exceeds the fixed staging area (max %d)\n", H,
             B200_NOALLOC_MAX_H);
@@ -145,7 +156,8 @@ extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const voi
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= 64) return e != cudaSuccess ? static_cast<int>(e) : 10001;
-  if (!g_partial_addr[dev]) {
+  float* partial = g_partial_addr[dev].load(std::memory_order_acquire);
+  if (!partial) {
     // set-up, once per device, with that device current
     float* p = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_dw_partial);
@@ -157,9 +169,9 @@ extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const voi
     e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return static_cast<int>(e);
     g_sm_count[dev] = sms;
-    g_partial_addr[dev] = p;
+    g_partial_addr[dev].store(p, std::memory_order_release);
+    partial = p;
   }
-  float* partial = g_partial_addr[dev];
   int grid = 2 * g_sm_count[dev];
   if (grid > B200_NOALLOC_MAX_ROWS) grid = B200_NOALLOC_MAX_ROWS;
   if (grid > T) grid = T;

@@ -34,9 +34,12 @@ class Trainer:
         grad_buffer = dp.allocate_grad_buffer(self._padded_numel(cfg)) if dp is not None else None
         self.model = Llama(cfg, device=self.device, grad_buffer=grad_buffer, seed=seed)
         n = self.model.numel
-        self.m = torch.zeros(n, device=self.device, dtype=torch.float32)
-        self.v = torch.zeros(n, device=self.device, dtype=torch.float32)
-        self.master = self.model.flat_params.float() if self.optim.master_weights else None
+        # a reducer in "zero" mode leaves each rank the optimizer state of its own shard only
+        self.shard = dp.shard_range(n) if getattr(dp, "mode", "") == "zero" else (0, n)
+        lo, hi = self.shard
+        self.m = torch.zeros(hi - lo, device=self.device, dtype=torch.float32)
+        self.v = torch.zeros(hi - lo, device=self.device, dtype=torch.float32)
+        self.master = self.model.flat_params[lo:hi].float() if self.optim.master_weights else None
         self.step_count = 0
         self.kernel_launches = 0
         if dp is not None:
@@ -60,9 +63,17 @@ class Trainer:
         if self.dp is not None:
             self.dp.finish_step()  # all buckets reduced (averaged) in place in the flat gradient buffer
         self.step_count += 1
-        llm_ops.adamw_step(model.flat_params, model.flat_grads, self.m, self.v, self.master, lr=oc.lr,
+        lo, hi = self.shard
+        grad_scale = float(getattr(self.dp, "grad_scale", 1.0))   # reducers that sum leave the 1/N to the optimizer
+        llm_ops.adamw_step(model.flat_params[lo:hi], model.flat_grads[lo:hi], self.m, self.v, self.master, lr=oc.lr,
                            beta1=oc.beta1, beta2=oc.beta2, eps=oc.eps, weight_decay=oc.weight_decay,
-                           step=self.step_count, grad_scale=1.0, zero_grad=True)
+                           step=self.step_count, grad_scale=grad_scale, zero_grad=True)
+        if (lo, hi) != (0, model.numel):
+            if lo > 0:
+                model.flat_grads[:lo].zero_()
+            if hi < model.numel:
+                model.flat_grads[hi:].zero_()
+            self.dp.gather_params(model.flat_params)
         return loss.detach()
 
     # ------------------------------------------------------------------ end to end: pinned host batch in, float out

@@ -150,9 +150,6 @@ class SymmetricMemory:
     def peer_ptr(self, r: int) -> int:
         return self.base + r * self.chunk
 
-    def peer_tensor(self, r: int) -> torch.Tensor:
-        return tensor_from_ptr(self.peer_ptr(r), self.chunk, self.device)
-
     def free(self) -> None:
         if self._freed:
             return
