@@ -140,18 +140,22 @@ def nccl_maker(world: int, rank: int, device):
             if coll == "all_reduce":
                 y = x.clone()
                 dist.all_reduce(y)
+                torch.cuda.synchronize(device)   # nothing else is queued while the collective is in flight
                 ok = bool(torch.allclose(y.double(), ref, **tol))
             elif coll == "reduce_scatter":
                 o = torch.empty(per, device=device, dtype=torch.bfloat16)
                 dist.reduce_scatter_tensor(o, x)
+                torch.cuda.synchronize(device)   # nothing else is queued while the collective is in flight
                 ok = bool(torch.allclose(o.double(), ref[rank * per:(rank + 1) * per], **tol))
             elif coll == "all_gather":
                 y = torch.empty(numel, device=device, dtype=torch.bfloat16)
                 dist.all_gather_into_tensor(y, x[:per].contiguous())
+                torch.cuda.synchronize(device)   # nothing else is queued while the collective is in flight
                 ok = bool(torch.equal(y, torch.cat([t[:per] for t in xs])))
             else:
                 y = torch.empty_like(x)
                 dist.all_to_all_single(y, x)
+                torch.cuda.synchronize(device)   # nothing else is queued while the collective is in flight
                 ok = bool(torch.equal(y, torch.cat([t[rank * per:(rank + 1) * per] for t in xs])))
             del xs, ref
             torch.cuda.synchronize(device)
