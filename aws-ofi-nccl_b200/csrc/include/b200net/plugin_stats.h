@@ -36,6 +36,11 @@ struct PluginStats {
   // accepted post to completion); no-ops unless histograms are on.
   void sample_send(size_t bytes, size_t stripes, uint64_t ns);
   void sample_recv(size_t bytes, uint64_t ns);
+  // Where a send's time goes: the launch call itself, launch to the completion word being seen by
+  // the proxy thread, and how often that thread comes round to this endpoint.
+  void sample_launch(uint64_t ns);
+  void sample_kernel_done(uint64_t ns);
+  void sample_poll_gap(uint64_t ns);
 
   static uint64_t now_ns();
   // Nanoseconds since a request's post time (0 when that was not recorded).

@@ -24,6 +24,9 @@ struct Hists {
   StripeHist stripes{"stripes_per_send", stats::LinearBinner<uint64_t>(0, 1, 18), "stripes"};
   NsHist send_ns{"send_request_latency", stats::Log2Binner<uint64_t>(40), "ns"};
   NsHist recv_ns{"recv_request_latency", stats::Log2Binner<uint64_t>(40), "ns"};
+  NsHist launch_ns{"copy_kernel_launch_call", stats::Log2Binner<uint64_t>(40), "ns"};
+  NsHist flag_ns{"copy_kernel_launch_to_completion_seen", stats::Log2Binner<uint64_t>(40), "ns"};
+  NsHist poll_gap_ns{"interval_between_progress_calls", stats::Log2Binner<uint64_t>(40), "ns"};
 };
 Hists* g_hists = nullptr;   // created once, never destroyed (requests may complete during teardown)
 
@@ -86,6 +89,16 @@ void PluginStats::sample_send(size_t bytes, size_t stripes, uint64_t ns) {
   g_hists->send_ns.insert(ns);
 }
 
+void PluginStats::sample_launch(uint64_t ns) {
+  if (g_hists) g_hists->launch_ns.insert(ns);
+}
+void PluginStats::sample_kernel_done(uint64_t ns) {
+  if (g_hists) g_hists->flag_ns.insert(ns);
+}
+void PluginStats::sample_poll_gap(uint64_t ns) {
+  if (g_hists) g_hists->poll_gap_ns.insert(ns);
+}
+
 void PluginStats::sample_recv(size_t bytes, uint64_t ns) {
   if (!g_hists) return;
   g_hists->recv_size.insert(bytes);
@@ -107,7 +120,7 @@ std::string PluginStats::to_json() const {
   o += "},\"histograms\":[";
   if (g_hists) {
     const stats::HistogramBase* all[] = {&g_hists->send_size, &g_hists->recv_size, &g_hists->stripes, &g_hists->send_ns,
-                                         &g_hists->recv_ns};
+                                         &g_hists->recv_ns, &g_hists->launch_ns, &g_hists->flag_ns, &g_hists->poll_gap_ns};
     first = true;
     for (const stats::HistogramBase* h : all) {
       const stats::HistogramSnapshot s = h->snapshot();

@@ -69,6 +69,7 @@ struct Stripe {
   cuda::Event event = nullptr;   // non-null while a copy-engine transfer is in flight (from the endpoint's pool)
   bool posted = false, complete = false, notified = false;
   int kslot = -1;      // completion slot of a copy-kernel transfer in flight
+  uint64_t t_launch_ns = 0;   // when its launch call returned (latency histograms only)
   std::shared_ptr<std::atomic<int>> job;  // status of a stripe handed to a host copy worker
 };
 
@@ -269,7 +270,7 @@ class RdmaEndpoint : public Endpoint {
   bool in_progress = false;
   // stall report: when requests are in flight and nothing has moved for STALL_REPORT_MS, the state
   // of every queue goes to the log once (and again after the next sign of life)
-  uint64_t last_activity_ns = 0;
+  uint64_t last_activity_ns = 0, last_progress_ns = 0;
   bool stall_reported = false;
   void note_activity() {
     last_activity_ns = PluginStats::now_ns();
@@ -773,6 +774,13 @@ int RdmaEndpoint::progress() {
   in_progress = true;
   const int budget = params().cq_read_count.get() * 16;
   B200NET_TRACE_EVENT(ProcessCompletionsRdma, domain->device->dev_id, 0, 0, 0, this);
+  if (PluginStats::get().histograms_on() && !live_send_reqs.empty()) {
+    const uint64_t now = PluginStats::now_ns();
+    if (last_progress_ns) PluginStats::get().sample_poll_gap(now - last_progress_ns);
+    last_progress_ns = now;
+  } else {
+    last_progress_ns = 0;
+  }
   if (fab.poll(budget, [this](const DgramHdr& h, const void* p) { handle_dgram(h, p); }) > 0) note_activity();
   if (!deferred.empty()) retire_deferred();
   if (outbox_total > 0) flush_outboxes();
@@ -1133,8 +1141,14 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
           // runs on this device, was seen never to complete.
           const char* ksrc = src_dev ? src : (r->bounce.empty() ? r->src_alias : nullptr);
           NetKernels* nk = ksrc ? e->kernels : nullptr;
+          const bool timing = PluginStats::get().histograms_on();
+          const uint64_t t0 = timing ? PluginStats::now_ns() : 0;
           if (nk && nk->copy_flag(dst, ksrc + s.offset, s.len, st, 0, &s.kslot, src_dev) == 0) {
             e->bytes_kernel += s.len;
+            if (timing) {
+              s.t_launch_ns = PluginStats::now_ns();
+              PluginStats::get().sample_launch(s.t_launch_ns - t0);
+            }
           } else {
             s.kslot = -1;
             s.event = e->take_event();
@@ -1159,6 +1173,7 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
             s.kslot = -1;
             s.done = s.len;
             s.complete = true;
+            if (s.t_launch_ns) PluginStats::get().sample_kernel_done(PluginStats::now_ns() - s.t_launch_ns);
           }
         } else {
           const int q = cuda::event_query(s.event);

@@ -112,6 +112,13 @@ class NcclGradReducer:
         self.buckets: list[dict] = []
         self.grads: torch.Tensor | None = None
         self.grad_scale = 1.0 / self.world   # the optimizer applies it (NCCL sums)
+        # The first steps allocate device memory and load kernels for the first time. When NCCL's
+        # traffic crosses a transport whose proxy thread has to launch device work for the collective
+        # to finish (this repository's plugin), such a call can wait for the device while the
+        # collective waits for the proxy, so these steps keep collectives apart from everything
+        # else: reductions run after backward, with the device idle before and after.
+        self.settle_steps = int(os.environ.get("B200NET_DP_SETTLE_STEPS", "2"))
+        self._steps_done = 0
 
     def allocate_grad_buffer(self, numel: int) -> torch.Tensor:
         pad = (numel + 128 * self.world - 1) // (128 * self.world) * (128 * self.world)
@@ -136,11 +143,16 @@ class NcclGradReducer:
         for b in self.buckets:
             b["pending"] = len(b["names"])
 
+    def _settling(self) -> bool:
+        return self._steps_done < self.settle_steps
+
     def _on_grad_ready(self, param) -> None:
         b = self.buckets[self._bucket_of[param.param_name]]
         b["pending"] -= 1
-        if b["pending"] == 0:
+        if b["pending"] == 0 and not self._settling():
             self._reduce(b)
+        elif b["pending"] == 0:
+            b["pending"] = -1   # reduced in finish_step
 
     def _reduce(self, b: dict) -> None:
         self.stream.wait_stream(torch.cuda.current_stream(self.device))
@@ -148,15 +160,21 @@ class NcclGradReducer:
             dist.all_reduce(self.grads[b["start"]:b["end"]], group=self.group)
 
     def finish_step(self) -> None:
+        settling = self._settling()
+        if settling:
+            torch.cuda.synchronize(self.device)
         if self.mode == "allreduce":
             for b in self.buckets:
-                if b["pending"] > 0:
+                if b["pending"] != 0:
                     b["pending"] = 0
                     self._reduce(b)
             torch.cuda.current_stream(self.device).wait_stream(self.stream)
         else:
             shard = self.grads.numel() // self.world
             dist.reduce_scatter_tensor(self.grads[self.rank * shard:(self.rank + 1) * shard], self.grads, group=self.group)
+        if settling:
+            torch.cuda.synchronize(self.device)
+        self._steps_done += 1
 
     # ---- sharded optimizer support (mode "zero")
     def shard_range(self, numel: int) -> tuple[int, int]:
@@ -167,8 +185,14 @@ class NcclGradReducer:
         """All ranks receive every shard of the updated parameters (in place)."""
         shard = self.grads.numel() // self.world
         n = flat_params.numel()
+        settling = self._steps_done <= self.settle_steps
         if n == shard * self.world:
-            dist.all_gather_into_tensor(flat_params, flat_params[self.rank * shard:(self.rank + 1) * shard].clone(), group=self.group)
+            mine = flat_params[self.rank * shard:(self.rank + 1) * shard].clone()
+            if settling:
+                torch.cuda.synchronize(self.device)
+            dist.all_gather_into_tensor(flat_params, mine, group=self.group)
+            if settling:
+                torch.cuda.synchronize(self.device)
             return
         full = torch.empty(shard * self.world, device=self.device, dtype=flat_params.dtype)
         mine = torch.zeros(shard, device=self.device, dtype=flat_params.dtype)

@@ -72,7 +72,8 @@ def run_child(argv: list[str], env: dict, port_offset: int, limit: float, tag: s
         env.pop(k, None)
     rc, out, err = run_job([sys.executable] + argv, env=env, cwd=ROOT, timeout=limit)
     if rc is None:
-        return None, f"{tag}: did not finish within {limit:.0f} s"
+        warns = [ln.split("NCCL WARN")[-1].strip()[:200] for ln in (out + err).splitlines() if "NCCL WARN" in ln][:6]
+        return None, f"{tag}: did not finish within {limit:.0f} s" + ("; " + " | ".join(warns) if warns else "")
     lines = [ln for ln in out.splitlines() if ln.startswith(tag + " ")]
     if rc != 0 or not lines:
         tail = (err or out).strip().splitlines()[-3:]
@@ -393,7 +394,7 @@ def main() -> None:
         for i, comm_mode in enumerate(("nccl", "nccl-zero")):
             r, note = run_child([os.path.abspath(__file__), "--child", "train", "--comm", comm_mode, "--steps", str(args.steps),
                                  "--warmup", str(args.warmup), "--model", args.model, "--seq", str(args.seq), "--gpus", str(world)],
-                                penv, 102 + i, 420, "TRAIN_CHILD")
+                                penv, 102 + i, 200, "TRAIN_CHILD")
             through["all_reduce" if comm_mode == "nccl" else "reduce_scatter_all_gather"] = r if r is not None else {"unavailable": note}
             dist.barrier()
         extras["through_plugin"] = through
