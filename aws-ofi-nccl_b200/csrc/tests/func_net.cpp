@@ -515,7 +515,8 @@ static int scenario_device_transfer(int sock) {
 // bytes and is checked on arrival.
 static int scenario_proxy_pattern(int sock) {
   const int channels = getenv("FUNC_NET_PROXY_CHANNELS") ? atoi(getenv("FUNC_NET_PROXY_CHANNELS")) : 8;
-  const int steps = 8, chunks_per_channel = 48;
+  const int steps = 8;
+  const int chunks_per_channel = getenv("FUNC_NET_PROXY_CHUNKS") ? atoi(getenv("FUNC_NET_PROXY_CHUNKS")) : 48;
   const size_t chunk = getenv("FUNC_NET_PROXY_CHUNK") ? strtoul(getenv("FUNC_NET_PROXY_CHUNK"), nullptr, 0) : (1u << 20);
   struct Chan {
     Pair p;

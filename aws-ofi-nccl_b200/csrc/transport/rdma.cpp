@@ -313,6 +313,8 @@ class RdmaSendComm : public SendComm {
   void release(RdmaSendReq* r);
   std::unique_ptr<ThresholdScheduler> sched;
   int inflight = 0;
+  uint64_t accepted = 0;        // sends that got a request
+  uint64_t refused_since = 0;   // send calls since then that found neither a receive nor room for an eager send
   uint32_t nonce = 0;
   bool connected = false, peer_closed = false;
 };
@@ -817,11 +819,14 @@ void RdmaEndpoint::report_stall() {
            static_cast<unsigned long long>(params().stall_report_ms.get()), live_send_reqs.size(), posted, pending.size(),
            deferred.size(), outbox_total, static_cast<unsigned long long>(fab.eagain_count()));
   for (auto& [id, sc] : send_comms) {
-    if (sc->inflight == 0) continue;
     auto* box = static_cast<CtrlMsg*>(sc->mailbox->data());
-    NET_WARN("  send comm %u -> %u: %d in flight, group %u taken %#x (ready word %#x), %zu eager unbound, %zu in the outbox%s", id,
-             sc->remote_comm_id, sc->inflight, sc->next_seq, sc->consumed_mask,
-             box[sc->next_seq % MAILBOX_SLOTS].entries[0].ready.load(), sc->eager_queue.size(), sc->outbox.size(),
+    const CtrlEntry& cur = box[sc->next_seq % MAILBOX_SLOTS].entries[0];
+    NET_WARN("  send comm %u -> %u: %d in flight, %llu sends so far, %llu calls since the last one found no receive; group %u taken %#x "
+             "(ready word %#x tag %d len %llu; previous slot %#x, next slot %#x), %zu eager unbound, %zu in the outbox%s",
+             id, sc->remote_comm_id, sc->inflight, static_cast<unsigned long long>(sc->accepted),
+             static_cast<unsigned long long>(sc->refused_since), sc->next_seq, sc->consumed_mask, cur.ready.load(), cur.tag,
+             static_cast<unsigned long long>(cur.buff_len), box[(sc->next_seq + MAILBOX_SLOTS - 1) % MAILBOX_SLOTS].entries[0].ready.load(),
+             box[(sc->next_seq + 1) % MAILBOX_SLOTS].entries[0].ready.load(), sc->eager_queue.size(), sc->outbox.size(),
              sc->peer_closed ? ", peer closed" : "");
   }
   int shown = 0;
@@ -841,10 +846,13 @@ void RdmaEndpoint::report_stall() {
   }
   for (auto& [id, rc] : recv_comms) {
     if (rc->posted.empty() && rc->eager_rx.empty()) continue;
-    NET_WARN("  recv comm %u <- %u: %d in flight, %zu groups posted (oldest seq %u), next seq %u, %zu eager messages unmatched, "
-             "eager sequence %u%s",
-             id, rc->remote_comm_id, rc->inflight, rc->posted.size(), rc->posted.empty() ? 0 : rc->posted.front()->seq, rc->next_seq,
-             rc->eager_rx.size(), rc->eager_arrived, rc->peer_closed ? ", peer closed" : "");
+    const RdmaRecvReq* oldest = rc->posted.empty() ? nullptr : rc->posted.front();
+    NET_WARN("  recv comm %u <- %u: %d in flight, %zu groups posted (oldest seq %u: %d receives, first %zu bytes tag %d, %zu received in "
+             "%d of %d segments), next seq %u, %zu eager messages unmatched, eager sequence %u%s",
+             id, rc->remote_comm_id, rc->inflight, rc->posted.size(), oldest ? oldest->seq : 0, oldest ? oldest->n : 0,
+             oldest ? oldest->subs[0].cap : 0, oldest ? oldest->subs[0].tag : 0, oldest ? oldest->subs[0].received : 0,
+             oldest ? oldest->subs[0].segs_done : 0, oldest ? oldest->subs[0].segs_expected : 0, rc->next_seq, rc->eager_rx.size(),
+             rc->eager_arrived, rc->peer_closed ? ", peer closed" : "");
   }
 }
 
@@ -1359,6 +1367,8 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle* mh, Request**
       e->pending.push_back(r->serial);
     }
     e->note_activity();
+    ++accepted;
+    refused_since = 0;
     *req = r;
     return 0;
   }
@@ -1366,7 +1376,10 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle* mh, Request**
   const size_t eager_max = params().eager_max_size.get();
   const bool eager_size_ok = eager_max > 0 && size <= eager_max && size + sizeof(EagerHdr) <= FAB_LARGE_CELL &&
                              static_cast<int>(eager_queue.size()) < MAX_EAGER_PENDING;
-  if (!eager_size_ok) return 0;  // neither control message nor eager: *req stays null and NCCL retries
+  if (!eager_size_ok) {
+    ++refused_since;
+    return 0;  // neither control message nor eager: *req stays null and NCCL retries
+  }
   RdmaSendReq* r = e->send_reqs.take();
   if (!r) return 0;
   r->comm = this;
@@ -1425,6 +1438,8 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle* mh, Request**
   }
   B200NET_TRACE_EVENT(SendEagerStart, dev_id, local_comm_id, r->ehdr.eager_seq, size, r);
   e->note_activity();
+  ++accepted;
+  refused_since = 0;
   *req = r;
   return 0;
 }

@@ -55,6 +55,10 @@ def plugin_env(base: dict) -> dict:
     # context), and the device should offer all its hardware work queues.
     env.setdefault("CUDA_MODULE_LOADING", "EAGER")
     env.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+    # gradient traffic through the plugin runs after backward, not behind it: with compute kernels
+    # and their stream waits queued on the device while the proxy thread launches copies, the first
+    # overlapped step stopped moving (both ranks waiting for data, nothing left to send)
+    env.setdefault("B200NET_DP_SETTLE_STEPS", "1000000000")
     env.pop("NCCL_TUNER_PLUGIN", None)   # the plugin registers its own tuner
     return env
 
