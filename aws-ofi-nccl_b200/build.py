@@ -187,6 +187,22 @@ def build_tests(force: bool = False, sanitize: str | None = None) -> list[Path]:
     return outs
 
 
+def build_cuda_tests(force: bool = False) -> list[Path]:
+    """csrc/tests/<name>.cu: GPU test programs that use the device API (nvcc, sm_100a)."""
+    tdir = CSRC / "tests"
+    outdir = LIB / "tests"
+    outdir.mkdir(parents=True, exist_ok=True)
+    hdrs = _headers()
+    jobs, outs = [], []
+    for s in sorted(tdir.glob("*.cu")):
+        o = outdir / s.stem
+        outs.append(o)
+        if force or _stale(o, [s] + hdrs):
+            jobs.append(([NVCC, *NVCC_FLAGS, "-cudart", "static", str(s), "-o", str(o), "-ldl"], o))
+    _compile_many(jobs)
+    return outs
+
+
 def build_fake_cuda(force: bool = False, sanitize: str | None = None) -> Path:
     """The stand-in driver for CPU tests of the device-buffer paths: lib/tests/fake_cuda/libcuda.so.1
     (with `sanitize`, an instrumented copy under build/san, so that a race detector sees the
@@ -206,6 +222,7 @@ def build_all(force: bool = False) -> None:
     build_kernels(force)
     build_host(force)
     build_tests(force)
+    build_cuda_tests(force)
     build_fake_cuda(force)
 
 

@@ -1,4 +1,5 @@
 #include "b200net/gin.h"
+#include "b200net/gin_dev_handle.h"
 #include "b200net/ipc_mapper.h"
 
 #include <unistd.h>
@@ -713,8 +714,16 @@ int CollComm::create_context(int n_signals, int n_counters, int n_contexts, bool
       max_sig = std::max(max_sig, counts[2 * r]);
       max_cnt = std::max(max_cnt, counts[2 * r + 1]);
     }
-    const size_t pad_bytes = static_cast<size_t>(n_contexts) * (2 * max_sig + max_cnt + 16) * 8;
-    if (!cuda::available() || cuda::mem_alloc(&c->dev_pad, pad_bytes) != 0) {
+    if (nranks > b200::GIN_MAX_RANKS || max_sig > b200::GIN_MAX_SIGNALS || max_cnt > b200::GIN_MAX_COUNTERS) {
+      NET_WARN("GIN: a kernel-initiated context serves at most %d ranks, %d signals and %d counters", b200::GIN_MAX_RANKS,
+               b200::GIN_MAX_SIGNALS, b200::GIN_MAX_COUNTERS);
+      delete c;
+      return -EINVAL;
+    }
+    // The pad has the layout of b200net/gin_dev_handle.h: barrier flags, signal words, reset
+    // offsets, counters and the status word at fixed offsets, the same on every rank.
+    const size_t pad_bytes = b200::GIN_PAD_BYTES;
+    if (!cuda::available() || cuda::mem_alloc(&c->dev_pad, pad_bytes) != 0) {   // zero-filled
       delete c;
       return -ENOMEM;
     }
@@ -744,25 +753,31 @@ int CollComm::create_context(int n_signals, int n_counters, int n_contexts, bool
       delete c;
       return -EIO;
     }
-    // the device-visible block: {rank, nranks, signals per context, counters per context, pad[nranks]}
-    std::vector<uint64_t> block(static_cast<size_t>(4 + nranks));
-    block[0] = static_cast<uint64_t>(rank);
-    block[1] = static_cast<uint64_t>(nranks);
-    block[2] = static_cast<uint64_t>(max_sig);
-    block[3] = static_cast<uint64_t>(max_cnt);
-    for (int r = 0; r < nranks; ++r) block[4 + r] = reinterpret_cast<uint64_t>(c->peer_pads[r]);
-    if (cuda::mem_alloc(&c->dev_handle_gpu, block.size() * 8) != 0) {
+    // the device-visible handle: exactly the structure the device API takes. Windows are not part
+    // of a context: a kernel reaches registered memory through the GinDevWindow of its registration.
+    b200::GinDevHandle h;
+    memset(&h, 0, sizeof(h));
+    h.rank = rank;
+    h.nranks = nranks;
+    for (int r = 0; r < nranks; ++r) h.pad[r] = static_cast<uint8_t*>(c->peer_pads[r]);
+    h.status = reinterpret_cast<int*>(static_cast<uint8_t*>(c->dev_pad) + b200::GIN_PAD_STATUS_OFF);
+    h.wait_limit_ns = params().device_wait_limit_ms.get() * 1000000ull;
+    if (cuda::mem_alloc(&c->dev_handle_gpu, sizeof(h)) != 0) {
+      for (int r = 0; r < nranks; ++r)
+        if (r != rank && c->peer_pads[r]) cuda::ipc_close(c->peer_pads[r]);
       cuda::mem_free(c->dev_pad);
       delete c;
       return -ENOMEM;
     }
     cuda::Stream st = nullptr;
     cuda::stream_create(&st);
-    cuda::memcpy_async(c->dev_handle_gpu, block.data(), block.size() * 8, st);
+    cuda::memcpy_async(c->dev_handle_gpu, &h, sizeof(h), st);
     cuda::stream_synchronize(st);
     cuda::stream_destroy(st);
+    c->n_signals = max_sig;
+    c->n_counters = max_cnt;
     c->net_dev_handle.handle = c->dev_handle_gpu;
-    c->net_dev_handle.size = block.size() * 8;
+    c->net_dev_handle.size = sizeof(h);
     NET_INFO(NCCL_INIT | NCCL_NET, "GIN context ready: %d ranks, %d signals, %d counters, %d contexts (kernel-initiated)",
              nranks, max_sig, max_cnt, n_contexts);
   }

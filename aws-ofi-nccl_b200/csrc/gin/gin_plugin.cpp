@@ -7,6 +7,7 @@
 
 #include "b200net/api.h"
 #include "b200net/gin.h"
+#include "b200net/gin_dev_handle.h"
 #include "b200net/log.h"
 #include "b200net/platform.h"
 
@@ -153,20 +154,24 @@ ncclResult_t reg_mr_sym_dmabuf(void* coll, void* data, size_t size, int type, ui
                                void** gin_handle) {
   return reg_mr_sym(coll, data, size, type, flags, mh, gin_handle);
 }
-// Kernel-initiated mode: the gin handle is a GPU-resident array of every rank's base pointer for
-// this registration, which device code indexes by rank.
+// Kernel-initiated mode: the gin handle is the device address of a GinDevWindow (where every rank's
+// registered range is mapped on this GPU, and its size), which the device API takes next to the
+// context's GinDevHandle (reference: the regMrSym block, src/rdma/gin/nccl_ofi_gin_gdaki.cpp:950-1164).
 ncclResult_t reg_mr_sym_kernel(void* coll, void* data, size_t size, int type, uint64_t flags, void** mh, void** gin_handle) {
   const ncclResult_t r = reg_mr_sym(coll, data, size, type, flags, mh, nullptr);
   if (r != ncclSuccess) return r;
   auto* m = static_cast<SymmMr*>(*mh);
   auto* c = static_cast<CollComm*>(coll);
   if (!m->gpu_handle_block && type == NCCL_PTR_CUDA) {
-    std::vector<uint64_t> ptrs(static_cast<size_t>(c->nranks));
-    for (int i = 0; i < c->nranks; ++i) ptrs[i] = reinterpret_cast<uint64_t>(m->mapped[i]);
-    if (cuda::mem_alloc(&m->gpu_handle_block, ptrs.size() * 8) != 0) return ncclSystemError;
+    if (c->nranks > b200::GIN_MAX_RANKS) return ncclInvalidArgument;
+    b200::GinDevWindow w;
+    memset(&w, 0, sizeof(w));
+    for (int i = 0; i < c->nranks; ++i) w.base[i] = static_cast<uint8_t*>(m->mapped[i]);
+    w.bytes = size;
+    if (cuda::mem_alloc(&m->gpu_handle_block, sizeof(w)) != 0) return ncclSystemError;
     cuda::Stream st = nullptr;
     cuda::stream_create(&st);
-    cuda::memcpy_async(m->gpu_handle_block, ptrs.data(), ptrs.size() * 8, st);
+    cuda::memcpy_async(m->gpu_handle_block, &w, sizeof(w), st);
     cuda::stream_synchronize(st);
     cuda::stream_destroy(st);
   }

@@ -15,41 +15,12 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
+#include "b200net/gin_dev_handle.h"
 #include "sm100_common.cuh"
 
 namespace b200 {
 
-constexpr int GIN_MAX_RANKS = 8;
-constexpr int GIN_MAX_BLOCKS = 256;    // barrier slots per channel
-constexpr int GIN_NUM_CHANNELS = 8;    // independent barrier sets (one per concurrently used stream)
-constexpr int GIN_MAX_SIGNALS = 4096;
-constexpr int GIN_MAX_COUNTERS = 1024;
-
-// Layout of the control pad (one per rank, symmetric):
-constexpr size_t GIN_PAD_FLAGS_OFF = 0;                                   // u32 [channel][block][src rank]
-constexpr size_t GIN_PAD_FLAGS_BYTES = size_t(GIN_NUM_CHANNELS) * GIN_MAX_BLOCKS * GIN_MAX_RANKS * 4;
-constexpr size_t GIN_PAD_EPOCH_OFF = GIN_PAD_FLAGS_OFF + GIN_PAD_FLAGS_BYTES;  // u32 [channel][block], local only
-constexpr size_t GIN_PAD_EPOCH_BYTES = size_t(GIN_NUM_CHANNELS) * GIN_MAX_BLOCKS * 4;
-constexpr size_t GIN_PAD_SIGNAL_OFF = GIN_PAD_EPOCH_OFF + GIN_PAD_EPOCH_BYTES;  // u64 [signal]
-constexpr size_t GIN_PAD_SIGNAL_BYTES = size_t(GIN_MAX_SIGNALS) * 8;
-constexpr size_t GIN_PAD_SIGBASE_OFF = GIN_PAD_SIGNAL_OFF + GIN_PAD_SIGNAL_BYTES;  // u64 [signal], local reset offsets
-constexpr size_t GIN_PAD_COUNTER_OFF = GIN_PAD_SIGBASE_OFF + GIN_PAD_SIGNAL_BYTES;  // u64 [counter], local
-constexpr size_t GIN_PAD_COUNTER_BYTES = size_t(GIN_MAX_COUNTERS) * 8;
-constexpr size_t GIN_PAD_SCRATCH_OFF = GIN_PAD_COUNTER_OFF + GIN_PAD_COUNTER_BYTES;  // free for kernels
-constexpr size_t GIN_PAD_BYTES = 2u << 20;
-
 enum GinSignalOp : uint32_t { GIN_SIGNAL_INC = 1, GIN_SIGNAL_ADD = 2 };
-
-struct GinDevHandle {
-  int rank;
-  int nranks;
-  uint8_t* window[GIN_MAX_RANKS];  // data window of every rank, mapped in this GPU's address space
-  uint8_t* mc_window;              // multicast alias of the data window (null without NVLS)
-  uint8_t* pad[GIN_MAX_RANKS];     // control pad of every rank
-  size_t window_bytes;
-  int* status;                     // device status word (first error wins)
-  uint64_t wait_limit_ns;
-};
 
 // ---------------------------------------------------------------- raw memory-model primitives
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
@@ -182,6 +153,28 @@ __device__ __forceinline__ bool gin_put(const GinDevHandle& h, int peer, size_t 
     return false;
   }
   uint8_t* dst = h.window[peer] + dst_off;
+  const uint8_t* s = static_cast<const uint8_t*>(src);
+  if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(s)) & 15) == 0) {
+    const size_t nvec = bytes >> 4;
+    const uint4* sv = reinterpret_cast<const uint4*>(s);
+    uint4* dv = reinterpret_cast<uint4*>(dst);
+    for (size_t i = tid; i < nvec; i += nthreads) dv[i] = sv[i];
+    for (size_t i = (nvec << 4) + tid; i < bytes; i += nthreads) dst[i] = s[i];
+  } else {
+    for (size_t i = tid; i < bytes; i += nthreads) dst[i] = s[i];
+  }
+  return true;
+}
+
+// The same put into a registration of its own (a window that regMrSym of the plugin's
+// kernel-initiated table described): the handle supplies the rank count and the status word.
+__device__ __forceinline__ bool gin_put_window(const GinDevHandle& h, const GinDevWindow& w, int peer, size_t dst_off,
+                                               const void* src, size_t bytes, int tid, int nthreads) {
+  if (dst_off + bytes > w.bytes || peer < 0 || peer >= h.nranks || !w.base[peer]) {
+    gin_record_error(h, DEV_ERR_BOUNDS);
+    return false;
+  }
+  uint8_t* dst = w.base[peer] + dst_off;
   const uint8_t* s = static_cast<const uint8_t*>(src);
   if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(s)) & 15) == 0) {
     const size_t nvec = bytes >> 4;

@@ -50,7 +50,10 @@ std::vector<std::pair<std::string, std::string>> PlatformB200::nccl_env() const 
                                                           {"NCCL_P2P_NET_CHUNKSIZE", "4194304"},
                                                           {"NCCL_NVLS_CHUNKSIZE", "524288"},
                                                           {"NCCL_NET_FORCE_FLUSH", "0"},
-                                                          {"NCCL_PROTO", "^LL128"}};
+                                                          {"NCCL_PROTO", "^LL128"},
+                                                          // sixteen channels are connected; the tuner gives each call as
+                                                          // many of them as its size is worth
+                                                          {"NCCL_MIN_NCHANNELS", "16"}};
   if (params().nccl_device_buffers.get()) {
     env.emplace_back("NCCL_NET_GDR_LEVEL", "SYS");
     env.emplace_back("NCCL_NET_GDR_READ", "1");

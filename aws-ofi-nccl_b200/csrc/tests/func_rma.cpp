@@ -20,6 +20,8 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+
+#include "b200net/gin_dev_handle.h"
 #include <vector>
 
 #include "nccl_abi.h"
@@ -266,19 +268,20 @@ static int run_rank(const char* so) {
     } else {
     OK(gin14->createContext(coll, &kcfg, &kctx, &dh));
     if (!dh || dh->netDeviceType != NCCL_NET_DEVICE_GIN_GDAKI || dh->needsProxyProgress) FAIL("unexpected device handle");
-    if (dh->size != (4 + (size_t)g_n) * 8) FAIL("handle block of %zu bytes", (size_t)dh->size);
-    const uint64_t* block = static_cast<const uint64_t*>(g_dev_view(dh->handle));
-    if (block[0] != (uint64_t)g_rank || block[1] != (uint64_t)g_n || block[2] != (uint64_t)(3 + g_n - 1) || block[3] != 2)
-      FAIL("handle block says rank %llu of %llu, %llu signals, %llu counters", (unsigned long long)block[0],
-           (unsigned long long)block[1], (unsigned long long)block[2], (unsigned long long)block[3]);
-    // each rank leaves its mark in word [rank] of every pad through the mapping it was given
+    if (dh->size != sizeof(b200::GinDevHandle)) FAIL("handle of %zu bytes", (size_t)dh->size);
+    const auto* hd = static_cast<const b200::GinDevHandle*>(g_dev_view(dh->handle));
+    if (hd->rank != g_rank || hd->nranks != g_n || !hd->status || hd->wait_limit_ns == 0)
+      FAIL("handle says rank %d of %d, status %p, wait limit %llu", hd->rank, hd->nranks, (void*)hd->status,
+           (unsigned long long)hd->wait_limit_ns);
+    if (reinterpret_cast<uint8_t*>(hd->status) != hd->pad[g_rank] + b200::GIN_PAD_STATUS_OFF) FAIL("status word is not inside the own pad");
+    // each rank leaves its mark in signal word [rank] of every pad through the mapping it was given
     for (int r = 0; r < g_n; ++r) {
-      if (!block[4 + r]) FAIL("pad of rank %d is not mapped", r);
-      auto* pad = static_cast<uint64_t*>(g_dev_view(reinterpret_cast<void*>(block[4 + r])));
-      __atomic_store_n(&pad[g_rank], 0xAB00u + g_rank, __ATOMIC_RELEASE);
+      if (!hd->pad[r]) FAIL("pad of rank %d is not mapped", r);
+      auto* sig = reinterpret_cast<uint64_t*>(static_cast<uint8_t*>(g_dev_view(hd->pad[r])) + b200::GIN_PAD_SIGNAL_OFF);
+      __atomic_store_n(&sig[g_rank], 0xAB00u + g_rank, __ATOMIC_RELEASE);
     }
     if (oob_barrier()) FAIL("barrier");
-    const auto* mine = static_cast<const uint64_t*>(g_dev_view(reinterpret_cast<void*>(block[4 + g_rank])));
+    const auto* mine = reinterpret_cast<const uint64_t*>(static_cast<const uint8_t*>(g_dev_view(hd->pad[g_rank])) + b200::GIN_PAD_SIGNAL_OFF);
     for (int r = 0; r < g_n; ++r)
       if (__atomic_load_n(&mine[r], __ATOMIC_ACQUIRE) != 0xAB00u + r) FAIL("pad word %d holds %llx", r, (unsigned long long)mine[r]);
     if (oob_barrier()) FAIL("barrier");

@@ -136,5 +136,25 @@ int main() {
   CHECK(find_instance("p6-b200.48xlarge")->gdaki && find_instance("p6e-b200.36xlarge") != nullptr);
   CHECK(find_instance("p3dn.24xlarge")->latency_us == 150.f && !find_instance("p3dn.24xlarge")->gdaki);
   CHECK(find_instance("c5.large") == nullptr && find_instance("") == nullptr);
+  // ranks that only reach each other through the plugin's own transport: channel counts by size, algorithm left to NCCL
+  {
+    TransportTuner t(PlatformKind::B200_NVSWITCH, 8, 8);
+    CHECK(t.supported());
+    CHECK(!TransportTuner(PlatformKind::B200_NVSWITCH, 8, 1).supported());   // one node: NVLink transports, not this one
+    CHECK(!TransportTuner(PlatformKind::P5EN, 8, 8).supported());
+    Decision d = t.decide(ncclFuncAllReduce, 1u << 20);   // 128 KiB per step
+    CHECK_EQ(d.algorithm, NCCL_ALGO_UNDEF);
+    CHECK_EQ(d.n_channels, 1);
+    CHECK_EQ(t.decide(ncclFuncAllGather, 1u << 20).n_channels, 4);
+    CHECK_EQ(t.decide(ncclFuncReduceScatter, 64u << 20).n_channels, 16);
+    CHECK_EQ(t.decide(ncclFuncAllReduce, 256u << 20).n_channels, 16);
+    CHECK_EQ(t.decide(ncclFuncSendRecv, 1u << 20).n_channels, 0);
+    int nch = 0;
+    float table[NCCL_NUM_ALGORITHMS][NCCL_NUM_PROTOCOLS];
+    for (auto& row : table) for (float& c : row) c = 1.0f;
+    CHECK(!apply_decision(d, reinterpret_cast<float**>(table), NCCL_NUM_ALGORITHMS, NCCL_NUM_PROTOCOLS, &nch));
+    CHECK_EQ(nch, 1);                 // the channel count is applied although no table entry was chosen
+    CHECK_EQ(table[0][0], 1.0f);      // and the table is untouched
+  }
   TEST_MAIN_END();
 }

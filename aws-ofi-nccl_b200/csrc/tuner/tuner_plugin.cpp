@@ -51,6 +51,31 @@ TunerContext::~TunerContext() {
   delete region;
   delete model;
   delete measured;
+  delete transport;
+}
+
+TransportTuner::TransportTuner(PlatformKind platform, size_t n_ranks, size_t n_nodes) : n_ranks_(n_ranks) {
+  supported_ = platform == PlatformKind::B200_NVSWITCH && n_ranks >= 2 && n_nodes == n_ranks;
+}
+
+int TransportTuner::channels_for(size_t bytes_per_step) {
+  if (bytes_per_step <= (128u << 10)) return 1;
+  if (bytes_per_step <= (512u << 10)) return 2;
+  if (bytes_per_step <= (2u << 20)) return 4;
+  if (bytes_per_step <= (16u << 20)) return 8;
+  return 16;
+}
+
+Decision TransportTuner::decide(ncclFunc_t coll, size_t bytes) const {
+  Decision d;
+  if (!supported_ || bytes == 0) return d;
+  // what one ring step moves: a 1/n slice of an all_reduce buffer; `bytes` already is the per-rank
+  // part for all_gather and reduce_scatter
+  size_t per_step = bytes;
+  if (coll == ncclFuncAllReduce) per_step = bytes / n_ranks_;
+  else if (coll != ncclFuncAllGather && coll != ncclFuncReduceScatter) return d;   // point-to-point and rooted calls: NCCL's own
+  d.n_channels = channels_for(per_step);
+  return d;
 }
 
 TunerContext* create_context(size_t n_ranks, size_t n_nodes) {
@@ -73,6 +98,15 @@ TunerContext* create_context(size_t n_ranks, size_t n_nodes) {
       return ctx;
     }
     delete m;
+  }
+  {
+    auto* t = new TransportTuner(plat, n_ranks, n_nodes);
+    if (t->supported() && type != "model" && type != "region") {
+      ctx->transport = t;
+      ctx->type = TunerType::TRANSPORT;
+      return ctx;
+    }
+    delete t;
   }
   if (type != "model") {
     auto* r = new RegionTuner(plat, n_ranks, n_nodes);
@@ -100,12 +134,16 @@ Decision get_decision(const TunerContext* ctx, ncclFunc_t coll, size_t bytes, in
     case TunerType::MEASURED: return ctx->measured->decide(coll, bytes);
     case TunerType::REGION: return ctx->region->decide(coll, bytes);
     case TunerType::MODEL: return ctx->model->decide(coll, bytes, pipe_ops);
+    case TunerType::TRANSPORT: return ctx->transport->decide(coll, bytes);
     default: return Decision();
   }
 }
 
 bool apply_decision(const Decision& d, float** cost_table, int num_algo, int num_proto, int* n_channels) {
-  if (d.algorithm == NCCL_ALGO_UNDEF || d.protocol == NCCL_PROTO_UNDEF) return false;
+  if (d.algorithm == NCCL_ALGO_UNDEF || d.protocol == NCCL_PROTO_UNDEF) {
+    if (n_channels && d.n_channels > 0) *n_channels = d.n_channels;   // channel count only
+    return false;
+  }
   if (d.algorithm >= num_algo || d.protocol >= num_proto || !cost_table) return false;
   float(*table)[NCCL_NUM_PROTOCOLS] = reinterpret_cast<float(*)[NCCL_NUM_PROTOCOLS]>(cost_table);
   if (table[d.algorithm][d.protocol] == NCCL_ALGO_PROTO_IGNORE) return false;  // NCCL ruled it out
@@ -180,7 +218,10 @@ ncclResult_t get_coll_info_v2(void* context, ncclFunc_t coll, size_t bytes, int 
                               int* algorithm, int* protocol, int* n_channels) {
   if (!context) return ncclSuccess;
   const Decision d = get_decision(static_cast<TunerContext*>(context), coll, bytes, pipe_ops);
-  if (d.algorithm == NCCL_ALGO_UNDEF) return ncclSuccess;
+  if (d.algorithm == NCCL_ALGO_UNDEF) {
+    if (n_channels && d.n_channels > 0) *n_channels = d.n_channels;
+    return ncclSuccess;
+  }
   if ((d.algorithm == NCCL_ALGO_NVLS || d.algorithm == NCCL_ALGO_NVLS_TREE) && !nvls) return ncclSuccess;
   if ((d.algorithm == NCCL_ALGO_COLLNET_DIRECT || d.algorithm == NCCL_ALGO_COLLNET_CHAIN) && !collnet) return ncclSuccess;
   if (algorithm) *algorithm = d.algorithm;

@@ -391,14 +391,14 @@ def main() -> None:
         # ---- arms whose NCCL traffic crosses this repository's net plugin (child processes)
         penv = plugin_env(os.environ)
         rows, note = run_child([os.path.abspath(__file__), "--child", "collectives", "--sizes"] + [str(s) for s in args.sizes],
-                               penv, 101, 240, "COLL_CHILD")
+                               penv, 101, 120, "COLL_CHILD")
         extras["nccl_over_plugin"] = rows if rows is not None else {"unavailable": note}
         dist.barrier()
         through = {}
         for i, comm_mode in enumerate(("nccl", "nccl-zero")):
             r, note = run_child([os.path.abspath(__file__), "--child", "train", "--comm", comm_mode, "--steps", str(args.steps),
                                  "--warmup", str(args.warmup), "--model", args.model, "--seq", str(args.seq), "--gpus", str(world)],
-                                penv, 102 + i, 200, "TRAIN_CHILD")
+                                penv, 102 + i, 150, "TRAIN_CHILD")
             through["all_reduce" if comm_mode == "nccl" else "reduce_scatter_all_gather"] = r if r is not None else {"unavailable": note}
             dist.barrier()
         extras["through_plugin"] = through
