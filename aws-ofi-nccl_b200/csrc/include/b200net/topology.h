@@ -12,6 +12,13 @@ namespace b200net {
 
 enum class LinkType : uint8_t { SELF, NVLINK, PCIE, NONE };
 
+// One PCI device on the way from the root complex to a GPU (a bridge or switch port).
+struct TopoPciHop {
+  std::string bus_id;       // "0000:17:00.0"
+  std::string link_speed;   // sysfs current_link_speed, e.g. "32.0 GT/s PCIe" ("" when unknown)
+  int link_width = 0;       // sysfs current_link_width
+};
+
 struct TopoGpu {
   int ordinal = 0;
   std::string pci_bus_id;   // "0000:1b:00.0"
@@ -21,6 +28,11 @@ struct TopoGpu {
   int sm_count = 0;
   bool multicast = false;   // NVSwitch multicast objects supported
   uint8_t uuid[16] = {0};
+  // From sysfs: the bridges above the GPU, root first (empty in a VM that puts the GPU directly on
+  // the root bus), and the GPU's own link.
+  std::vector<TopoPciHop> pci_path;
+  std::string link_speed;
+  int link_width = 0;
 };
 
 struct TopoGroup {          // one GPU and the rails serving it
@@ -33,6 +45,11 @@ class Topology {
  public:
   // Discover through the CUDA driver. Empty (no GPUs) when no driver is present.
   static Topology discover();
+  // Fills numa_node, the link and the chain of bridges of `gpu` from <sysfs_root>/bus/pci/devices
+  // (sysfs_root is "/sys" outside tests). False when the device is not there
+  // (reference: the hwloc walk of src/nccl_ofi_topo.cpp:859-1259 and the link speed / width it
+  // reads from sysfs, :1312-1498).
+  static bool read_pci(TopoGpu* gpu, const std::string& sysfs_root = "/sys");
   // Build from a description (tests, tools): `links[i][j]` for every GPU pair.
   static Topology from_description(std::vector<TopoGpu> gpus, std::vector<std::vector<LinkType>> links);
 

@@ -1,10 +1,12 @@
 #include "b200net/topology.h"
 
+#include <limits.h>
 #include <sys/mman.h>
 #include <unistd.h>
 
 #include <algorithm>
 #include <cctype>
+#include <cstdlib>
 #include <cstring>
 #include <cstdio>
 
@@ -14,15 +16,54 @@
 
 namespace b200net {
 
-static int read_numa_node(const std::string& bus_id) {
-  std::string id = bus_id;
-  std::transform(id.begin(), id.end(), id.begin(), [](unsigned char c) { return std::tolower(c); });
-  int n = -1;
-  if (FILE* f = fopen(("/sys/bus/pci/devices/" + id + "/numa_node").c_str(), "r")) {
-    if (fscanf(f, "%d", &n) != 1) n = -1;
+static std::string read_line(const std::string& path) {
+  std::string out;
+  if (FILE* f = fopen(path.c_str(), "r")) {
+    char buf[128];
+    if (fgets(buf, sizeof(buf), f)) out = buf;
     fclose(f);
   }
-  return n;
+  while (!out.empty() && (out.back() == '\n' || out.back() == ' ')) out.pop_back();
+  return out;
+}
+
+static bool looks_like_bdf(const std::string& s) {   // dddd:bb:dd.f
+  return s.size() >= 12 && s[4] == ':' && s[7] == ':' && s[10] == '.';
+}
+
+bool Topology::read_pci(TopoGpu* gpu, const std::string& sysfs_root) {
+  std::string id = gpu->pci_bus_id;
+  std::transform(id.begin(), id.end(), id.begin(), [](unsigned char c) { return std::tolower(c); });
+  if (id.empty()) return false;
+  const std::string link = sysfs_root + "/bus/pci/devices/" + id;
+  char real[PATH_MAX];
+  if (!realpath(link.c_str(), real)) return false;
+  const std::string numa = read_line(link + "/numa_node");
+  gpu->numa_node = numa.empty() ? -1 : atoi(numa.c_str());
+  gpu->link_speed = read_line(link + "/current_link_speed");
+  gpu->link_width = atoi(read_line(link + "/current_link_width").c_str());
+  // /sys/devices/pci0000:15/0000:15:01.0/0000:16:00.0/0000:17:00.0/<gpu>: every component that is a
+  // bus address, except the last, is a bridge above the GPU
+  gpu->pci_path.clear();
+  std::string path(real), built;
+  size_t pos = 0;
+  std::vector<std::string> parts;
+  while (pos <= path.size()) {
+    const size_t next = path.find('/', pos);
+    parts.push_back(path.substr(pos, next == std::string::npos ? std::string::npos : next - pos));
+    if (next == std::string::npos) break;
+    pos = next + 1;
+  }
+  for (size_t i = 0; i < parts.size(); ++i) {
+    built += (i ? "/" : "") + parts[i];
+    if (i + 1 == parts.size() || !looks_like_bdf(parts[i])) continue;
+    TopoPciHop hop;
+    hop.bus_id = parts[i];
+    hop.link_speed = read_line(built + "/current_link_speed");
+    hop.link_width = atoi(read_line(built + "/current_link_width").c_str());
+    gpu->pci_path.push_back(hop);
+  }
+  return true;
 }
 
 Topology Topology::discover() {
@@ -33,7 +74,7 @@ Topology Topology::discover() {
     g.ordinal = i;
     char bus[32] = {0};
     if (cuda::device_pci_bus_id(i, bus, sizeof(bus)) == 0) g.pci_bus_id = bus;
-    g.numa_node = read_numa_node(g.pci_bus_id);
+    read_pci(&g);
     cuda::device_attribute(75, i, &g.cc_major);   // COMPUTE_CAPABILITY_MAJOR
     cuda::device_attribute(76, i, &g.cc_minor);   // COMPUTE_CAPABILITY_MINOR
     cuda::device_attribute(16, i, &g.sm_count);   // MULTIPROCESSOR_COUNT
@@ -112,28 +153,66 @@ std::string Topology::to_nccl_xml(const std::vector<TopoGroup>& groups) const {
     snprintf(line, sizeof(line),
              "  <cpu numaid=\"%d\" affinity=\"\" arch=\"x86_64\" vendor=\"\" familyid=\"0\" modelid=\"0\">\n", numa);
     o += line;
-    for (const auto& grp : groups) {
+    // GPUs of this NUMA node as a tree of the bridges above them (GPUs behind one switch share its
+    // node); a GPU with no bridge above it gets a virtual one, so that it and its NIC have a
+    // common parent below the CPU and NCCL's search pairs them with the shortest path
+    std::vector<std::string> open_path;   // bridges currently open in the output
+    auto close_to = [&](size_t depth) {
+      while (open_path.size() > depth) {
+        o += std::string(2 + 2 * open_path.size(), ' ') + "</pci>\n";
+        open_path.pop_back();
+      }
+    };
+    std::vector<const TopoGroup*> here;
+    for (const auto& grp : groups)
+      if ((gpus_[grp.gpu].numa_node < 0 ? 0 : gpus_[grp.gpu].numa_node) == numa) here.push_back(&grp);
+    auto path_key = [&](const TopoGroup* grp) {
+      std::string k;
+      for (const TopoPciHop& h : gpus_[grp->gpu].pci_path) k += h.bus_id + "/";
+      return k;
+    };
+    std::stable_sort(here.begin(), here.end(), [&](const TopoGroup* a, const TopoGroup* b) { return path_key(a) < path_key(b); });
+    for (const TopoGroup* grp_p : here) {
+      const TopoGroup& grp = *grp_p;
       const TopoGpu& g = gpus_[grp.gpu];
-      if ((g.numa_node < 0 ? 0 : g.numa_node) != numa) continue;
-      snprintf(line, sizeof(line),
-               "    <pci busid=\"ffff:%02x:00.0\" class=\"0x060400\" link_speed=\"32.0 GT/s PCIe\" link_width=\"16\">\n",
+      std::vector<TopoPciHop> path = g.pci_path;
+      if (path.empty()) {
+        TopoPciHop v;
+        char id[32];
+        snprintf(id, sizeof(id), "ffff:%02x:00.0", g.ordinal);
+        v.bus_id = id;
+        v.link_speed = "32.0 GT/s PCIe";
+        v.link_width = 16;
+        path.push_back(v);
+      }
+      size_t common = 0;
+      while (common < open_path.size() && common < path.size() && open_path[common] == path[common].bus_id) ++common;
+      close_to(common);
+      for (size_t d = common; d < path.size(); ++d) {
+        snprintf(line, sizeof(line), "%*s<pci busid=\"%s\" class=\"0x060400\" link_speed=\"%s\" link_width=\"%d\">\n",
+                 static_cast<int>(4 + 2 * d), "", path[d].bus_id.c_str(),
+                 path[d].link_speed.empty() ? "32.0 GT/s PCIe" : path[d].link_speed.c_str(), path[d].link_width ? path[d].link_width : 16);
+        o += line;
+        open_path.push_back(path[d].bus_id);
+      }
+      const int ind = static_cast<int>(4 + 2 * path.size());
+      snprintf(line, sizeof(line), "%*s<pci busid=\"%s\" class=\"0x030200\" link_speed=\"%s\" link_width=\"%d\"/>\n", ind, "",
+               g.pci_bus_id.empty() ? "0000:00:00.0" : g.pci_bus_id.c_str(), g.link_speed.empty() ? "32.0 GT/s PCIe" : g.link_speed.c_str(),
+               g.link_width ? g.link_width : 16);
+      o += line;
+      snprintf(line, sizeof(line), "%*s<pci busid=\"ffff:%02x:01.0\" class=\"0x020000\" link_speed=\"32.0 GT/s PCIe\" link_width=\"16\">\n", ind, "",
                g.ordinal);
       o += line;
-      snprintf(line, sizeof(line),
-               "      <pci busid=\"%s\" class=\"0x030200\" link_speed=\"32.0 GT/s PCIe\" link_width=\"16\"/>\n",
-               g.pci_bus_id.empty() ? "0000:00:00.0" : g.pci_bus_id.c_str());
+      snprintf(line, sizeof(line), "%*s<nic>\n", ind + 2, "");
       o += line;
       snprintf(line, sizeof(line),
-               "      <pci busid=\"ffff:%02x:01.0\" class=\"0x020000\" link_speed=\"32.0 GT/s PCIe\" link_width=\"16\">\n",
-               g.ordinal);
-      o += line;
-      o += "        <nic>\n";
-      snprintf(line, sizeof(line),
-               "          <net name=\"nvl%d\" dev=\"%d\" speed=\"%d\" port=\"0\" guid=\"0x%llx\" maxconn=\"32768\" gdr=\"1\"/>\n",
+               "%*s<net name=\"nvl%d\" dev=\"%d\" speed=\"%d\" port=\"0\" guid=\"0x%llx\" maxconn=\"32768\" gdr=\"1\"/>\n", ind + 4, "",
                g.ordinal, g.ordinal, grp.speed_mbps, 0xb200000000ull | static_cast<unsigned>(g.ordinal));
       o += line;
-      o += "        </nic>\n      </pci>\n    </pci>\n";
+      snprintf(line, sizeof(line), "%*s</nic>\n%*s</pci>\n", ind + 2, "", ind, "");
+      o += line;
     }
+    close_to(0);
     o += "  </cpu>\n";
   }
   o += "</system>\n";

@@ -80,6 +80,56 @@ int main() {
   CHECK(!Topology::from_description(gpus, links).nvls_capable());
   CHECK(!Topology::from_description({}, {}).all_nvlink());
 
+  // ---- PCI hierarchy from a (fake) sysfs tree: two GPUs behind one switch, a third on a root port of its own
+  {
+    char tmpl[] = "/tmp/b200net-sysfs-XXXXXX";
+    const std::string root = mkdtemp(tmpl);
+    auto sh = [&](const std::string& cmd) { return system(cmd.c_str()); };
+    const std::string dev = root + "/devices/pci0000:15";
+    CHECK_EQ(sh("mkdir -p " + dev + "/0000:15:01.0/0000:16:00.0/0000:17:00.0/0000:18:00.0 " + dev + "/0000:15:01.0/0000:16:00.0/0000:17:01.0/0000:19:00.0 " +
+                root + "/devices/pci0000:80/0000:80:01.0/0000:81:00.0 " + root + "/bus/pci/devices"), 0);
+    for (const char* bdf : {"0000:15:01.0/0000:16:00.0/0000:17:00.0/0000:18:00.0", "0000:15:01.0/0000:16:00.0/0000:17:01.0/0000:19:00.0"}) {
+      const std::string d = dev + "/" + bdf, leaf = d.substr(d.rfind('/') + 1);
+      sh("echo 0 > " + d + "/numa_node; echo '32.0 GT/s PCIe' > " + d + "/current_link_speed; echo 16 > " + d + "/current_link_width");
+      sh("ln -s " + d + " " + root + "/bus/pci/devices/" + leaf);
+    }
+    sh("echo '16.0 GT/s PCIe' > " + dev + "/0000:15:01.0/0000:16:00.0/current_link_speed; echo 8 > " + dev + "/0000:15:01.0/0000:16:00.0/current_link_width");
+    const std::string d3 = root + "/devices/pci0000:80/0000:80:01.0/0000:81:00.0";
+    sh("echo 1 > " + d3 + "/numa_node; ln -s " + d3 + " " + root + "/bus/pci/devices/0000:81:00.0");
+    std::vector<TopoGpu> pg(3);
+    const char* ids[] = {"0000:18:00.0", "0000:19:00.0", "0000:81:00.0"};
+    for (int i = 0; i < 3; ++i) {
+      pg[i].ordinal = i;
+      pg[i].pci_bus_id = ids[i];
+      CHECK(Topology::read_pci(&pg[i], root));
+    }
+    CHECK_EQ(pg[0].pci_path.size(), 3u);
+    CHECK(pg[0].pci_path[0].bus_id == "0000:15:01.0" && pg[0].pci_path[2].bus_id == "0000:17:00.0");
+    CHECK(pg[0].pci_path[1].link_speed == "16.0 GT/s PCIe" && pg[0].pci_path[1].link_width == 8);
+    CHECK(pg[0].link_width == 16 && pg[0].numa_node == 0 && pg[2].numa_node == 1);
+    CHECK_EQ(pg[2].pci_path.size(), 1u);
+    TopoGpu missing;
+    missing.pci_bus_id = "0000:ff:00.0";
+    CHECK(!Topology::read_pci(&missing, root));
+    std::vector<std::vector<LinkType>> l3(3, std::vector<LinkType>(3, LinkType::NVLINK));
+    Topology pt = Topology::from_description(pg, l3);
+    const std::string px = pt.to_nccl_xml(pt.group(1, 7200000));
+    // the two GPUs behind the switch share its upstream bridges (each named once), then split at the switch ports
+    CHECK(px.find("0000:16:00.0") != std::string::npos && px.find("0000:16:00.0") == px.rfind("0000:16:00.0"));
+    CHECK(px.find("busid=\"0000:17:00.0\"") < px.find("busid=\"0000:18:00.0\"") && px.find("busid=\"0000:18:00.0\"") < px.find("nvl0"));
+    CHECK(px.find("nvl0") < px.find("busid=\"0000:17:01.0\"") && px.find("busid=\"0000:17:01.0\"") < px.find("nvl1"));
+    CHECK(px.find("link_speed=\"16.0 GT/s PCIe\" link_width=\"8\"") != std::string::npos);
+    CHECK(px.find("numaid=\"1\"") < px.find("busid=\"0000:80:01.0\"") && px.find("busid=\"0000:80:01.0\"") < px.find("nvl2"));
+    size_t opens = 0, closes = 0;
+    for (size_t p2 = 0; (p2 = px.find("<pci ", p2)) != std::string::npos; ++p2) ++opens;
+    for (size_t p2 = 0; (p2 = px.find("</pci>", p2)) != std::string::npos; ++p2) ++closes;
+    size_t selfclosed = 0;
+    for (size_t p2 = 0; (p2 = px.find("\"/>\n", p2)) != std::string::npos; ++p2) ++selfclosed;
+    CHECK_EQ(opens, closes + 3u);   // the three GPU nodes are self-closing (the <net/> lines are not <pci>)
+    (void)selfclosed;
+    sh("rm -rf " + root);
+  }
+
   // ---- system helpers
   setenv("OFI_NCCL_FORCE_PRODUCT_NAME", "p5en.48xlarge", 1);
   CHECK(system_product_name() == "p5en.48xlarge");
