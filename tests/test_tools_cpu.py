@@ -51,17 +51,11 @@ def test_calibration_table_feeds_the_measured_tuner(built, tmp_path, monkeypatch
     which Ring/LL wins below 64 KiB and Ring/Simple above."""
     from aws_ofi_nccl_b200.utils import tuner_calibrate as tc
 
-    def fake_run(cmd, capture_output, text, timeout, env):
+    def fake_run(cmd, env=None, cwd=None, timeout=600.0):
+        """Stands in for utils.proc.run_job: (returncode, stdout, stderr)."""
         algo, proto = env["NCCL_ALGO"], env["NCCL_PROTO"]
-
-        class R:
-            returncode = 0
-            stdout = ""
-            stderr = ""
-        r = R()
         if algo != "Ring":
-            r.returncode = 1   # "not available here"
-            return r
+            return 1, "", ""   # "not available here"
         rows = []
         for size in (1 << 10, 1 << 14, 1 << 18, 1 << 22, 1 << 26):
             if proto == "LL":
@@ -71,10 +65,9 @@ def test_calibration_table_feeds_the_measured_tuner(built, tmp_path, monkeypatch
             else:
                 continue
             rows.append({"coll": tc.COLLS["all_reduce"], "bytes": size, "time_us": t})
-        r.stdout = "noise\nCALIBRATION_ROWS " + json.dumps(rows) + "\n"
-        return r
+        return 0, "noise\nCALIBRATION_ROWS " + json.dumps(rows) + "\n", ""
 
-    monkeypatch.setattr(tc.subprocess, "run", fake_run)
+    monkeypatch.setattr(tc, "run_job", fake_run)
     table = tmp_path / "measured.json"
     assert tc.main(["--gpus", "8", "--out", str(table), "--algos", "Ring", "Tree", "--protos", "LL", "Simple"]) == 0
     doc = json.loads(table.read_text())
