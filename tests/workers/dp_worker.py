@@ -1,5 +1,7 @@
 """Multi-GPU worker: data-parallel tiny Llama — gradients after the fused all-reduce must equal the
-average of the per-rank gradients, and the ranks must stay bit-identical after optimizer steps."""
+average of the per-rank gradients, the ranks must stay bit-identical after optimizer steps, and N
+ranks fed identical batches must reproduce the loss curve of a single replica step for step (with
+this library's reducer and with the NCCL-based one in both of its modes)."""
 import os
 import sys
 
@@ -57,6 +59,32 @@ def main():
     if not torch.equal(pmax, pmin):
         ok = False
         print(f"[{rank}] replicas diverged: {(pmax - pmin).abs().max().item()}")
+    # ---- loss parity: the same batches on every rank, so the averaged gradient equals one
+    # replica's gradient and the loss curve has to match a run without any reducer
+    from aws_ofi_nccl_b200.parallel.data_parallel import NcclGradReducer
+    from aws_ofi_nccl_b200.parallel.engine import OptimConfig
+
+    gen2 = torch.Generator().manual_seed(4242)
+    batches = [(torch.randint(0, cfg.vocab_size, (2, 128), generator=gen2).to(dev),
+                torch.randint(0, cfg.vocab_size, (2, 128), generator=gen2).to(dev)) for _ in range(3)]
+
+    def curve(reducer):
+        trainer = Trainer(cfg, OptimConfig(lr=1e-3), device=dev, dp=reducer, seed=11)
+        out = [trainer.step_device(*batches[i % 3]).item() for i in range(6)]
+        torch.cuda.synchronize()
+        return out
+
+    single = curve(None)
+    for name, make in (("fused", lambda: GradReducer(dist.group.WORLD, dev, bucket_bytes=256 << 10, channel=3)),
+                       ("nccl all-reduce", lambda: NcclGradReducer(dist.group.WORLD, dev, bucket_bytes=256 << 10)),
+                       ("nccl reduce-scatter + all-gather", lambda: NcclGradReducer(dist.group.WORLD, dev, mode="zero"))):
+        red = make()
+        got = curve(red)
+        red.close()
+        worst = max(abs(a - b) / max(abs(b), 1e-6) for a, b in zip(got, single))
+        if worst > 2e-2:
+            ok = False
+            print(f"[{rank}] loss curve with the {name} reducer differs from the single replica: {got} vs {single}")
     t = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
     status = _lib.read_status()
