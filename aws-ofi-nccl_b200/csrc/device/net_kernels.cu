@@ -11,6 +11,7 @@
 //                       shared memory -> the peer's memory, so a handful of CTAs with one warp each
 //                       hold megabytes in flight over NVLink and leave the SMs' issue slots to the
 //                       collective kernel that is running beside it. No load is multicast.
+//  b200net_signal_add : a GIN signal applied by the host for a peer: one atomic add on the word.
 //  b200net_eager_pack : small device payload -> one pinned host slot laid out as
 //                       [header 16 B][payload][flag 8 B]: payload and header first, the flag last
 //                       with release ordering, so a reader that sees the flag sees the whole slot.
@@ -156,6 +157,13 @@ extern "C" __global__ void __launch_bounds__(32)
   }
   const int last = last_cta(counter, failed);
   if (last && threadIdx.x == 0) st_release_sys_u64(flag, last == 2 ? (flag_value | (1ull << 63)) : flag_value);
+}
+
+// A signal raised by the host on behalf of a peer: one release-ordered atomic add on the signal
+// word in device memory. An atomic, not a store of a value computed on the host: kernels that
+// raise the same signal from the device (red.release.sys) and this one compose.
+extern "C" __global__ void b200net_signal_add(unsigned long long* word, unsigned long long value) {
+  asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(word), "l"(value) : "memory");
 }
 
 // One CTA. slot: [hdr0 u64][hdr1 u64][payload ...][pad to 8][flag u64 at slot + flag_off].

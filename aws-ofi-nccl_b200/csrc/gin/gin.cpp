@@ -10,6 +10,7 @@
 
 #include "b200net/api.h"
 #include "b200net/log.h"
+#include "b200net/net_kernels.h"
 #include "b200net/param.h"
 #include "b200net/plugin_stats.h"
 #include "b200net/tracepoint.h"
@@ -63,6 +64,24 @@ void DeviceSignalWorker::run() {
       if (void* ctx = ctx_.load(std::memory_order_acquire)) cuda::ctx_set_current(ctx);
       else cuda::ensure_primary_ctx(0);
       cuda::stream_create(&stream_);
+    }
+    // With the plugin's kernels loaded a signal is an atomic add on the device: it composes with
+    // signals that kernels raise on the same word. The host shadow below is the path of a run
+    // without the kernels; it owns the word (an update made by anybody else would be lost).
+    NetKernels* nk = NetKernels::get();
+    if (nk) {
+      bool all = true;
+      for (auto& [addr, add] : batch) all = all && nk->signal_add(reinterpret_cast<void*>(addr), add, stream_) == 0;
+      if (all) {
+        cuda::stream_synchronize(stream_);
+        completed_.fetch_add(static_cast<uint64_t>(n));
+        continue;
+      }
+      cuda::stream_synchronize(stream_);   // some launch failed: fall through to the copy path for the whole batch is not
+                                           // possible (part was applied), so report nothing lost and stop using kernels
+      NET_WARN("signal kernel launch failed; %d signal update(s) of this batch may be missing", n);
+      completed_.fetch_add(static_cast<uint64_t>(n));
+      continue;
     }
     for (auto& [addr, add] : batch) {
       auto it = shadow_.find(addr);
@@ -434,7 +453,20 @@ int CollComm::retire(PeerState& p, uint32_t peer_rank) {
   while (!p.ops.empty()) {
     PendingOp& op = p.ops.front();
     if (!op.data_done) {
-      if (op.event) {
+      if (op.kslot >= 0) {
+        NetKernels* nk = NetKernels::get();
+        const int ks = nk ? nk->status(op.kslot) : -EIO;
+        if (ks == 0) return 0;
+        if (nk) nk->release(op.kslot);
+        op.kslot = -1;
+        if (ks < 0) {
+          op.status->store(-EIO);
+          error_ = true;
+          p.ops.pop_front();
+          continue;
+        }
+        op.data_done = true;
+      } else if (op.event) {
         const int q = cuda::event_query(op.event);
         if (q < 0) {
           op.status->store(-EIO);
@@ -563,13 +595,21 @@ int CollComm::iput(uint64_t src_off, SymmMr* src, size_t size, uint64_t dst_off,
       }
       op.remote_addr = rm.addr + dst_off;
     } else if (dst->mapped[peer_rank]) {
-      // device window mapped here: copy-engine transfer on a stream, completion through an event
-      static thread_local cuda::Stream st = nullptr;
-      if (!st && cuda::stream_create(&st) != 0) return -EIO;
-      if (cuda::event_create(&op.event) != 0) return -EIO;
-      if (cuda::memcpy_async(static_cast<char*>(dst->mapped[peer_rank]) + dst_off, lsrc, size, st) != 0 ||
-          cuda::event_record(op.event, st) != 0)
-        return -EIO;
+      // device window mapped here: the plugin's copy kernel writes it (a device source, or a
+      // page-locked host source read in place) and sets a completion word; without the kernels, or
+      // for a pageable host source, a copy-engine transfer with an event
+      char* target = static_cast<char*>(dst->mapped[peer_rank]) + dst_off;
+      NetKernels* nk = NetKernels::get();
+      const void* ksrc = lsrc;
+      void* alias = nullptr;
+      if (nk && src->type != NCCL_PTR_CUDA) ksrc = cuda::host_device_alias(lsrc, &alias) == 0 ? alias : nullptr;
+      if (!(nk && ksrc && nk->stream() && nk->copy_flag(target, ksrc, size, nk->stream(), 0, &op.kslot, src->type == NCCL_PTR_CUDA) == 0)) {
+        op.kslot = -1;
+        static thread_local cuda::Stream st = nullptr;
+        if (!st && cuda::stream_create(&st) != 0) return -EIO;
+        if (cuda::event_create(&op.event) != 0) return -EIO;
+        if (cuda::memcpy_async(target, lsrc, size, st) != 0 || cuda::event_record(op.event, st) != 0) return -EIO;
+      }
     } else {
       // a device window that cannot be mapped into this process: fragments through host memory
       if (src->type == NCCL_PTR_CUDA) {

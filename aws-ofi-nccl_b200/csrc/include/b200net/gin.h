@@ -92,7 +92,8 @@ class GinRequest {
 
 struct PendingOp {            // a put whose data copy may still be running
   uint64_t seq = 0;
-  cuda::Event event = nullptr;
+  cuda::Event event = nullptr;   // copy-engine transfer in flight (runs without the copy kernels)
+  int kslot = -1;                // copy-kernel transfer in flight: its completion slot
   size_t len = 0, done = 0;
   uint64_t remote_addr = 0;
   const void* local = nullptr;

@@ -38,6 +38,10 @@ class NetKernels {
   int status(int slot) const;
   void release(int slot);
 
+  // *word += value on the device, release-ordered at system scope (stream-ordered on `st`; the
+  // caller synchronises or orders later work on the same stream). -ENOSYS without the kernel.
+  int signal_add(void* word, uint64_t value, cuda::Stream st);
+
   // Packs a device payload (n <= EAGER_PAYLOAD_MAX) and a 16-byte header into a pinned slot.
   int eager_pack(const void* dev_src, size_t n, uint64_t hdr0, uint64_t hdr1, cuda::Stream st, int* slot);
   bool eager_done(int slot) const;
@@ -60,6 +64,7 @@ class NetKernels {
   void* module_ = nullptr;
   void* fn_copy_ = nullptr;
   void* fn_pack_ = nullptr;
+  void* fn_signal_ = nullptr;
   cuda::Stream stream_ = nullptr;
   void* fn_bulk_ = nullptr;      // null: not in the image or shared memory cannot be raised
   volatile uint64_t* flags_ = nullptr;   // pinned host, NUM_FLAGS words

@@ -177,7 +177,7 @@ void run_later(std::function<void()> fn) {
   g_wcv.notify_one();
 }
 
-enum FakeFn : uintptr_t { FN_COPY_FLAG = 0x101, FN_EAGER_PACK = 0x102, FN_COPY_BULK = 0x103 };
+enum FakeFn : uintptr_t { FN_COPY_FLAG = 0x101, FN_EAGER_PACK = 0x102, FN_COPY_BULK = 0x103, FN_SIGNAL_ADD = 0x104 };
 
 // ------------------------------------------------------------------------------------------ entry points
 CUresult fInit(unsigned) {
@@ -477,6 +477,7 @@ CUresult fModuleGetFunction(CUfunction* f, CUmodule, const char* name) {
   if (!strcmp(name, "b200net_copy_flag")) *f = reinterpret_cast<CUfunction>(FN_COPY_FLAG);
   else if (!strcmp(name, "b200net_eager_pack")) *f = reinterpret_cast<CUfunction>(FN_EAGER_PACK);
   else if (!strcmp(name, "b200net_copy_bulk")) *f = reinterpret_cast<CUfunction>(FN_COPY_BULK);
+  else if (!strcmp(name, "b200net_signal_add")) *f = reinterpret_cast<CUfunction>(FN_SIGNAL_ADD);
   else return CUDA_ERROR_NOT_FOUND;
   return CUDA_SUCCESS;
 }
@@ -493,6 +494,12 @@ CUresult fLaunchKernel(CUfunction f, unsigned, unsigned, unsigned, unsigned, uns
       memcpy(dev_view(dst, bytes), dev_view(src, bytes), bytes);
       __atomic_store_n(static_cast<unsigned long long*>(dev_view(flag)), value, __ATOMIC_RELEASE);
     });
+    return CUDA_SUCCESS;
+  }
+  if (id == FN_SIGNAL_ADD) {
+    auto* word = *static_cast<unsigned long long**>(args[0]);
+    const unsigned long long value = *static_cast<unsigned long long*>(args[1]);
+    run_later([=] { __atomic_fetch_add(static_cast<unsigned long long*>(dev_view(word, 8)), value, __ATOMIC_ACQ_REL); });
     return CUDA_SUCCESS;
   }
   if (id == FN_EAGER_PACK) {
