@@ -136,6 +136,25 @@ int main() {
   CHECK(find_instance("p6-b200.48xlarge")->gdaki && find_instance("p6e-b200.36xlarge") != nullptr);
   CHECK(find_instance("p3dn.24xlarge")->latency_us == 150.f && !find_instance("p3dn.24xlarge")->gdaki);
   CHECK(find_instance("c5.large") == nullptr && find_instance("") == nullptr);
+  // p5 / p5en region tables are cut out of the cost model: they must agree with it at the sampled rank counts
+  for (PlatformKind plat : {PlatformKind::P5_P5E, PlatformKind::P5EN}) {
+    for (size_t nodes : {4, 16, 64, 256}) {
+      RegionTuner r(plat, nodes * 8, nodes);
+      ModelTuner m(plat, nodes * 8, nodes);
+      CHECK(r.supported() && m.supported());
+      int disagreements = 0, checked = 0;
+      for (double x = 4.1; x < 35.0; x += 0.9) {   // between the sampled sizes too
+        const size_t bytes = static_cast<size_t>(std::exp2(x));
+        const Decision a = r.decide(ncclFuncAllReduce, bytes), b = m.decide(ncclFuncAllReduce, bytes, 1);
+        ++checked;
+        if (a.algorithm != b.algorithm || a.protocol != b.protocol) ++disagreements;
+      }
+      CHECK(checked > 30);
+      CHECK(disagreements <= 2);   // only within a quarter octave of a crossover
+    }
+    CHECK(!RegionTuner(plat, 16, 2).supported());    // two nodes: NCCL's own choice
+    CHECK(!RegionTuner(plat, 40, 8).supported());    // not 8 ranks per node
+  }
   // ranks that only reach each other through the plugin's own transport: channel counts by size, algorithm left to NCCL
   {
     TransportTuner t(PlatformKind::B200_NVSWITCH, 8, 8);

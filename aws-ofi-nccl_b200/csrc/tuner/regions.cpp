@@ -105,9 +105,43 @@ static void b200_nvswitch_tables(std::vector<Region>* regions, size_t n_ranks) {
   }
 }
 
+// Hopper-generation instance types (p5 / p5e / p5en): the regions are cut out of the cost model of
+// model.cpp rather than measured: for every power-of-two node count from 4 to 256 (8 ranks each)
+// the all-reduce decision is evaluated at quarter-octave steps of the size, and every run of equal
+// decisions becomes a rectangle that spans half an octave of ranks around that node count. The
+// tables therefore agree with the model at the sampled rank counts and keep its crossovers between
+// them, which is what a region tuner is for: a cheap look-up at run time.
+static void hopper_tables_from_model(PlatformKind platform, std::vector<Region>* regions) {
+  auto& ar = regions[ncclFuncAllReduce];
+  const double xmax = lg(static_cast<double>(TUNER_MAX_SIZE));
+  for (size_t nodes = 4; nodes <= 256; nodes *= 2) {
+    const size_t ranks = nodes * 8;
+    ModelTuner model(platform, ranks, nodes);
+    if (!model.supported()) return;
+    const double y = lg(static_cast<double>(ranks));
+    const double ylo = nodes == 4 ? lg(24.0) : y - 0.5, yhi = nodes == 256 ? lg(static_cast<double>(TUNER_MAX_RANKS)) : y + 0.5;
+    Decision cur;
+    double start = 0;
+    for (double x = 3.0; x <= 36.0 + 1e-9; x += 0.25) {
+      const Decision d = model.decide(ncclFuncAllReduce, static_cast<size_t>(std::exp2(x)), 1);
+      const bool same = d.algorithm == cur.algorithm && d.protocol == cur.protocol;
+      if (!same) {
+        if (cur.algorithm != NCCL_ALGO_UNDEF) add(ar, cur.algorithm, cur.protocol, {{start, ylo}, {x, ylo}, {x, yhi}, {start, yhi}});
+        cur = d;
+        start = x <= 3.0 ? 0 : x;
+      }
+    }
+    if (cur.algorithm != NCCL_ALGO_UNDEF) add(ar, cur.algorithm, cur.protocol, {{start, ylo}, {xmax, ylo}, {xmax, yhi}, {start, yhi}});
+  }
+}
+
 RegionTuner::RegionTuner(PlatformKind platform, size_t n_ranks, size_t n_nodes)
     : platform_(platform), n_ranks_(n_ranks), n_nodes_(n_nodes) {
   switch (platform) {
+    case PlatformKind::P5_P5E:
+    case PlatformKind::P5EN:
+      if (n_nodes > 2 && n_ranks == 8 * n_nodes) hopper_tables_from_model(platform, regions_);
+      break;
     case PlatformKind::P6_B200:
     case PlatformKind::P6_B300:
       // tables were taken with 8 ranks per node
