@@ -9,6 +9,7 @@
 #include "b200net/plugin_stats.h"
 #include "b200net/log.h"
 #include "b200net/param.h"
+#include "b200net/tracepoint.h"
 
 namespace b200net::api {
 
@@ -48,6 +49,7 @@ static ncclResult_t check_return(ncclResult_t r) {
 ncclResult_t init(ncclDebugLogger_t log_fn) {
   API_GUARD_BEGIN
   if (log_fn) set_logger(log_fn);
+  trace::enable_from_params();
   Plugin* p = nullptr;
   const int rc = net_create_plugin(&p);
   if (rc != 0) {
@@ -63,6 +65,7 @@ ncclResult_t fini() {
   net_destroy_plugin();   // endpoints add their byte counts to the totals as they go
   stats::print_all_histograms();
   PluginStats::get().report();
+  trace::write_trace_file();
   return ncclSuccess;
   API_GUARD_END
 }

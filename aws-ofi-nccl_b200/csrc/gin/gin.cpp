@@ -399,6 +399,7 @@ void CollComm::handle_dgram(const DgramHdr& h, const void* payload) {
         }
         read_landings_.erase(landing);
       }
+      B200NET_TRACE_EVENT(GinGetEnd, dev, comm_id, 0, 0, it->second.get());
       it->second->store(status);
       reads_in_flight_.erase(it);
     }
@@ -450,6 +451,14 @@ int CollComm::serve_reads() {
 // its signal, and advances the peer's applied count) goes out only after its data has landed and
 // after every earlier operation's metadata.
 int CollComm::retire(PeerState& p, uint32_t peer_rank) {
+  auto finish = [&](int status) {   // the front operation is over: publish its status, close its range
+    PendingOp& op = p.ops.front();
+    if (status < 0) error_ = true;
+    if (op.has_signal) B200NET_TRACE_EVENT(GinPutSignalEnd, dev, comm_id, static_cast<uint32_t>(op.seq), op.len, op.status.get());
+    else B200NET_TRACE_EVENT(GinPutEnd, dev, comm_id, static_cast<uint32_t>(op.seq), op.len, op.status.get());
+    op.status->store(status);
+    p.ops.pop_front();
+  };
   while (!p.ops.empty()) {
     PendingOp& op = p.ops.front();
     if (!op.data_done) {
@@ -460,18 +469,14 @@ int CollComm::retire(PeerState& p, uint32_t peer_rank) {
         if (nk) nk->release(op.kslot);
         op.kslot = -1;
         if (ks < 0) {
-          op.status->store(-EIO);
-          error_ = true;
-          p.ops.pop_front();
+          finish(-EIO);
           continue;
         }
         op.data_done = true;
       } else if (op.event) {
         const int q = cuda::event_query(op.event);
         if (q < 0) {
-          op.status->store(-EIO);
-          error_ = true;
-          p.ops.pop_front();
+          finish(-EIO);
           continue;
         }
         if (q == 1) return 0;
@@ -491,9 +496,7 @@ int CollComm::retire(PeerState& p, uint32_t peer_rank) {
         }
         if (rc == -EAGAIN) return 0;
         if (rc != 0) {
-          op.status->store(rc);
-          error_ = true;
-          p.ops.pop_front();
+          finish(rc);
           continue;
         }
         op.staged = true;   // the metadata must queue behind the fragments
@@ -502,9 +505,7 @@ int CollComm::retire(PeerState& p, uint32_t peer_rank) {
         const int rc = fab_.write_host(p.map, op.remote_addr, op.local, op.len, &op.done);
         if (rc == -EAGAIN) return 0;
         if (rc != 0) {
-          op.status->store(rc);
-          error_ = true;
-          p.ops.pop_front();
+          finish(rc);
           continue;
         }
         op.staged = fab_.writes_are_staged(p.map);
@@ -518,16 +519,13 @@ int CollComm::retire(PeerState& p, uint32_t peer_rank) {
                                sizeof(op.meta));
       if (rc == -EAGAIN) return 0;
       if (rc != 0) {
-        op.status->store(rc);
-        error_ = true;
-        p.ops.pop_front();
+        finish(rc);
         continue;
       }
       op.signal_sent = true;
       B200NET_TRACE_EVENT(GinMetadataSend, dev, comm_id, static_cast<uint32_t>(op.seq), 0, this);
     }
-    op.status->store(1);
-    p.ops.pop_front();
+    finish(1);
     (void)peer_rank;
   }
   return 0;
@@ -535,8 +533,8 @@ int CollComm::retire(PeerState& p, uint32_t peer_rank) {
 
 int CollComm::progress() {
   std::lock_guard<std::recursive_mutex> g(lock);
-  B200NET_TRACE_EVENT(GinProgress, dev, comm_id, 0, 0, this);
-  fab_.poll(256, [this](const DgramHdr& h, const void* p) { handle_dgram(h, p); });
+  if (const int got = fab_.poll(256, [this](const DgramHdr& h, const void* p) { handle_dgram(h, p); }); got > 0)
+    B200NET_TRACE_EVENT(GinProgress, dev, comm_id, 0, static_cast<uint64_t>(got), this);
   while (!deferred_signals_.empty()) {
     if (apply_signal(deferred_signals_.front()) == -EAGAIN) break;
     deferred_signals_.pop_front();
@@ -573,7 +571,6 @@ int CollComm::iput(uint64_t src_off, SymmMr* src, size_t size, uint64_t dst_off,
     op.meta.signal_op = sig_op;
     op.meta.signal_is_device = sig->remote[peer_rank].kind != static_cast<uint32_t>(MrKind::HOST);
   }
-  B200NET_TRACE_EVENT(GinPutSignalBegin, dev, comm_id, static_cast<uint32_t>(op.seq), size, nullptr);
   if (size) {
     const char* lsrc = static_cast<const char*>(src->base) + src_off;
     const RemoteMr& rm = dst->remote[peer_rank];
@@ -627,6 +624,10 @@ int CollComm::iput(uint64_t src_off, SymmMr* src, size_t size, uint64_t dst_off,
   }
   PluginStats::bump(PluginStats::get().gin_puts);
   auto status = op.status;
+  // the range of a put runs from here to the moment its metadata has left (or it has failed); the
+  // status word is what tells two puts with equal per-peer sequence numbers apart
+  if (with_signal) B200NET_TRACE_EVENT(GinPutSignalBegin, dev, comm_id, static_cast<uint32_t>(op.seq), size, status.get());
+  else B200NET_TRACE_EVENT(GinPutBegin, dev, comm_id, static_cast<uint32_t>(op.seq), size, status.get());
   p.ops.push_back(std::move(op));
   retire(p, peer_rank);
   *req = new StatusRequest(this, status);
@@ -640,9 +641,15 @@ int CollComm::iget(uint64_t remote_off, SymmMr* remote, size_t size, uint64_t lo
   if (peer_rank >= static_cast<uint32_t>(nranks) || !remote || !local) return -EINVAL;
   if (remote_off + size > remote->remote[peer_rank].size || local_off + size > local->size) return -EINVAL;
   progress();
-  B200NET_TRACE_EVENT(GinGetBegin, dev, comm_id, 0, size, nullptr);
   PluginStats::bump(PluginStats::get().gin_gets);
   auto status = std::make_shared<std::atomic<int>>(0);
+  // the range of a get ends when this call returns, unless the read was handed to the owner: then
+  // it ends when the response arrives
+  struct GetRange {
+    CollComm* c; size_t size; const void* key; bool armed;
+    ~GetRange() { if (armed) B200NET_TRACE_EVENT(GinGetEnd, c->dev, c->comm_id, 0, size, key); }
+  } range{this, size, status.get(), true};
+  B200NET_TRACE_EVENT(GinGetBegin, dev, comm_id, 0, size, status.get());
   char* ldst = static_cast<char*>(local->base) + local_off;
   const RemoteMr& rm = remote->remote[peer_rank];
   int rc = 0;
@@ -669,6 +676,7 @@ int CollComm::iget(uint64_t remote_off, SymmMr* remote, size_t size, uint64_t lo
       if (rc == -EAGAIN) return 0;  // no request: call again
       if (rc != 0) return rc;
       reads_in_flight_[rq.req_id] = status;
+      range.armed = false;
       *req = new StatusRequest(this, status);
       return 0;
     }
@@ -700,12 +708,12 @@ int CollComm::iget(uint64_t remote_off, SymmMr* remote, size_t size, uint64_t lo
     if (rc == -EAGAIN) return 0;  // no request: call again
     if (rc != 0) return rc;
     reads_in_flight_[rq.req_id] = status;
+    range.armed = false;
     *req = new StatusRequest(this, status);
     return 0;
   }
   if (rc != 0) return rc;
   status->store(1);
-  B200NET_TRACE_EVENT(GinGetEnd, dev, comm_id, 0, size, nullptr);
   *req = new StatusRequest(this, status);
   return 0;
 }

@@ -170,7 +170,11 @@ struct Params {
                                   "publish NCCL_TUNER_PLUGIN=<this library> at start-up unless the user has set it"};
   Param<std::string> tuner_table{"TUNER_TABLE", "", "path of a measured-bandwidth JSON table"};
   Param<std::string> platform{"PLATFORM", "", "force a platform implementation by name"};
-  EnumParam nvtx_trace_dimension{"NVTX_TRACE_DIMENSION", "PER_COMM", {"PER_COMM", "PER_DEV"}, ""};
+  EnumParam nvtx_trace_dimension{"NVTX_TRACE_DIMENSION", "PER_COMM", {"PER_COMM", "PER_DEV"},
+                                 "NVTX domains: one per communicator or one per device"};
+  EnumParam trace{"TRACE", "none", {"none", "ring", "nvtx", "all"},
+                  "tracepoints: into the in-process ring (dumped to TRACE_FILE at finalize), as NVTX ranges and marks, or both"};
+  Param<std::string> trace_file{"TRACE_FILE", "", "Chrome trace-event JSON of the ring, written at finalize (%p = process id)"};
   Param<int> cm_num_rx_buffers{"CM_NUM_RX_BUFFERS", 32, "connection-manager receive slots"};
   Param<bool> errorcheck_mutex{"ERRORCHECK_MUTEX",
 #ifdef NDEBUG

@@ -1,6 +1,10 @@
 // Tracepoints: one call per protocol event, fanned out to (a) an in-process ring of trace records
-// that can be dumped as Chrome trace-event JSON, (b) NVTX ranges/marks when libnvToolsExt can be
-// dlopen()ed, and (c) per-event counters. Disabled events cost one relaxed atomic load.
+// that can be dumped as Chrome trace-event JSON, (b) NVTX: a begin / end pair of events becomes a
+// range in the domain of its communicator (or of its device, NVTX_TRACE_DIMENSION=PER_DEV), every
+// other event a mark (NVTX 3 is header-only: with no tool attached the calls do nothing), and
+// (c) per-event counters. Disabled events cost one relaxed atomic load.
+// B200NET_TRACE = ring | nvtx | all switches it on when the plugin starts; B200NET_TRACE_FILE
+// receives the ring as Chrome trace JSON at finalize.
 // The event vocabulary follows the reference's LTTng/NVTX layer (include/nccl_ofi_tracepoint.h,
 // include/tracing_impl/lttng.h, nvtx.h) so traces of the two plugins can be read side by side.
 #pragma once
@@ -45,6 +49,21 @@ std::vector<Record> snapshot_ring();
 std::string to_chrome_json(const std::vector<Record>& recs);
 bool nvtx_available();
 NvtxDimension nvtx_dimension();
+// Reads B200NET_TRACE / B200NET_TRACE_FILE (plugin start), writes the file (plugin finalize).
+void enable_from_params();
+void write_trace_file();
+
+// Where NVTX calls go. The default sink calls NVTX 3; tests install one that records.
+struct NvtxSink {
+  void* (*domain_create)(const char* name);
+  uint64_t (*range_start)(void* domain, const char* message, uint32_t argb, uint64_t payload);
+  void (*range_end)(void* domain, uint64_t id);
+  void (*mark)(void* domain, const char* message, uint32_t argb, uint64_t payload);
+};
+void set_nvtx_sink(const NvtxSink* sink);   // nullptr restores the default; drops open ranges
+// The event that closes the range `begin` opens, or NumEvents when `begin` opens none.
+Event range_end_of(Event begin);
+size_t nvtx_open_ranges();
 
 }  // namespace b200net::trace
 

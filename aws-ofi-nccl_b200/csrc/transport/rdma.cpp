@@ -775,7 +775,6 @@ int RdmaEndpoint::progress() {
   if (in_progress) return 0;  // re-entered from a handler
   in_progress = true;
   const int budget = params().cq_read_count.get() * 16;
-  B200NET_TRACE_EVENT(ProcessCompletionsRdma, domain->device->dev_id, 0, 0, 0, this);
   if (PluginStats::get().histograms_on() && !live_send_reqs.empty()) {
     const uint64_t now = PluginStats::now_ns();
     if (last_progress_ns) PluginStats::get().sample_poll_gap(now - last_progress_ns);
@@ -783,7 +782,11 @@ int RdmaEndpoint::progress() {
   } else {
     last_progress_ns = 0;
   }
-  if (fab.poll(budget, [this](const DgramHdr& h, const void* p) { handle_dgram(h, p); }) > 0) note_activity();
+  // traced only when the poll found something: an idle proxy thread polls millions of times
+  if (const int got = fab.poll(budget, [this](const DgramHdr& h, const void* p) { handle_dgram(h, p); }); got > 0) {
+    B200NET_TRACE_EVENT(ProcessCompletionsRdma, domain->device->dev_id, 0, 0, static_cast<uint64_t>(got), this);
+    note_activity();
+  }
   if (!deferred.empty()) retire_deferred();
   if (outbox_total > 0) flush_outboxes();
   // retry queue: strictly in order, stop at the first post that is still back-pressured
@@ -1043,7 +1046,7 @@ void RdmaSendComm::bind_eager_queue() {
     r->seq = next_seq;
     r->recv_idx = static_cast<uint8_t>(idx);
     if (r->state == ReqState::PENDING) r->state = ReqState::COMPLETED;
-    B200NET_TRACE_EVENT(SendEagerComplete, dev_id, local_comm_id, r->seq, r->size, r);
+    B200NET_TRACE_EVENT(SendEagerComplete, dev_id, local_comm_id, r->ehdr.eager_seq, r->size, r);
     const uint16_t before = next_seq;
     it = eager_queue.erase(it);
     consume_entry(idx, n);
@@ -1436,6 +1439,9 @@ int RdmaSendComm::send(void* data, size_t size, int tag, MrHandle* mh, Request**
     ++e->outbox_total;
     flush_outbox();
   }
+  // an eager send learns its message sequence number when a receive is matched: until then it is
+  // known by its eager sequence number (ranges are keyed by the request, not by the number)
+  B200NET_TRACE_EVENT(Send, dev_id, local_comm_id, r->ehdr.eager_seq, size, r);
   B200NET_TRACE_EVENT(SendEagerStart, dev_id, local_comm_id, r->ehdr.eager_seq, size, r);
   e->note_activity();
   ++accepted;

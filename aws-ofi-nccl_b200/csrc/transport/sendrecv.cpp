@@ -128,8 +128,7 @@ class SrListenComm : public ListenComm {
 void SrEndpoint::progress() {
   if (in_progress) return;
   in_progress = true;
-  B200NET_TRACE_EVENT(ProcessCompletionsSendRecv, domain->device->dev_id, 0, 0, 0, this);
-  fab.poll(params().cq_read_count.get() * 16, [this](const DgramHdr& h, const void* p) {
+  const int got = fab.poll(params().cq_read_count.get() * 16, [this](const DgramHdr& h, const void* p) {
     if (cm.handle_dgram(h, p)) return;
     if (h.type == static_cast<uint16_t>(DgramType::SENDRECV_FRAG) && h.len >= sizeof(FragHdr)) {
       const auto* fh = static_cast<const FragHdr*>(p);
@@ -140,6 +139,8 @@ void SrEndpoint::progress() {
         NET_WARN("fragment for unknown communicator %u dropped", fh->remote_comm_id);
     }
   });
+  if (got > 0)
+    B200NET_TRACE_EVENT(ProcessCompletionsSendRecv, domain->device->dev_id, 0, 0, static_cast<uint64_t>(got), this);
   // any call that makes progress also pushes queued sends of every communicator
   for (auto& [id, sc] : send_comms) sc->drive();
   in_progress = false;

@@ -94,6 +94,26 @@ def test_rma_gin_tables_n_processes(built, nranks, env):
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
 
 
+def test_gin_trace_ranges_are_closed(built, tmp_path):
+    """Every put, put + signal, get and flush that opens a range in the trace closes it, also the
+    gets that are served by the owner (staged fabric) and end when the response arrives."""
+    import collections
+    import json
+
+    e = dict(os.environ)
+    e.update({"B200NET_PROTOCOL": "RDMA", "B200NET_DISABLE_CMA": "1", "B200NET_TRACE": "ring",
+              "B200NET_TRACE_FILE": str(tmp_path / "trace.%p.json")})
+    res = subprocess.run([str(built / "tests" / "func_rma"), str(built / "libnccl-net-ofi-b200.so"), "3"],
+                         capture_output=True, text=True, timeout=300, env=e, cwd=built)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    files = sorted(tmp_path.glob("trace.*.json"))
+    assert len(files) == 3, files
+    for f in files:
+        n = collections.Counter(ev["name"] for ev in json.loads(f.read_text())["traceEvents"])
+        for kind in ("gin_put", "gin_put_signal", "gin_get", "gin_flush"):
+            assert n[kind + "_begin"] == n[kind + "_end"] > 0, (kind, n)
+
+
 def test_gin_rma_tuner_symbols_exported(built):
     lib = ctypes.CDLL(str(built / "libnccl-net-ofi-b200.so"))
     for sym in ("ncclGinPlugin_v11", "ncclGinPlugin_v13", "ncclGinPlugin_v14", "ncclRmaPlugin_v14", "ncclRmaPlugin_v15",
@@ -101,6 +121,29 @@ def test_gin_rma_tuner_symbols_exported(built):
                 "ncclTunerPlugin_v6"):
         assert hasattr(lib, sym), sym
     assert (built / "libnccl-tuner-ofi-b200.so").exists()
+
+
+def test_trace_file_at_finalize(built, tmp_path):
+    """B200NET_TRACE=all + B200NET_TRACE_FILE: the ring of tracepoints leaves the process as Chrome
+    trace-event JSON, every Send has its SendEnd and every Recv its RecvEnd (the pairs NVTX shows as
+    ranges; with no profiler attached the NVTX calls do nothing)."""
+    import collections
+    import json
+
+    _run(built, {"B200NET_PROTOCOL": "RDMA", "B200NET_TRACE": "all",
+                 "B200NET_TRACE_FILE": str(tmp_path / "trace.%p.json")}, "message_transfer")
+    files = sorted(tmp_path.glob("trace.*.json"))
+    assert len(files) == 2, files
+    for f in files:
+        ev = json.loads(f.read_text())["traceEvents"]
+        n = collections.Counter(e["name"] for e in ev)
+        assert n["Send"] == n["SendEnd"] > 0 and n["Recv"] == n["RecvEnd"] > 0, n
+        assert n["Send_eager_start"] == n["Send_eager_complete"] > 0, n
+        assert n["Send_write_segment_start"] == n["Send_write_segment_complete"] > 0, n
+        assert n["Write_ctrl_start"] == n["Write_ctrl_end"] > 0, n
+        assert n["ProcessCompletionsRdma"] < len(ev) // 2    # polls that found nothing are not traced
+        ts = [e["ts"] for e in ev]
+        assert ts == sorted(ts)
 
 
 def test_statistics_file_at_finalize(built, tmp_path):
