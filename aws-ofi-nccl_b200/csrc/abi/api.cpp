@@ -1,5 +1,8 @@
 #include "b200net/api.h"
 
+#include <sys/stat.h>
+#include <unistd.h>
+
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -174,10 +177,27 @@ ncclResult_t reg_mr(void* comm, void* data, size_t size, int type, void** mhandl
   API_GUARD_END
 }
 
+// A dma-buf descriptor names the allocation that the virtual address already identifies, and peers
+// reach the memory through a mapping of that allocation, so the descriptor is not exported. It is
+// still held to what it claims: it must be an open descriptor, and when it reports a size (dma-buf
+// descriptors answer lseek(SEEK_END)) the registered range must lie inside it.
+static int check_dmabuf(int fd, uint64_t offset, size_t size) {
+  struct stat st;
+  if (fd < 0 || fstat(fd, &st) != 0) return -EBADF;
+  const off_t total = lseek(fd, 0, SEEK_END);
+  if (total > 0 && (offset > static_cast<uint64_t>(total) || size > static_cast<uint64_t>(total) - offset)) return -EINVAL;
+  return 0;
+}
+
 ncclResult_t reg_mr_dmabuf(void* comm, void* data, size_t size, int type, uint64_t offset, int fd, void** mhandle) {
   API_GUARD_BEGIN
   if (!comm || !mhandle || (!data && size)) return check_return(ncclInvalidArgument);
   if (type != NCCL_PTR_HOST && type != NCCL_PTR_CUDA) return check_return(ncclInvalidArgument);
+  if (const int bad = check_dmabuf(fd, offset, size)) {
+    NET_WARN("regMrDmaBuf: descriptor %d does not cover offset %llu + %zu bytes (%d)", fd,
+             static_cast<unsigned long long>(offset), size, bad);
+    return check_return(ncclInvalidArgument);
+  }
   auto* c = static_cast<Comm*>(comm);
   if (!c->ep->is_active()) return check_return(ncclRemoteError);
   MrHandle* mh = nullptr;

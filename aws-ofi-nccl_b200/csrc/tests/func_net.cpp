@@ -4,7 +4,8 @@
 // in flight, the 8 B - 4 MiB ping-pong with tags 0-7 and 8 concurrent requests, grouped receives,
 // eager early/late receives, many connections on one listen communicator, close with requests in
 // flight, a bandwidth sweep, NCCL's proxy pattern (many channels, one driving thread), transfers
-// of device payloads, and the table of eager / grouped-receive orderings. Every poll loop has a
+// of device payloads, the table of eager / grouped-receive orderings, and dma-buf registrations
+// (descriptor and range checks). Every poll loop has a
 // 20 s deadline; ranks report through exit codes.
 // usage: func_net [plugin.so] [scenario]      env: B200NET_* / OFI_NCCL_* parameters apply
 //   FUNC_NET_DEVICE=1  payload buffers of the device scenarios (and of proxy_pattern) live in device
@@ -12,6 +13,8 @@
 //                      allocations, FUNC_NET_GPU=n to pin the GPU), on a CPU box through the
 //                      stand-in driver when it is on the library path (see test_buf.h)
 //   FUNC_NET_VERBOSE=1 pass the plugin's INFO lines through
+#include <sys/mman.h>
+
 #include <deque>
 #include <map>
 #include <set>
@@ -34,6 +37,31 @@ static int scenario_connection(int sock) {
     if (connect_pair(dev, sock, &p)) return 1;
     if (close_pair(&p)) return 1;
   }
+  return barrier(sock);
+}
+
+// regMrDmaBuf: the descriptor has to be open and, where it reports a size, cover offset + size.
+// A memfd stands in for a dma-buf descriptor (both answer lseek(SEEK_END) with their size).
+static int scenario_dmabuf_registration(int sock) {
+  Pair p;
+  if (connect_pair(0, sock, &p)) return 1;
+  const int fd = memfd_create("func_net_dmabuf", 0);
+  if (fd < 0 || ftruncate(fd, 1 << 16) != 0) FAIL("memfd");
+  void* buf = mmap(nullptr, 1 << 16, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  if (buf == MAP_FAILED) FAIL("mmap");
+  void* mh = nullptr;
+  OK(net->regMrDmaBuf(p.s, buf, 1 << 16, NCCL_PTR_HOST, 0, fd, &mh));
+  if (!mh) FAIL("no handle");
+  OK(net->deregMr(p.s, mh));
+  OK(net->regMrDmaBuf(p.s, static_cast<char*>(buf) + 4096, 4096, NCCL_PTR_HOST, 4096, fd, &mh));
+  OK(net->deregMr(p.s, mh));
+  if (net->regMrDmaBuf(p.s, buf, (1 << 16) + 1, NCCL_PTR_HOST, 0, fd, &mh) == ncclSuccess) FAIL("range past the end accepted");
+  if (net->regMrDmaBuf(p.s, buf, 4096, NCCL_PTR_HOST, (1 << 16) - 100, fd, &mh) == ncclSuccess) FAIL("offset + size past the end accepted");
+  if (net->regMrDmaBuf(p.s, buf, 4096, NCCL_PTR_HOST, 0, -1, &mh) == ncclSuccess) FAIL("descriptor -1 accepted");
+  munmap(buf, 1 << 16);
+  close(fd);
+  if (net->regMrDmaBuf(p.s, buf, 4096, NCCL_PTR_HOST, 0, fd, &mh) == ncclSuccess) FAIL("closed descriptor accepted");
+  if (close_pair(&p)) return 1;
   return barrier(sock);
 }
 
@@ -1058,6 +1086,7 @@ static const Scenario kScenarios[] = {
     {"bandwidth", scenario_bandwidth},       {"proxy_pattern", scenario_proxy_pattern},
     {"device_transfer", scenario_device_transfer}, {"eager_multirecv", scenario_eager_multirecv},
     {"device_bandwidth", scenario_device_bandwidth}, {"seq_wrap", scenario_seq_wrap},
+    {"dmabuf_registration", scenario_dmabuf_registration},
 };
 
 static int run_rank(const char* so, const char* only, int sock) {
