@@ -101,13 +101,14 @@ def _embed_net_kernels(force: bool = False) -> Path:
     gen.mkdir(parents=True, exist_ok=True)
     src = CSRC / "device" / "net_kernels.cu"
     cubin, inc = gen / "net_kernels.cubin", gen / "net_kernels_cubin.inc"
-    if force or _stale(inc, [src]):
+    if force or _stale(inc, [src, CSRC / "include" / "b200net" / "net_kernel_args.h"]):
         try:
             _run([NVCC, "-cubin", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
-                  str(src), "-o", str(cubin)])
+                  "-I", str(CSRC / "include"), str(src), "-o", str(cubin)])
             data = cubin.read_bytes()
-        except (RuntimeError, OSError):
+        except OSError:
             data = b"\0"   # no nvcc: the plugin then reports the kernels as unavailable and uses the copy engine
+                           # (a compile error is a build failure, not a reason to ship without the kernels)
         inc.write_text(",".join(str(b) for b in data) + "\n")
     return gen
 
@@ -127,7 +128,9 @@ def build_host(force: bool = False, sanitize: str | None = None) -> Path | None:
         if not _stale(fresh, deps) and not _stale(LIB / "libinternal_plugin.a", deps) and all(
                 (LIB / a).exists() for a in ("libnccl-net.so", "libnccl-tuner-ofi-b200.so", "libnccl-net-b200.so")):
             return fresh   # newer than every source: nothing to do, even without the object files
-    flags = list(CXX_FLAGS) + ["-I", str(_embed_net_kernels(force))]
+    gen = _embed_net_kernels(force)
+    hdrs = hdrs + [gen / "net_kernels_cubin.inc"]   # the kernel image is compiled into device/net_kernels.cpp
+    flags = list(CXX_FLAGS) + ["-I", str(gen)]
     if sanitize:
         flags += [f"-fsanitize={sanitize}", "-fno-omit-frame-pointer"]
     objs, jobs = [], []
@@ -211,9 +214,10 @@ def build_fake_cuda(force: bool = False, sanitize: str | None = None) -> Path:
     outdir = LIB / "tests" / "fake_cuda" if not sanitize else OBJ / "san" / f"fake_cuda-{sanitize}"
     outdir.mkdir(parents=True, exist_ok=True)
     out = outdir / "libcuda.so.1"
-    if force or _stale(out, [src]):
+    if force or _stale(out, [src, CSRC / "include" / "b200net" / "net_kernel_args.h"]):
         extra = [f"-fsanitize={sanitize}", "-fno-omit-frame-pointer"] if sanitize else []
         _run([SAN_CXX if sanitize else CXX, "-std=c++20", "-O1", "-g", "-fPIC", "-shared", *extra, "-I", f"{CUDA_HOME}/include",
+              "-I", str(CSRC / "include"),
               str(src), "-o", str(out), "-pthread", "-lrt"])
     return out
 

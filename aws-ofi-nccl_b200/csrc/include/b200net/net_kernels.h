@@ -34,9 +34,26 @@ class NetKernels {
   // CTA driving cp.async.bulk through shared memory) unless B200NET_COPY_KERNEL_BULK=0.
   int copy_flag(void* dst, const void* src, size_t n, cuda::Stream st, int ctas, int* slot, bool allow_bulk = true);
   bool done(int slot) const;
-  // 0 while the copy runs, 1 when it has completed, -EIO when the kernel gave up on a wait.
-  int status(int slot) const;
+  // 0 while the copy runs, 1 when it has completed, -EIO when the kernel gave up on a wait (or its
+  // launch failed). Also drives the queue of copy_queue(): a caller that polls its slot needs no
+  // other call for its copy to start.
+  int status(int slot);
   void release(int slot);
+
+  // The same transfer on the instance's own stream, but the launch may wait for company: while
+  // fewer than B200NET_COPY_BATCH_DEPTH launches are in flight it goes out at once (a lone message
+  // pays nothing); otherwise it is queued, and everything queued leaves in ONE launch of the batch
+  // kernel (up to MAX_BATCH transfers, each with its own completion slot) as soon as an earlier
+  // launch has been seen complete, the queue is full, or the oldest entry is
+  // B200NET_COPY_BATCH_MAX_AGE_US old. The launches of a burst of stripes (NCCL posts one per
+  // channel) then cost one launch latency per batch instead of one per stripe, serialised on the
+  // one stream.
+  int copy_queue(void* dst, const void* src, size_t n, int* slot, bool allow_bulk = true);
+  // Launches what is due; cheap when nothing is queued. Called from the endpoints' progress loops.
+  void poll();
+  static constexpr int MAX_BATCH = 16;
+  uint64_t batch_launches() const { return batch_launches_.load(); }
+  uint64_t batched_jobs() const { return batched_jobs_.load(); }
 
   // *word += value on the device, release-ordered at system scope (stream-ordered on `st`; the
   // caller synchronises or orders later work on the same stream). -ENOSYS without the kernel.
@@ -61,6 +78,27 @@ class NetKernels {
   NetKernels() = default;
   int init();
   int copy_impl(void* dst, const void* src, size_t n, cuda::Stream st, int ctas, int* slot, bool warm_bulk, bool allow_bulk);
+  struct Job {
+    void* dst;
+    const void* src;
+    size_t n;
+    int slot;
+    uint64_t value;
+    bool allow_bulk;
+  };
+  bool bulk_ok(const Job& j, bool warm = false) const;
+  int launch_single(const Job& j, cuda::Stream st, int ctas, bool warm_bulk);
+  int flush_locked(bool force);            // lock_ held
+  void launched_locked(const Job* jobs, int n);   // bookkeeping of one launch that carries n slots
+  void* fn_batch_ = nullptr;
+  std::vector<Job> queue_;                 // transfers waiting for their launch (at most MAX_BATCH)
+  std::atomic<int> queued_{0};
+  uint64_t first_queued_ns_ = 0;
+  int launches_in_flight_ = 0;             // launches with a slot that has not been released yet
+  std::vector<int> slot_launch_;           // slot -> index into launch_remaining_, -1 none, -2 queued
+  std::vector<int> launch_remaining_;      // slots of that launch not released yet
+  uint64_t launch_seq_ = 0;
+  std::atomic<uint64_t> batch_launches_{0}, batched_jobs_{0};
   void* module_ = nullptr;
   void* fn_copy_ = nullptr;
   void* fn_pack_ = nullptr;

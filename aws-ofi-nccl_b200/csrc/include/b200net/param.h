@@ -144,6 +144,11 @@ struct Params {
                                   "this long writes one report of its queues to the log (0: never)"};
   Param<bool> shared_stream{"SHARED_STREAM", true,
                             "all device work of the plugin runs on one stream per process (0: one stream per rail and endpoint)"};
+  Param<bool> copy_batch{"COPY_BATCH", true,
+                         "stripes posted while earlier copy launches are still running leave together, in one launch of the "
+                         "batch kernel (up to 16 transfers, each with its own completion word)"};
+  Param<uint64_t> copy_batch_depth{"COPY_BATCH_DEPTH", 2, "copy launches in flight below which a stripe is launched at once"};
+  Param<uint64_t> copy_batch_max_age_us{"COPY_BATCH_MAX_AGE_US", 30, "a queued stripe is launched at the latest after this long"};
   Param<bool> copy_kernel_bulk{"COPY_KERNEL_BULK", true,
                                "aligned stripes of 64 KiB and more use the bulk-copy (TMA) kernel; 0: the vector-copy kernel only"};
   Param<uint64_t> copy_kernel_ctas{"COPY_KERNEL_CTAS", 0, "CTAs per copy-kernel launch (0: chosen from the size)"};

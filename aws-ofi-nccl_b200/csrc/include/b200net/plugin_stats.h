@@ -21,6 +21,7 @@ struct PluginStats {
   Counter eager_sends{0}, rendezvous_sends{0};
   Counter send_backoffs{0}, recv_backoffs{0};   // calls answered with "no request, call again"
   Counter bytes_kernel{0}, bytes_copy_engine{0}, bytes_staged{0}, bytes_host{0}, bytes_eager{0};
+  Counter copy_launches{0}, copy_batch_launches{0}, copy_batched_stripes{0};   // kernel launches; those of the batch kernel; stripes they carried
   Counter flushes{0}, requests_failed{0};
   Counter ipc_maps{0}, ipc_map_failures{0}, ipc_map_deferred{0};
   Counter connects{0}, accepts{0}, endpoints_aborted{0};

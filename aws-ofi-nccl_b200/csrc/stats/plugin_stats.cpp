@@ -44,6 +44,9 @@ const Named kCounters[] = {
     {"send_backoffs", &PluginStats::send_backoffs},
     {"recv_backoffs", &PluginStats::recv_backoffs},
     {"bytes_copy_kernel", &PluginStats::bytes_kernel},
+    {"copy_kernel_launches", &PluginStats::copy_launches},
+    {"copy_batch_launches", &PluginStats::copy_batch_launches},
+    {"copy_batched_stripes", &PluginStats::copy_batched_stripes},
     {"bytes_copy_engine", &PluginStats::bytes_copy_engine},
     {"bytes_staged_through_host", &PluginStats::bytes_staged},
     {"bytes_host_writes", &PluginStats::bytes_host},

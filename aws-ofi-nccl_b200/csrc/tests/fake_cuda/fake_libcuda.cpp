@@ -43,6 +43,8 @@
 #include <string>
 #include <thread>
 
+#include "b200net/net_kernel_args.h"
+
 namespace {
 
 struct Alloc {
@@ -177,7 +179,7 @@ void run_later(std::function<void()> fn) {
   g_wcv.notify_one();
 }
 
-enum FakeFn : uintptr_t { FN_COPY_FLAG = 0x101, FN_EAGER_PACK = 0x102, FN_COPY_BULK = 0x103, FN_SIGNAL_ADD = 0x104 };
+enum FakeFn : uintptr_t { FN_COPY_FLAG = 0x101, FN_EAGER_PACK = 0x102, FN_COPY_BULK = 0x103, FN_SIGNAL_ADD = 0x104, FN_COPY_BATCH = 0x105 };
 
 // ------------------------------------------------------------------------------------------ entry points
 CUresult fInit(unsigned) {
@@ -478,6 +480,7 @@ CUresult fModuleGetFunction(CUfunction* f, CUmodule, const char* name) {
   else if (!strcmp(name, "b200net_eager_pack")) *f = reinterpret_cast<CUfunction>(FN_EAGER_PACK);
   else if (!strcmp(name, "b200net_copy_bulk")) *f = reinterpret_cast<CUfunction>(FN_COPY_BULK);
   else if (!strcmp(name, "b200net_signal_add")) *f = reinterpret_cast<CUfunction>(FN_SIGNAL_ADD);
+  else if (!strcmp(name, "b200net_copy_batch")) *f = reinterpret_cast<CUfunction>(FN_COPY_BATCH);
   else return CUDA_ERROR_NOT_FOUND;
   return CUDA_SUCCESS;
 }
@@ -493,6 +496,17 @@ CUresult fLaunchKernel(CUfunction f, unsigned, unsigned, unsigned, unsigned, uns
     run_later([=] {
       memcpy(dev_view(dst, bytes), dev_view(src, bytes), bytes);
       __atomic_store_n(static_cast<unsigned long long*>(dev_view(flag)), value, __ATOMIC_RELEASE);
+    });
+    return CUDA_SUCCESS;
+  }
+  if (id == FN_COPY_BATCH) {
+    const B200NetBatchArgs a = *static_cast<const B200NetBatchArgs*>(args[0]);
+    run_later([=] {
+      for (unsigned j = 0; j < a.njobs; ++j) {
+        const B200NetBatchJob& job = a.job[j];
+        memcpy(dev_view(job.dst, job.bytes), dev_view(job.src, job.bytes), job.bytes);
+        __atomic_store_n(static_cast<unsigned long long*>(dev_view(job.flag)), job.flag_value, __ATOMIC_RELEASE);
+      }
     });
     return CUDA_SUCCESS;
   }

@@ -789,6 +789,7 @@ int RdmaEndpoint::progress() {
   }
   if (!deferred.empty()) retire_deferred();
   if (outbox_total > 0) flush_outboxes();
+  if (kernels) kernels->poll();   // stripes waiting for company leave when an earlier launch has finished
   // retry queue: strictly in order, stop at the first post that is still back-pressured
   while (!pending.empty()) {
     auto live = live_send_reqs.find(pending.front());
@@ -1154,7 +1155,10 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
           NetKernels* nk = ksrc ? e->kernels : nullptr;
           const bool timing = PluginStats::get().histograms_on();
           const uint64_t t0 = timing ? PluginStats::now_ns() : 0;
-          if (nk && nk->copy_flag(dst, ksrc + s.offset, s.len, st, 0, &s.kslot, src_dev) == 0) {
+          // on the shared stream a stripe may share its launch with the stripes posted around it
+          const bool queued = nk && st == nk->stream() && params().copy_batch.get();
+          if (nk && (queued ? nk->copy_queue(dst, ksrc + s.offset, s.len, &s.kslot, src_dev)
+                            : nk->copy_flag(dst, ksrc + s.offset, s.len, st, 0, &s.kslot, src_dev)) == 0) {
             e->bytes_kernel += s.len;
             if (timing) {
               s.t_launch_ns = PluginStats::now_ns();
