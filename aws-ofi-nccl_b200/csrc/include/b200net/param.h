@@ -169,6 +169,8 @@ struct Params {
   Param<bool> abort_on_error{"ABORT_ON_ERROR", false, "abort() instead of returning an error code"};
   Param<int> force_num_rails{"FORCE_NUM_RAILS", 0, "override the number of copy channels per peer (0 = from topology)"};
   EnumParam tuner_type{"TUNER_TYPE", "Measured", {"Internal", "Region", "Model", "Measured"}, "tuner back-end"};
+  Param<int> tuner_force_channels{"TUNER_FORCE_CHANNELS", 0,
+                                  "calibration: the transport tuner answers this channel count for every size (0 = its table)"};
   Param<int> tuner_num_channels{"TUNER_NUM_CHANNELS", 8, ""};
   Param<float> tuner_net_latency{"TUNER_NET_LATENCY", 20.f, "network latency assumed by the model tuner (us)"};
   Param<bool> tuner_self_register{"TUNER_SELF_REGISTER", true,

@@ -108,17 +108,21 @@ class MeasuredTuner {
 // Ranks that reach each other only through this library's own net transport (one GPU per "node" in
 // NCCL's eyes: its intra-node transports are off, or the ranks sit in separate containers of one
 // NVSwitch box). The algorithm and protocol stay NCCL's choice; what is decided here is the number
-// of channels. Every channel's chunk is one copy-kernel launch on the transport's single stream
-// (about 10 us each, one after the other), while one channel's kernel side sustains about 17 GB/s,
-// so the time of a ring step is roughly  n * 10 us + bytes / (n * 17 GB/s), least near
-// n = sqrt(bytes / 170 KB). Measured on two B200: 1 MiB all_gather 120 us on 8 channels and 190 us
-// on 16; 256 MiB all_reduce 135 GB/s bus bandwidth on 8 channels and 213 GB/s on 16.
+// of channels. Every channel's chunk is a transfer of the copy kernels on the transport's single
+// stream: chunks posted together share a launch (about 5 us per message at 8 in flight), a lone one
+// pays about 10 us, and one channel's kernel side sustains about 20 GB/s, so small calls want few
+// channels and large ones all sixteen. The table is the best channel count per size of a sweep over
+// 1 / 2 / 4 / 8 / 16 / 32 forced channels on two B200 (B200NET_TUNER_FORCE_CHANNELS), smoothed to be
+// monotonic: e.g. all_reduce of 8 MiB 393 / 230 / 175 / 174 / 303 us on 1 / 2 / 4 / 8 / 16 channels,
+// of 64 MiB 3158 / 1678 / 894 / 498 / 363 us; all_gather of 1 MiB 233 / 143 / 107 / 67 / 84 us.
 class TransportTuner {
  public:
   TransportTuner(PlatformKind platform, size_t n_ranks, size_t n_nodes);
   bool supported() const { return supported_; }
   Decision decide(ncclFunc_t coll, size_t bytes) const;
-  static int channels_for(size_t bytes_per_step);
+  // bytes_per_step: what one ring step moves (a 1/n slice of an all_reduce buffer, the per-rank part
+  // of an all_gather or reduce_scatter)
+  static int channels_for(ncclFunc_t coll, size_t bytes_per_step);
 
  private:
   size_t n_ranks_;

@@ -1,6 +1,7 @@
 // GPU test of the plugin's own kernels (copy with completion flag, eager pack) through the driver
 // shim: byte-exact against host memcpy for aligned and unaligned addresses, odd sizes, slot reuse
 // past the pool size. Exit status 0 = pass, 77 = no GPU here.
+#include <algorithm>
 #include <chrono>
 #include <functional>
 #include <cstring>
@@ -84,6 +85,74 @@ int main() {
   CHECK_EQ(cuda::stream_synchronize(st), 0);
   const int last_round = 3 * NetKernels::NUM_FLAGS / 8 - 1;
   CHECK(memcmp(back.data(), host.data() + (last_round % 5) * 512, 8 * 4096) == 0);
+
+  // ---- queued copies: bursts leave in launches of the batch kernel, every transfer with its own
+  // completion word. The regions do not overlap; sizes and offsets mix the bulk path (16-byte
+  // aligned, 64 KiB and more), the vector path, unaligned ends and an empty transfer.
+  {
+    struct Q { size_t n, src_off, dst_off; };
+    const Q qs[] = {{2u << 20, 0, 0},          {65536, 16, 32},          {100, 3, 1},           {0, 0, 0},
+                    {(1u << 20) + 5, 7, 9},    {3u << 20, 64, 128},      {4096, 0, 0},          {65536 + 16, 0, 16},
+                    {12345, 1, 2},             {8u << 20, 0, 0},         {1u << 20, 48, 16},    {70000, 5, 5},
+                    {16, 0, 0},                {1u << 20, 0, 0},         {262144, 16, 16},      {1, 0, 0},
+                    {2u << 20, 32, 0},         {65536, 0, 0},            {999, 0, 3},           {4u << 20, 0, 16}};
+    const int nq = static_cast<int>(sizeof(qs) / sizeof(qs[0]));
+    const size_t region = 9u << 20;   // per transfer; nq regions do not fit the buffers at once: two passes
+    const uint64_t batches_before = nk->batch_launches(), jobs_before = nk->batched_jobs();
+    for (int pass = 0; pass < 3; ++pass) {
+      const int per_pass = 7;   // 7 regions of 9 MiB fit the 64 MiB buffers
+      for (int base = 0; base < nq; base += per_pass) {
+        const int cnt = std::min(per_pass, nq - base);
+        std::vector<uint8_t> poison(region, 0x5A);
+        for (int i = 0; i < cnt; ++i) CHECK_EQ(cuda::memcpy_async(static_cast<char*>(ddst) + i * region, poison.data(), region, st), 0);
+        CHECK_EQ(cuda::stream_synchronize(st), 0);
+        int slots[per_pass];
+        for (int i = 0; i < cnt; ++i) {
+          const Q& q = qs[base + i];
+          CHECK_EQ(nk->copy_queue(static_cast<char*>(ddst) + i * region + q.dst_off, static_cast<char*>(dsrc) + i * region + q.src_off,
+                                  q.n, &slots[i]), 0);
+        }
+        for (int i = 0; i < cnt; ++i) {
+          CHECK(wait_until([&] { return nk->status(slots[i]) != 0; }, 10.0));
+          CHECK_EQ(nk->status(slots[i]), 1);
+          nk->release(slots[i]);
+        }
+        CHECK_EQ(cuda::memcpy_async(back.data(), ddst, cnt * region, st), 0);
+        CHECK_EQ(cuda::stream_synchronize(st), 0);
+        for (int i = 0; i < cnt; ++i) {
+          const Q& q = qs[base + i];
+          const uint8_t* got = back.data() + i * region;
+          CHECK(memcmp(got + q.dst_off, host.data() + i * region + q.src_off, q.n) == 0);
+          bool around = true;
+          for (size_t b = 0; b < q.dst_off; ++b) around &= got[b] == 0x5A;
+          for (size_t b = q.dst_off + q.n; b < q.dst_off + q.n + 64; ++b) around &= got[b] == 0x5A;
+          CHECK(around);   // nothing written before the start or past the end
+        }
+      }
+    }
+    // with seven transfers queued back to back some of them must have shared a launch
+    CHECK(nk->batch_launches() > batches_before);
+    CHECK(nk->batched_jobs() - jobs_before >= 2 * (nk->batch_launches() - batches_before));
+    // a slot given back before its launch never runs: the destination keeps its bytes
+    std::vector<uint8_t> mark(4096, 0x77);
+    CHECK_EQ(cuda::memcpy_async(ddst, mark.data(), 4096, st), 0);
+    CHECK_EQ(cuda::stream_synchronize(st), 0);
+    int held[4], dropped = -1;
+    for (int& h : held) CHECK_EQ(nk->copy_queue(static_cast<char*>(ddst) + (1u << 20), dsrc, 1u << 20, &h), 0);   // keeps launches in flight
+    CHECK_EQ(nk->copy_queue(ddst, static_cast<char*>(dsrc) + 4096, 4096, &dropped), 0);
+    nk->release(dropped);
+    for (int h : held) {
+      CHECK(wait_until([&] { return nk->status(h) != 0; }, 10.0));
+      nk->release(h);
+    }
+    nk->poll();
+    CHECK_EQ(cuda::stream_synchronize(nk->stream()), 0);
+    CHECK_EQ(cuda::memcpy_async(back.data(), ddst, 4096, st), 0);
+    CHECK_EQ(cuda::stream_synchronize(st), 0);
+    // (when the queue happened to be empty at that moment the transfer was launched at once and did
+    // run: both outcomes leave whole bytes, never a torn mix)
+    CHECK(memcmp(back.data(), mark.data(), 4096) == 0 || memcmp(back.data(), host.data() + 4096, 4096) == 0);
+  }
 
   // ---- eager pack: header, payload and flag in one pinned slot
   const size_t sizes[] = {1, 7, 8, 15, 16, 17, 255, 1024, 4097, 8191, 8192};

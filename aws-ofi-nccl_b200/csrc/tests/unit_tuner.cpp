@@ -161,10 +161,23 @@ int main() {
     CHECK(t.supported());
     CHECK(!TransportTuner(PlatformKind::B200_NVSWITCH, 8, 1).supported());   // one node: NVLink transports, not this one
     CHECK(!TransportTuner(PlatformKind::P5EN, 8, 8).supported());
-    Decision d = t.decide(ncclFuncAllReduce, 1u << 20);   // 128 KiB per step
+    Decision d = t.decide(ncclFuncAllReduce, 256u << 10);   // 32 KiB per step
     CHECK_EQ(d.algorithm, NCCL_ALGO_UNDEF);
     CHECK_EQ(d.n_channels, 1);
-    CHECK_EQ(t.decide(ncclFuncAllGather, 1u << 20).n_channels, 4);
+    CHECK_EQ(t.decide(ncclFuncAllReduce, 8u << 20).n_channels, 2);     // 1 MiB per step
+    CHECK_EQ(t.decide(ncclFuncAllReduce, 64u << 20).n_channels, 8);    // 8 MiB per step
+    CHECK_EQ(t.decide(ncclFuncAllGather, 64u << 10).n_channels, 1);
+    CHECK_EQ(t.decide(ncclFuncAllGather, 256u << 10).n_channels, 4);
+    CHECK_EQ(t.decide(ncclFuncAllGather, 1u << 20).n_channels, 8);
+    // never fewer channels for a larger call of the same kind
+    for (ncclFunc_t f : {ncclFuncAllReduce, ncclFuncAllGather, ncclFuncReduceScatter}) {
+      int prev = 0;
+      for (size_t b = 8; b <= (size_t{1} << 33); b *= 2) {
+        const int n = t.decide(f, b).n_channels;
+        CHECK(n >= prev && n >= 1 && n <= 16);
+        prev = n;
+      }
+    }
     CHECK_EQ(t.decide(ncclFuncReduceScatter, 64u << 20).n_channels, 16);
     CHECK_EQ(t.decide(ncclFuncAllReduce, 256u << 20).n_channels, 16);
     CHECK_EQ(t.decide(ncclFuncSendRecv, 1u << 20).n_channels, 0);

@@ -58,11 +58,18 @@ TransportTuner::TransportTuner(PlatformKind platform, size_t n_ranks, size_t n_n
   supported_ = platform == PlatformKind::B200_NVSWITCH && n_ranks >= 2 && n_nodes == n_ranks;
 }
 
-int TransportTuner::channels_for(size_t bytes_per_step) {
-  if (bytes_per_step <= (128u << 10)) return 1;
-  if (bytes_per_step <= (512u << 10)) return 2;
-  if (bytes_per_step <= (2u << 20)) return 4;
-  if (bytes_per_step <= (16u << 20)) return 8;
+int TransportTuner::channels_for(ncclFunc_t coll, size_t bytes_per_step) {
+  if (coll == ncclFuncAllReduce) {
+    if (bytes_per_step <= (32u << 10)) return 1;
+    if (bytes_per_step <= (1u << 20)) return 2;
+    if (bytes_per_step <= (2u << 20)) return 4;
+    if (bytes_per_step <= (8u << 20)) return 8;
+    return 16;
+  }
+  if (bytes_per_step <= (64u << 10)) return 1;
+  if (bytes_per_step <= (128u << 10)) return 2;
+  if (bytes_per_step <= (256u << 10)) return 4;
+  if (bytes_per_step <= (8u << 20)) return 8;
   return 16;
 }
 
@@ -74,7 +81,8 @@ Decision TransportTuner::decide(ncclFunc_t coll, size_t bytes) const {
   size_t per_step = bytes;
   if (coll == ncclFuncAllReduce) per_step = bytes / n_ranks_;
   else if (coll != ncclFuncAllGather && coll != ncclFuncReduceScatter) return d;   // point-to-point and rooted calls: NCCL's own
-  d.n_channels = channels_for(per_step);
+  const int forced = params().tuner_force_channels.get();
+  d.n_channels = forced > 0 ? forced : channels_for(coll, per_step);
   return d;
 }
 

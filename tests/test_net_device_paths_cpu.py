@@ -42,6 +42,34 @@ def _payload_counters(log):
     return total
 
 
+def test_bursts_of_stripes_share_launches_of_the_batch_kernel(built, tmp_path):
+    """NCCL's proxy pattern (many channels, one driving thread) with kernels that take a while: the
+    stripes posted while earlier launches run leave in launches of the batch kernel, several per
+    launch, and every byte still arrives (the scenario checks them). With B200NET_COPY_BATCH=0
+    every stripe is a launch of its own."""
+    import json
+
+    def counters(extra, tag):
+        env = {"B200NET_PROTOCOL": "RDMA", "FAKE_CUDA_LAUNCH_DELAY_US": "300",
+               "B200NET_STATS_FILE": str(tmp_path / f"{tag}.%p.json")}
+        env.update(extra)
+        _run(built, env, "proxy_pattern")
+        total = {}
+        for f in tmp_path.glob(f"{tag}.*.json"):
+            for k, v in json.loads(f.read_text())["counters"].items():
+                total[k] = total.get(k, 0) + v
+        return total
+
+    on = counters({}, "on")
+    assert on["bytes_copy_kernel"] > 0
+    assert on["copy_batch_launches"] > 0, on
+    assert on["copy_batched_stripes"] >= 2 * on["copy_batch_launches"]
+    off = counters({"B200NET_COPY_BATCH": "0"}, "off")
+    assert off["bytes_copy_kernel"] == on["bytes_copy_kernel"]
+    assert off["copy_batch_launches"] == 0
+    assert off["copy_kernel_launches"] > on["copy_kernel_launches"]
+
+
 @pytest.mark.parametrize("delay_us", ["0", "300"], ids=["sync-kernels", "async-kernels"])
 @pytest.mark.parametrize("proto", ["RDMA", "SENDRECV"])
 def test_every_scenario_with_device_buffers(built, proto, delay_us):
