@@ -40,12 +40,12 @@ class NetKernels {
   int status(int slot);
   void release(int slot);
 
-  // The same transfer on the instance's own stream, but the launch may wait for company: while
-  // fewer than B200NET_COPY_BATCH_DEPTH launches are in flight it goes out at once (a lone message
-  // pays nothing); otherwise it is queued, and everything queued leaves in ONE launch of the batch
-  // kernel (up to MAX_BATCH transfers, each with its own completion slot) as soon as an earlier
-  // launch has been seen complete, the queue is full, or the oldest entry is
-  // B200NET_COPY_BATCH_MAX_AGE_US old. The launches of a burst of stripes (NCCL posts one per
+  // The same transfer on the instance's own stream, but the launch waits for company: the transfer
+  // is queued, and everything queued leaves in ONE launch of the batch kernel (up to MAX_BATCH
+  // transfers, each with its own completion slot) once no further transfer has been queued for
+  // B200NET_COPY_BATCH_QUIET_NS (at most B200NET_COPY_BATCH_HOLD_NS after the first) and fewer than
+  // B200NET_COPY_BATCH_DEPTH launches are in flight, or the queue is full, or the oldest entry is
+  // B200NET_COPY_BATCH_MAX_AGE_US old. A lone message pays the quiet period (1 us). The launches of a burst of stripes (NCCL posts one per
   // channel) then cost one launch latency per batch instead of one per stripe, serialised on the
   // one stream.
   int copy_queue(void* dst, const void* src, size_t n, int* slot, bool allow_bulk = true);
@@ -93,7 +93,7 @@ class NetKernels {
   void* fn_batch_ = nullptr;
   std::vector<Job> queue_;                 // transfers waiting for their launch (at most MAX_BATCH)
   std::atomic<int> queued_{0};
-  uint64_t first_queued_ns_ = 0;
+  uint64_t first_queued_ns_ = 0, last_queued_ns_ = 0;
   int launches_in_flight_ = 0;             // launches with a slot that has not been released yet
   std::vector<int> slot_launch_;           // slot -> index into launch_remaining_, -1 none, -2 queued
   std::vector<int> launch_remaining_;      // slots of that launch not released yet

@@ -148,6 +148,11 @@ struct Params {
                          "stripes posted while earlier copy launches are still running leave together, in one launch of the "
                          "batch kernel (up to 16 transfers, each with its own completion word)"};
   Param<uint64_t> copy_batch_depth{"COPY_BATCH_DEPTH", 2, "copy launches in flight below which a stripe is launched at once"};
+  Param<uint64_t> copy_batch_quiet_ns{"COPY_BATCH_QUIET_NS", 1000,
+                                      "a queued stripe waits for this long without a further stripe being posted before it is "
+                                      "launched (NCCL posts the chunks of all channels within a microsecond or two; they then "
+                                      "leave in one launch), 0 = launch at once"};
+  Param<uint64_t> copy_batch_hold_ns{"COPY_BATCH_HOLD_NS", 4000, "and for no longer than this after the first stripe of the queue"};
   Param<uint64_t> copy_batch_max_age_us{"COPY_BATCH_MAX_AGE_US", 30, "a queued stripe is launched at the latest after this long"};
   Param<bool> copy_kernel_bulk{"COPY_KERNEL_BULK", true,
                                "aligned stripes of 64 KiB and more use the bulk-copy (TMA) kernel; 0: the vector-copy kernel only"};

@@ -436,7 +436,7 @@ static int scenario_inflight_close(int sock) {
 static int scenario_device_transfer(int sock) {
   Pair p;
   if (connect_pair(0, sock, &p)) return 1;
-  const size_t sizes[] = {1, 8, 100, 4096, 8192, 8193, 65536, 300000, 1u << 20, (4u << 20) + 16};
+  const size_t sizes[] = {0, 1, 8, 100, 4096, 8192, 8193, 65536, 300000, 1u << 20, (4u << 20) + 16};
   const int nmsg = sizeof(sizes) / sizeof(sizes[0]);
   size_t eager_limit = 8192;   // the plugin's default; the suite also runs with eager switched off
   for (const char* name : {"B200NET_EAGER_MAX_SIZE", "OFI_NCCL_EAGER_MAX_SIZE"})

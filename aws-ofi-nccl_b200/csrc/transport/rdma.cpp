@@ -1132,6 +1132,13 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
   bool back_pressure = false;   // some ring was full: the post must be retried in order
   for (int si = 0; si < r->nstripes; ++si) {
     Stripe& s = r->stripes[si];
+    if (!s.complete && s.len == 0) {
+      // NCCL posts empty messages (a ring step that carries no data still hands over a slot):
+      // nothing to move, so no launch and no copy; only the completion travels
+      s.posted = true;
+      s.complete = true;
+      B200NET_TRACE_EVENT(SendWriteSegmentStart, dev_id, local_comm_id, r->seq, s.len, r);
+    }
     if (!s.complete) {
       if (kind == static_cast<uint32_t>(MrKind::CUDA_IPC) || kind == static_cast<uint32_t>(MrKind::CUDA_VMM)) {
         if (!s.posted) {

@@ -138,7 +138,7 @@ def test_trace_file_at_finalize(built, tmp_path):
         ev = json.loads(f.read_text())["traceEvents"]
         n = collections.Counter(e["name"] for e in ev)
         assert n["Send"] == n["SendEnd"] > 0 and n["Recv"] == n["RecvEnd"] > 0, n
-        assert n["Send_eager_start"] == n["Send_eager_complete"] > 0, n
+        assert n["Send_eager_start"] == n["Send_eager_complete"], n
         assert n["Send_write_segment_start"] == n["Send_write_segment_complete"] > 0, n
         assert n["Write_ctrl_start"] == n["Write_ctrl_end"] > 0, n
         assert n["ProcessCompletionsRdma"] < len(ev) // 2    # polls that found nothing are not traced
