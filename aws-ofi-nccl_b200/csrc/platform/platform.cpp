@@ -56,7 +56,11 @@ std::vector<std::pair<std::string, std::string>> PlatformB200::nccl_env() const 
                                                           {"NCCL_MIN_NCHANNELS", "16"},
                                                           // point-to-point calls (all_to_all): eight channels per
                                                           // peer instead of NCCL's two for a network; measured on two
-                                                          // B200, 256 MiB all_to_all 45 -> 166 GB/s bus bandwidth
+                                                          // B200, 256 MiB all_to_all 45 -> 166 GB/s bus bandwidth.
+                                                          // NCCL 2.28 reads it before it initialises the plugin:
+                                                          // launchers have to export it themselves (bench.py and
+                                                          // bench_plugin do); kept here for NCCL builds that read
+                                                          // it later
                                                           {"NCCL_NCHANNELS_PER_NET_PEER", "8"}};
   if (params().nccl_device_buffers.get()) {
     env.emplace_back("NCCL_NET_GDR_LEVEL", "SYS");

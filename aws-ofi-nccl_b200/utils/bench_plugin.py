@@ -124,6 +124,10 @@ def main(argv=None) -> int:
         # full set of hardware work queues (fewer queues shared by more streams).
         env.setdefault("CUDA_MODULE_LOADING", "EAGER")
         env.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+        # all_to_all: eight channels per peer (NCCL reads this before it loads the plugin, whose own
+        # environment defaults therefore cannot supply it)
+        if arm == "plugin":
+            env.setdefault("NCCL_NCHANNELS_PER_NET_PEER", "8")
         if arm == "plugin":
             env.update(NCCL_NET_PLUGIN="ofi-b200", LD_LIBRARY_PATH=f"{LIB}:" + env.get("LD_LIBRARY_PATH", ""))
         else:

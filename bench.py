@@ -55,6 +55,10 @@ def plugin_env(base: dict) -> dict:
     # context), and the device should offer all its hardware work queues.
     env.setdefault("CUDA_MODULE_LOADING", "EAGER")
     env.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+    # point-to-point calls (all_to_all): eight channels per peer instead of NCCL's two for a network.
+    # NCCL reads this before it initialises the plugin, so the plugin's own environment defaults come
+    # too late for it.
+    env.setdefault("NCCL_NCHANNELS_PER_NET_PEER", "8")
     # gradient traffic through the plugin runs after backward, not behind it: with compute kernels
     # and their stream waits queued on the device while the proxy thread launches copies, the first
     # overlapped step stopped moving (both ranks waiting for data, nothing left to send)
