@@ -19,6 +19,7 @@
 //                               and an event is complete once everything queued before its record
 //                               has been performed: completions are asynchronous, as on a device
 //   FAKE_CUDA_FAIL_MEMCPY_AFTER=n the n-th cuMemcpyAsync from now on and every later one fails
+//   (fake_cuda_fail_launch_after(n), a function tests call: the same for cuLaunchKernel)
 //   FAKE_CUDA_SUBALLOC_MAX=n    cuMemAlloc requests below n bytes (default 65536) are carved at
 //                               256-byte granularity out of shared 2 MiB blocks, as the driver does
 //                               with small allocations: several allocations share a page, an IPC
@@ -75,6 +76,7 @@ std::map<int, Block> g_blocks;          // guarded by g_mu
 int g_next_block = 0;
 std::atomic<int> g_next_alloc{0};
 std::atomic<long> g_memcpy_budget{-1};  // < 0: copies never fail
+std::atomic<long> g_launch_budget{-1};  // < 0: kernel launches never fail
 bool g_fail_ipc_open = false;
 int g_launch_delay_us = 0;
 
@@ -487,6 +489,10 @@ CUresult fModuleGetFunction(CUfunction* f, CUmodule, const char* name) {
 CUresult fLaunchKernel(CUfunction f, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void** args,
                        void**) {
   const uintptr_t id = reinterpret_cast<uintptr_t>(f);
+  if (g_launch_budget.load() >= 0 && g_launch_budget.fetch_sub(1) <= 0) {
+    g_launch_budget.store(0);
+    return CUDA_ERROR_LAUNCH_FAILED;
+  }
   if (id == FN_COPY_FLAG || id == FN_COPY_BULK) {
     auto* dst = *static_cast<unsigned char**>(args[0]);
     auto* src = *static_cast<const unsigned char**>(args[1]);
@@ -778,6 +784,8 @@ int fake_cuda_live_peer_mappings() {
 }
 // From now on the n-th asynchronous copy and every later one fails (n < 0: copies work again).
 void fake_cuda_fail_memcpy_after(long n) { g_memcpy_budget.store(n); }
+// The same for kernel launches.
+void fake_cuda_fail_launch_after(long n) { g_launch_budget.store(n); }
 // The accessible view of a "device" address (what a test uses to fill and check device buffers).
 void* fake_cuda_host_view(void* p) { return dev_view(p); }
 }

@@ -214,6 +214,55 @@ static int scenario_device_copy_failure(int sock) {
   return close_pair(&p);
 }
 
+// A copy-kernel launch fails (error code from the stand-in driver's cuLaunchKernel) after the send
+// was accepted: test() of that send must report the error. The stripes of the message were queued
+// for a shared launch, so the failure reaches the request through its completion word.
+static int scenario_kernel_launch_failure(int sock) {
+  void* drv = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+  auto dev_alloc = drv ? reinterpret_cast<int (*)(void**, size_t)>(dlsym(drv, "fake_cuda_mem_alloc")) : nullptr;
+  auto fail_after = drv ? reinterpret_cast<void (*)(long)>(dlsym(drv, "fake_cuda_fail_launch_after")) : nullptr;
+  if (!dev_alloc || !fail_after) FAIL("this scenario needs the stand-in driver on the library path");
+  Pair p;
+  if (connect_pair(0, sock, &p)) return 1;
+  const size_t n = 1 << 20;   // far above the eager limit: a write into the receiver's device buffer
+  void *src = nullptr, *dst = nullptr;
+  if (dev_alloc(&src, n) != 0 || dev_alloc(&dst, n) != 0) FAIL("device allocation failed");
+  void *mhs = nullptr, *mhr = nullptr;
+  OK(net->regMr(p.s, src, n, NCCL_PTR_CUDA, &mhs));
+  OK(net->regMr(p.r, dst, n, NCCL_PTR_CUDA, &mhr));
+  if (g_rank == 0) {
+    void* data = dst;
+    size_t sz = n;
+    int tag = 5;
+    void* rr = nullptr;
+    if (post_recv(p.r, 1, &data, &sz, &tag, &mhr, &rr)) return 1;
+    if (barrier(sock)) FAIL("barrier");
+    // the sender's request fails; this receive never completes and is abandoned with the communicator
+    if (barrier(sock)) FAIL("barrier");
+  } else {
+    if (barrier(sock)) FAIL("barrier");
+    fail_after(0);
+    void* rs = nullptr;
+    if (post_send(p.s, src, n, 5, mhs, &rs)) return 1;
+    const auto t0 = Clock::now();
+    int done = 0, rc = 0;
+    while (!done && rc == 0 && !expired(t0, kGiveUpSeconds)) {
+      int szs[8];
+      rc = timed([&] { return (int)net->test(rs, &done, szs); }, "test(send)");
+    }
+    fail_after(-1);
+    if (done) FAIL("the send reported success although its copy kernel was never launched");
+    if (rc == 0) FAIL("the send neither failed nor completed");
+    if (rc >= 1000) FAIL("test blocked");
+    if (barrier(sock)) FAIL("barrier");
+  }
+  // one request on each side is beyond repair: the communicators are closed with them in flight
+  OK(net->deregMr(p.s, mhs));
+  OK(net->deregMr(p.r, mhr));
+  if (close_pair(&p)) return 1;
+  return 0;
+}
+
 static const struct {
   const char* name;
   int (*fn)(int);
@@ -225,6 +274,7 @@ static const struct {
     {"drop_completion", scenario_drop_completion, "", "4:1", false},   // WRITE_COMPLETION
     {"peer_exit", scenario_peer_exit, "", "", true},
     {"device_copy_failure", scenario_device_copy_failure, "", "", false},
+    {"kernel_launch_failure", scenario_kernel_launch_failure, "", "", false},
 };
 
 static int run_rank(const char* so, const char* only, int sock) {

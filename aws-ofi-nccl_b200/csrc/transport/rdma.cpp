@@ -1185,7 +1185,7 @@ int RdmaSendComm::post_stripes(RdmaSendReq* r) {
           if (!nk) return -EIO;
           const int ks = nk->status(s.kslot);
           if (ks < 0) {
-            NET_WARN("the copy kernel gave up on a wait: stripe of %zu bytes not delivered", s.len);
+            NET_WARN("stripe of %zu bytes not delivered: its copy kernel could not be launched or gave up on a wait", s.len);
             nk->release(s.kslot);
             s.kslot = -1;
             return ks;

@@ -25,3 +25,14 @@ def test_failed_copy_to_the_device_is_reported_by_test(built):
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=120, cwd=built, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     assert "ok" in res.stdout
+
+
+def test_a_failed_copy_kernel_launch_fails_the_send(built):
+    """The stand-in driver refuses the launch that carries a queued stripe: the send's test() reports
+    an error (it must neither hang nor claim the bytes were delivered)."""
+    import os
+    env = dict(os.environ, LD_LIBRARY_PATH=f"{built / 'tests' / 'fake_cuda'}:" + os.environ.get("LD_LIBRARY_PATH", ""))
+    cmd = [str(built / "tests" / "func_fault"), str(built / "libnccl-net-ofi-b200.so"), "kernel_launch_failure"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=120, cwd=built, env=env)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    assert "ok" in res.stdout

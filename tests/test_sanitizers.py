@@ -57,6 +57,8 @@ def test_address_and_undefined_behaviour():
                   {"FAKE_CUDA_VMM": "1"}, {"FAKE_CUDA_FAIL_IPC_GET": "1"}, {"FUNC_RMA_MULTISEG": "1"}):
         _run([tests / "func_rma", so, 3],
              {"ASAN_OPTIONS": "detect_leaks=0", "FUNC_NET_DEVICE": "1", "LD_LIBRARY_PATH": fake, **extra})
+    # a copy-kernel launch that fails: the error path through the completion word of a queued stripe
+    _run([tests / "func_fault", so, "kernel_launch_failure"], {"ASAN_OPTIONS": "detect_leaks=0", "LD_LIBRARY_PATH": fake})
     for extra in ({"FAKE_CUDA_LAUNCH_DELAY_US": "200"}, {"FAKE_CUDA_FAIL_IPC_OPEN": "1"}, {"FAKE_CUDA_VMM": "1"}):
         for sc in ("device_transfer", "grouped_recv", "eager", "proxy_pattern"):
             _run([tests / "func_net", so, sc],
