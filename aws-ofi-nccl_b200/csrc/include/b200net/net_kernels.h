@@ -94,9 +94,12 @@ class NetKernels {
   std::vector<Job> queue_;                 // transfers waiting for their launch (at most MAX_BATCH)
   std::atomic<int> queued_{0};
   uint64_t first_queued_ns_ = 0, last_queued_ns_ = 0;
-  int launches_in_flight_ = 0;             // launches with a slot that has not been released yet
-  std::vector<int> slot_launch_;           // slot -> index into launch_remaining_, -1 none, -2 queued
-  std::vector<int> launch_remaining_;      // slots of that launch not released yet
+  int launches_in_flight_ = 0;             // launches with a transfer whose completion word is not set yet
+  std::vector<int> slot_launch_;           // slot -> index into launch_remaining_, -1 none (or counted), -2 queued
+  std::vector<int> launch_remaining_;      // transfers of that launch not seen complete yet
+  std::vector<int> live_slots_;            // launched, completion not counted yet
+  void count_slot_locked(int slot);        // the transfer in `slot` is over: one less for its launch
+  void reap_locked();                      // counts the live transfers whose completion words are set
   uint64_t launch_seq_ = 0;
   std::atomic<uint64_t> batch_launches_{0}, batched_jobs_{0};
   void* module_ = nullptr;

@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <chrono>
 #include <functional>
+#include <cstdlib>
 #include <cstring>
 #include <random>
 #include <vector>
@@ -23,6 +24,9 @@ static bool wait_until(const std::function<bool()>& f, double seconds) {
 }
 
 int main() {
+  // no rescue by age in this test: a queued transfer has to leave because the launches before it are
+  // seen complete, or it stays queued for longer than any wait below
+  setenv("B200NET_COPY_BATCH_MAX_AGE_US", "5000000", 1);
   if (cuda::init() != 0 || cuda::device_count() < 1) {
     printf("no GPU: skipped\n");
     return 77;
@@ -133,6 +137,20 @@ int main() {
     // with seven transfers queued back to back some of them must have shared a launch
     CHECK(nk->batch_launches() > batches_before);
     CHECK(nk->batched_jobs() - jobs_before >= 2 * (nk->batch_launches() - batches_before));
+    // finished transfers whose slots are still held do not count as launches in flight: NCCL tests
+    // the requests of a channel in order, so a finished one can stay unreleased for long
+    {
+      int first[6], later = -1;
+      for (int& f : first) {
+        CHECK_EQ(nk->copy_queue(static_cast<char*>(ddst) + (2u << 20), dsrc, 4096, &f), 0);
+        CHECK(wait_until([&] { return nk->status(f) != 0; }, 10.0));   // each one a launch of its own
+      }
+      CHECK_EQ(nk->copy_queue(static_cast<char*>(ddst) + (3u << 20), dsrc, 4096, &later), 0);
+      CHECK(wait_until([&] { return nk->status(later) != 0; }, 3.0));
+      CHECK_EQ(nk->status(later), 1);
+      for (int f : first) nk->release(f);
+      nk->release(later);
+    }
     // a slot given back before its launch never runs: the destination keeps its bytes
     std::vector<uint8_t> mark(4096, 0x77);
     CHECK_EQ(cuda::memcpy_async(ddst, mark.data(), 4096, st), 0);
