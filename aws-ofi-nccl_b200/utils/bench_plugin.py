@@ -79,7 +79,9 @@ def _worker(args) -> None:
                 fn()
             torch.cuda.synchronize(dev)
             dist.barrier()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            # the waiting thread sleeps instead of spinning: with traffic through a net plugin every rank also has a
+            # proxy thread that has to run, and a box may have no more cores than that
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True, blocking=True)
             a.record()
             for _ in range(iters):
                 fn()

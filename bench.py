@@ -101,7 +101,9 @@ def collective_rows(fn_ours, fn_nccl, world: int, sizes, device, check: bool):
             fn()
         torch.cuda.synchronize(device)
         dist.barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # the waiting thread sleeps instead of spinning: with traffic through a net plugin every rank also has a
+        # proxy thread that has to run, and a box may have no more cores than that
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True, blocking=True)
         a.record()
         for _ in range(iters):
             fn()
