@@ -45,7 +45,9 @@ class NetKernels {
   // transfers, each with its own completion slot) once no further transfer has been queued for
   // B200NET_COPY_BATCH_QUIET_NS (at most B200NET_COPY_BATCH_HOLD_NS after the first) and fewer than
   // B200NET_COPY_BATCH_DEPTH launches are in flight, or the queue is full, or the oldest entry is
-  // B200NET_COPY_BATCH_MAX_AGE_US old. A lone message pays the quiet period (1 us). The launches of a burst of stripes (NCCL posts one per
+  // B200NET_COPY_BATCH_MAX_AGE_US old. A lone message pays the quiet period (1 us).
+  // (The reference coalesces the doorbells of consecutive posts with FI_MORE,
+  // src/nccl_ofi_rdma.cpp:1876-1919; on this transport the doorbell is a kernel launch.) The launches of a burst of stripes (NCCL posts one per
   // channel) then cost one launch latency per batch instead of one per stripe, serialised on the
   // one stream.
   int copy_queue(void* dst, const void* src, size_t n, int* slot, bool allow_bulk = true);
