@@ -87,6 +87,7 @@ struct MeasuredRow {
   int coll, algo, proto, n_channels;
   size_t bytes;
   double time_us;
+  int reg = -1;   // 1: measured with registered user buffers, 0: without, -1: not recorded
 };
 class MeasuredTuner {
  public:
@@ -96,8 +97,14 @@ class MeasuredTuner {
   bool load_from_string(const std::string& json);
   bool supported() const { return !rows_.empty(); }
   size_t world() const { return world_; }
-  // Best measured combination at the nearest measured size (log scale) for this collective.
-  Decision decide(ncclFunc_t coll, size_t bytes) const;
+  // The (algorithm, protocol) with the least time at `bytes`, where the time of a combination is
+  // interpolated on a log-log scale between the two measured sizes that bracket `bytes` (measured
+  // on the nearer side only it counts with that side's time; outside the measured range the nearest
+  // size decides); the channel count is the one of its best row at the nearer size. Times within
+  // 3 % of the best count as tied and the fewest channels win (their SMs stay with the application). reg_buff (v4+ of the
+  // tuner interface: the call's buffers are registered with the network) restricts the choice to
+  // rows recorded with the same setting when the table has any ("reg": 0 / 1); -1 = not known.
+  Decision decide(ncclFunc_t coll, size_t bytes, int reg_buff = -1) const;
   size_t num_rows() const { return rows_.size(); }
 
  private:
@@ -147,7 +154,8 @@ TunerContext* create_context(size_t n_ranks, size_t n_nodes);
 // NCCL_ALGO_PROTO_IGNORE. Returns true when the table was changed. A decision that names no
 // algorithm but a channel count still sets the channel count.
 bool apply_decision(const Decision& d, float** cost_table, int num_algo, int num_proto, int* n_channels);
-Decision get_decision(const TunerContext* ctx, ncclFunc_t coll, size_t bytes, int pipe_ops);
+// reg_buff: 1 / 0 when the caller knows whether the call's buffers are registered, -1 otherwise
+Decision get_decision(const TunerContext* ctx, ncclFunc_t coll, size_t bytes, int pipe_ops, int reg_buff = -1);
 // Chunk size hint (v6 getChunkSize); 0 = no opinion.
 size_t get_chunk_size(const TunerContext* ctx, ncclFunc_t coll, size_t bytes, int algo, int proto, int n_channels);
 

@@ -103,6 +103,25 @@ int main() {
     CHECK_EQ(d.algorithm, NCCL_ALGO_NVLS); CHECK_EQ(d.n_channels, 24);
     CHECK_EQ(mt.decide(ncclFuncReduceScatter, 1 << 20).algorithm, NCCL_ALGO_UNDEF);  // nothing measured
     CHECK_EQ(mt.decide(ncclFuncAllGather, 1 << 10).algorithm, NCCL_ALGO_RING);
+    // between two measured sizes every combination's time is interpolated (log-log): ring LL goes
+    // 9 -> 900 us over 16 octaves, NVLS simple 14 -> 210 us; they cross near 2^(10 + 16 * 0.23)
+    CHECK_EQ(mt.decide(ncclFuncAllReduce, 8u << 10).algorithm, NCCL_ALGO_RING);     // 3 octaves up: 21 vs 23 us
+    CHECK_EQ(mt.decide(ncclFuncAllReduce, 64u << 10).algorithm, NCCL_ALGO_NVLS);    // 6 octaves up: 51 vs 39 us
+    // ties within 3 %: the fewer channels; registered-buffer rows only for calls that say so
+    const char* js2 =
+        "{\"world\": 8, \"rows\": ["
+        "{\"coll\":4,\"algo\":1,\"proto\":2,\"nchannels\":16,\"bytes\":1048576,\"time_us\":100.0},"
+        "{\"coll\":4,\"algo\":1,\"proto\":2,\"nchannels\":8,\"bytes\":1048576,\"time_us\":102.0},"
+        "{\"coll\":4,\"algo\":1,\"proto\":2,\"nchannels\":4,\"bytes\":1048576,\"time_us\":110.0},"
+        "{\"coll\":3,\"algo\":1,\"proto\":2,\"nchannels\":8,\"bytes\":1048576,\"time_us\":50.0,\"reg\":0},"
+        "{\"coll\":3,\"algo\":6,\"proto\":2,\"nchannels\":8,\"bytes\":1048576,\"time_us\":30.0,\"reg\":1}]}";
+    MeasuredTuner m2;
+    CHECK(m2.load_from_string(js2));
+    CHECK_EQ(m2.decide(ncclFuncAllReduce, 1u << 20).n_channels, 8);
+    CHECK_EQ(m2.decide(ncclFuncReduceScatter, 1u << 20, 0).algorithm, NCCL_ALGO_RING);
+    CHECK_EQ(m2.decide(ncclFuncReduceScatter, 1u << 20, 1).algorithm, NCCL_ALGO_PAT);
+    CHECK_EQ(m2.decide(ncclFuncReduceScatter, 1u << 20).algorithm, NCCL_ALGO_PAT);   // not known: the fastest row
+    CHECK_EQ(m2.decide(ncclFuncAllReduce, 1u << 20, 1).n_channels, 8);               // table silent about registration
   }
   // ---- cost table mutation
   {

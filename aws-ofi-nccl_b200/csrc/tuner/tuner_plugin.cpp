@@ -136,10 +136,10 @@ TunerContext* create_context(size_t n_ranks, size_t n_nodes) {
   return nullptr;  // unknown platform: NCCL's internal tuner decides
 }
 
-Decision get_decision(const TunerContext* ctx, ncclFunc_t coll, size_t bytes, int pipe_ops) {
+Decision get_decision(const TunerContext* ctx, ncclFunc_t coll, size_t bytes, int pipe_ops, int reg_buff) {
   if (!ctx) return Decision();
   switch (ctx->type) {
-    case TunerType::MEASURED: return ctx->measured->decide(coll, bytes);
+    case TunerType::MEASURED: return ctx->measured->decide(coll, bytes, reg_buff);
     case TunerType::REGION: return ctx->region->decide(coll, bytes);
     case TunerType::MODEL: return ctx->model->decide(coll, bytes, pipe_ops);
     case TunerType::TRANSPORT: return ctx->transport->decide(coll, bytes);
@@ -219,8 +219,11 @@ ncclResult_t get_coll_info_v3(void* context, ncclFunc_t coll, size_t bytes, int 
   return ncclSuccess;
 }
 ncclResult_t get_coll_info_v4(void* context, ncclFunc_t coll, size_t bytes, int pipe_ops, float** table, int num_algo,
-                              int num_proto, int, int* n_channels) {
-  return get_coll_info_v3(context, coll, bytes, pipe_ops, table, num_algo, num_proto, n_channels);
+                              int num_proto, int reg_buff, int* n_channels) {
+  if (!context) return ncclSuccess;
+  const Decision d = get_decision(static_cast<TunerContext*>(context), coll, bytes, pipe_ops, reg_buff ? 1 : 0);
+  apply_decision(d, table, num_algo, num_proto, n_channels);
+  return ncclSuccess;
 }
 ncclResult_t get_coll_info_v2(void* context, ncclFunc_t coll, size_t bytes, int collnet, int nvls, int pipe_ops,
                               int* algorithm, int* protocol, int* n_channels) {
