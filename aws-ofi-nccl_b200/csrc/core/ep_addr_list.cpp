@@ -5,7 +5,7 @@
 namespace b200net {
 
 void* EpAddrList::get(const std::string& addr) {
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   for (auto& it : items_) {
     if (!it.addrs.count(addr)) {
       it.addrs.insert(addr);
@@ -16,7 +16,7 @@ void* EpAddrList::get(const std::string& addr) {
 }
 
 int EpAddrList::insert(void* ep, const std::string& addr) {
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   for (auto& it : items_)
     if (it.ep == ep) return -EINVAL;
   items_.push_back(Item{ep, {addr}});
@@ -24,7 +24,7 @@ int EpAddrList::insert(void* ep, const std::string& addr) {
 }
 
 int EpAddrList::remove(void* ep) {
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   for (auto it = items_.begin(); it != items_.end(); ++it) {
     if (it->ep == ep) {
       items_.erase(it);
@@ -35,7 +35,7 @@ int EpAddrList::remove(void* ep) {
 }
 
 size_t EpAddrList::size() const {
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   return items_.size();
 }
 

@@ -13,7 +13,7 @@ IdPool::IdPool(size_t size) : size_(size), free_bits_(div_ceil<size_t>(size, 64)
 }
 
 uint64_t IdPool::allocate() {
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   for (size_t w = 0; w < free_bits_.size(); ++w) {
     if (free_bits_[w]) {
       const int bit = __builtin_ffsll(static_cast<long long>(free_bits_[w])) - 1;
@@ -25,7 +25,7 @@ uint64_t IdPool::allocate() {
 }
 
 void IdPool::free_id(uint64_t id) {
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   if (id >= size_) throw std::logic_error("IdPool: id out of range");
   const uint64_t m = uint64_t{1} << (id % 64);
   if (free_bits_[id / 64] & m) throw std::logic_error("IdPool: double free");
@@ -33,7 +33,7 @@ void IdPool::free_id(uint64_t id) {
 }
 
 size_t IdPool::in_use() const {
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   size_t free_cnt = 0;
   for (uint64_t w : free_bits_) free_cnt += static_cast<size_t>(__builtin_popcountll(w));
   return size_ - free_cnt;

@@ -26,7 +26,7 @@ void* MrCache::lookup(const MrCacheKey& key) {
   uintptr_t base;
   size_t pages;
   page_range(key, &base, &pages);
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   // entries sorted by addr: candidates start at or before base
   auto it = std::upper_bound(entries_.begin(), entries_.end(), base,
                              [](uintptr_t v, const Entry& e) { return v < e.addr; });
@@ -49,7 +49,7 @@ int MrCache::insert(const MrCacheKey& key, void* handle) {
   uintptr_t base;
   size_t pages;
   page_range(key, &base, &pages);
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   auto it = std::lower_bound(entries_.begin(), entries_.end(), base,
                              [](const Entry& e, uintptr_t v) { return e.addr < v; });
   for (auto j = it; j != entries_.end() && j->addr == base; ++j) {
@@ -61,7 +61,7 @@ int MrCache::insert(const MrCacheKey& key, void* handle) {
 }
 
 int MrCache::del(void* handle) {
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   for (auto it = entries_.begin(); it != entries_.end(); ++it) {
     if (it->handle == handle) {
       if (--it->refcnt > 0) return 0;
@@ -73,7 +73,7 @@ int MrCache::del(void* handle) {
 }
 
 size_t MrCache::size() const {
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   return entries_.size();
 }
 

@@ -27,7 +27,7 @@ MsgStatus MsgBuff::status_of(uint16_t seq) const {
 }
 
 MsgResult MsgBuff::insert(uint16_t seq, void* elem, MsgElemType type, MsgStatus* status) {
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   seq &= field_mask_;
   *status = status_of(seq);
   if (*status != MsgStatus::NOTSTARTED) return MsgResult::INVALID_IDX;
@@ -37,7 +37,7 @@ MsgResult MsgBuff::insert(uint16_t seq, void* elem, MsgElemType type, MsgStatus*
 }
 
 MsgResult MsgBuff::replace(uint16_t seq, void* elem, MsgElemType type, MsgStatus* status) {
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   seq &= field_mask_;
   *status = status_of(seq);
   if (*status != MsgStatus::INPROGRESS) return MsgResult::INVALID_IDX;
@@ -47,7 +47,7 @@ MsgResult MsgBuff::replace(uint16_t seq, void* elem, MsgElemType type, MsgStatus
 }
 
 MsgResult MsgBuff::retrieve(uint16_t seq, void** elem, MsgElemType* type, MsgStatus* status) {
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   seq &= field_mask_;
   *status = status_of(seq);
   if (*status != MsgStatus::INPROGRESS) return MsgResult::INVALID_IDX;
@@ -57,7 +57,7 @@ MsgResult MsgBuff::retrieve(uint16_t seq, void** elem, MsgElemType* type, MsgSta
 }
 
 MsgResult MsgBuff::complete(uint16_t seq, MsgStatus* status) {
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   seq &= field_mask_;
   *status = status_of(seq);
   if (*status != MsgStatus::INPROGRESS) return MsgResult::INVALID_IDX;

@@ -40,7 +40,7 @@ size_t ThresholdScheduler::stripe_size_for(size_t size, int num_stripes) {
 
 Schedule* ThresholdScheduler::get_schedule(size_t size, int num_rails) {
   B200NET_ASSERT_ALWAYS(num_rails >= 1 && num_rails <= MAX_NUM_RAILS);
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   FreelistEntry* fe = pool_.entry_alloc();
   if (!fe) return nullptr;
   Schedule* s = new (fe->ptr) Schedule();
@@ -69,7 +69,7 @@ Schedule* ThresholdScheduler::get_schedule(size_t size, int num_rails) {
 
 void ThresholdScheduler::release_schedule(Schedule* s) {
   if (!s) return;
-  std::lock_guard<std::mutex> g(mu_);
+  ScopedLock g(mu_);
   FreelistEntry* fe = s->fl_entry;
   s->~Schedule();
   pool_.entry_free(fe);

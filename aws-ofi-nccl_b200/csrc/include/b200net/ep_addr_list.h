@@ -1,7 +1,7 @@
 // Tracks which peer addresses each endpoint is already connected to, to answer "give me an
 // endpoint that has no connection to this address yet" (reference: src/nccl_ofi_ep_addr_list.cpp).
 #pragma once
-#include <mutex>
+#include "b200net/pthread_wrap.h"
 #include <set>
 #include <string>
 #include <vector>
@@ -19,8 +19,8 @@ class EpAddrList {
 
  private:
   struct Item { void* ep; std::set<std::string> addrs; };
-  mutable std::mutex mu_;
-  std::vector<Item> items_;
+  mutable Mutex mu_;
+  std::vector<Item> items_ TSA_GUARDED_BY(mu_);
 };
 
 }  // namespace b200net

@@ -4,7 +4,7 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
-#include <mutex>
+#include "b200net/pthread_wrap.h"
 #include <vector>
 
 namespace b200net {
@@ -20,8 +20,8 @@ class IdPool {
 
  private:
   size_t size_;
-  mutable std::mutex mu_;
-  std::vector<uint64_t> free_bits_;  // bit set = id free
+  mutable Mutex mu_;
+  std::vector<uint64_t> free_bits_ TSA_GUARDED_BY(mu_);  // bit set = id free
 };
 
 }  // namespace b200net

@@ -10,7 +10,7 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
-#include <mutex>
+#include "b200net/pthread_wrap.h"
 #include <vector>
 
 namespace b200net {
@@ -51,17 +51,18 @@ class MrCache {
   // 0: references remain; 1: last reference dropped, entry removed; -ENOENT: unknown handle.
   int del(void* handle);
   size_t size() const;
-  uint64_t hits() const { return hits_; }
-  uint64_t misses() const { return misses_; }
+  uint64_t hits() const { ScopedLock g(mu_); return hits_; }
+  uint64_t misses() const { ScopedLock g(mu_); return misses_; }
   void page_range(const MrCacheKey& key, uintptr_t* base, size_t* pages) const;
 
  private:
   struct Entry { uintptr_t addr; size_t pages; int refcnt; void* handle; const void* ep; MrKeyKind kind; int fd;
                  bool exact; uintptr_t raw_addr; size_t raw_len; };
   size_t page_size_;
-  mutable std::mutex mu_;
-  std::vector<Entry> entries_;  // sorted by addr
-  uint64_t hits_ = 0, misses_ = 0;
+  mutable Mutex mu_;
+  std::vector<Entry> entries_ TSA_GUARDED_BY(mu_);  // sorted by addr
+  uint64_t hits_ TSA_GUARDED_BY(mu_) = 0;
+  uint64_t misses_ TSA_GUARDED_BY(mu_) = 0;
 };
 
 }  // namespace b200net

@@ -5,7 +5,7 @@
 // (reference: src/nccl_ofi_msgbuff.cpp, include/nccl_ofi_msgbuff.h).
 #pragma once
 #include <cstdint>
-#include <mutex>
+#include "b200net/pthread_wrap.h"
 #include <vector>
 
 namespace b200net {
@@ -28,14 +28,14 @@ class MsgBuff {
  private:
   struct Slot { MsgStatus stat; MsgElemType type; void* elem; };
   uint16_t distance(uint16_t front, uint16_t back) const;  // (front - back) mod field
-  MsgStatus status_of(uint16_t seq) const;
-  Slot& slot(uint16_t seq) { return buff_[seq % max_inprogress_]; }
-  const Slot& slot(uint16_t seq) const { return buff_[seq % max_inprogress_]; }
+  MsgStatus status_of(uint16_t seq) const TSA_REQUIRES(mu_);
+  Slot& slot(uint16_t seq) TSA_REQUIRES(mu_) { return buff_[seq % max_inprogress_]; }
+  const Slot& slot(uint16_t seq) const TSA_REQUIRES(mu_) { return buff_[seq % max_inprogress_]; }
   uint16_t max_inprogress_, field_size_, field_mask_;
-  uint16_t last_incomplete_;  // oldest sequence number not yet completed
-  uint16_t next_;             // one past the newest sequence number ever inserted
-  std::vector<Slot> buff_;
-  mutable std::mutex mu_;
+  mutable Mutex mu_;
+  uint16_t last_incomplete_ TSA_GUARDED_BY(mu_);  // oldest sequence number not yet completed
+  uint16_t next_ TSA_GUARDED_BY(mu_);             // one past the newest sequence number ever inserted
+  std::vector<Slot> buff_ TSA_GUARDED_BY(mu_);
 };
 
 }  // namespace b200net

@@ -6,7 +6,7 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
-#include <mutex>
+#include "b200net/pthread_wrap.h"
 #include "b200net/freelist.h"
 
 namespace b200net {
@@ -42,9 +42,9 @@ class ThresholdScheduler {
  private:
   int num_rails_;
   size_t min_stripe_, max_small_;
-  unsigned rr_counter_ = 0;
-  std::mutex mu_;
-  Freelist pool_;
+  Mutex mu_;
+  unsigned rr_counter_ TSA_GUARDED_BY(mu_) = 0;
+  Freelist pool_ TSA_GUARDED_BY(mu_);
 };
 
 }  // namespace b200net
