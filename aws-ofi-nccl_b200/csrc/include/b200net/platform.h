@@ -54,6 +54,10 @@ class PlatformB200 : public Platform {
   bool gdaki_capable() const override { return true; }
   std::vector<std::pair<std::string, std::string>> nccl_env() const override;
   std::string log_error_hint(int err) const override;
+  // Ascending rail ids, whatever order discovery produced: rail i of a sender is the stream and
+  // completion ring that rail i of its receiver expects (reference: the cloud platform sorts a
+  // group's NICs by their virtual-function index for the same reason, src/platform-aws.cpp sort_rails).
+  void sort_rails(std::vector<int>& rails) override;
 
  private:
   bool detected_;

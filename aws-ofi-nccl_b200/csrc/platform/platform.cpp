@@ -1,5 +1,7 @@
 #include "b200net/platform.h"
 
+#include <algorithm>
+
 #include <dlfcn.h>
 #include <limits.h>
 
@@ -81,6 +83,8 @@ std::string PlatformB200::log_error_hint(int err) const {
       return "";
   }
 }
+
+void PlatformB200::sort_rails(std::vector<int>& rails) { std::sort(rails.begin(), rails.end()); }
 
 // ---------------------------------------------------------------- cloud instance table
 const std::vector<InstanceEntry>& instance_table() {

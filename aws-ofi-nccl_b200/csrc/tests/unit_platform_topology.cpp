@@ -135,6 +135,12 @@ int main() {
   CHECK(system_product_name() == "p5en.48xlarge");
   unsetenv("OFI_NCCL_FORCE_PRODUCT_NAME");
   setenv("NCCL_HOSTID", "abc", 1);
+  {
+    PlatformB200 b200(true);
+    std::vector<int> rails{3, 0, 2, 1};
+    b200.sort_rails(rails);
+    CHECK(rails == (std::vector<int>{0, 1, 2, 3}));   // both ends of a connection enumerate rails alike
+  }
   const uint64_t h1 = system_host_hash();
   setenv("NCCL_HOSTID", "abd", 1);
   CHECK(h1 != system_host_hash());
