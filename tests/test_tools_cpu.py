@@ -84,3 +84,38 @@ def test_calibration_table_feeds_the_measured_tuner(built, tmp_path, monkeypatch
     # the crossover of the two canned cost lines is at 20 us * (1 / (1/20e3 - 1/300e3)) = 428 571 bytes
     switch = next(r["from_bytes"] for r in rows if r["decision"][1] == "Simple")
     assert 64 << 10 < switch < 4 << 20
+
+
+def test_packaging_install_steps_produce_a_loadable_plugin(built, tmp_path):
+    """The install steps of the Debian rules file and of the RPM spec, run against the built tree
+    into a scratch root: the shared object and the two names NCCL searches for land in the library
+    directory, and a C program can dlopen the plugin through the installed `libnccl-net.so` name."""
+    import ctypes
+    import os
+    import re
+    import subprocess
+
+    repo = REPO if "REPO" in globals() else os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    work = tmp_path / "tree"
+    work.mkdir()
+    os.symlink(os.path.join(repo, "aws-ofi-nccl_b200"), work / "aws-ofi-nccl_b200")
+    # Debian: the override_dh_auto_install target, with the variable dpkg-buildpackage exports
+    res = subprocess.run(["make", "-f", os.path.join(repo, "contrib", "debian", "rules"), "override_dh_auto_install",
+                          "DEB_HOST_MULTIARCH=x86_64-linux-gnu"], cwd=work, capture_output=True, text=True, timeout=60)
+    assert res.returncode == 0, res.stdout + res.stderr
+    libdir = work / "debian" / "libnccl-net-ofi-b200" / "usr" / "lib" / "x86_64-linux-gnu"
+    for name in ("libnccl-net-ofi-b200.so", "libnccl-net.so", "libnccl-tuner-ofi-b200.so"):
+        assert (libdir / name).exists(), name
+    assert os.readlink(libdir / "libnccl-net.so") == "libnccl-net-ofi-b200.so"
+    lib = ctypes.CDLL(str(libdir / "libnccl-net.so"))
+    assert hasattr(lib, "ncclNetPlugin_v11") and hasattr(lib, "ncclTunerPlugin_v6")
+    # RPM: the %install section with its macros expanded by hand
+    spec = open(os.path.join(repo, "contrib", "fedora", "aws-ofi-nccl-b200.spec")).read()
+    install = spec[spec.index("%install") + len("%install"):spec.index("%files")]
+    root = tmp_path / "buildroot"
+    script = install.replace("%{buildroot}", str(root)).replace("%{_libdir}", "/usr/lib64")
+    assert "%{" not in script, script
+    res = subprocess.run(["sh", "-ec", script], cwd=work, capture_output=True, text=True, timeout=60)
+    assert res.returncode == 0, res.stdout + res.stderr
+    listed = re.findall(r"^%\{_libdir\}/(\S+)$", spec[spec.index("%files"):], flags=re.M)
+    assert sorted(listed) == sorted(os.listdir(root / "usr" / "lib64"))
