@@ -557,14 +557,12 @@ int CollComm::iput(uint64_t src_off, SymmMr* src, size_t size, uint64_t dst_off,
   PeerState& p = peers_[peer_rank];
   if (p.tx_head - p.tx_acked >= GIN_ACK_REQ_THRESHOLD) return 0;  // window full: no request, call again
   PendingOp op;
-  op.seq = ++p.tx_head;
   op.len = size;
   op.status = std::make_shared<std::atomic<int>>(0);
   op.has_signal = with_signal;
   memset(&op.meta, 0, sizeof(op.meta));
   op.meta.comm_id = p.comm_id;
   op.meta.src_rank = static_cast<uint32_t>(rank);
-  op.meta.seq = op.seq;
   if (with_signal) {
     op.meta.signal_addr = sig->remote[peer_rank].addr + sig_off;
     op.meta.signal_value = sig_value;
@@ -605,7 +603,10 @@ int CollComm::iput(uint64_t src_off, SymmMr* src, size_t size, uint64_t dst_off,
         static thread_local cuda::Stream st = nullptr;
         if (!st && cuda::stream_create(&st) != 0) return -EIO;
         if (cuda::event_create(&op.event) != 0) return -EIO;
-        if (cuda::memcpy_async(target, lsrc, size, st) != 0 || cuda::event_record(op.event, st) != 0) return -EIO;
+        if (cuda::memcpy_async(target, lsrc, size, st) != 0 || cuda::event_record(op.event, st) != 0) {
+          cuda::event_destroy(op.event);
+          return -EIO;
+        }
       }
     } else {
       // a device window that cannot be mapped into this process: fragments through host memory
@@ -626,6 +627,10 @@ int CollComm::iput(uint64_t src_off, SymmMr* src, size_t size, uint64_t dst_off,
   auto status = op.status;
   // the range of a put runs from here to the moment its metadata has left (or it has failed); the
   // status word is what tells two puts with equal per-peer sequence numbers apart
+  // the sequence number is taken only now: a put that failed above must not leave a hole in the
+  // numbers the peer acknowledges in order
+  op.seq = ++p.tx_head;
+  op.meta.seq = op.seq;
   if (with_signal) B200NET_TRACE_EVENT(GinPutSignalBegin, dev, comm_id, static_cast<uint32_t>(op.seq), size, status.get());
   else B200NET_TRACE_EVENT(GinPutBegin, dev, comm_id, static_cast<uint32_t>(op.seq), size, status.get());
   p.ops.push_back(std::move(op));
