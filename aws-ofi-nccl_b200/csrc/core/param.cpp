@@ -104,3 +104,36 @@ std::string to_string_value(const std::string& v) { return v; }
 
 }  // namespace detail
 }  // namespace b200net
+
+// Every parameter with its present value, where the value came from and its description, as a JSON
+// array: what `python -m aws_ofi_nccl_b200.utils.params` prints. Returns the length of the whole
+// text; at most cap - 1 characters and a terminator are written to out.
+extern "C" __attribute__((visibility("default"))) size_t b200net_describe_parameters(char* out, size_t cap) {
+  using namespace b200net;
+  params();   // the parameter objects register themselves when the set is first built
+  auto quoted = [](const std::string& v) {
+    std::string q = "\"";
+    for (const char c : v) {
+      if (c == '"' || c == '\\') q += '\\';
+      if (static_cast<unsigned char>(c) >= 0x20) q += c;
+    }
+    return q + "\"";
+  };
+  std::string js = "[";
+  bool first = true;
+  for (ParamBase* p : param_registry()) {
+    p->load_from_env();
+    const char* src = p->source() == ParamSource::ENVIRONMENT ? "environment" : p->source() == ParamSource::API ? "api" : "default";
+    js += std::string(first ? "" : ",") + "{\"name\":" + quoted(p->name()) + ",\"value\":" + quoted(p->value_string()) +
+          ",\"source\":\"" + src + "\",\"doc\":" + quoted(p->doc()) + "}";
+    first = false;
+  }
+  js += "]";
+  if (out && cap) {
+    const size_t n = std::min(js.size(), cap - 1);
+    memcpy(out, js.data(), n);
+    out[n] = 0;
+  }
+  return js.size();
+}
+

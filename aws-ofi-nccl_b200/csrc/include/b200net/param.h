@@ -162,10 +162,11 @@ struct Params {
   Param<int> cq_read_count{"CQ_READ_COUNT", 4, "completions drained per poll of one rail"};
   Param<int> cq_size{"CQ_SIZE", 12288, "entries of a completion ring"};
   Param<bool> mr_cache_disable{"MR_CACHE_DISABLE", false, "do not cache registrations"};
-  Param<int> min_posted_eager_buffers{"RDMA_MIN_POSTED_EAGER_BUFFERS", 64, ""};
-  Param<int> max_posted_eager_buffers{"RDMA_MAX_POSTED_EAGER_BUFFERS", 128, ""};
-  Param<int> min_posted_control_buffers{"RDMA_MIN_POSTED_CONTROL_BUFFERS", 16, ""};
-  Param<int> max_posted_control_buffers{"RDMA_MAX_POSTED_CONTROL_BUFFERS", 32, ""};
+  Param<int> min_posted_eager_buffers{"RDMA_MIN_POSTED_EAGER_BUFFERS", 64,
+                                      "accepted for scripts written for the reference plugin and not used: this transport posts no receive buffers (its rings are sized by CQ_SIZE)"};
+  Param<int> max_posted_eager_buffers{"RDMA_MAX_POSTED_EAGER_BUFFERS", 128, "see RDMA_MIN_POSTED_EAGER_BUFFERS"};
+  Param<int> min_posted_control_buffers{"RDMA_MIN_POSTED_CONTROL_BUFFERS", 16, "see RDMA_MIN_POSTED_EAGER_BUFFERS"};
+  Param<int> max_posted_control_buffers{"RDMA_MAX_POSTED_CONTROL_BUFFERS", 32, "see RDMA_MIN_POSTED_EAGER_BUFFERS"};
   Param<bool> early_completion{"EARLY_COMPLETION", false,
                                "report a receive whose completion NCCL calls optional (LL / LL128) as done when it is posted. "
                                "Only honoured with eager sends off (EAGER_MAX_SIZE=0): once such a receive is done NCCL stops "
@@ -176,7 +177,7 @@ struct Params {
   EnumParam tuner_type{"TUNER_TYPE", "Measured", {"Internal", "Region", "Model", "Measured"}, "tuner back-end"};
   Param<int> tuner_force_channels{"TUNER_FORCE_CHANNELS", 0,
                                   "calibration: the transport tuner answers this channel count for every size (0 = its table)"};
-  Param<int> tuner_num_channels{"TUNER_NUM_CHANNELS", 8, ""};
+  Param<int> tuner_num_channels{"TUNER_NUM_CHANNELS", 8, "channels the model tuner assumes when it prices an algorithm"};
   Param<float> tuner_net_latency{"TUNER_NET_LATENCY", 20.f, "network latency assumed by the model tuner (us)"};
   Param<bool> tuner_self_register{"TUNER_SELF_REGISTER", true,
                                   "publish NCCL_TUNER_PLUGIN=<this library> at start-up unless the user has set it"};
@@ -205,7 +206,9 @@ struct Params {
   Param<uint64_t> device_wait_limit_ms{"DEVICE_WAIT_LIMIT_MS", 20000, "bound of every device-side wait"};
   Param<int> gin_ack_interval{"GIN_ACK_INTERVAL", 64, "operations between GIN acknowledgements"};
   Param<bool> rr_ctrl_msg{"RR_CTRL_MSG", true, "rotate control messages over the control rails"};
-  EnumParam progress_model{"PROGRESS_MODEL", "unspec", {"unspec", "auto", "manual"}, ""};
+  EnumParam progress_model{"PROGRESS_MODEL", "unspec", {"unspec", "auto", "manual"},
+                           "accepted for scripts written for the reference plugin and not used: progress is always made by the "
+                           "calls of the thread that owns the endpoint"};
   Param<bool> nccl_topo_inject{"NCCL_TOPO_INJECT", false, "publish the generated topology through NCCL_TOPO_FILE"};
   Param<std::string> topo_file_write{"TOPO_FILE_WRITE_PATH", "", "also write the generated NCCL topology here"};
 };

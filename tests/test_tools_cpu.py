@@ -119,3 +119,31 @@ def test_packaging_install_steps_produce_a_loadable_plugin(built, tmp_path):
     assert res.returncode == 0, res.stdout + res.stderr
     listed = re.findall(r"^%\{_libdir\}/(\S+)$", spec[spec.index("%files"):], flags=re.M)
     assert sorted(listed) == sorted(os.listdir(root / "usr" / "lib64"))
+
+
+def test_parameter_listing_comes_from_the_library_and_the_committed_table_matches(built):
+    """`utils.params` asks the built library for its parameters: an environment override shows up
+    with its source, the compatibility prefix of the reference works, and docs/PARAMETERS.md is the
+    tool's own markdown output."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, B200NET_COPY_BATCH_DEPTH="3", OFI_NCCL_EAGER_MAX_SIZE="4096")
+    env.pop("B200NET_EAGER_MAX_SIZE", None)
+    out = subprocess.run([sys.executable, "-m", "aws_ofi_nccl_b200.utils.params", "--json"], cwd=repo, env=env,
+                         capture_output=True, text=True, timeout=60)
+    assert out.returncode == 0, out.stderr
+    rows = {r["name"]: r for r in json.loads(out.stdout)}
+    assert len(rows) > 40
+    assert rows["COPY_BATCH_DEPTH"]["value"] == "3" and rows["COPY_BATCH_DEPTH"]["source"] == "environment"
+    assert rows["EAGER_MAX_SIZE"]["value"] == "4096" and rows["EAGER_MAX_SIZE"]["source"] == "environment"
+    assert rows["COPY_BATCH"]["source"] == "default" and rows["COPY_BATCH"]["doc"]
+    clean = {k: v for k, v in os.environ.items() if not k.startswith(("B200NET_", "OFI_NCCL_"))}
+    md = subprocess.run([sys.executable, "-m", "aws_ofi_nccl_b200.utils.params", "--markdown"], cwd=repo, env=clean,
+                        capture_output=True, text=True, timeout=60)
+    assert md.returncode == 0, md.stderr
+    committed = open(os.path.join(repo, "docs", "PARAMETERS.md")).read()
+    assert md.stdout.strip() in committed, "docs/PARAMETERS.md is stale: regenerate it with utils.params --markdown"
