@@ -127,8 +127,8 @@ class TransportTuner {
   TransportTuner(PlatformKind platform, size_t n_ranks, size_t n_nodes);
   bool supported() const { return supported_; }
   Decision decide(ncclFunc_t coll, size_t bytes) const;
-  // bytes_per_step: what one ring step moves (a 1/n slice of an all_reduce buffer, the per-rank part
-  // of an all_gather or reduce_scatter)
+  // bytes_per_step: what one ring step moves (a 1/n slice of the buffer: of the reduced buffer for
+  // all_reduce, of the gathered / scattered one for all_gather and reduce_scatter)
   static int channels_for(ncclFunc_t coll, size_t bytes_per_step);
 
  private:

@@ -185,9 +185,10 @@ int main() {
     CHECK_EQ(d.n_channels, 1);
     CHECK_EQ(t.decide(ncclFuncAllReduce, 8u << 20).n_channels, 2);     // 1 MiB per step
     CHECK_EQ(t.decide(ncclFuncAllReduce, 64u << 20).n_channels, 8);    // 8 MiB per step
-    CHECK_EQ(t.decide(ncclFuncAllGather, 64u << 10).n_channels, 1);
-    CHECK_EQ(t.decide(ncclFuncAllGather, 256u << 10).n_channels, 4);
-    CHECK_EQ(t.decide(ncclFuncAllGather, 1u << 20).n_channels, 8);
+    CHECK_EQ(t.decide(ncclFuncAllGather, 512u << 10).n_channels, 1);   // 64 KiB per rank
+    CHECK_EQ(t.decide(ncclFuncAllGather, 2u << 20).n_channels, 4);      // 256 KiB per rank
+    CHECK_EQ(t.decide(ncclFuncAllGather, 8u << 20).n_channels, 8);      // 1 MiB per rank
+    CHECK_EQ(t.decide(ncclFuncReduceScatter, 8u << 20).n_channels, 8);
     // never fewer channels for a larger call of the same kind
     for (ncclFunc_t f : {ncclFuncAllReduce, ncclFuncAllGather, ncclFuncReduceScatter}) {
       int prev = 0;
@@ -197,7 +198,7 @@ int main() {
         prev = n;
       }
     }
-    CHECK_EQ(t.decide(ncclFuncReduceScatter, 64u << 20).n_channels, 16);
+    CHECK_EQ(t.decide(ncclFuncReduceScatter, 256u << 20).n_channels, 16);  // 32 MiB per rank
     CHECK_EQ(t.decide(ncclFuncAllReduce, 256u << 20).n_channels, 16);
     CHECK_EQ(t.decide(ncclFuncSendRecv, 1u << 20).n_channels, 0);
     int nch = 0;

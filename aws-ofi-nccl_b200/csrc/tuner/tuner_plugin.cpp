@@ -76,11 +76,11 @@ int TransportTuner::channels_for(ncclFunc_t coll, size_t bytes_per_step) {
 Decision TransportTuner::decide(ncclFunc_t coll, size_t bytes) const {
   Decision d;
   if (!supported_ || bytes == 0) return d;
-  // what one ring step moves: a 1/n slice of an all_reduce buffer; `bytes` already is the per-rank
-  // part for all_gather and reduce_scatter
-  size_t per_step = bytes;
-  if (coll == ncclFuncAllReduce) per_step = bytes / n_ranks_;
-  else if (coll != ncclFuncAllGather && coll != ncclFuncReduceScatter) return d;   // point-to-point and rooted calls: NCCL's own
+  // what one ring step moves: a 1/n slice of the buffer. NCCL passes the size of the whole buffer
+  // for all three (for all_gather and reduce_scatter the larger of its send and receive sides,
+  // which is n times the per-rank count)
+  if (coll != ncclFuncAllReduce && coll != ncclFuncAllGather && coll != ncclFuncReduceScatter) return d;   // point-to-point and rooted calls: NCCL's own
+  const size_t per_step = bytes / n_ranks_;
   const int forced = params().tuner_force_channels.get();
   d.n_channels = forced > 0 ? forced : channels_for(coll, per_step);
   return d;
