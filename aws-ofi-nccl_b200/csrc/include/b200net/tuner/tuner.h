@@ -92,7 +92,10 @@ struct MeasuredRow {
 class MeasuredTuner {
  public:
   // Parses the calibration JSON ({"world":N,"rows":[{"coll":..,"algo":..,"proto":..,"nchannels":..,
-  // "bytes":..,"time_us":..},...]}). Returns false (and stays unsupported) on a malformed file.
+  // "bytes":..,"time_us":..},...]}). "algo" and "proto" of -1 mark a row that timed a channel count
+  // with the algorithm and protocol left to NCCL: it decides channels only. "bytes" is the size NCCL
+  // reports for the call (the whole buffer, also for all_gather and reduce_scatter). Returns false
+  // (and stays unsupported) on a malformed file.
   bool load(const std::string& path);
   bool load_from_string(const std::string& json);
   bool supported() const { return !rows_.empty(); }

@@ -4,6 +4,7 @@
 #include <cstring>
 #include "b200net/platform.h"
 #include "b200net/tuner/tuner.h"
+#include <cstdlib>
 #include "test_util.h"
 using namespace b200net;
 using namespace b200net::tuner;
@@ -122,6 +123,24 @@ int main() {
     CHECK_EQ(m2.decide(ncclFuncReduceScatter, 1u << 20, 1).algorithm, NCCL_ALGO_PAT);
     CHECK_EQ(m2.decide(ncclFuncReduceScatter, 1u << 20).algorithm, NCCL_ALGO_PAT);   // not known: the fastest row
     CHECK_EQ(m2.decide(ncclFuncAllReduce, 1u << 20, 1).n_channels, 8);               // table silent about registration
+    // rows that timed channel counts only (algorithm and protocol -1): the shipped sweep of two B200
+    MeasuredTuner sweep;
+    const char* path = getenv("B200NET_TEST_CHANNEL_TABLE");
+    if (path && sweep.load(path)) {
+      CHECK_EQ(sweep.world(), 2u);
+      Decision c = sweep.decide(ncclFuncAllReduce, 64u << 10);
+      CHECK_EQ(c.algorithm, NCCL_ALGO_UNDEF); CHECK_EQ(c.protocol, NCCL_PROTO_UNDEF); CHECK_EQ(c.n_channels, 1);
+      CHECK_EQ(sweep.decide(ncclFuncAllReduce, 64u << 20).n_channels, 16);
+      CHECK_EQ(sweep.decide(ncclFuncAllGather, 1u << 20).n_channels, 8);
+      CHECK_EQ(sweep.decide(ncclFuncReduceScatter, 8u << 20).n_channels, 8);
+      int nch = 0;
+      float table[NCCL_NUM_ALGORITHMS][NCCL_NUM_PROTOCOLS];
+      for (auto& row : table) for (float& v : row) v = 5.0f;
+      CHECK(!apply_decision(c, reinterpret_cast<float**>(table), NCCL_NUM_ALGORITHMS, NCCL_NUM_PROTOCOLS, &nch));
+      CHECK_EQ(nch, 1); CHECK_EQ(table[NCCL_ALGO_RING][NCCL_PROTO_SIMPLE], 5.0f);   // channels only, NCCL's costs untouched
+    } else if (path) {
+      CHECK(false);   // the table named by the test did not load
+    }
   }
   // ---- cost table mutation
   {

@@ -53,9 +53,13 @@ bool MeasuredTuner::load_from_string(const std::string& json) {
     parse_number_after(json, open, close, "nchannels", &nch);
     double reg = -1;
     parse_number_after(json, open, close, "reg", &reg);
-    if (t > 0 && coll >= 0 && coll < ncclNumFuncs && algo >= 0 && algo < NCCL_NUM_ALGORITHMS && proto >= 0 &&
-        proto < NCCL_NUM_PROTOCOLS)
-      rows_.push_back(MeasuredRow{static_cast<int>(coll), static_cast<int>(algo), static_cast<int>(proto),
+    // algo / proto -1: the row times a channel count with the algorithm and protocol left to NCCL
+    // (sweeps of the transport's channel count); such a row decides channels only
+    const bool nccl_choice = algo < 0 && proto < 0;
+    if (t > 0 && coll >= 0 && coll < ncclNumFuncs &&
+        (nccl_choice || (algo >= 0 && algo < NCCL_NUM_ALGORITHMS && proto >= 0 && proto < NCCL_NUM_PROTOCOLS)))
+      rows_.push_back(MeasuredRow{static_cast<int>(coll), nccl_choice ? NCCL_ALGO_UNDEF : static_cast<int>(algo),
+                                  nccl_choice ? NCCL_PROTO_UNDEF : static_cast<int>(proto),
                                   static_cast<int>(nch), static_cast<size_t>(bytes), t, reg < 0 ? -1 : (reg != 0 ? 1 : 0)});
     pos = close + 1;
   }

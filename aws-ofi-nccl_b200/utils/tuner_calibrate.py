@@ -3,6 +3,12 @@ on this machine and writes the table that ``B200NET_TUNER_TYPE=Measured`` loads.
 
     python -m aws_ofi_nccl_b200.utils.tuner_calibrate --gpus 8 --out measured.json \
         [--algos Ring Tree NVLS NVLSTree PAT] [--protos LL LL128 Simple] [--min-bytes 8] [--max-bytes 1073741824]
+    python -m aws_ofi_nccl_b200.utils.tuner_calibrate --gpus 8 --plugin-channels 1 2 4 8 16 --out channels.json
+
+The second form times NCCL with all traffic routed through this repository's net plugin, once per
+forced channel count (``B200NET_TUNER_FORCE_CHANNELS``), algorithm and protocol left to NCCL; its rows
+carry ``algo`` / ``proto`` -1 and decide channels only (``data/transport_channels_b200_x2.json`` is
+such a table, measured on two B200).
 
 NCCL reads NCCL_ALGO / NCCL_PROTO once per process, so every (algorithm, protocol) pair is timed by
 a torchrun job of its own; pairs NCCL refuses for a collective are simply absent from the table.
@@ -73,6 +79,41 @@ def _worker(args) -> None:
     dist.destroy_process_group()
 
 
+def plugin_rows_to_table(world: int, per_channel: dict[int, list[dict]]) -> dict:
+    """bench_plugin rows per forced channel count -> the measured tuner's table (rows that failed
+    their fp64 check are dropped; all_to_all is point-to-point traffic and not the tuner's call)."""
+    rows = []
+    for ch, got in sorted(per_channel.items()):
+        for r in got:
+            if r["coll"] in COLLS and r.get("correct", True):
+                rows.append({"coll": COLLS[r["coll"]], "algo": -1, "proto": -1, "nchannels": ch, "bytes": r["bytes"],
+                             "time_us": round(r["us"], 1)})
+    return {"world": world, "rows": rows}
+
+
+def _sweep_plugin_channels(args) -> int:
+    import tempfile
+
+    per_channel = {}
+    for ch in args.plugin_channels:
+        with tempfile.NamedTemporaryFile(suffix=".json") as tmp:
+            env = dict(os.environ, B200NET_TUNER_FORCE_CHANNELS=str(ch))
+            cmd = [sys.executable, "-m", "aws_ofi_nccl_b200.utils.bench_plugin", "--gpus", str(args.gpus), "--min-bytes",
+                   str(max(args.min_bytes, 8)), "--max-bytes", str(args.max_bytes), "--iters", str(args.iters), "--timeout",
+                   str(args.timeout), "--json", tmp.name]
+            rc, out, err = run_job(cmd, env=env, timeout=args.timeout + 30)
+            if rc != 0:
+                print(f"{ch} channels: no result ({'timed out' if rc is None else 'failed'})", flush=True)
+                continue
+            per_channel[ch] = json.load(open(tmp.name)).get("plugin", [])
+            print(f"{ch} channels: {len(per_channel[ch])} measurements", flush=True)
+    table = plugin_rows_to_table(args.gpus, per_channel)
+    with open(args.out, "w") as f:
+        json.dump(table, f, indent=1)
+    print(f"wrote {len(table['rows'])} rows to {args.out}")
+    return 0 if table["rows"] else 1
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=2)
@@ -84,11 +125,15 @@ def main(argv=None) -> int:
     ap.add_argument("--step", type=int, default=4, help="size multiplier between measurements")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--timeout", type=int, default=300, help="seconds per (algorithm, protocol) job")
+    ap.add_argument("--plugin-channels", nargs="+", type=int, default=None,
+                    help="sweep these channel counts with the traffic routed through this repository's net plugin")
     ap.add_argument("--worker", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args(argv)
     if args.worker:
         _worker(args)
         return 0
+    if args.plugin_channels:
+        return _sweep_plugin_channels(args)
     rows = []
     for algo in args.algos:
         for proto in args.protos:

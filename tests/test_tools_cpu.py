@@ -147,3 +147,19 @@ def test_parameter_listing_comes_from_the_library_and_the_committed_table_matche
     assert md.returncode == 0, md.stderr
     committed = open(os.path.join(repo, "docs", "PARAMETERS.md")).read()
     assert md.stdout.strip() in committed, "docs/PARAMETERS.md is stale: regenerate it with utils.params --markdown"
+
+
+def test_channel_sweep_rows_become_a_measured_table():
+    """bench_plugin rows per forced channel count -> rows of the measured tuner's table: collective
+    ids of the ABI, algorithm / protocol left open, failed checks and all_to_all dropped."""
+    from aws_ofi_nccl_b200.utils import tuner_calibrate as tc
+
+    per = {2: [{"coll": "all_reduce", "bytes": 1 << 20, "us": 123.44, "busbw_GBs": 1.0, "correct": True},
+               {"coll": "all_to_all", "bytes": 1 << 20, "us": 50.0, "busbw_GBs": 1.0, "correct": True}],
+           8: [{"coll": "all_gather", "bytes": 1 << 20, "us": 67.0, "busbw_GBs": 1.0, "correct": True},
+               {"coll": "reduce_scatter", "bytes": 1 << 20, "us": 66.0, "busbw_GBs": 1.0, "correct": False}]}
+    table = tc.plugin_rows_to_table(2, per)
+    assert table["world"] == 2
+    assert table["rows"] == [
+        {"coll": 4, "algo": -1, "proto": -1, "nchannels": 2, "bytes": 1 << 20, "time_us": 123.4},
+        {"coll": 2, "algo": -1, "proto": -1, "nchannels": 8, "bytes": 1 << 20, "time_us": 67.0}]
