@@ -55,15 +55,10 @@ std::vector<std::pair<std::string, std::string>> PlatformB200::nccl_env() const 
                                                           {"NCCL_PROTO", "^LL128"},
                                                           // sixteen channels are connected; the tuner gives each call as
                                                           // many of them as its size is worth
-                                                          {"NCCL_MIN_NCHANNELS", "16"},
-                                                          // point-to-point calls (all_to_all): eight channels per
-                                                          // peer instead of NCCL's two for a network; measured on two
-                                                          // B200, 256 MiB all_to_all 45 -> 166 GB/s bus bandwidth.
-                                                          // NCCL 2.28 reads it before it initialises the plugin:
-                                                          // launchers have to export it themselves (bench.py and
-                                                          // bench_plugin do); kept here for NCCL builds that read
-                                                          // it later
-                                                          {"NCCL_NCHANNELS_PER_NET_PEER", "8"}};
+                                                          {"NCCL_MIN_NCHANNELS", "16"}};
+  // NCCL_NCHANNELS_PER_NET_PEER (channels per peer for point-to-point calls; 8 instead of NCCL's 2
+  // took a 256 MiB all_to_all on two B200 from 45 to 166 GB/s) cannot be set from here: NCCL reads
+  // it before it initialises its net plugin. Launchers export it (README).
   if (params().nccl_device_buffers.get()) {
     env.emplace_back("NCCL_NET_GDR_LEVEL", "SYS");
     env.emplace_back("NCCL_NET_GDR_READ", "1");

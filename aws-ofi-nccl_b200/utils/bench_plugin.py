@@ -127,8 +127,9 @@ def main(argv=None) -> int:
         env.setdefault("CUDA_MODULE_LOADING", "EAGER")
         env.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
         # all_to_all: eight channels per peer (NCCL reads this before it loads the plugin, whose own
-        # environment defaults therefore cannot supply it)
-        if arm == "plugin":
+        # environment defaults therefore cannot supply it); measured on two GPUs only, larger jobs keep
+        # NCCL's default unless the caller exports the variable
+        if arm == "plugin" and args.gpus <= 2:
             env.setdefault("NCCL_NCHANNELS_PER_NET_PEER", "8")
         if arm == "plugin":
             env.update(NCCL_NET_PLUGIN="ofi-b200", LD_LIBRARY_PATH=f"{LIB}:" + env.get("LD_LIBRARY_PATH", ""))

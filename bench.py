@@ -57,8 +57,10 @@ def plugin_env(base: dict) -> dict:
     env.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
     # point-to-point calls (all_to_all): eight channels per peer instead of NCCL's two for a network.
     # NCCL reads this before it initialises the plugin, so the plugin's own environment defaults come
-    # too late for it.
-    env.setdefault("NCCL_NCHANNELS_PER_NET_PEER", "8")
+    # too late for it. Measured on two GPUs only (256 MiB all_to_all 45 -> 166 GB/s), so larger jobs
+    # keep NCCL's default here.
+    if int(base.get("WORLD_SIZE", "1")) <= 2:
+        env.setdefault("NCCL_NCHANNELS_PER_NET_PEER", "8")
     # gradient traffic through the plugin runs after backward, not behind it: with compute kernels
     # and their stream waits queued on the device while the proxy thread launches copies, the first
     # overlapped step stopped moving (both ranks waiting for data, nothing left to send)
