@@ -58,7 +58,7 @@ std::vector<std::pair<std::string, std::string>> PlatformB200::nccl_env() const 
                                                           {"NCCL_MIN_NCHANNELS", "16"}};
   // NCCL_NCHANNELS_PER_NET_PEER (channels per peer for point-to-point calls; 8 instead of NCCL's 2
   // took a 256 MiB all_to_all on two B200 from 45 to 166 GB/s) cannot be set from here: NCCL reads
-  // it before it initialises its net plugin. Launchers export it (README).
+  // it before it initialises its net plugin. Launchers export it themselves.
   if (params().nccl_device_buffers.get()) {
     env.emplace_back("NCCL_NET_GDR_LEVEL", "SYS");
     env.emplace_back("NCCL_NET_GDR_READ", "1");
