@@ -48,7 +48,8 @@ class Tuner:
         return bool(self.ctx.value)
 
     def decide(self, coll: int, nbytes: int, pipe_ops: int = 1):
-        """Returns (algo, proto, channels) or None when the tuner leaves the choice to NCCL."""
+        """Returns (algo, proto, channels), (None, None, channels) when only the channel count is set,
+        or None when the tuner leaves everything to NCCL."""
         cost = ((C.c_float * len(PROTOS)) * len(ALGOS))()
         for a in range(len(ALGOS)):
             for p in range(len(PROTOS)):
@@ -62,6 +63,8 @@ class Tuner:
             for p in range(len(PROTOS)):
                 if cost[a][p] == 0.0:
                     return ALGOS[a], PROTOS[p], nch.value
+        if nch.value > 0:   # channels only: algorithm and protocol stay NCCL's choice
+            return None, None, nch.value
         return None
 
     def close(self) -> None:
@@ -122,8 +125,8 @@ def _print(result: dict) -> None:
         pd = None
     for coll, rows in result["collectives"].items():
         table = [{"from": _fmt_bytes(r["from_bytes"]),
-                  "algorithm": r["decision"][0] if r["decision"] else "-",
-                  "protocol": r["decision"][1] if r["decision"] else "-",
+                  "algorithm": (r["decision"][0] or "NCCL's") if r["decision"] else "-",
+                  "protocol": (r["decision"][1] or "NCCL's") if r["decision"] else "-",
                   "channels": (r["decision"][2] or "-") if r["decision"] else "-"} for r in rows]
         print(f"-- {coll}")
         if pd is not None:

@@ -43,3 +43,25 @@ def test_measured_table_drives_decisions(built, tmp_path):
     rows = out["collectives"]["all_reduce"]
     assert rows[0]["decision"] == ["Ring", "LL", 2]
     assert rows[-1]["decision"] == ["NVLS", "Simple", 16]
+
+
+def test_transport_tuner_and_channel_sweep_show_channel_only_decisions(built):
+    """Ranks that only reach each other through the plugin (one per "node"): the tuner sets channel
+    counts and leaves algorithm and protocol to NCCL; the shipped sweep of two B200 does the same
+    through the measured tuner."""
+    (out,) = _cli("--platform", "DGX B200", "--nodes", "8", "--ranks-per-node", "1", "--collectives", "all_reduce",
+                  "all_gather")
+    assert out["active"]
+    for coll in ("all_reduce", "all_gather"):
+        rows = out["collectives"][coll]
+        assert all(r["decision"][0] is None and r["decision"][1] is None for r in rows)
+        chans = [r["decision"][2] for r in rows]
+        assert chans[0] == 1 and chans[-1] == 16 and chans == sorted(chans)
+    # an all_gather of 8 MiB over 8 ranks moves 1 MiB per step: 8 channels, as a 1 MiB step of all_reduce would not (2)
+    ag = {r["from_bytes"]: r["decision"][2] for r in out["collectives"]["all_gather"]}
+    assert max(c for b, c in ag.items() if b <= 8 << 20) == 8
+    table = ROOT / "aws-ofi-nccl_b200" / "data" / "transport_channels_b200_x2.json"
+    (swept,) = _cli("--platform", "DGX B200", "--nodes", "2", "--ranks-per-node", "1", "--tuner-type", "Measured", "--table",
+                    str(table), "--collectives", "all_reduce")
+    rows = swept["collectives"]["all_reduce"]
+    assert rows[0]["decision"] == [None, None, 1] and rows[-1]["decision"][2] >= 16
