@@ -283,7 +283,7 @@ static int run_rank(const char* so, const char* only, int sock) {
   for (const auto& s : kScenarios) {
     if (strcmp(only, s.name)) continue;
     setenv("B200NET_FAULT_DROP", g_rank == 0 ? s.env_rank0 : s.env_rank1, 1);
-    setenv("B200NET_PROTOCOL", "RDMA", 0);   // the scenarios name datagram types of the RDMA-style protocol
+    setenv("B200NET_PROTOCOL", "RDMA", 1);   // the scenarios name datagram types of the RDMA-style protocol, whatever the caller runs
     void* h = dlopen(so, RTLD_NOW | RTLD_LOCAL);
     if (!h) FAIL("dlopen(%s): %s", so, dlerror());
     net = (ncclNet_v11_t*)dlsym(h, "ncclNetPlugin_v11");
