@@ -18,11 +18,21 @@ ParamBase::ParamBase(const char* name, const char* doc) : name_(name), doc_(doc 
   param_registry().push_back(this);
 }
 
+ParamBase::~ParamBase() {
+  auto& reg = param_registry();
+  reg.erase(std::remove(reg.begin(), reg.end(), this), reg.end());
+}
+
 const char* ParamBase::find_env(const std::string& name) {
   const std::string own = "B200NET_" + name;
   if (const char* e = getenv(own.c_str())) return e;
   const std::string compat = "OFI_NCCL_" + name;
   return getenv(compat.c_str());
+}
+
+void warn_retired(const std::string& name, const char* advice, bool removed) {
+  NET_WARN("B200NET_%s / OFI_NCCL_%s is %s. %s", name.c_str(), name.c_str(), removed ? "no longer supported" : "deprecated",
+           advice ? advice : "");
 }
 
 int parameters_init() {

@@ -19,7 +19,7 @@ enum class ParamSource { DEFAULT, ENVIRONMENT, API };
 class ParamBase {
  public:
   ParamBase(const char* name, const char* doc);
-  virtual ~ParamBase() = default;
+  virtual ~ParamBase();   // leaves the registry
   const std::string& name() const { return name_; }
   const std::string& doc() const { return doc_; }
   virtual std::string value_string() = 0;
@@ -31,6 +31,9 @@ class ParamBase {
   std::string name_, doc_;
   ParamSource source_ = ParamSource::DEFAULT;
 };
+
+// Says once per parameter that a retired setting was found in the environment.
+void warn_retired(const std::string& name, const char* advice, bool removed);
 
 // Registry of every parameter object (for init-time env parsing and for dumps).
 std::vector<ParamBase*>& param_registry();
@@ -101,6 +104,27 @@ class Param : public ParamBase {
   std::mutex mu_;
   T value_;
   bool loaded_ = false, frozen_ = false;
+};
+
+// A parameter that is on its way out (still read, with a warning) or gone (setting it is an error
+// at start-up, so that a script that relies on it does not run with something else silently)
+// (reference: include/nccl_ofi_param_impl.h:318-345, OFI_NCCL_PARAM_DEPRECATED / _REMOVED).
+template <typename T>
+class RetiredParam : public Param<T> {
+ public:
+  RetiredParam(const char* name, T def, const char* advice, bool error_on_use)
+      : Param<T>(name, std::move(def), advice), advice_(advice), error_on_use_(error_on_use) {}
+  int load_from_env() override {
+    const int rc = Param<T>::load_from_env();
+    if (rc != 0) return rc;
+    if (this->source() == ParamSource::DEFAULT) return 0;
+    warn_retired(this->name(), advice_, error_on_use_);
+    return error_on_use_ ? -22 : 0;
+  }
+
+ private:
+  const char* advice_;
+  bool error_on_use_;
 };
 
 // String parameter restricted to a fixed set of spellings (case-insensitive), e.g. PROTOCOL.
@@ -211,6 +235,15 @@ struct Params {
                            "calls of the thread that owns the endpoint"};
   Param<bool> nccl_topo_inject{"NCCL_TOPO_INJECT", false, "publish the generated topology through NCCL_TOPO_FILE"};
   Param<std::string> topo_file_write{"TOPO_FILE_WRITE_PATH", "", "also write the generated NCCL topology here"};
+  // settings of earlier versions of the reference plugin that scripts may still carry
+  RetiredParam<uint64_t> rdma_min_posted_bounce_buffers{
+      "RDMA_MIN_POSTED_BOUNCE_BUFFERS", 0,
+      "removed: use RDMA_MIN_POSTED_CONTROL_BUFFERS or RDMA_MIN_POSTED_EAGER_BUFFERS", true};
+  RetiredParam<uint64_t> rdma_max_posted_bounce_buffers{
+      "RDMA_MAX_POSTED_BOUNCE_BUFFERS", 0,
+      "removed: use RDMA_MAX_POSTED_CONTROL_BUFFERS or RDMA_MAX_POSTED_EAGER_BUFFERS", true};
+  RetiredParam<bool> endpoint_per_comm{"ENDPOINT_PER_COMM", false,
+                                       "deprecated and ignored: endpoints are per thread and device", false};
 };
 Params& params();
 

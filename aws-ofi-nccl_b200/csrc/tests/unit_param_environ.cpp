@@ -68,5 +68,25 @@ int main() {
   CHECK(!strcmp(getenv("REPLACE_ME"), "new"));
   CHECK(!strcmp(find(before, "REPLACE_ME"), "old"));  // the retired array is intact
   CHECK_EQ(em.pending(), 0u);
+
+  // retired settings: a deprecated one is read with a warning, a removed one fails start-up
+  {
+    RetiredParam<bool> dep("UNIT_DEPRECATED_SETTING", false, "use something else", false);
+    RetiredParam<uint64_t> gone("UNIT_REMOVED_SETTING", 0, "use something else", true);
+    CHECK_EQ(dep.load_from_env(), 0);                 // not set: silent
+    CHECK_EQ(gone.load_from_env(), 0);
+    setenv("B200NET_UNIT_DEPRECATED_SETTING", "1", 1);
+    setenv("OFI_NCCL_UNIT_REMOVED_SETTING", "7", 1);  // the reference's prefix counts as well
+    dep.reset_for_testing(false);
+    gone.reset_for_testing(0);
+    CHECK_EQ(dep.load_from_env(), 0);
+    CHECK(dep.get());                                 // still honoured
+    CHECK_EQ(gone.load_from_env(), -22);
+    unsetenv("B200NET_UNIT_DEPRECATED_SETTING");
+    unsetenv("OFI_NCCL_UNIT_REMOVED_SETTING");
+  }
+  // the three settings retired from the reference are known
+  CHECK_EQ(params().rdma_min_posted_bounce_buffers.load_from_env(), 0);
+  CHECK_EQ(params().endpoint_per_comm.load_from_env(), 0);
   TEST_MAIN_END();
 }

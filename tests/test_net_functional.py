@@ -167,3 +167,17 @@ def test_statistics_file_at_finalize(built, tmp_path):
         assert h["send_message_size"]["samples"] == c["sends"]
         assert h["stripes_per_send"]["max"] <= 4
         assert h["send_request_latency"]["unit"] == "ns"
+
+
+def test_a_removed_setting_stops_the_plugin_at_init(built):
+    """A script that still carries a setting the reference removed must not run with something else
+    silently: init fails and the log says which variable; a deprecated one only warns."""
+    exe = [str(built / "tests" / "func_net"), str(built / "libnccl-net-ofi-b200.so"), "connection"]
+    env = dict(os.environ, OFI_NCCL_RDMA_MIN_POSTED_BOUNCE_BUFFERS="8", FUNC_NET_VERBOSE="1")
+    res = subprocess.run(exe, capture_output=True, text=True, timeout=120, env=env, cwd=built)
+    assert res.returncode != 0
+    assert "RDMA_MIN_POSTED_BOUNCE_BUFFERS is no longer supported" in res.stderr
+    env = dict(os.environ, B200NET_ENDPOINT_PER_COMM="1", FUNC_NET_VERBOSE="1")
+    res = subprocess.run(exe, capture_output=True, text=True, timeout=120, env=env, cwd=built)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert "ENDPOINT_PER_COMM is deprecated" in res.stderr
