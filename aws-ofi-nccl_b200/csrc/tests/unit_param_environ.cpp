@@ -51,24 +51,6 @@ int main() {
   CHECK_EQ(params().min_stripe_size.get(), 128u * 1024);
   CHECK_THROWS(B200NET_ASSERT_ALWAYS(1 == 2));
 
-  // environment manager: no setenv, fresh array, overwrite semantics
-  setenv("KEEP_ME", "old", 1);
-  setenv("REPLACE_ME", "old", 1);
-  char** before = environ;
-  EnvManager& em = EnvManager::instance();
-  em.insert_envvar("NEW_VAR", "v1", false);
-  em.insert_envvar("NEW_VAR", "v2", false);     // first writer wins
-  em.insert_envvar("KEEP_ME", "new", false);    // exists in the process: kept
-  em.insert_envvar("REPLACE_ME", "new", true);
-  CHECK_EQ(em.pending(), 3u);
-  em.update_environment(&environ);
-  CHECK(environ != before);
-  CHECK(!strcmp(getenv("NEW_VAR"), "v1"));
-  CHECK(!strcmp(getenv("KEEP_ME"), "old"));
-  CHECK(!strcmp(getenv("REPLACE_ME"), "new"));
-  CHECK(!strcmp(find(before, "REPLACE_ME"), "old"));  // the retired array is intact
-  CHECK_EQ(em.pending(), 0u);
-
   // retired settings: a deprecated one is read with a warning, a removed one fails start-up
   {
     RetiredParam<bool> dep("UNIT_DEPRECATED_SETTING", false, "use something else", false);
@@ -88,5 +70,24 @@ int main() {
   // the three settings retired from the reference are known
   CHECK_EQ(params().rdma_min_posted_bounce_buffers.load_from_env(), 0);
   CHECK_EQ(params().endpoint_per_comm.load_from_env(), 0);
+
+  // environment manager: no setenv, fresh array, overwrite semantics
+  setenv("KEEP_ME", "old", 1);
+  setenv("REPLACE_ME", "old", 1);
+  char** before = environ;
+  EnvManager& em = EnvManager::instance();
+  em.insert_envvar("NEW_VAR", "v1", false);
+  em.insert_envvar("NEW_VAR", "v2", false);     // first writer wins
+  em.insert_envvar("KEEP_ME", "new", false);    // exists in the process: kept
+  em.insert_envvar("REPLACE_ME", "new", true);
+  CHECK_EQ(em.pending(), 3u);
+  em.update_environment(&environ);
+  CHECK(environ != before);
+  CHECK(!strcmp(getenv("NEW_VAR"), "v1"));
+  CHECK(!strcmp(getenv("KEEP_ME"), "old"));
+  CHECK(!strcmp(getenv("REPLACE_ME"), "new"));
+  CHECK(!strcmp(find(before, "REPLACE_ME"), "old"));  // the retired array is intact
+  CHECK_EQ(em.pending(), 0u);
+
   TEST_MAIN_END();
 }
