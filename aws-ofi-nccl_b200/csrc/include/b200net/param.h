@@ -4,6 +4,7 @@
 // plugin never sees two different values of one knob (reference: include/nccl_ofi_param_impl.h
 // :197-314, the list in include/nccl_ofi_param.h).
 #pragma once
+#include <atomic>
 #include <cstdint>
 #include <cstdlib>
 #include <mutex>
@@ -61,9 +62,13 @@ class Param : public ParamBase {
 
   // First get() freezes the value.
   const T& get() {
+    // once read, a value can no longer change (set() refuses): later reads take no lock. Hot paths
+    // read several parameters per message.
+    if (fast_.load(std::memory_order_acquire)) return value_;
     std::lock_guard<std::mutex> g(mu_);
     if (!loaded_) load_locked();
     frozen_ = true;
+    fast_.store(true, std::memory_order_release);
     return value_;
   }
   const T& operator()() { return get(); }
@@ -85,6 +90,7 @@ class Param : public ParamBase {
   // test hook: forget the frozen state and the cached value
   void reset_for_testing(const T& def) {
     std::lock_guard<std::mutex> g(mu_);
+    fast_.store(false, std::memory_order_release);
     value_ = def; loaded_ = false; frozen_ = false; source_ = ParamSource::DEFAULT;
   }
 
@@ -104,6 +110,7 @@ class Param : public ParamBase {
   std::mutex mu_;
   T value_;
   bool loaded_ = false, frozen_ = false;
+  std::atomic<bool> fast_{false};   // set once frozen: value_ is immutable from then on
 };
 
 // A parameter that is on its way out (still read, with a warning) or gone (setting it is an error

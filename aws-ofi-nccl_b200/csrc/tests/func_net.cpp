@@ -4,8 +4,8 @@
 // in flight, the 8 B - 4 MiB ping-pong with tags 0-7 and 8 concurrent requests, grouped receives,
 // eager early/late receives, many connections on one listen communicator, close with requests in
 // flight, a bandwidth sweep, NCCL's proxy pattern (many channels, one driving thread), transfers
-// of device payloads, the table of eager / grouped-receive orderings, and dma-buf registrations
-// (descriptor and range checks). Every poll loop has a
+// of device payloads, the table of eager / grouped-receive orderings, dma-buf registrations
+// (descriptor and range checks), and the cost of a test() call on a request that is not done. Every poll loop has a
 // 20 s deadline; ranks report through exit codes.
 // usage: func_net [plugin.so] [scenario]      env: B200NET_* / OFI_NCCL_* parameters apply
 //   FUNC_NET_DEVICE=1  payload buffers of the device scenarios (and of proxy_pattern) live in device
@@ -580,7 +580,7 @@ static int scenario_proxy_pattern(int sock) {
     b.to_device(chunk - 1, 1);
   };
   auto t0 = Clock::now();
-  long done_total = 0;
+  long done_total = 0, calls = 0;
   const long want_total = 2L * channels * chunks_per_channel;
   while (done_total < want_total) {
     for (int c = 0; c < channels; ++c) {
@@ -593,6 +593,7 @@ static int scenario_proxy_pattern(int sock) {
         int tag = c;
         void* req = nullptr;
         OK(net->irecv(x.p.r, 1, &d, &sz, &tag, &x.rmh[slot], nullptr, &req));
+        ++calls;
         if (!req) break;
         x.rreq[slot] = req;
         x.rreq_chunk[slot] = x.posted++;
@@ -603,6 +604,7 @@ static int scenario_proxy_pattern(int sock) {
         stamp(x.sbuf[slot], c, x.sent);
         void* req = nullptr;
         OK(net->isend(x.p.s, x.sbuf[slot].data(), chunk, c, x.smh[slot], nullptr, &req));
+        ++calls;
         if (!req) break;
         x.sreq[slot] = req;
         x.sreq_chunk[slot] = x.sent++;
@@ -612,6 +614,7 @@ static int scenario_proxy_pattern(int sock) {
         const int slot = x.send_done % steps;
         int d = 0;
         OK(net->test(x.sreq[slot], &d, nullptr));
+        ++calls;
         if (d) {
           ++x.send_done;
           ++done_total;
@@ -621,6 +624,7 @@ static int scenario_proxy_pattern(int sock) {
         const int slot = x.recv_done % steps;
         int d = 0, sz = 0;
         OK(net->test(x.rreq[slot], &d, &sz));
+        ++calls;
         if (d) {
           uint32_t hdr[4];
           x.rbuf[slot].from_device(0, sizeof(hdr));
@@ -645,8 +649,10 @@ static int scenario_proxy_pattern(int sock) {
   }
   if (g_rank == 0) {
     const double secs = std::chrono::duration<double>(Clock::now() - t0).count();
-    fprintf(stderr, "[rank 0] proxy pattern: %.2f GB/s per direction (%d channels x %d chunks of %zu KiB in %.3f s)\n",
-            static_cast<double>(channels) * chunks_per_channel * chunk / secs / 1e9, channels, chunks_per_channel, chunk >> 10, secs);
+    fprintf(stderr, "[rank 0] proxy pattern: %.2f GB/s per direction (%d channels x %d chunks of %zu KiB in %.3f s; %ld plugin "
+            "calls, %.0f ns of the loop per call)\n",
+            static_cast<double>(channels) * chunks_per_channel * chunk / secs / 1e9, channels, chunks_per_channel, chunk >> 10, secs,
+            calls, secs * 1e9 / static_cast<double>(calls));
   }
   if (barrier(sock)) FAIL("barrier");
   for (int c = 0; c < channels; ++c) {
@@ -659,6 +665,43 @@ static int scenario_proxy_pattern(int sock) {
     if (close_pair(&ch[c].p)) return 1;
   }
   return 0;
+}
+
+// What one call of test() costs on a request that is not done yet (NCCL's proxy thread makes
+// thousands of them per collective): a receive is posted and tested 2 million times before its
+// send is posted; then a send whose receive is not posted yet. Prints nanoseconds per call.
+static int scenario_test_call_cost(int sock) {
+  Pair p;
+  if (connect_pair(0, sock, &p)) return 1;
+  const size_t n = 65536;
+  TestBuf sb, rb;
+  if (buf_alloc(&sb, n) || buf_alloc(&rb, n)) FAIL("buffer allocation failed");
+  void *smh = nullptr, *rmh = nullptr;
+  OK(net->regMr(p.s, sb.data(), n, buf_type(), &smh));
+  OK(net->regMr(p.r, rb.data(), n, buf_type(), &rmh));
+  const int calls = getenv("FUNC_NET_TEST_CALLS") ? atoi(getenv("FUNC_NET_TEST_CALLS")) : 2000000;
+  void* data = rb.data();
+  size_t sz = n;
+  int tag = 3;
+  void* rreq = nullptr;
+  if (post_recv(p.r, 1, &data, &sz, &tag, &rmh, &rreq)) return 1;
+  auto t0 = Clock::now();
+  int done = 0, szs[8];
+  for (int i = 0; i < calls && !done; ++i) OK(net->test(rreq, &done, szs));
+  const double recv_ns = std::chrono::duration<double>(Clock::now() - t0).count() * 1e9 / calls;
+  if (done) FAIL("the receive completed although nothing was sent");
+  if (barrier(sock)) FAIL("barrier");   // both ranks have measured: now the sends may go
+  void* sreq = nullptr;
+  if (post_send(p.s, sb.data(), n, 3, smh, &sreq)) return 1;
+  std::vector<void*> reqs{sreq, rreq};
+  if (wait_all(reqs)) return 1;
+  if (g_rank == 0) fprintf(stderr, "[rank 0] test() on a pending receive: %.0f ns per call\n", recv_ns);
+  OK(net->deregMr(p.s, smh));
+  OK(net->deregMr(p.r, rmh));
+  buf_free(&sb);
+  buf_free(&rb);
+  if (close_pair(&p)) return 1;
+  return barrier(sock);
 }
 
 // Large rendezvous messages, eight in flight: reports the one-way bandwidth of the host path.
@@ -1086,7 +1129,7 @@ static const Scenario kScenarios[] = {
     {"bandwidth", scenario_bandwidth},       {"proxy_pattern", scenario_proxy_pattern},
     {"device_transfer", scenario_device_transfer}, {"eager_multirecv", scenario_eager_multirecv},
     {"device_bandwidth", scenario_device_bandwidth}, {"seq_wrap", scenario_seq_wrap},
-    {"dmabuf_registration", scenario_dmabuf_registration},
+    {"dmabuf_registration", scenario_dmabuf_registration}, {"test_call_cost", scenario_test_call_cost},
 };
 
 static int run_rank(const char* so, const char* only, int sock) {
