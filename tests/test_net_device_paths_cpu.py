@@ -163,12 +163,12 @@ def test_rma_and_gin_tables_on_device_buffers(built, nranks, env):
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
 
 
-@pytest.mark.parametrize("proto,ranks", [("RDMA", 4), ("SENDRECV", 3)])
+@pytest.mark.parametrize("proto,ranks", [("RDMA", 4), ("SENDRECV", 3), ("RDMA", 8)])
 def test_ring_of_processes_on_device_buffers(built, proto, ranks):
     """N ranks in a ring, 32 sends and 32 receives of device memory in flight per rank, flush."""
     fake = built / "tests" / "fake_cuda"
     e = dict(os.environ, FUNC_NET_DEVICE="1", B200NET_PROTOCOL=proto, B200NET_FORCE_NUM_RAILS="4",
-             FAKE_CUDA_LAUNCH_DELAY_US="100")
+             FAKE_CUDA_LAUNCH_DELAY_US="100", FAKE_CUDA_DEVICES=str(max(2, ranks)))
     e["LD_LIBRARY_PATH"] = f"{fake}:" + e.get("LD_LIBRARY_PATH", "")
     res = subprocess.run([str(built / "tests" / "func_ring"), str(built / "libnccl-net-ofi-b200.so"), str(ranks)],
                          capture_output=True, text=True, timeout=300, env=e, cwd=built)

@@ -40,7 +40,7 @@ def test_proxy_pattern_with_many_channels_in_flight(built, threads):
         _run(built, env, "proxy_pattern")
 
 
-@pytest.mark.parametrize("proto,rails,ranks", [("RDMA", "4", 4), ("RDMA", "1", 3), ("SENDRECV", "1", 4)])
+@pytest.mark.parametrize("proto,rails,ranks", [("RDMA", "4", 4), ("RDMA", "1", 3), ("SENDRECV", "1", 4), ("RDMA", "1", 8)])
 def test_ring_of_processes(built, proto, rails, ranks):
     """N ranks in a ring, 32 sends and 32 receives in flight per rank and round, flush, byte-exact."""
     env = dict(os.environ, B200NET_PROTOCOL=proto, B200NET_FORCE_NUM_RAILS=rails)
